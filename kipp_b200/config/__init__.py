@@ -1,0 +1,9 @@
+from .base import ConfigError, ModelConfig, read_config_json
+from .qwen3 import Qwen3Config
+from .registry import (Architecture, config_from_dict, get_architecture, load_config,
+                       register_architecture, registered_architectures,
+                       unregister_architecture)
+
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "Architecture", "config_from_dict",
+           "get_architecture", "load_config", "read_config_json", "register_architecture",
+           "registered_architectures", "unregister_architecture"]

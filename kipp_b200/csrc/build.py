@@ -1,0 +1,177 @@
+"""Builds the CUDA sources of this folder into shared libraries for sm_100a
+and loads them with ctypes.
+
+Each ``<name>.cu`` becomes ``_build/lib<name>.so`` the first time one of its
+kernels is needed, so a run compiles only what its model uses.  A library is
+rebuilt when its source, a shared header or the flags change.  While nvcc runs,
+a line is printed to stderr every few seconds.  There is no fallback: a missing
+compiler or a failed build raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import fcntl
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_HEADERS = ("common.cuh",)
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+]
+
+_loaded: dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+_build_dir: str | None = None
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def source_names() -> list[str]:
+    return sorted(f[:-3] for f in os.listdir(_HERE) if f.endswith(".cu"))
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("KIPP_B200_NVCC"),
+                 os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+                 shutil.which("nvcc")):
+        if cand and os.path.isfile(cand):
+            return cand
+    raise BuildError("nvcc not found (set CUDA_HOME or KIPP_B200_NVCC); the CUDA kernels of "
+                     "kipp_b200 cannot be built and there is no fallback")
+
+
+def build_dir() -> str:
+    """In-tree ``_build`` when writable, else a per-user temporary folder."""
+    global _build_dir
+    if _build_dir is not None:
+        return _build_dir
+    override = os.environ.get("KIPP_B200_BUILD_DIR")
+    cands = [override] if override else [os.path.join(_HERE, "_build")]
+    cands.append(os.path.join(tempfile.gettempdir(), f"kipp_b200_build_{os.getuid()}"))
+    for d in cands:
+        try:
+            os.makedirs(d, exist_ok=True)
+            fd, probe = tempfile.mkstemp(prefix=".probe", dir=d)
+            os.close(fd)
+            os.unlink(probe)
+            _build_dir = d
+            return d
+        except OSError:
+            continue
+    raise BuildError(f"no writable build folder among {cands}")
+
+
+def _digest(name: str, extra_flags: list[str]) -> str:
+    h = hashlib.sha256()
+    for f in (name + ".cu",) + _HEADERS + tuple(sorted(
+            x for x in os.listdir(_HERE) if x.endswith(".cuh") and x not in _HEADERS)):
+        with open(os.path.join(_HERE, f), "rb") as fh:
+            h.update(f.encode())
+            h.update(fh.read())
+    h.update(" ".join(NVCC_FLAGS + extra_flags).encode())
+    return h.hexdigest()
+
+
+def _extra_flags(name: str) -> list[str]:
+    flags: list[str] = []
+    path = os.path.join(_HERE, name + ".cu")
+    with open(path, "r", encoding="utf-8") as f:
+        head = f.read(4096)
+    for line in head.splitlines():
+        if line.startswith("// nvcc-flags:"):
+            flags += line.split(":", 1)[1].split()
+    return flags
+
+
+def library_path(name: str) -> str:
+    return os.path.join(build_dir(), f"lib{name}.so")
+
+
+def compile_library(name: str, *, verbose: bool = True, force: bool = False) -> str:
+    """Compile ``<name>.cu`` if its library is missing or stale; return the path."""
+    src = os.path.join(_HERE, name + ".cu")
+    if not os.path.isfile(src):
+        raise BuildError(f"no CUDA source {src}")
+    out_dir = build_dir()
+    so = os.path.join(out_dir, f"lib{name}.so")
+    stamp = so + ".sha256"
+    extra = _extra_flags(name)
+    digest = _digest(name, extra)
+
+    def fresh() -> bool:
+        try:
+            with open(stamp, "r") as f:
+                return os.path.isfile(so) and f.read().strip() == digest
+        except OSError:
+            return False
+
+    if not force and fresh():
+        return so
+    lock_path = os.path.join(out_dir, f".{name}.lock")
+    with open(lock_path, "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and fresh():
+                return so
+            tmp = f"{so}.{os.getpid()}.tmp"
+            cmd = [_nvcc()] + NVCC_FLAGS + extra + ["-I", _HERE, "-o", tmp, src]
+            if verbose:
+                print(f"[kipp_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+            t0 = time.time()
+            proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                                    cwd=out_dir)
+            out_chunks: list[str] = []
+            reader = threading.Thread(target=lambda: out_chunks.append(proc.stdout.read()), daemon=True)
+            reader.start()
+            while True:
+                try:
+                    proc.wait(timeout=10)
+                    break
+                except subprocess.TimeoutExpired:
+                    if verbose:
+                        print(f"[kipp_b200] still compiling {name}.cu ({time.time() - t0:.0f} s)",
+                              file=sys.stderr, flush=True)
+            reader.join()
+            if proc.returncode != 0:
+                try:
+                    os.unlink(tmp)
+                except OSError:
+                    pass
+                raise BuildError(f"nvcc failed for {name}.cu:\n{' '.join(cmd)}\n{''.join(out_chunks)}")
+            os.replace(tmp, so)
+            with open(stamp, "w") as f:
+                f.write(digest)
+            if verbose:
+                print(f"[kipp_b200] built lib{name}.so in {time.time() - t0:.1f} s", file=sys.stderr,
+                      flush=True)
+            return so
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def load_library(name: str) -> ctypes.CDLL:
+    with _lock:
+        lib = _loaded.get(name)
+        if lib is None:
+            lib = ctypes.CDLL(compile_library(name))
+            _loaded[name] = lib
+        return lib
+
+
+def build_all(verbose: bool = True, jobs: int | None = None) -> list[str]:
+    """Compile every source of this folder (in parallel); used by the build check."""
+    from concurrent.futures import ThreadPoolExecutor
+    names = source_names()
+    jobs = jobs or min(len(names), os.cpu_count() or 1) or 1
+    with ThreadPoolExecutor(max_workers=jobs) as pool:
+        return list(pool.map(lambda n: compile_library(n, verbose=verbose), names))

@@ -1,0 +1,172 @@
+// Per-head RMSNorm of queries and keys, rotary position encoding, and the
+// write of keys and values into the paged cache, in one pass over the fused
+// q/k/v projection output.
+//
+// Reference counterparts, one launch each per token: head_norm_kernel
+// (cuda/kipp_kernels.cu:67), rope_kernel (:121), kv_write_kernel (:143);
+// formulas src/kipp.c:2480-2500 (norm over head_dim with one weight vector for
+// all heads, before the rotation), src/kipp.c:2368-2382 (half-split pairs
+// (i, i + rot/2), angle = position * theta^(-2i/rot)), and the cache row
+// src/kipp.c:2806-2811 (keys stored after norm and rotation).
+//
+// One warp handles one (token, head).  Heads [0, Nq) are queries, [Nq, Nq+Nkv)
+// keys, the rest values.  All arithmetic is float32; cosf/sinf are the full
+// range-reduced versions.
+//
+// Cache layout of one layer: [page][kv_head][slot][head_dim]; a token at
+// position p of entry e lives in page table[e][p / page_size], slot
+// p % page_size.
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_PER_LANE = 8;   // head_dim <= 512 (pairs: 256 per half / 32 lanes)
+
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(
+    const T* __restrict__ qkv, int ld_qkv, T* __restrict__ q_out,
+    T* __restrict__ k_pages, T* __restrict__ v_pages,
+    const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_dtype, float eps,
+    const float* __restrict__ inv_freq, int rotary_dim,
+    const int* __restrict__ positions, const int* __restrict__ entry_of_token,
+    const int* __restrict__ block_table, int table_width, int page_size,
+    int tokens, int n_q, int n_kv, int head_dim, int write_cache, int* __restrict__ status) {
+    const int lane = threadIdx.x & 31;
+    const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int heads_total = n_q + 2 * n_kv;
+    if (warp_global >= tokens * heads_total) return;
+    const int t = warp_global / heads_total;
+    const int h = warp_global % heads_total;
+    const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
+    if (!is_q && !write_cache) return;
+    const T* src = qkv + (size_t)t * ld_qkv + (size_t)h * head_dim;
+    const int pos = positions[t];
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * n_q + h) * head_dim;
+    } else {
+        const int e = entry_of_token[t];
+        const int page = block_table[(size_t)e * table_width + pos / page_size];
+        if (page < 0) {                       // unmapped page: refuse, never write
+            if (lane == 0) atomicExch(status, 2);
+            return;
+        }
+        const int g = is_k ? h - n_q : h - n_q - n_kv;
+        T* base = is_k ? k_pages : v_pages;
+        dst = base + (((size_t)page * n_kv + g) * page_size + (pos % page_size)) * head_dim;
+    }
+
+    if (!is_q && !is_k) {                     // values: copy
+        for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+        return;
+    }
+
+    const int half = head_dim / 2;
+    // Lane owns pairs (i, i + half) for i = lane, lane + 32, ...
+    float lo[MAX_PER_LANE], hi[MAX_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half) {
+            lo[j] = to_f32(src[i]);
+            hi[j] = to_f32(src[i + half]);
+            ss += lo[j] * lo[j] + hi[j] * hi[j];
+        }
+    }
+    const void* nw = is_q ? q_norm_w : k_norm_w;
+    if (nw != nullptr) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)head_dim + eps);
+#pragma unroll
+        for (int j = 0; j < MAX_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half) {
+                lo[j] = lo[j] * scale * load_w(nw, norm_dtype, i);
+                hi[j] = hi[j] * scale * load_w(nw, norm_dtype, i + half);
+            }
+        }
+    }
+    // Rotation of the first rotary_dim dims, pairs (i, i + rotary_dim/2).
+    // With rotary_dim == head_dim a pair is exactly this lane's (lo, hi).
+    if (inv_freq != nullptr && rotary_dim == head_dim) {
+#pragma unroll
+        for (int j = 0; j < MAX_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half) {
+                const float angle = (float)pos * inv_freq[i];
+                const float c = cosf(angle), s = sinf(angle);
+                const float a = lo[j], b = hi[j];
+                lo[j] = a * c - b * s;
+                hi[j] = b * c + a * s;
+            }
+        }
+    }
+    if (inv_freq == nullptr || rotary_dim == head_dim || rotary_dim == 0) {
+#pragma unroll
+        for (int j = 0; j < MAX_PER_LANE; ++j) {
+            const int i = lane + 32 * j;
+            if (i < half) {
+                dst[i] = from_f32<T>(lo[j]);
+                dst[i + half] = from_f32<T>(hi[j]);
+            }
+        }
+        return;
+    }
+    // Partial rotation (rotary_dim < head_dim): pairs (i, i + rotary_dim/2)
+    // cross lanes, so the normalised head goes through shared memory in float32.
+    __shared__ float stage[4][64 * MAX_PER_LANE];
+    float* row = stage[threadIdx.x >> 5];
+#pragma unroll
+    for (int j = 0; j < MAX_PER_LANE; ++j) {
+        const int i = lane + 32 * j;
+        if (i < half) {
+            row[i] = lo[j];
+            row[i + half] = hi[j];
+        }
+    }
+    __syncwarp();
+    const int rh = rotary_dim / 2;
+    for (int i = lane; i < head_dim; i += 32) {
+        float v = row[i];
+        if (i < rotary_dim) {
+            const int p = i < rh ? i : i - rh;
+            const float angle = (float)pos * inv_freq[p];
+            const float c = cosf(angle), s = sinf(angle);
+            v = i < rh ? row[i] * c - row[i + rh] * s : row[i] * c + row[i - rh] * s;
+        }
+        dst[i] = from_f32<T>(v);
+    }
+}
+}  // namespace
+
+extern "C" int kipp_qk_norm_rope_write(
+    const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v_pages, int dtype,
+    const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
+    const float* inv_freq, int rotary_dim, const int* positions, const int* entry_of_token,
+    const int* block_table, int table_width, int page_size, int tokens, int n_q, int n_kv,
+    int head_dim, int write_cache, int* status, void* stream) {
+    if (tokens <= 0) return 0;
+    if (head_dim <= 0 || (head_dim & 1) || head_dim > 64 * MAX_PER_LANE) return KIPP_ERR_ARG;
+    if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return KIPP_ERR_ARG;
+    if (page_size <= 0 || n_q <= 0 || n_kv <= 0) return KIPP_ERR_ARG;
+    if (norm_dtype != KIPP_DT_F32 && norm_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long warps = (long long)tokens * (n_q + 2 * n_kv);
+    const int threads = 128;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
+    if (dtype == KIPP_DT_F32)
+        qk_norm_rope_write_kernel<float><<<(unsigned)blocks, threads, 0, s>>>(
+            (const float*)qkv, ld_qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, q_norm_w,
+            k_norm_w, norm_dtype, eps, inv_freq, rotary_dim, positions, entry_of_token, block_table,
+            table_width, page_size, tokens, n_q, n_kv, head_dim, write_cache, status);
+    else if (dtype == KIPP_DT_BF16)
+        qk_norm_rope_write_kernel<bf16><<<(unsigned)blocks, threads, 0, s>>>(
+            (const bf16*)qkv, ld_qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, q_norm_w,
+            k_norm_w, norm_dtype, eps, inv_freq, rotary_dim, positions, entry_of_token, block_table,
+            table_width, page_size, tokens, n_q, n_kv, head_dim, write_cache, status);
+    else
+        return KIPP_ERR_DTYPE;
+    return kipp_launch_status();
+}

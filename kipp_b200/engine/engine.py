@@ -1,0 +1,239 @@
+"""The engine: a model bound to a device, its cache, and the step function.
+
+``step`` takes a batch of (request, its next tokens) — portions of prompts
+beside single decoded tokens, cut anywhere — runs exactly those tokens as one
+batch against the cache that earlier steps left, and returns the logits at the
+wanted places.  It generalises the reference's ``kipp_eval_batch``
+(src/kipp.c:3984-4082): any mixture of items, nothing changes on error, lengths
+advance on success.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Iterable, Optional
+
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..config.base import ModelConfig
+from ..config.registry import get_architecture, load_config
+from ..models.spec import LayerRun, ModelSpec
+from ..weights.loader import load_tensors
+from ..weights.random_init import random_tensors
+from .batch import Staging, StepEntry, StepMeta, pack_step
+from .runtime import Runtime
+
+
+@dataclasses.dataclass
+class CacheView:
+    k_pages: Optional[torch.Tensor]      # [pages, kv_heads, page_size, head_dim] of one run's cache
+    v_pages: Optional[torch.Tensor]
+    block_table: torch.Tensor            # int32 [entries, width] for this step
+    page_size: int
+
+
+class StepContext:
+    """What a part sees during one step."""
+
+    def __init__(self, engine: "Engine", meta: StepMeta):
+        rt = engine.runtime
+        self.engine = engine
+        self.meta = meta
+        self.device = rt.device
+        self.dtype = rt.dtype
+        self.ops = rt.ops
+        self.workspace = rt.workspace
+        self.status = rt.status
+
+    def cache_view(self, run: LayerRun) -> CacheView:
+        gi, j = self.engine.cache.group_of_cache[run.cache]
+        g = self.engine.cache.groups[gi]
+        return CacheView(g.k[j], g.v[j], self.meta.block_tables[gi], g.page_size)
+
+    def state_view(self, run: LayerRun) -> torch.Tensor:
+        """[max_requests, *shape] state of this run's cache id; index it with
+        ``meta.slots``."""
+        return self.engine.states[run.cache]
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, tensors: dict, *, dtype="bfloat16",
+                 device: str | torch.device = "cuda:0", page_size: int = 16,
+                 cache_tokens: int = 8192, max_requests: int = 64,
+                 max_batch_tokens: int = 8192):
+        self.spec = spec
+        self.runtime = Runtime(device, dtype)
+        self.page_size = page_size
+        self.max_requests = max_requests
+        self.max_batch_tokens = max_batch_tokens
+        rt = self.runtime
+        with torch.cuda.device(rt.device):
+            # -- weights -------------------------------------------------------
+            spec.embedding.bind(tensors, spec.embedding_prefix, rt)
+            for prefix, block in spec.layers:
+                block.bind(tensors, prefix, rt)
+            spec.final_norm[1].bind(tensors, spec.final_norm[0], rt)
+            spec.head[1].bind(tensors, spec.head[0], rt)
+            # -- cache ------------------------------------------------------------
+            cache_specs, state_specs = {}, {}
+            for run in spec.order:
+                mixer = spec.layers[run.layer][1].mixer
+                cs, ss = mixer.cache_spec(), mixer.state_spec()
+                if cs is not None:
+                    if cache_specs.setdefault(run.cache, cs) != cs:
+                        raise ValueError(f"runs that share cache {run.cache} need equal cache specs")
+                if ss is not None:
+                    if state_specs.setdefault(run.cache, ss) != ss:
+                        raise ValueError(f"runs that share cache {run.cache} need equal state specs")
+            n_pages = max(1, -(-cache_tokens // page_size))
+            self.cache = CacheManager(cache_specs, page_size, n_pages, max_requests)
+            for g in self.cache.groups:
+                shape = (len(g.cache_ids), n_pages, g.spec.kv_heads, page_size, g.spec.head_dim)
+                g.k = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+                g.v = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+            self.states = {cid: torch.zeros((max_requests,) + tuple(ss.shape), dtype=ss.dtype,
+                                            device=rt.device)
+                           for cid, ss in state_specs.items()}
+        self._staging = Staging()
+        self.steps_run = 0
+
+    # -- construction ------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder: str, **options) -> "Engine":
+        """Load ``folder/config.json`` and its safetensors; the model class is
+        chosen by ``architectures[0]``."""
+        config = load_config(folder)
+        spec = get_architecture(config.architecture).build(config)
+        tensors = load_tensors(folder, spec.tensor_specs())
+        return cls(spec, tensors, **options)
+
+    @classmethod
+    def from_config(cls, config: ModelConfig, seed: int, *, sigma: Optional[float] = None,
+                    norm_jitter: float = 0.1, weight_dtype: torch.dtype = torch.bfloat16,
+                    **options) -> "Engine":
+        """Random weights made on the device (no files): for benchmarks of
+        sizes too large to write out."""
+        spec = get_architecture(config.architecture).build(config)
+        device = options.get("device", "cuda:0")
+        if sigma is None:
+            sigma = float(getattr(config, "initializer_range", 0.02))
+        tensors = _LazyRandom(spec.tensor_specs(), seed, sigma, norm_jitter, weight_dtype, device)
+        return cls(spec, tensors, **options)
+
+    # -- requests ------------------------------------------------------------------
+    def add_request(self, rid) -> int:
+        slot = self.cache.admit(rid)
+        for st in self.states.values():
+            st[slot].zero_()
+        return slot
+
+    def finish(self, rid) -> None:
+        """The request is over: its pages and its slot are given back."""
+        self.cache.release(rid)
+
+    def length(self, rid) -> int:
+        return self.cache.length(rid)
+
+    def is_live(self, rid) -> bool:
+        return rid in self.cache
+
+    # -- the step ----------------------------------------------------------------------
+    def step(self, entries: Iterable[StepEntry], *, check: bool = False) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits ``[wanted, vocab]`` on the
+        device in the order of the entries and of their ``want`` lists (None if
+        nothing is wanted).  The tensor is workspace memory: read or copy it
+        before the next step.  Raises ``OutOfPages`` with no request changed
+        when the cache cannot hold the step."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries:
+            return None
+        vocab = self.spec.vocab_size
+        seen = set()
+        total = 0
+        for e in entries:
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            if len(e.tokens) == 0:
+                raise ValueError(f"request {e.request!r} brings no tokens")
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                raise ValueError(f"request {e.request!r} has a token id outside [0, {vocab})")
+            total += len(e.tokens)
+        if total > self.max_batch_tokens:
+            raise ValueError(f"step of {total} tokens exceeds max_batch_tokens {self.max_batch_tokens}")
+        admitted = []
+        try:
+            for e in entries:
+                if e.request not in self.cache:
+                    self.add_request(e.request)
+                    admitted.append(e.request)
+            starts = [self.cache.length(e.request) for e in entries]
+            limit = self.spec.max_positions
+            for e, s in zip(entries, starts):
+                if limit is not None and s + len(e.tokens) > limit:
+                    raise ValueError(f"request {e.request!r} would pass max positions {limit}")
+            self.cache.reserve([(e.request, s + len(e.tokens)) for e, s in zip(entries, starts)])
+        except Exception:
+            for rid in admitted:
+                self.cache.release(rid)
+            raise
+        rids = [e.request for e in entries]
+        slots = [self.cache.slot(r) for r in rids]
+        tables = [self.cache.block_table_rows(rids, gi) for gi in range(len(self.cache.groups))]
+        rt = self.runtime
+        with torch.cuda.device(rt.device):
+            meta = pack_step(entries, starts, slots, tables, rt.device, self._staging)
+            logits = self._forward(StepContext(self, meta))
+        for e, s in zip(entries, starts):
+            self.cache.advance(e.request, s + len(e.tokens))
+        self.steps_run += 1
+        if check:
+            rt.check_status()
+        return logits
+
+    def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        spec = self.spec
+        x = spec.embedding.forward(ctx)
+        for run in spec.order:
+            spec.layers[run.layer][1].forward(ctx, run, x)
+        meta = ctx.meta
+        if meta.n_logit_rows == 0:
+            return None
+        h = spec.final_norm[1].forward(ctx, x, rows=meta.logit_rows, n_rows=meta.n_logit_rows,
+                                       key="final_normed")
+        return spec.head[1].forward(ctx, h, meta.n_logit_rows)
+
+    # -- accounting -----------------------------------------------------------------
+    def weight_bytes(self) -> int:
+        """Bytes of weights one step reads (each weight once)."""
+        spec = self.spec
+        n = sum(spec.layers[run.layer][1].weight_bytes() for run in spec.order)
+        n += spec.final_norm[1].weight_bytes() + spec.head[1].weight_bytes()
+        return n
+
+    def cache_bytes_per_token(self) -> int:
+        es = torch.empty((), dtype=self.runtime.dtype).element_size()
+        return sum(2 * len(g.cache_ids) * g.spec.kv_heads * g.spec.head_dim * es
+                   for g in self.cache.groups)
+
+
+class _LazyRandom(dict):
+    """Mapping name -> random tensor made on first access and not kept, so that
+    a large model never exists twice."""
+
+    def __init__(self, specs, seed, sigma, norm_jitter, dtype, device):
+        super().__init__()
+        self._specs = {s.name: s for s in specs}
+        self._args = (seed, sigma, norm_jitter, dtype, device)
+
+    def __contains__(self, name) -> bool:
+        s = self._specs.get(name)
+        return s is not None and not (s.optional and s.alias_of is not None)
+
+    def __getitem__(self, name):
+        seed, sigma, jitter, dtype, device = self._args
+        s = self._specs[name]
+        for _, t in random_tensors([s], seed, sigma=sigma, norm_jitter=jitter, dtype=dtype,
+                                   device=device, skip_aliased=False):
+            return t
+        raise KeyError(name)

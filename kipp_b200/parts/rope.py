@@ -1,0 +1,41 @@
+"""Rotary position encoding with half-split pairs (src/kipp.c:2368-2382):
+pair (i, i + rot/2) of a head is rotated by position * theta^(-2i/rot)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .base import PositionEncoding
+
+
+class RotaryEncoding(PositionEncoding):
+    """``rotary_dim`` leading dims of each head are rotated (all of them by
+    default); ``theta`` is the frequency base."""
+
+    def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
+        self.head_dim = head_dim
+        self.theta = float(theta)
+        self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
+        if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= head_dim:
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {head_dim}")
+        self._table: dict[str, torch.Tensor] = {}
+
+    def frequencies(self) -> torch.Tensor:
+        """float32 theta^(-2i/rot) for i < rot/2, evaluated in float32 as the
+        reference does with powf."""
+        i = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
+        exponent = -(2.0 * i) / float(self.rotary_dim)
+        return torch.pow(torch.tensor(self.theta, dtype=torch.float32), exponent)
+
+    def inv_freq(self, device) -> Optional[torch.Tensor]:
+        if self.rotary_dim == 0:
+            return None
+        key = str(device)
+        if key not in self._table:
+            self._table[key] = self.frequencies().to(device)
+        return self._table[key]
+
+
+class NoPositionEncoding(PositionEncoding):
+    rotary_dim = 0
