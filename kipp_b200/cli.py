@@ -1,0 +1,149 @@
+"""Command line in the reference's manner (src/kipp_cli.c): one prompt is
+evaluated, then tokens are sampled and fed back one at a time.
+
+Options the reference has keep their names and meanings (usage text
+src/kipp_cli.c:571-610): --model, --decode, --temperature, --top-p, --top-k,
+--min-p, --seed, --top, --ctx.  The prompt is token ids (there is no
+tokenizer here): --prompt-ids, --prompt-file or --random-prompt.  --backend
+and --kv-quant have one value each here (cuda, the compute dtype's cache), so
+--dtype stands in their place.  Output: ``generated\\t<ids>`` on stdout, the
+final top-N logits as ``rank\\tid\\tlogit``, and on stderr the line
+``KIPP_METRIC backend=... prefill_tokens=... prefill_seconds=...
+decode_tokens=... decode_seconds=...`` (src/kipp_cli.c:1213-1217).
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="kipp", description="Qwen3 dense inference on one B200")
+    ap.add_argument("--model", help="folder with config.json and *.safetensors")
+    ap.add_argument("--random", metavar="CONFIG.json",
+                    help="instead of --model: a config.json to fill with random weights from --weights-seed")
+    ap.add_argument("--weights-seed", type=int, default=0)
+    prompt = ap.add_mutually_exclusive_group(required=True)
+    prompt.add_argument("--prompt-ids", help="comma-separated token ids")
+    prompt.add_argument("--prompt-file", help="file of little-endian uint32 token ids")
+    prompt.add_argument("--random-prompt", type=int, metavar="LEN", help="LEN seeded random token ids")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="compute precision (default bfloat16; float32 = true 32-bit path)")
+    ap.add_argument("--decode", type=int, default=0, help="greedy/sampled tokens to generate")
+    ap.add_argument("--temperature", type=float, default=0.0, help="0 = greedy argmax (default)")
+    ap.add_argument("--top-p", type=float, default=1.0, help="nucleus mass, 0 < F <= 1 (default 1)")
+    ap.add_argument("--top-k", type=int, default=0, help="keep N highest logits (0 = off)")
+    ap.add_argument("--min-p", type=float, default=0.0, help="min prob vs top, 0 <= F <= 1 (0 = off)")
+    ap.add_argument("--seed", type=int, default=1, help="nonzero sampling seed (default 1)")
+    ap.add_argument("--top", type=int, default=10, help="final top-N logits to print (default 10)")
+    ap.add_argument("--ctx", type=int, default=None, help="session capacity in tokens (default prompt + decode)")
+    ap.add_argument("--kv-block-size", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--chunk", type=int, default=2048, help="largest prompt portion of one step")
+    ap.add_argument("--stop-token", type=int, action="append", default=None,
+                    help="token id that ends decoding (default: the config's eos_token_id)")
+    ap.add_argument("--device", default="cuda:0")
+    return ap
+
+
+def _prompt_tokens(args, vocab: int) -> list:
+    if args.prompt_ids is not None:
+        return [int(t) for t in args.prompt_ids.replace(" ", "").split(",") if t]
+    if args.prompt_file is not None:
+        import numpy as np
+        return np.fromfile(args.prompt_file, dtype="<u4").astype("int64").tolist()
+    import torch
+    g = torch.Generator().manual_seed(args.seed)
+    return torch.randint(0, vocab, (args.random_prompt,), generator=g).tolist()
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    if (args.model is None) == (args.random is None):
+        print("kipp: give exactly one of --model and --random", file=sys.stderr)
+        return 2
+    if args.decode < 0 or args.decode > (1 << 20):
+        print("kipp: --decode must be between 0 and 2^20", file=sys.stderr)
+        return 2
+    if args.temperature > 0 and args.seed == 0:
+        print("kipp: --seed must be nonzero", file=sys.stderr)
+        return 2
+    import torch
+    from .config.registry import config_from_dict, load_config
+    from .engine import Engine, StepEntry
+    from .sampling.params import SamplingParams
+    from .sampling.sampler import Sampler
+
+    if args.model is not None:
+        config = load_config(args.model)
+    else:
+        import json
+        with open(args.random) as f:
+            config = config_from_dict(json.load(f))
+    tokens = _prompt_tokens(args, config.vocab_size)
+    if not tokens:
+        print("kipp: the prompt is empty", file=sys.stderr)
+        return 2
+    capacity = args.ctx or (len(tokens) + args.decode)
+    if len(tokens) + args.decode > capacity:
+        print(f"kipp: prompt ({len(tokens)}) + decode ({args.decode}) exceeds --ctx {capacity}",
+              file=sys.stderr)
+        return 2
+    opts = dict(dtype=args.dtype, device=args.device, page_size=args.kv_block_size,
+                cache_tokens=capacity + args.kv_block_size, max_requests=1,
+                max_batch_tokens=max(args.chunk, 1))
+    engine = (Engine.from_folder(args.model, **opts) if args.model is not None
+              else Engine.from_config(config, args.weights_seed, **opts))
+    sampler = Sampler(engine.runtime.device)
+    params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
+                            min_p=args.min_p, seed=args.seed or 1)
+    try:
+        params.validate()
+    except ValueError as e:
+        print(f"kipp: {e}", file=sys.stderr)
+        return 2
+    stops = set(args.stop_token) if args.stop_token else (
+        {config.eos_token_id} if getattr(config, "eos_token_id", None) is not None else set())
+    print(f"kipp: evaluating {len(tokens)} token{'' if len(tokens) == 1 else 's'} of "
+          f"{config.architecture} on cuda ({args.dtype})", file=sys.stderr)
+
+    def sync():
+        torch.cuda.synchronize(engine.runtime.device)
+
+    sync()
+    t0 = time.perf_counter()
+    logits = None
+    for a in range(0, len(tokens), args.chunk):
+        part = tokens[a:a + args.chunk]
+        last = a + len(part) == len(tokens)
+        logits = engine.step([StepEntry("cli", part, [len(part) - 1] if last else [])])
+    sync()
+    prefill_seconds = time.perf_counter() - t0
+
+    generated, rng = [], [params.seed]
+    t0 = time.perf_counter()
+    if args.decode:
+        sys.stdout.write("generated\t")
+        for _ in range(args.decode):
+            token = int(sampler.sample(logits, [params], rng, [generated[-64:]]).item())
+            if token in stops:
+                break
+            sys.stdout.write(("" if not generated else " ") + str(token))
+            sys.stdout.flush()
+            generated.append(token)
+            logits = engine.step([StepEntry("cli", [token], [0])])
+        sync()
+        sys.stdout.write("\n")
+    decode_seconds = time.perf_counter() - t0 if args.decode else 0.0
+    if args.top > 0:
+        values, ids = torch.topk(logits[0], min(args.top, logits.shape[1]))
+        for rank, (v, i) in enumerate(zip(values.tolist(), ids.tolist()), 1):
+            print(f"{rank}\t{i}\t{v:.9g}")
+    engine.runtime.check_status()
+    print(f"KIPP_METRIC backend=cuda prefill_tokens={len(tokens)} prefill_seconds={prefill_seconds:.9f} "
+          f"decode_tokens={len(generated)} decode_seconds={decode_seconds:.9f}", file=sys.stderr)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

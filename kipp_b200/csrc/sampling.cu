@@ -1,0 +1,377 @@
+// Greedy and temperature sampling on the device, one thread block per row of
+// logits.
+//
+// The token drawn is the one the reference's host sampler draws from the same
+// logits and the same uniform number (kipp_sample_ex, src/kipp.c:3433-3559):
+//   * greedy (temperature <= 0): first index of the maximum, strict '>';
+//   * else scaled = logit * (1/T); candidates are scaled >= max - 20; they are
+//     ordered by scaled value descending, ties by token id ascending; top-k
+//     keeps the first k; weights w = expf(scaled - max) in float32, sums in
+//     double; min-p keeps w >= min_p * w_top; the nucleus is the shortest
+//     prefix whose sum reaches top_p * total; draw = u * kept picks the first
+//     candidate whose inclusive prefix sum exceeds it.
+// The reference sorts the candidates.  Here nothing is sorted: a position in
+// that order is found by radix selection over the (value, token) keys, with
+// per-bucket counts and weight sums, four 8-bit passes over the value and,
+// only among equal values, four over the token id.  Bucket sums add the same
+// float32 weights in another order than the reference's running double sum, so
+// a draw that lies within double rounding of a boundary may pick the
+// neighbour.
+//
+// Also here: the penalties and logit bias the reference applies before
+// sampling (apply_bias_and_penalties, src/kipp.c:3386-3431).
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+constexpr int THREADS = 1024;
+
+__device__ __forceinline__ unsigned desc_key(float x) {
+    // Ascending unsigned order of the result == descending float order of x.
+    unsigned k = __float_as_uint(x);
+    k = (k & 0x80000000u) ? ~k : (k | 0x80000000u);
+    return ~k;
+}
+
+struct RowCtx {
+    const float* v;
+    int n;
+    float inv_t, smax, cutoff;
+    // filters
+    bool has_topk;   unsigned topk_key, topk_tok;
+    bool has_minp;   double minp_threshold;
+    bool has_nucleus; unsigned nuc_key, nuc_tok;
+};
+
+__device__ __forceinline__ bool before_or_at(unsigned key, unsigned tok, unsigned bkey, unsigned btok) {
+    return key < bkey || (key == bkey && tok <= btok);
+}
+
+// Whether element i is in the current candidate set; gives its key and weight.
+__device__ __forceinline__ bool member(const RowCtx& c, int i, unsigned& key, float& w) {
+    const float scaled = c.v[i] * c.inv_t;
+    if (!(scaled >= c.cutoff)) return false;
+    key = desc_key(scaled);
+    if (c.has_topk && !before_or_at(key, (unsigned)i, c.topk_key, c.topk_tok)) return false;
+    w = expf(scaled - c.smax);
+    if (c.has_minp && (double)w < c.minp_threshold) return false;
+    if (c.has_nucleus && !before_or_at(key, (unsigned)i, c.nuc_key, c.nuc_tok)) return false;
+    return true;
+}
+
+struct Shared {
+    unsigned cnt[256];
+    double wsum[256];
+    float red_val[32];
+    int red_idx[32];
+    double red_d[32];
+    unsigned long long red_u[32];
+    // results broadcast
+    unsigned sel_digit; unsigned long long sel_cnt_before; double sel_w_before;
+    unsigned sel_bucket_cnt; int found;
+    int i_val; float f_val; double d_val; unsigned long long u_val;
+};
+
+enum { MODE_COUNT = 0, MODE_W_GE = 1, MODE_W_GT = 2 };
+
+// One histogram pass.  level 0..3: value key digits (high to low); level 4..7:
+// token digits among elements whose key == prefix_key.
+__device__ void histogram_pass(const RowCtx& c, Shared& sh, int level, unsigned prefix_key,
+                               unsigned prefix_tok) {
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) { sh.cnt[b] = 0; sh.wsum[b] = 0.0; }
+    __syncthreads();
+    int cur = -1; unsigned ccnt = 0; double cw = 0.0;
+    for (int i = threadIdx.x; i < c.n; i += blockDim.x) {
+        unsigned key; float w;
+        if (!member(c, i, key, w)) continue;
+        unsigned digit;
+        if (level < 4) {
+            const int shift = 24 - 8 * level;
+            if (level > 0 && (key >> (shift + 8)) != (prefix_key >> (shift + 8))) continue;
+            digit = (key >> shift) & 0xffu;
+        } else {
+            if (key != prefix_key) continue;
+            const int shift = 24 - 8 * (level - 4);
+            const unsigned tok = (unsigned)i;
+            if (level > 4 && (tok >> (shift + 8)) != (prefix_tok >> (shift + 8))) continue;
+            digit = (tok >> shift) & 0xffu;
+        }
+        if ((int)digit != cur) {
+            if (cur >= 0) { atomicAdd(&sh.cnt[cur], ccnt); atomicAdd(&sh.wsum[cur], cw); }
+            cur = (int)digit; ccnt = 0; cw = 0.0;
+        }
+        ccnt += 1; cw += (double)w;
+    }
+    if (cur >= 0) { atomicAdd(&sh.cnt[cur], ccnt); atomicAdd(&sh.wsum[cur], cw); }
+    __syncthreads();
+}
+
+// Position selection in the (value desc, token asc) order of the current set.
+//   MODE_COUNT: the element with 1-based rank `target_count`;
+//   MODE_W_GE : the first element whose inclusive weight sum >= target_w;
+//   MODE_W_GT : the first element whose inclusive weight sum >  target_w.
+// If no element qualifies, the last element of the set is returned.
+// Outputs (uniform over the block): key, token, inclusive weight sum at it.
+__device__ void select(const RowCtx& c, Shared& sh, int mode, unsigned long long target_count,
+                       double target_w, unsigned& out_key, unsigned& out_tok, double& out_cum) {
+    unsigned prefix_key = 0, prefix_tok = 0;
+    unsigned long long cnt_before = 0;
+    double w_before = 0.0;
+    for (int level = 0; level < 8; ++level) {
+        histogram_pass(c, sh, level, prefix_key, prefix_tok);
+        if (threadIdx.x == 0) {
+            unsigned long long cb = cnt_before; double wb = w_before;
+            int chosen = -1, last_nonempty = -1;
+            unsigned long long cb_last = 0; double wb_last = 0.0;
+            for (int b = 0; b < 256; ++b) {
+                const unsigned n = sh.cnt[b];
+                if (n == 0) continue;
+                last_nonempty = b; cb_last = cb; wb_last = wb;
+                bool hit;
+                if (mode == MODE_COUNT) hit = cb + n >= target_count;
+                else if (mode == MODE_W_GE) hit = wb + sh.wsum[b] >= target_w;
+                else hit = wb + sh.wsum[b] > target_w;
+                if (hit) { chosen = b; break; }
+                cb += n; wb += sh.wsum[b];
+            }
+            if (chosen < 0) { chosen = last_nonempty; cb = cb_last; wb = wb_last; }
+            sh.found = chosen;
+            sh.sel_cnt_before = cb; sh.sel_w_before = wb;
+            sh.sel_bucket_cnt = chosen >= 0 ? sh.cnt[chosen] : 0;
+            sh.d_val = chosen >= 0 ? wb + sh.wsum[chosen] : wb;
+        }
+        __syncthreads();
+        const int chosen = sh.found;
+        cnt_before = sh.sel_cnt_before; w_before = sh.sel_w_before;
+        const double cum_incl = sh.d_val;
+        const unsigned bucket_cnt = sh.sel_bucket_cnt;
+        __syncthreads();
+        if (chosen < 0) { out_key = 0xffffffffu; out_tok = 0; out_cum = w_before; return; }  // empty set
+        const int shift = 24 - 8 * (level & 3);
+        if (level < 4) prefix_key |= (unsigned)chosen << shift;
+        else prefix_tok |= (unsigned)chosen << shift;
+        if (level == 7) { out_key = prefix_key; out_tok = prefix_tok; out_cum = cum_incl; return; }
+        if (level == 3 && bucket_cnt == 1) {
+            // One element has this value: find its token in one pass.
+            if (threadIdx.x == 0) sh.i_val = 0x7fffffff;
+            __syncthreads();
+            for (int i = threadIdx.x; i < c.n; i += blockDim.x) {
+                unsigned key; float w;
+                if (member(c, i, key, w) && key == prefix_key) atomicMin(&sh.i_val, i);
+            }
+            __syncthreads();
+            out_key = prefix_key; out_tok = (unsigned)sh.i_val; out_cum = cum_incl;
+            __syncthreads();
+            return;
+        }
+    }
+}
+
+__device__ void block_argmax(const float* v, int n, Shared& sh, float& best_v, int& best_i) {
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float x = v[i];
+        if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
+    }
+    // A row of NaNs or -inf leaves bi unset in some threads; index 0 then wins
+    // as in the reference (argmax starts at 0 and only '>' replaces it).
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sh.red_val[warp] = bv; sh.red_idx[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        bv = lane < nw ? sh.red_val[lane] : -INFINITY;
+        bi = lane < nw ? sh.red_idx[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { sh.f_val = bv; sh.i_val = (bi == 0x7fffffff) ? 0 : bi; }
+    }
+    __syncthreads();
+    best_v = sh.f_val; best_i = sh.i_val;
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_rows_kernel(const float* __restrict__ logits, long long ld, int n, int* __restrict__ out) {
+    __shared__ Shared sh;
+    float bv; int bi;
+    block_argmax(logits + (size_t)blockIdx.x * ld, n, sh, bv, bi);
+    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_rows_kernel(const float* __restrict__ logits, long long ld, int n,
+                   const float* __restrict__ temperature, const int* __restrict__ top_k,
+                   const float* __restrict__ top_p, const float* __restrict__ min_p,
+                   const double* __restrict__ uniform, int* __restrict__ out) {
+    __shared__ Shared sh;
+    const int r = blockIdx.x;
+    const float* v = logits + (size_t)r * ld;
+    float best_v; int best_i;
+    block_argmax(v, n, sh, best_v, best_i);
+    const float T = temperature[r];
+    if (!(T > 0.0f)) {
+        if (threadIdx.x == 0) out[r] = best_i;
+        return;
+    }
+    RowCtx c;
+    c.v = v; c.n = n;
+    c.inv_t = 1.0f / T;
+    c.smax = v[best_i] * c.inv_t;
+    c.cutoff = c.smax - 20.0f;
+    c.has_topk = c.has_minp = c.has_nucleus = false;
+    c.topk_key = c.topk_tok = c.nuc_key = c.nuc_tok = 0;
+    c.minp_threshold = 0.0;
+
+    unsigned key, tok; double cum;
+    const int k = top_k[r];
+    if (k > 0) {
+        // rank k in the order, or the last candidate when there are fewer
+        select(c, sh, MODE_COUNT, (unsigned long long)k, 0.0, key, tok, cum);
+        c.has_topk = true; c.topk_key = key; c.topk_tok = tok;
+    }
+    const float mp = min_p[r];
+    if (mp > 0.0f) {
+        // The top weight is expf(smax - smax) = 1.
+        c.has_minp = true;
+        c.minp_threshold = (double)mp * (double)expf(0.0f);
+    }
+    // total weight of the set (and, with a nucleus, the prefix that is kept)
+    const float tp = top_p[r];
+    double kept;
+    if (tp < 1.0f) {
+        // total = sum of all weights: select with an unreachable target returns
+        // the last element and the sum before it; simpler: one pass for the sum.
+        double local = 0.0;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            unsigned kk; float w;
+            if (member(c, i, kk, w)) local += (double)w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((threadIdx.x & 31) == 0) sh.red_d[threadIdx.x >> 5] = local;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh.red_d[w];
+            sh.d_val = t;
+        }
+        __syncthreads();
+        const double total = sh.d_val;
+        __syncthreads();
+        select(c, sh, MODE_W_GE, 0, (double)tp * total, key, tok, cum);
+        c.has_nucleus = true; c.nuc_key = key; c.nuc_tok = tok;
+        kept = cum;
+    } else {
+        // kept = total: the draw's own selection needs only u * total; get total
+        // from a selection that never hits (returns the sum up to the last).
+        double local = 0.0;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            unsigned kk; float w;
+            if (member(c, i, kk, w)) local += (double)w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+        if ((threadIdx.x & 31) == 0) sh.red_d[threadIdx.x >> 5] = local;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh.red_d[w];
+            sh.d_val = t;
+        }
+        __syncthreads();
+        kept = sh.d_val;
+        __syncthreads();
+    }
+    const double draw = uniform[r] * kept;
+    select(c, sh, MODE_W_GT, 0, draw, key, tok, cum);
+    if (threadIdx.x == 0) out[r] = (key == 0xffffffffu && tok == 0 && kept == 0.0) ? best_i : (int)tok;
+}
+
+// Logit bias, then repetition / presence / frequency penalties over each row's
+// window of recent tokens; each distinct token is adjusted once
+// (src/kipp.c:3386-3431).  One block per row; the window is short.
+__global__ void apply_penalties_kernel(float* __restrict__ logits, long long ld, int n,
+                                       const int* __restrict__ recent, int recent_width,
+                                       const int* __restrict__ recent_count,
+                                       const float* __restrict__ repetition,
+                                       const float* __restrict__ presence,
+                                       const float* __restrict__ frequency,
+                                       const int* __restrict__ bias_tokens,
+                                       const float* __restrict__ bias_values, int bias_width,
+                                       const int* __restrict__ bias_count) {
+    const int r = blockIdx.x;
+    float* v = logits + (size_t)r * ld;
+    if (bias_tokens != nullptr && threadIdx.x == 0) {
+        // sequential: the same token may be listed twice and both add up
+        const int nb = bias_count[r];
+        for (int i = 0; i < nb; ++i) {
+            const int tok = bias_tokens[(size_t)r * bias_width + i];
+            if (tok >= 0 && tok < n) v[tok] += bias_values[(size_t)r * bias_width + i];
+        }
+    }
+    __syncthreads();
+    if (recent == nullptr) return;
+    const float rep = repetition[r], pres = presence[r], freq = frequency[r];
+    const bool has = freq != 0.0f || pres != 0.0f || (rep != 0.0f && rep != 1.0f);
+    const int nr = recent_count[r];
+    if (!has || nr == 0) return;
+    const int* win = recent + (size_t)r * recent_width;
+    for (int p = threadIdx.x; p < nr; p += blockDim.x) {
+        const int tok = win[p];
+        if (tok < 0 || tok >= n) continue;
+        bool seen = false;
+        for (int e = 0; e < p; ++e) if (win[e] == tok) { seen = true; break; }
+        if (seen) continue;
+        int count = 0;
+        for (int o = 0; o < nr; ++o) count += win[o] == tok;
+        float x = v[tok];
+        if (rep != 0.0f && rep != 1.0f) x = x > 0.0f ? x / rep : x * rep;
+        x -= pres;
+        x -= freq * (float)count;
+        v[tok] = x;
+    }
+}
+}  // namespace
+
+extern "C" int kipp_argmax_rows(const float* logits, long long ld, int rows, int n, int* out,
+                                void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0) return KIPP_ERR_ARG;
+    argmax_rows_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ld, n, out);
+    return kipp_launch_status();
+}
+
+extern "C" int kipp_sample_rows(const float* logits, long long ld, int rows, int n,
+                                const float* temperature, const int* top_k, const float* top_p,
+                                const float* min_p, const double* uniform, int* out, void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0) return KIPP_ERR_ARG;
+    sample_rows_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ld, n, temperature, top_k,
+                                                                   top_p, min_p, uniform, out);
+    return kipp_launch_status();
+}
+
+extern "C" int kipp_apply_penalties(float* logits, long long ld, int rows, int n, const int* recent,
+                                    int recent_width, const int* recent_count,
+                                    const float* repetition, const float* presence,
+                                    const float* frequency, const int* bias_tokens,
+                                    const float* bias_values, int bias_width, const int* bias_count,
+                                    void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0) return KIPP_ERR_ARG;
+    apply_penalties_kernel<<<rows, 64, 0, (cudaStream_t)stream>>>(
+        logits, ld, n, recent, recent_width, recent_count, repetition, presence, frequency,
+        bias_tokens, bias_values, bias_width, bias_count);
+    return kipp_launch_status();
+}

@@ -1,0 +1,136 @@
+"""The Python entry point: token ids in, token ids out.
+
+The reference has no Python entry to its engine (Python is tooling only,
+docs/ARCHITECTURE.md:25-26); this one follows its C API's vocabulary
+(src/kipp.h: open a model, evaluate, sample) and its CLI's option names
+(src/kipp_cli.c:571-610): ``decode`` = tokens to generate, ``temperature`` 0 =
+greedy, ``top_p``, ``top_k``, ``min_p``, ``seed``.
+"""
+from __future__ import annotations
+
+import dataclasses
+import time
+from typing import Optional, Sequence
+
+import torch
+
+from ..config.base import ModelConfig
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .engine import Engine
+from .scheduler import Request, Scheduler
+
+
+@dataclasses.dataclass
+class GenerationResult:
+    request_id: object
+    prompt: list
+    tokens: list                       # generated token ids
+    finish_reason: str                 # "stop" | "length" | "abort"
+    preemptions: int = 0
+
+
+class LLM:
+    """A model on one GPU with a scheduler above it.
+
+    ``model``            folder with config.json + safetensors, or a ModelConfig
+                         (random weights from ``seed``)
+    ``dtype``            "bfloat16" (serving kernels) or "float32" (true 32-bit)
+    ``kv_block_size``    tokens per cache page
+    ``kv_blocks``        pages in each cache group (default: enough for ``ctx`` tokens
+                         of ``max_requests`` requests, capped by ``kv_tokens``)
+    ``ctx``              most tokens one request may hold (default: the model's
+                         max_position_embeddings)
+    ``max_batch_tokens`` token budget of one step
+    ``chunk``            largest prompt portion of one request in one step
+    ``policy``           "reserve" or "preempt": what happens when pages run out
+    """
+
+    def __init__(self, model, *, dtype="bfloat16", device="cuda:0", kv_block_size: int = 16,
+                 kv_blocks: Optional[int] = None, kv_tokens: Optional[int] = None,
+                 ctx: Optional[int] = None, max_requests: int = 64, max_batch_tokens: int = 8192,
+                 chunk: Optional[int] = None, policy: str = "reserve", seed: int = 0,
+                 stop_token_ids: Sequence[int] = ()):
+        if kv_blocks is not None:
+            cache_tokens = kv_blocks * kv_block_size
+        elif kv_tokens is not None:
+            cache_tokens = kv_tokens
+        else:
+            cache_tokens = None
+        opts = dict(dtype=dtype, device=device, page_size=kv_block_size, max_requests=max_requests,
+                    max_batch_tokens=max_batch_tokens)
+        if isinstance(model, ModelConfig):
+            limit = ctx or model.max_position_embeddings
+            opts["cache_tokens"] = cache_tokens or min(limit * max_requests, 1 << 20)
+            self.engine = Engine.from_config(model, seed, **opts)
+        else:
+            from ..config.registry import load_config
+            limit = ctx or getattr(load_config(model), "max_position_embeddings", 8192)
+            opts["cache_tokens"] = cache_tokens or min(limit * max_requests, 1 << 20)
+            self.engine = Engine.from_folder(model, **opts)
+        self.ctx = limit
+        self.chunk = chunk
+        self.policy = policy
+        self.max_batch_tokens = max_batch_tokens
+        self.stop_token_ids = tuple(stop_token_ids)
+        eos = getattr(self.engine.spec.config, "eos_token_id", None)
+        if eos is not None and not self.stop_token_ids:
+            self.stop_token_ids = (int(eos),)
+        self.sampler = Sampler(self.engine.runtime.device)
+        self.metrics: dict = {}
+
+    def new_scheduler(self) -> Scheduler:
+        e = self.engine
+        return Scheduler(e.cache, max_batch_tokens=self.max_batch_tokens, chunk_size=self.chunk,
+                         max_positions=min(self.ctx, e.spec.max_positions or self.ctx),
+                         policy=self.policy, admit=e.add_request, release=e.finish)
+
+    def generate(self, prompts: Sequence[Sequence[int]], decode: int = 16, *,
+                 temperature: float = 0.0, top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0,
+                 seed: int = 1, sampling: Optional[Sequence[SamplingParams]] = None,
+                 stop_token_ids: Optional[Sequence[int]] = None) -> list:
+        """Generate up to ``decode`` tokens for every prompt (lists of token ids).
+        Request i samples with seed ``seed + i`` (never 0), as the reference
+        seeds its choices (src/kipp_server.c:1852-1862)."""
+        sched = self.new_scheduler()
+        stops = tuple(stop_token_ids) if stop_token_ids is not None else self.stop_token_ids
+        requests = []
+        for i, prompt in enumerate(prompts):
+            sp = sampling[i] if sampling is not None else SamplingParams(
+                temperature=temperature, top_p=top_p, top_k=top_k, min_p=min_p,
+                seed=(seed + i) or 1)
+            r = Request(id=i, prompt=[int(t) for t in prompt], max_new_tokens=decode, sampling=sp,
+                        stop_token_ids=stops)
+            sched.add(r)
+            requests.append(r)
+        self.run(sched)
+        return [GenerationResult(r.id, r.prompt, list(r.output), r.finish_reason or "abort",
+                                 r.preemptions) for r in requests]
+
+    def run(self, sched: Scheduler) -> None:
+        """Drive ``sched`` until no request is left: plan, step, sample, record."""
+        engine = self.engine
+        steps = tokens = sampled_total = 0
+        t0 = time.perf_counter()
+        while sched.has_work():
+            plan = sched.schedule()
+            if plan is None:
+                raise RuntimeError("requests are waiting but none can be admitted")
+            logits = engine.step(plan.entries)
+            sampled = []
+            if plan.sampled:
+                rs = [plan.requests[i] for i in plan.sampled]
+                states = [r.rng_state for r in rs]
+                out = self.sampler.sample(logits, [r.sampling for r in rs], states,
+                                          [r.recent for r in rs])
+                sampled = out.to("cpu").tolist()        # device -> host: the step's result
+                for r, s in zip(rs, states):
+                    r.rng_state = s
+            sched.complete(plan, sampled)
+            steps += 1
+            tokens += plan.tokens
+            sampled_total += len(sampled)
+        engine.runtime.check_status()
+        self.metrics = {"steps": steps, "tokens_fed": tokens, "tokens_sampled": sampled_total,
+                        "seconds": time.perf_counter() - t0, **sched.stats}
+

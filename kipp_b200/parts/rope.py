@@ -22,11 +22,13 @@ class RotaryEncoding(PositionEncoding):
         self._table: dict[str, torch.Tensor] = {}
 
     def frequencies(self) -> torch.Tensor:
-        """float32 theta^(-2i/rot) for i < rot/2, evaluated in float32 as the
-        reference does with powf."""
+        """float32 theta^(-2i/rot) for i < rot/2, as the reference's
+        powf(theta, -(2.0f * i) / rot): a float32 exponent, the power rounded
+        to float32 once."""
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
-        exponent = -(2.0 * i) / float(self.rotary_dim)
-        return torch.pow(torch.tensor(self.theta, dtype=torch.float32), exponent)
+        exponent = (-(2.0 * i) / float(self.rotary_dim)).double()
+        theta = torch.tensor(self.theta, dtype=torch.float32).double()
+        return torch.pow(theta, exponent).float()
 
     def inv_freq(self, device) -> Optional[torch.Tensor]:
         if self.rotary_dim == 0:

@@ -61,8 +61,11 @@ def plain_rope(h: torch.Tensor, positions, theta: float) -> torch.Tensor:
     does; (h_i, h_{i+D/2}) <- (h_i cos a - h_{i+D/2} sin a, h_{i+D/2} cos a + h_i sin a)."""
     T, _, D = h.shape
     half = D // 2
-    i = torch.arange(half, dtype=torch.float32)
-    freq = torch.pow(torch.tensor(float(theta), dtype=torch.float32), -(2.0 * i) / float(D))
+    # powf(theta, -(2.0f * i) / D): the exponent is a float32 quotient; the power
+    # is taken in double and rounded to float32 once, which is what a correctly
+    # rounded powf returns.
+    exponent = (-(2.0 * torch.arange(half, dtype=torch.float32)) / float(D)).to(F64)
+    freq = torch.pow(torch.tensor(float(theta), dtype=torch.float32).to(F64), exponent).to(torch.float32)
     pos = torch.as_tensor(positions, dtype=torch.float32).reshape(T, 1)
     angle = (pos * freq).to(F64)                      # float32 product, then exact widening
     cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
@@ -119,7 +122,7 @@ def layer_window(config: dict, layer: int):
 
 
 def plain_block(x, config: dict, w: dict, prefix: str, layer: int, rounding=no_round,
-                positions=None) -> torch.Tensor:
+                positions=None, kv_rounding=None) -> torch.Tensor:
     """One layer in the reference's order (cpu_forward, src/kipp.c:2587-2652):
     norm -> q,k,v -> per-head norm of q and k -> rotation of q and k ->
     attention -> output projection -> add -> norm -> SwiGLU -> add."""
@@ -129,6 +132,8 @@ def plain_block(x, config: dict, w: dict, prefix: str, layer: int, rounding=no_r
     eps, theta = config["rms_norm_eps"], config["rope_theta"]
     if positions is None:
         positions = list(range(T))
+    if kv_rounding is None:
+        kv_rounding = rounding
     n = rounding(plain_rmsnorm(x, w[prefix + "input_layernorm.weight"], eps))
     q = rounding(plain_linear(n, w[prefix + "self_attn.q_proj.weight"])).reshape(T, n_q, D)
     k = rounding(plain_linear(n, w[prefix + "self_attn.k_proj.weight"])).reshape(T, n_kv, D)
@@ -136,7 +141,10 @@ def plain_block(x, config: dict, w: dict, prefix: str, layer: int, rounding=no_r
     q = plain_head_norm(q, w[prefix + "self_attn.q_norm.weight"], eps)
     k = plain_head_norm(k, w[prefix + "self_attn.k_norm.weight"], eps)
     q = rounding(plain_rope(q, positions, theta))
-    k = rounding(plain_rope(k, positions, theta))      # keys are stored after norm and rotation
+    # keys are stored after norm and rotation; the reference rounds stored keys
+    # and values to bfloat16 (round_trip_bf16, src/kipp.c:2614-2615)
+    k = kv_rounding(plain_rope(k, positions, theta))
+    v = kv_rounding(v)
     a = rounding(plain_attention(q, k, v, layer_window(config, layer))).reshape(T, n_q * D)
     x = x + plain_linear(a, w[prefix + "self_attn.o_proj.weight"])
     n = rounding(plain_rmsnorm(x, w[prefix + "post_attention_layernorm.weight"], eps))
@@ -145,12 +153,12 @@ def plain_block(x, config: dict, w: dict, prefix: str, layer: int, rounding=no_r
     return x
 
 
-def plain_forward(config: dict, w: dict, tokens, rounding=no_round) -> torch.Tensor:
+def plain_forward(config: dict, w: dict, tokens, rounding=no_round, kv_rounding=None) -> torch.Tensor:
     """Logits [T, vocab] (float64) of every position of one whole sequence
     (cpu_forward, src/kipp.c:2564-2664, which returns the last row only)."""
     x = plain_embedding(w["model.embed_tokens.weight"], tokens)
     for layer in range(config["num_hidden_layers"]):
-        x = plain_block(x, config, w, f"model.layers.{layer}.", layer, rounding)
+        x = plain_block(x, config, w, f"model.layers.{layer}.", layer, rounding, kv_rounding=kv_rounding)
     n = rounding(plain_rmsnorm(x, w["model.norm.weight"], config["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings") else w["lm_head.weight"]
     return plain_linear(n, head)

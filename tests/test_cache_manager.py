@@ -1,0 +1,146 @@
+"""The cache manager under random orders of requests (no GPU): no page is
+lost, held twice or freed twice; window groups give pages back; growth is
+all-or-nothing."""
+import random
+
+import pytest
+
+from kipp_b200.cache import UNMAPPED, CacheManager, OutOfPages, OutOfSlots, PagePool, StateSlots
+from kipp_b200.parts.base import PagedKVSpec
+
+FULL = PagedKVSpec(2, 16)
+WIN = PagedKVSpec(2, 16, window=10)
+
+
+def test_pool_basics_and_reuse_order():
+    p = PagePool(3)
+    a, b, c = p.alloc("x"), p.alloc("x"), p.alloc("y")
+    assert (a, b, c) == (0, 1, 2)
+    with pytest.raises(OutOfPages):
+        p.alloc("z")
+    p.free(b, "x")
+    with pytest.raises(RuntimeError, match="freed twice"):
+        p.free(b, "x")
+    with pytest.raises(RuntimeError, match="belongs to"):
+        p.free(c, "x")
+    p.free(a, "x")
+    assert p.alloc("z") == b and p.alloc("z") == a          # freed pages come back in order
+    p.check()
+
+
+def test_slots():
+    s = StateSlots(2)
+    a, b = s.alloc("r1"), s.alloc("r2")
+    assert {a, b} == {0, 1}
+    with pytest.raises(OutOfSlots):
+        s.alloc("r3")
+    s.free(a, "r1")
+    with pytest.raises(RuntimeError):
+        s.free(a, "r1")
+    assert s.alloc("r3") == a
+    s.check()
+
+
+def test_groups_by_spec_and_block_tables():
+    m = CacheManager({0: FULL, 1: WIN, 2: WIN, 3: FULL}, page_size=4, pages_per_group=8, max_requests=4)
+    assert [g.cache_ids for g in m.groups] == [[0, 3], [1, 2]]
+    assert m.group_of_cache == {0: (0, 0), 3: (0, 1), 1: (1, 0), 2: (1, 1)}
+    m.admit("a")
+    m.reserve([("a", 9)])
+    m.advance("a", 9)
+    assert m.table("a", 0) == [0, 1, 2] and m.table("a", 1) == [0, 1, 2]
+    m.admit("b")
+    m.reserve([("b", 3)])
+    m.advance("b", 3)
+    rows = m.block_table_rows(["b", "a"], 0)
+    assert rows.tolist() == [[3, UNMAPPED, UNMAPPED], [0, 1, 2]] and rows.dtype.name == "int32"
+    m.check()
+
+
+def test_window_pages_are_given_back():
+    m = CacheManager({0: FULL, 1: WIN}, page_size=4, pages_per_group={FULL: 16, WIN: 5}, max_requests=2)
+    m.admit("a")
+    length = 0
+    for n in (7, 1, 1, 6, 2, 9, 1, 1, 1, 5, 8):
+        m.reserve([("a", length + n)])
+        # every position a token of this step may read is mapped in the window group
+        lo = max(0, length - 10 + 1)
+        for pos in range(lo, length + n):
+            assert m.table("a", 1)[pos // 4] != UNMAPPED
+        length += n
+        m.advance("a", length)
+        held = m.pages_held("a")
+        assert held[0] == -(-length // 4)
+        assert held[1] <= m.groups[1].peak_pages(10_000, 9)
+        first_needed = max(0, length - 10 + 1)
+        assert all(p == UNMAPPED for p in m.table("a", 1)[:first_needed // 4])
+        m.check()
+    assert length == 42 and m.pages_held("a")[1] <= 4      # 42 tokens passed through 5 pages
+    m.release("a")
+    assert m.free_pages() == [16, 5]
+
+
+def test_all_or_nothing_growth():
+    m = CacheManager({0: FULL}, page_size=4, pages_per_group=6, max_requests=3)
+    for r in "abc":
+        m.admit(r)
+    m.reserve([("a", 8), ("b", 5)])
+    m.advance("a", 8); m.advance("b", 5)
+    before = (list(m.table("a", 0)), list(m.table("b", 0)), list(m.table("c", 0)), m.free_pages())
+    with pytest.raises(OutOfPages):
+        m.reserve([("c", 4), ("a", 12), ("b", 9)])          # needs 1 + 1 + 1 > 2 free
+    assert (m.table("a", 0), m.table("b", 0), m.table("c", 0), m.free_pages()) == before
+    m.check()
+    m.reserve([("c", 4), ("a", 12)])                          # exactly the two free pages
+    assert m.free_pages() == [0]
+    m.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_the_invariants(seed):
+    rng = random.Random(seed)
+    m = CacheManager({0: FULL, 1: WIN, 2: FULL}, page_size=rng.choice([2, 4, 8]),
+                     pages_per_group={FULL: 24, WIN: 10}, max_requests=4)
+    lengths: dict[str, int] = {}
+    seen_pages = [set(), set()]
+    reused = False
+    next_id = 0
+    for _ in range(600):
+        action = rng.random()
+        if action < 0.25 and len(lengths) < 4:
+            rid = f"r{next_id}"; next_id += 1
+            m.admit(rid); lengths[rid] = 0
+        elif action < 0.40 and lengths:
+            rid = rng.choice(sorted(lengths))
+            m.release(rid); del lengths[rid]
+        elif lengths:
+            batch = rng.sample(sorted(lengths), rng.randint(1, len(lengths)))
+            wants = [(r, lengths[r] + rng.choice([1, 1, 1, 2, 5, 13])) for r in batch]
+            snapshot = {r: [list(m.table(r, g)) for g in range(2)] for r in lengths}
+            free_before = m.free_pages()
+            try:
+                m.reserve(wants)
+            except OutOfPages:
+                assert m.free_pages() == free_before
+                for r in lengths:
+                    assert [list(m.table(r, g)) for g in range(2)] == snapshot[r]
+                victim = max(lengths, key=lengths.get)
+                m.release(victim); del lengths[victim]
+            else:
+                for r, n in wants:
+                    for g in range(2):
+                        for p in m.table(r, g):
+                            if p != UNMAPPED:
+                                if p in seen_pages[g] and p not in snapshot[r][g]:
+                                    reused = True
+                                seen_pages[g].add(p)
+                    m.advance(r, n); lengths[r] = n
+        m.check()
+        for r, n in lengths.items():
+            assert m.length(r) == n
+            assert m.pages_held(r)[0] == -(-n // m.page_size)
+    for r in list(lengths):
+        m.release(r)
+    m.check()
+    assert m.free_pages() == [24, 10] and m.slots.free_slots == 4
+    assert reused                                               # pages were used again
