@@ -1,0 +1,124 @@
+"""Helpers of the GPU tests: model folders, plain logits, trace replay, bounds."""
+from __future__ import annotations
+
+import functools
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import torch
+
+import plain_qwen3 as P
+from tiny import CONFIGS, make_model_folder, nmse, read_config, read_weights
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
+
+# Error bounds, fixed before the kernels were written.  float32: the engine
+# against the float64 plain model.  bfloat16: against the plain model with the
+# same bfloat16 weights and with activations rounded where the engine stores
+# 16-bit values (the reference's bound for its GPU path against its CPU oracle
+# is NMSE <= 1e-4, tests/kipp_test.c:2945-3083).
+BOUND = {"float32": 1e-10, "bfloat16": 1e-4}
+
+_tmp = tempfile.TemporaryDirectory(prefix="kipp_b200_tests_")
+
+
+@functools.lru_cache(maxsize=None)
+def model_folder(name: str) -> str:
+    return make_model_folder(os.path.join(_tmp.name, name), name)
+
+
+@functools.lru_cache(maxsize=None)
+def plain_weights(name: str, dtype: str):
+    w = read_weights(model_folder(name))
+    if dtype == "bfloat16":
+        # matrices are rounded to bfloat16 for the tensor cores; 1-D scales stay float32
+        w = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in w.items()}
+    return read_config(model_folder(name)), w
+
+
+_plain_cache: dict = {}
+
+
+def plain_logits(name: str, dtype: str, tokens: list) -> torch.Tensor:
+    """[len(tokens), vocab] logits of the plain model for one whole sequence."""
+    key = (name, dtype, tuple(tokens))
+    if key not in _plain_cache:
+        cfg, w = plain_weights(name, dtype)
+        rounding = P.bf16_round if dtype == "bfloat16" else P.no_round
+        with torch.no_grad():
+            _plain_cache[key] = P.plain_forward(cfg, w, list(tokens), rounding=rounding)
+    return _plain_cache[key]
+
+
+def random_tokens(name: str, n: int, seed: int) -> list:
+    vocab = CONFIGS[name][0]["vocab_size"]
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def replay(name: str, dtype: str, steps: list, max_tokens: int, page_size: int = 16) -> dict:
+    """Run ``steps`` (dicts as bin/trace_run reads them) through the program;
+    returns {step: float32 array [wanted, vocab]}."""
+    vocab = CONFIGS[name][0]["vocab_size"]
+    with tempfile.TemporaryDirectory(prefix="trace_") as out:
+        proc = subprocess.run(
+            [sys.executable, TRACE_RUN, "--model", model_folder(name), "--dtype", dtype, "--out", out,
+             "--max-tokens", str(max_tokens), "--page-size", str(page_size)],
+            input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+            timeout=600)
+        assert proc.returncode == 0, proc.stderr[-4000:]
+        done = [line for line in proc.stdout.splitlines() if line.startswith("done ")]
+        assert done == [f"done {s['step']}" for s in steps], proc.stdout[-2000:]
+        result = {}
+        for s in steps:
+            wanted = sum(len(e.get("want", [])) for e in s["entries"])
+            path = os.path.join(out, f"{s['step']}.f32")
+            if wanted:
+                result[s["step"]] = np.fromfile(path, dtype="<f4").reshape(wanted, vocab)
+            else:
+                assert not os.path.exists(path)
+        return result
+
+
+class Trace:
+    """Builds replay steps and remembers which sequence position each wanted
+    logits row belongs to."""
+
+    def __init__(self):
+        self.steps: list = []
+        self.rows: dict = {}          # step -> [(request, position)]
+        self.fed: dict = {}
+
+    def step(self, entries: list, end: list = ()) -> None:
+        """entries: (request id, tokens, want indices)."""
+        n = len(self.steps)
+        rows, out = [], []
+        for rid, tokens, want in entries:
+            start = self.fed.get(rid, 0)
+            out.append({"id": rid, "tokens": list(tokens), "want": list(want)})
+            rows += [(rid, start + w) for w in want]
+            self.fed[rid] = start + len(tokens)
+        self.steps.append({"step": n, "entries": out, "end": list(end)})
+        self.rows[n] = rows
+        for rid in end:
+            self.fed.pop(rid, None)
+
+    def collect(self, result: dict) -> dict:
+        """{(request, position): logits row}"""
+        out = {}
+        for step, rows in self.rows.items():
+            for i, key in enumerate(rows):
+                assert key not in out
+                out[key] = torch.from_numpy(result[step][i].copy())
+        return out
+
+
+def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "") -> None:
+    e = nmse(got, want)
+    assert e <= BOUND[dtype], f"{what}: NMSE {e:.3e} above {BOUND[dtype]:.0e}"
+    assert torch.isfinite(got).all(), what
