@@ -1,0 +1,280 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens/s (headline: batch 8),
+prefill tokens/s at 2,048 tokens, decode at batch 1 and 64, each with its
+fraction of the measured roofline.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+The model has the layer sizes of the Qwen3-4B row of BASELINE.json with random
+bfloat16 weights made on the device; prompts are seeded random token ids.  A
+"step" is one decode step of the whole batch.  Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_4B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=2560,
+    intermediate_size=9728, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=128, max_position_embeddings=8192, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, hidden_act="silu", attention_bias=False, initializer_range=0.02,
+    torch_dtype="bfloat16")
+WEIGHT_SEED = 2
+CONTEXT = 8192            # BASELINE.json configs[2]: context length 8192
+POINT_PROMPT = 2048       # ... decode at batch 1/8/64 with 2,048-token prompts
+PREFILL_TOKENS = 2048
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            return out, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm() -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference is a C project without setup.py or pyproject.toml: pip cannot "
+                       "install it, and its CUDA path needs a GGUF checkpoint of a registered repository"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="run fewer layers than the configuration has (named in the record)")
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and the prefill")
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from kipp_b200 import kernels
+    from kipp_b200.config import config_from_dict
+    from kipp_b200.engine import StepEntry
+    from kipp_b200.engine.llm import LLM
+    from kipp_b200.kernels import ops as kops
+
+    pk, pk_src = peaks()
+    cfg = dict(QWEN3_4B)
+    layers_full = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    config = config_from_dict(cfg)
+    K, W, B = args.steps, args.warmup, args.batch
+    span = K + W + 2
+    batches = [B] if args.skip_points else sorted({1, B, 64})
+    cache_tokens = max([B * (args.context + PAGE)] +
+                       [b * (POINT_PROMPT + span + PAGE) for b in batches if b != B])
+    llm = LLM(config, dtype="bfloat16", kv_block_size=PAGE, kv_tokens=cache_tokens, ctx=args.context,
+              max_requests=max(batches), max_batch_tokens=max(PREFILL_TOKENS, max(batches)),
+              chunk=PREFILL_TOKENS, seed=WEIGHT_SEED)
+    eng = llm.engine
+    dev = eng.runtime.device
+    g = torch.Generator().manual_seed(1234)
+
+    def prompt(n):
+        return torch.randint(0, config.vocab_size, (n,), generator=g).tolist()
+
+    weight_bytes = eng.weight_bytes()
+    kv_bytes_token = eng.cache_bytes_per_token()
+
+    # ---- prefill of one 2,048-token prompt ------------------------------------------
+    prefill = None
+    if not args.skip_points:
+        toks = prompt(PREFILL_TOKENS)
+        times = []
+        for i in range(3 + 3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            a.record()
+            eng.step([StepEntry(("prefill", i), toks, [PREFILL_TOKENS - 1])])
+            b.record()
+            torch.cuda.synchronize(dev)
+            eng.finish(("prefill", i))
+            if i >= 3:
+                times.append(a.elapsed_time(b))
+        ms = statistics.median(times)
+        c = config
+        gemm_params = c.num_hidden_layers * (c.hidden_size * (c.q_dim + 2 * c.kv_dim) +
+                                             c.q_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+        T = PREFILL_TOKENS
+        flops = 2.0 * T * gemm_params + 2.0 * c.hidden_size * c.vocab_size \
+            + c.num_hidden_layers * 2.0 * T * (T + 1) * c.head_dim * c.num_attention_heads
+        prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+                   "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "flops": flops, "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src}
+
+    # ---- decode ------------------------------------------------------------------------
+    def fill(batch: int, context: int, tag: str) -> list:
+        """``batch`` live requests holding ``context`` tokens each (real prefill)."""
+        rids = [(tag, i) for i in range(batch)]
+        for rid in rids:
+            toks = prompt(context)
+            for a in range(0, context, PREFILL_TOKENS):
+                eng.step([StepEntry(rid, toks[a:a + PREFILL_TOKENS], [])])
+        return rids
+
+    def decode_run(rids: list, steps: int, warmup: int, sample_clocks: bool):
+        """Greedy decode of all ``rids`` for warmup + steps steps; device-timed."""
+        batch = len(rids)
+        next_tokens = prompt(batch)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = None
+        launches0 = 0
+        for i in range(warmup + steps):
+            if i == warmup:
+                torch.cuda.synchronize(dev)
+                sampler = ClockSampler() if sample_clocks else None
+                launches0 = kops.launch_count()
+                a.record()
+            logits = eng.step([StepEntry(r, [t], [0]) for r, t in zip(rids, next_tokens)])
+            next_tokens = kernels.argmax_rows(logits).tolist()
+        b.record()
+        torch.cuda.synchronize(dev)
+        clocks = sampler.stop() if sampler else None
+        ms = a.elapsed_time(b) / steps
+        return ms, clocks, kops.launch_count() - launches0
+
+    headline_ctx = args.context - span
+    rids = fill(B, headline_ctx, "head")
+    ms_step, clocks, launches = decode_run(rids, K, W, True)
+    ctx_mid = headline_ctx + W + K / 2.0
+    step_bytes = weight_bytes + B * ctx_mid * kv_bytes_token
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    for r in rids:
+        eng.finish(r)
+    eng.runtime.check_status()
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            if b == B and args.context == POINT_PROMPT + span:
+                points[f"decode_b{b}"] = round(B / (ms_step / 1e3), 1)
+                continue
+            rr = fill(b, POINT_PROMPT, f"p{b}")
+            ms_b, _, _ = decode_run(rr, min(K, 32), 3, False)
+            points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
+            points[f"decode_b{b}_ms"] = round(ms_b, 4)
+            for r in rr:
+                eng.finish(r)
+
+    # ---- end to end through the Python entry point: host token ids in and out --------
+    from kipp_b200.engine.scheduler import Request
+    sched = llm.new_scheduler()
+    e2e_ctx = min(headline_ctx, args.context - (K + 2))
+    for i in range(B):
+        sched.add(Request(id=("e2e", i), prompt=prompt(e2e_ctx), max_new_tokens=K + 1))
+    llm.run(sched, record_steps=True)
+    dec = [s for s in llm.step_log if s["decode_only"]][1:]            # first decode step = warm-up
+    e2e_s = sum(s["seconds"] for s in dec)
+    e2e = {"value": round(sum(s["sampled"] for s in dec) / e2e_s, 1) if dec else None,
+           "unit": "tokens/s",
+           "h2d_bytes_per_step": int(statistics.median(s["h2d_bytes"] for s in dec)) if dec else 0,
+           "d2h_bytes_per_step": int(statistics.median(s["d2h_bytes"] for s in dec)) if dec else 0,
+           "steps": len(dec)}
+
+    record = {
+        "metric": "decode tokens/s, Qwen3-4B-shaped bf16, batch 8 (prefill and batch 1/64 beside it)",
+        "value": round(B / (ms_step / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K,
+        "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02) seed 2, seeded random token ids",
+        "config": {"model": "Qwen3-4B-shaped", "layers": config.num_hidden_layers,
+                   "layers_full": layers_full, "hidden": config.hidden_size,
+                   "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
+                   "head_dim": config.head_dim, "intermediate": config.intermediate_size,
+                   "vocab": config.vocab_size, "tied": config.tie_word_embeddings,
+                   "global_batch": B, "seq_len": args.context, "decode_context": int(ctx_mid),
+                   "points_prompt": POINT_PROMPT, "kv_block": PAGE, "parallelism": "none (1 GPU)",
+                   "l2": "inputs larger than L2 (weights + cache read once per step)",
+                   "weight_gb": round(weight_bytes / 1e9, 3)},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "bytes_per_step": int(step_bytes), "peak_source": pk_src},
+        "points": points,
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,552 @@
+// bfloat16 attention over the paged cache on the tensor cores: a flash-style
+// kernel for prompt portions and a split-K kernel for single decoded tokens.
+//
+// Reference counterpart: cached_gqa_kernel (cuda/kipp_kernels.cu:160), which
+// walks the keys one by one with block-wide reductions and a serial softmax;
+// the formula is src/kipp.c:2882-2922 (scores (q.k)/sqrt(D) over the keys the
+// token may see, softmax with the maximum subtracted, weighted sum of values,
+// kv head = q head / group).  The split over keys with a final merge follows
+// the idea of the reference's Metal kernels (metal/kipp_kernels.metal:517-626,
+// 741-779): the split length depends only on the query's own context length,
+// so a token is reduced the same way in any batch.
+//
+// Both kernels: keys and values are gathered page by page with cp.async into
+// shared memory (16-byte chunks, XOR-swizzled rows), scores and the weighted
+// sum run on mma.sync m16n8k16 (bf16 in, float32 accumulate), maxima, sums and
+// the rescaling are float32.  tcgen05 is not used here: with 4 to 16 query rows
+// per key (decode) the tensor memory round trip costs more than it saves, and
+// the decode kernel is bound by HBM reads.
+//
+// Cache layout of one layer: [page][kv_head][slot][head_dim].
+#include "common.cuh"
+#include <math.h>
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr int TILE_KEYS = 64;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+// 16-byte asynchronous copy; src_bytes == 0 fills the destination with zeros.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a swizzled tile whose
+// rows hold D bf16 (D * 2 bytes, at least 128).
+template <int D> __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+    return (uint32_t)(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+// Gathers TILE_KEYS rows of keys and of values, positions [j0, j0 + TILE_KEYS),
+// for kv head g into swizzled tiles.  Rows outside [lo, hi] are zero-filled
+// (their scores are masked; zero values keep 0 * v finite).
+template <int D>
+__device__ __forceinline__ void load_kv_tile(uint32_t k_tile, uint32_t v_tile, const bf16* __restrict__ k_pages,
+                                             const bf16* __restrict__ v_pages, const int* __restrict__ table,
+                                             int table_width, int page_size, int n_kv, int g, int j0, int lo,
+                                             int hi) {
+    constexpr int CHUNKS = D / 8;                        // 16-byte chunks per row
+    for (int i = threadIdx.x; i < TILE_KEYS * CHUNKS; i += THREADS) {
+        const int row = i / CHUNKS, chunk = i % CHUNKS;
+        const int j = j0 + row;
+        const bool valid = j >= lo && j <= hi;
+        size_t src = 0;
+        int bytes = 0;
+        if (valid) {
+            const int page = j / page_size < table_width ? table[j / page_size] : -1;
+            if (page >= 0) {
+                src = (((size_t)page * n_kv + g) * page_size + (j % page_size)) * D + chunk * 8;
+                bytes = 16;
+            }
+        }
+        const uint32_t off = tile_offset<D>(row, chunk);
+        cp_async16(k_tile + off, k_pages + src, bytes);
+        cp_async16(v_tile + off, v_pages + src, bytes);
+    }
+}
+
+// One warp: scores of its 16 query rows against `N_TILES * 8` keys starting at
+// tile row `key0`.  q holds the A fragments of the rows (D / 16 k-steps).
+template <int D, int N_TILES>
+__device__ __forceinline__ void qk_scores(float (*s)[4], const uint32_t (*q)[4], uint32_t k_tile, int key0, int lane) {
+#pragma unroll
+    for (int nt = 0; nt < N_TILES; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+    const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int nt = 0; nt < N_TILES; nt += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int row = key0 + (nt + (m >> 1)) * 8 + r;
+            ldmatrix_x4(k_tile + tile_offset<D>(row, 2 * ks + (m & 1)), b0, b1, b2, b3);
+            mma_bf16(s[nt], q[ks], b0, b1);
+            mma_bf16(s[nt + 1], q[ks], b2, b3);
+        }
+    }
+}
+
+// One warp: o += p v for `K_STEPS * 16` keys starting at tile row `key0`; p are
+// the probabilities as A fragments.
+template <int D, int K_STEPS>
+__device__ __forceinline__ void pv_accumulate(float (*o)[4], const uint32_t (*p)[4], uint32_t v_tile, int key0,
+                                              int lane) {
+    const int m = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < K_STEPS; ++kk) {
+#pragma unroll
+        for (int dt = 0; dt < D / 8; dt += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int row = key0 + kk * 16 + (m & 1) * 8 + r;
+            ldmatrix_x4_trans(v_tile + tile_offset<D>(row, dt + (m >> 1)), b0, b1, b2, b3);
+            mma_bf16(o[dt], p[kk], b0, b1);
+            mma_bf16(o[dt + 1], p[kk], b2, b3);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------- prefill
+// Work item = 64 consecutive tokens of one entry (16 per warp) x one query head.
+struct PrefillParams {
+    bf16* out; const bf16* q; const bf16* k_pages; const bf16* v_pages;
+    const int* q_start; const int* context_len; const int* block_table;
+    const int* work;            // [items][2] = (entry, first token of the tile within the entry)
+    int table_width, page_size, n_q, n_kv, window;
+    float scale_log2;           // scale * log2(e)
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(const PrefillParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int TILE_BYTES = TILE_KEYS * D * 2;
+    const uint32_t k_base = smem_u32(smem), v_base = k_base + 2 * TILE_BYTES;    // [2 stages] each
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g4 = lane >> 2, t4 = lane & 3;
+    const int entry = p.work[2 * blockIdx.x], tile_tok = p.work[2 * blockIdx.x + 1];
+    const int h = blockIdx.y, g = h / (p.n_q / p.n_kv);
+    const int qs = p.q_start[entry], q_len = p.q_start[entry + 1] - qs;
+    const int ctx = p.context_len[entry];
+    const int* table = p.block_table + (size_t)entry * p.table_width;
+
+    // this thread's two rows: tokens r0 and r0 + 8 of the tile
+    const int tok0 = tile_tok + warp * 16 + g4, tok1 = tok0 + 8;
+    const bool live0 = tok0 < q_len, live1 = tok1 < q_len;
+    const int pos0 = ctx + tok0, pos1 = ctx + tok1;
+    uint32_t qf[D / 16][4];
+    {
+        const bf16* q0 = p.q + ((size_t)(qs + min(tok0, q_len - 1)) * p.n_q + h) * D;
+        const bf16* q1 = p.q + ((size_t)(qs + min(tok1, q_len - 1)) * p.n_q + h) * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qf[ks][0] = *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t4);
+            qf[ks][1] = *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t4);
+            qf[ks][2] = *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t4);
+            qf[ks][3] = *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t4);
+        }
+    }
+    // keys the tile may see: from the first token's window start to the last token
+    const int tile_first = ctx + tile_tok, tile_last = ctx + min(tile_tok + 63, q_len - 1);
+    const int lo = p.window > 0 ? max(0, tile_first - p.window + 1) : 0, hi = tile_last;
+    const int first_tile = lo / TILE_KEYS, last_tile = hi / TILE_KEYS;
+    const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo1 = p.window > 0 ? max(0, pos1 - p.window + 1) : 0;
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    load_kv_tile<D>(k_base, v_base, p.k_pages, p.v_pages, table, p.table_width, p.page_size, p.n_kv, g,
+                    first_tile * TILE_KEYS, lo, hi);
+    cp_async_commit();
+    for (int kt = first_tile; kt <= last_tile; ++kt) {
+        const int buf = (kt - first_tile) & 1;
+        if (kt < last_tile) {
+            load_kv_tile<D>(k_base + (buf ^ 1) * TILE_BYTES, v_base + (buf ^ 1) * TILE_BYTES, p.k_pages, p.v_pages,
+                            table, p.table_width, p.page_size, p.n_kv, g, (kt + 1) * TILE_KEYS, lo, hi);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        float s[8][4];
+        qk_scores<D, 8>(s, qf, k_base + buf * TILE_BYTES, 0, lane);
+        // mask, running maximum
+        const int j_base = kt * TILE_KEYS + 2 * t4;
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = j_base + nt * 8 + e;
+                s[nt][e] = (live0 && j >= lo0 && j <= pos0) ? s[nt][e] * p.scale_log2 : -INFINITY;
+                s[nt][2 + e] = (live1 && j >= lo1 && j <= pos1) ? s[nt][2 + e] * p.scale_log2 : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][e]);
+                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float c0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mx0);
+        const float c1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mx1);
+        const float b0 = (mx0 == -INFINITY) ? 0.f : mx0, b1 = (mx1 == -INFINITY) ? 0.f : mx1;
+        float sum0 = 0.f, sum1 = 0.f;
+        uint32_t pf[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const float p00 = exp2f(s[nt][0] - b0), p01 = exp2f(s[nt][1] - b0);
+            const float p10 = exp2f(s[nt][2] - b1), p11 = exp2f(s[nt][3] - b1);
+            sum0 += p00 + p01;
+            sum1 += p10 + p11;
+            pf[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p00, p01);
+            pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p10, p11);
+        }
+        l0 = l0 * c0 + sum0;
+        l1 = l1 * c1 + sum1;
+        m0 = mx0;
+        m1 = mx1;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+        pv_accumulate<D, 4>(o, pf, v_base + buf * TILE_BYTES, 0, lane);
+        __syncthreads();
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if (live0) {
+        bf16* dst = p.out + ((size_t)(qs + tok0) * p.n_q + h) * D + 2 * t4;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    }
+    if (live1) {
+        bf16* dst = p.out + ((size_t)(qs + tok1) * p.n_q + h) * D + 2 * t4;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i)
+            *reinterpret_cast<uint32_t*>(dst + i * 8) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    }
+}
+
+// ------------------------------------------------------------------------------ decode
+// CTA = (key split, kv head, decode entry).  Rows of the MMA are the query
+// heads of the kv head's group (at most 16).  The four warps share each 64-key
+// tile and take 16 keys each; their partial results are merged through shared
+// memory, the splits through global scratch by attn_decode_merge_kernel.
+struct DecodeParams {
+    const bf16* q; const bf16* k_pages; const bf16* v_pages;
+    const int* q_start; const int* context_len; const int* block_table;
+    const int* rows;            // [n] entries that are single decoded tokens
+    float* part_o;              // [n][n_q][max_splits][D]
+    float* part_ml;             // [n][n_q][max_splits][2]  (max in log2 units, sum)
+    int table_width, page_size, n_q, n_kv, window, max_splits, split_keys_min;
+    float scale_log2;
+};
+
+// Keys per split for a context of kv_len keys: a function of kv_len alone.
+__host__ __device__ __forceinline__ int decode_split_keys(int kv_len, int max_splits, int split_keys_min) {
+    int keys = split_keys_min;
+    if ((long long)keys * max_splits < kv_len) {
+        keys = (kv_len + max_splits - 1) / max_splits;
+        keys = (keys + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS;
+    }
+    return keys;
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int TILE_BYTES = TILE_KEYS * D * 2;
+    constexpr int STAGES = 3;
+    const uint32_t k_base = smem_u32(smem), v_base = k_base + STAGES * TILE_BYTES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g4 = lane >> 2, t4 = lane & 3;
+    const int n = blockIdx.z, entry = p.rows[n], g = blockIdx.y, split = blockIdx.x;
+    const int group = p.n_q / p.n_kv;
+    const int tok = p.q_start[entry];
+    const int pos = p.context_len[entry];                  // position of the decoded token
+    const int kv_len = pos + 1;
+    const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int split_keys = decode_split_keys(kv_len, p.max_splits, p.split_keys_min);
+    const int n_splits = (kv_len + split_keys - 1) / split_keys;
+    if (split >= n_splits) return;
+    const int lo = max(first_key, split * split_keys), hi = min(pos, (split + 1) * split_keys - 1);
+    const int* table = p.block_table + (size_t)entry * p.table_width;
+    float* my_ml = p.part_ml + (((size_t)n * p.n_q + g * group) * p.max_splits + split) * 2;
+    float* my_o = p.part_o + (((size_t)n * p.n_q + g * group) * p.max_splits + split) * D;
+    const size_t head_stride_ml = (size_t)p.max_splits * 2, head_stride_o = (size_t)p.max_splits * D;
+
+    if (lo > hi) {                                         // split wholly behind the window
+        for (int i = threadIdx.x; i < group; i += THREADS) {
+            my_ml[i * head_stride_ml] = -INFINITY;
+            my_ml[i * head_stride_ml + 1] = 0.f;
+        }
+        return;
+    }
+    // rows g4 and g4 + 8 = heads of the group (zero rows beyond it)
+    uint32_t qf[D / 16][4];
+    {
+        const bf16* q0 = p.q + ((size_t)tok * p.n_q + g * group + min(g4, group - 1)) * D;
+        const bf16* q1 = p.q + ((size_t)tok * p.n_q + g * group + min(g4 + 8, group - 1)) * D;
+        const bool v0 = g4 < group, v1 = g4 + 8 < group;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t4) : 0u;
+            qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t4) : 0u;
+            qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t4) : 0u;
+            qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t4) : 0u;
+        }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const int first_tile = lo / TILE_KEYS, last_tile = hi / TILE_KEYS, n_tiles = last_tile - first_tile + 1;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_tiles)
+            load_kv_tile<D>(k_base + s * TILE_BYTES, v_base + s * TILE_BYTES, p.k_pages, p.v_pages, table,
+                            p.table_width, p.page_size, p.n_kv, g, (first_tile + s) * TILE_KEYS, lo, hi);
+        cp_async_commit();
+    }
+    for (int i = 0; i < n_tiles; ++i) {
+        const int buf = i % STAGES;
+        if (i + STAGES - 1 < n_tiles) {
+            const int nb = (i + STAGES - 1) % STAGES;
+            load_kv_tile<D>(k_base + nb * TILE_BYTES, v_base + nb * TILE_BYTES, p.k_pages, p.v_pages, table,
+                            p.table_width, p.page_size, p.n_kv, g, (first_tile + i + STAGES - 1) * TILE_KEYS, lo, hi);
+        }
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        float s[2][4];
+        qk_scores<D, 2>(s, qf, k_base + buf * TILE_BYTES, warp * 16, lane);
+        const int j_base = (first_tile + i) * TILE_KEYS + warp * 16 + 2 * t4;
+        float mx0 = m0, mx1 = m1;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = j_base + nt * 8 + e;
+                const bool ok = j >= lo && j <= hi;
+                s[nt][e] = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+                s[nt][2 + e] = ok ? s[nt][2 + e] * p.scale_log2 : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][e]);
+                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float c0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mx0);
+        const float c1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mx1);
+        const float b0 = (mx0 == -INFINITY) ? 0.f : mx0, b1 = (mx1 == -INFINITY) ? 0.f : mx1;
+        uint32_t pf[1][4];
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const float p00 = exp2f(s[nt][0] - b0), p01 = exp2f(s[nt][1] - b0);
+            const float p10 = exp2f(s[nt][2] - b1), p11 = exp2f(s[nt][3] - b1);
+            sum0 += p00 + p01;
+            sum1 += p10 + p11;
+            pf[0][nt * 2 + 0] = pack_bf16(p00, p01);
+            pf[0][nt * 2 + 1] = pack_bf16(p10, p11);
+        }
+        l0 = l0 * c0 + sum0;
+        l1 = l1 * c1 + sum1;
+        m0 = mx0;
+        m1 = mx1;
+#pragma unroll
+        for (int d = 0; d < D / 8; ++d) { o[d][0] *= c0; o[d][1] *= c0; o[d][2] *= c1; o[d][3] *= c1; }
+        pv_accumulate<D, 1>(o, pf, v_base + buf * TILE_BYTES, warp * 16, lane);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // merge the four warps: [warp][row 0..15] max and sum, [warp][row][D] values
+    __syncthreads();
+    float* w_m = reinterpret_cast<float*>(smem);                  // [WARPS][16]
+    float* w_l = w_m + WARPS * 16;                                // [WARPS][16]
+    float* w_o = w_l + WARPS * 16;                                // [WARPS][16][D]
+    if (t4 == 0) {
+        w_m[warp * 16 + g4] = m0; w_m[warp * 16 + g4 + 8] = m1;
+        w_l[warp * 16 + g4] = l0; w_l[warp * 16 + g4 + 8] = l1;
+    }
+#pragma unroll
+    for (int d = 0; d < D / 8; ++d) {
+        float* r0 = w_o + ((size_t)warp * 16 + g4) * D + d * 8 + 2 * t4;
+        float* r1 = w_o + ((size_t)warp * 16 + g4 + 8) * D + d * 8 + 2 * t4;
+        r0[0] = o[d][0]; r0[1] = o[d][1];
+        r1[0] = o[d][2]; r1[1] = o[d][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < group * D; i += THREADS) {
+        const int row = i / D, d = i % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, w_m[w * 16 + row]);
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {                          // fixed order
+            const float wm = w_m[w * 16 + row];
+            const float c = (wm == -INFINITY) ? 0.f : exp2f(wm - m);
+            l += w_l[w * 16 + row] * c;
+            acc += w_o[((size_t)w * 16 + row) * D + d] * c;
+        }
+        my_o[row * head_stride_o + d] = acc;
+        if (d == 0) {
+            my_ml[row * head_stride_ml] = m;
+            my_ml[row * head_stride_ml + 1] = l;
+        }
+    }
+}
+
+// out[token, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m), splits in order.
+__global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml, const int* __restrict__ rows,
+                                         const int* __restrict__ q_start, const int* __restrict__ context_len,
+                                         int n_q, int head_dim, int max_splits, int split_keys_min) {
+    const int n = blockIdx.y, h = blockIdx.x;
+    const int entry = rows[n];
+    const int kv_len = context_len[entry] + 1;
+    const int split_keys = decode_split_keys(kv_len, max_splits, split_keys_min);
+    const int n_splits = (kv_len + split_keys - 1) / split_keys;
+    const float* ml = part_ml + ((size_t)n * n_q + h) * max_splits * 2;
+    const float* po = part_o + ((size_t)n * n_q + h) * max_splits * head_dim;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = ml[2 * s];
+        l += (ms == -INFINITY) ? 0.f : ml[2 * s + 1] * exp2f(ms - m);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    bf16* dst = out + ((size_t)q_start[entry] * n_q + h) * head_dim;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = ml[2 * s];
+            if (ms != -INFINITY) acc += po[(size_t)s * head_dim + d] * exp2f(ms - m);
+        }
+        dst[d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int D> int launch_prefill(const PrefillParams& p, int items, cudaStream_t s) {
+    constexpr int SMEM = 4 * TILE_KEYS * D * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_prefill_kernel<D><<<dim3(items, p.n_q), THREADS, SMEM, s>>>(p);
+    return kipp_launch_status();
+}
+
+template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s) {
+    constexpr int PIPE = 6 * TILE_KEYS * D * 2;
+    constexpr int MERGE = (2 * WARPS * 16 + WARPS * 16 * D) * 4;
+    constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_decode_kernel<D><<<dim3(p.max_splits, p.n_kv, n), THREADS, SMEM, s>>>(p);
+    return kipp_launch_status();
+}
+}  // namespace
+
+// Whether these kernels take a head size / group.
+extern "C" int kipp_attn_mma_supported(int head_dim, int n_q, int n_kv) {
+    if (head_dim != 64 && head_dim != 128) return 0;
+    if (n_kv <= 0 || n_q % n_kv) return 0;
+    return 1;
+}
+extern "C" int kipp_attn_decode_supported(int head_dim, int n_q, int n_kv) {
+    return kipp_attn_mma_supported(head_dim, n_q, n_kv) && n_q / n_kv <= 16;
+}
+
+// Prompt portions: `work` lists (entry, first token) of every 64-token tile.
+extern "C" int kipp_attn_prefill_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
+                                     const int* q_start, const int* context_len, const int* block_table,
+                                     int table_width, int page_size, const int* work, int items, int n_q,
+                                     int n_kv, int head_dim, float scale, int window, void* stream) {
+    if (items <= 0) return 0;
+    if (!kipp_attn_mma_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0) return KIPP_ERR_ARG;
+    PrefillParams p;
+    p.out = (bf16*)out; p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+    p.q_start = q_start; p.context_len = context_len; p.block_table = block_table; p.work = work;
+    p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    cudaStream_t s = (cudaStream_t)stream;
+    return head_dim == 64 ? launch_prefill<64>(p, items, s) : launch_prefill<128>(p, items, s);
+}
+
+// Bytes of scratch for n decode entries: partial outputs and (max, sum) pairs.
+extern "C" long long kipp_attn_decode_scratch_bytes(int n, int n_q, int head_dim, int max_splits) {
+    return (long long)n * n_q * max_splits * (head_dim + 2) * 4;
+}
+
+// Single decoded tokens: `rows` lists the n entries; scratch as sized above
+// (part_o first, then part_ml).
+extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
+                                    const int* q_start, const int* context_len, const int* block_table,
+                                    int table_width, int page_size, const int* rows, int n, int n_q, int n_kv,
+                                    int head_dim, float scale, int window, int max_splits, int split_keys_min,
+                                    float* scratch, void* stream) {
+    if (n <= 0) return 0;
+    if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
+        max_splits > 65535 || split_keys_min <= 0 || split_keys_min % TILE_KEYS || scratch == nullptr)
+        return KIPP_ERR_ARG;
+    DecodeParams p;
+    p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+    p.q_start = q_start; p.context_len = context_len; p.block_table = block_table; p.rows = rows;
+    p.part_o = scratch;
+    p.part_ml = scratch + (size_t)n * n_q * max_splits * head_dim;
+    p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
+    p.max_splits = max_splits; p.split_keys_min = split_keys_min;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
+    if (rc) return rc;
+    attn_decode_merge_kernel<<<dim3(n_q, n), head_dim >= 128 ? 128 : 64, 0, s>>>(
+        (bf16*)out, p.part_o, p.part_ml, rows, q_start, context_len, n_q, head_dim, max_splits, split_keys_min);
+    return kipp_launch_status();
+}

@@ -55,7 +55,7 @@ paged_attention_simt_kernel(T* __restrict__ out, const T* __restrict__ q,
         float s = -INFINITY;
         const T* vrow = nullptr;
         if (valid) {
-            const int page = table[j / page_size];
+            const int page = j / page_size < table_width ? table[j / page_size] : -1;
             if (page < 0) {
                 atomicExch(status, 3);        // a needed key is not mapped
             } else {

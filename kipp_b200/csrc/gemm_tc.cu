@@ -1,0 +1,501 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+// TMA -> shared memory -> tcgen05.mma -> tensor memory -> epilogue.
+//
+//   C[t, f] (+)= sum_k X[t, k] * W[f, k]        X [tokens, K], W [features, K]
+//
+// The reference computes these products one output row per block and one token
+// per launch on the CUDA cores (matvec_kernel, cuda/kipp_kernels.cu:93); this
+// kernel is the replacement for all seven projections and the output head.
+//
+// Orientation.  The WEIGHT tile is the M operand of the MMA (128 features per
+// CTA) and the TOKENS are its N operand (16 to 256 per CTA).  So the same
+// kernel serves a 2,048-token prompt (N tile 256, tensor-core bound) and a
+// single decoded token (N tile 16, weight-streaming, HBM bound): a narrow token
+// tile wastes no MMA rows on padding.  The accumulator of a CTA is D[feature
+// lane, token column] in tensor memory; in the epilogue a warp's 32 lanes hold
+// 32 neighbouring features of one token, so stores are contiguous.
+//
+// Work split.  grid = (token tiles, feature tiles, K splits).  With few tokens
+// there are too few tiles to pull the whole HBM bandwidth, so K is split over
+// the CTAs of one thread-block cluster (up to 8, along grid z).  Each CTA puts
+// its partial accumulator into its own shared memory; after a cluster barrier
+// CTA r adds, in split order, the partial sums of its share of the tokens out
+// of all the CTAs' shared memory (distributed shared memory) and runs the
+// epilogue for them.  No global scratch, no atomics, and the order of the sum
+// is fixed.
+//
+// Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor
+// memory and issues the MMAs, warps 2-5 run the epilogue (warp w reads the
+// tensor-memory lanes 32*(w%4) .. +31).  Every mbarrier wait gives up after a
+// bounded number of polls, records it in `status[1]` and lets the CTA drain and
+// free its tensor memory.
+//
+// No cluster, no multicast: every CTA fetches its own tiles.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#define EPI_STORE 0
+#define EPI_ADD 1
+#define EPI_SWIGLU 2
+
+namespace {
+
+constexpr int TILE_F = 128;          // features per CTA = MMA M
+constexpr int TILE_K = 64;           // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr unsigned SPIN_LIMIT = 1u << 24;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false after SPIN_LIMIT polls (or when another role gave up).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` when all MMAs issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// 16 consecutive float32 columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte
+// swizzle, 8-row groups 1024 bytes apart (tile base 1024-byte aligned).
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);          // start address, bits 0-13
+    d |= (uint64_t)0 << 16;                            // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024u >> 4) << 32;                 // stride byte offset: next 8-row group
+    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4)                 // D format f32
+           | (1u << 7)               // A format bf16
+           | (1u << 10)              // B format bf16
+           | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int TILE_T> struct Cfg {
+    static constexpr int W_BYTES = TILE_F * TILE_K * 2;
+    static constexpr int X_BYTES = TILE_T * TILE_K * 2;
+    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+    // stages: as many as fit in ~96 KB for narrow token tiles (two CTAs per
+    // SM), ~192 KB for wide ones
+    static constexpr int STAGES = TILE_T >= 128 ? (192 * 1024) / STAGE_BYTES
+                                                : ((96 * 1024) / STAGE_BYTES > 8 ? 8 : (96 * 1024) / STAGE_BYTES);
+    static constexpr int TMEM_COLS = TILE_T < 32 ? 32 : TILE_T;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct Params {
+    void* C;
+    int out_dtype;          // KIPP_DT_*
+    int epilogue;
+    int tokens, features, K;
+    long long ldc;
+    int k_blocks_per_split; // TILE_K blocks each split handles
+    int splits;
+    int* status;
+};
+
+// Epilogue of one value: thread holds feature f of token t.
+template <typename TC>
+__device__ __forceinline__ void store_value(const Params& p, int t, int f, float v, float partner, int lane) {
+    if (p.epilogue == EPI_SWIGLU) {
+        // gate rows are even, up rows odd; the even lane writes silu(g) * u
+        if ((lane & 1) == 0 && f + 1 < p.features) {
+            const float g = v, u = partner;
+            reinterpret_cast<TC*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = from_f32<TC>(g / (1.0f + __expf(-g)) * u);
+        }
+    } else if (f < p.features) {
+        TC* c = reinterpret_cast<TC*>(p.C) + (size_t)t * p.ldc + f;
+        if (p.epilogue == EPI_ADD) *c = from_f32<TC>(to_f32(*c) + v);
+        else *c = from_f32<TC>(v);
+    }
+}
+
+template <int TILE_T>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const Params p) {
+    using C = Cfg<TILE_T>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_ready = empty + C::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // token tiles vary fastest: CTAs that run together share a weight tile (L2)
+    const int t0 = blockIdx.x * TILE_T;
+    const int f0 = blockIdx.y * TILE_F;
+    const int split = blockIdx.z;
+    const int total_kb = (p.K + TILE_K - 1) / TILE_K;
+    const int kb_begin = split * p.k_blocks_per_split;
+    const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
+    const int n_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                if (i >= C::STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+                uint8_t* wt = tiles + (size_t)s * C::STAGE_BYTES;
+                uint8_t* xt = wt + C::W_BYTES;
+                mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                const int k = (kb_begin + i) * TILE_K;
+                tma_load_2d(wt, &map_w, &full[s], k, f0);
+                tma_load_2d(xt, &map_x, &full[s], k, t0);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(TILE_F, TILE_T);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t wa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+                const uint64_t wd = umma_smem_desc(wa), xd = umma_smem_desc(wa + C::W_BYTES);
+#pragma unroll
+                for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                    // advance 16 elements = 32 bytes inside the swizzled row: +2 in the address field
+                    umma_bf16(tmem_base, wd + 2 * k, xd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);            // stage reusable when these MMAs are done
+            }
+            if (ok) umma_commit(acc_ready);
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue warps 2..5
+        const int q = warp & 3;                    // tensor-memory lane quarter of this warp
+        const int f = f0 + q * 32 + lane;
+        bool ok = n_kb > 0 ? mbar_wait(acc_ready, 0, abort_flag) : true;
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+        if (ok && p.splits == 1) {
+#pragma unroll 1
+            for (int c = 0; c < TILE_T; c += 16) {
+                float v[16];
+                if (n_kb > 0) tmem_ld16(taddr + c, v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int t = t0 + c + j;
+                    const float partner = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                    if (t < p.tokens) {
+                        if (p.out_dtype == KIPP_DT_F32) store_value<float>(p, t, f, v[j], partner, lane);
+                        else store_value<bf16>(p, t, f, v[j], partner, lane);
+                    }
+                }
+            }
+        } else if (ok) {
+            // partial sums of this split into this CTA's shared memory, [token][feature]
+            // (the pipeline stages are idle once the accumulator is complete)
+            float* red = reinterpret_cast<float*>(tiles) + q * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < TILE_T; c += 16) {
+                float v[16];
+                tmem_ld16(taddr + c, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) red[(size_t)(c + j) * TILE_F] = v[j];
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------- split-K fix-up
+    if (p.splits > 1) {
+        // all threads of all CTAs of the cluster: partial sums are visible afterwards
+        asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                     "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+        if (warp >= 2) {
+            const int q = warp & 3;
+            const int f = f0 + q * 32 + lane;
+            const int per = (TILE_T + p.splits - 1) / p.splits;       // tokens this CTA finishes
+            const int j0 = split * per, j1 = min(TILE_T, j0 + per);
+            const uint32_t local = smem_u32(reinterpret_cast<float*>(tiles) + q * 32 + lane);
+            for (int j = j0; j < j1; ++j) {
+                float v = 0.f;
+                for (int s = 0; s < p.splits; ++s) {                    // fixed order
+                    uint32_t remote;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
+                                 : "r"(local + (uint32_t)(j * TILE_F * 4)), "r"(s));
+                    float part;
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(remote) : "memory");
+                    v += part;
+                }
+                const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+                const int t = t0 + j;
+                if (t < p.tokens) {
+                    if (p.out_dtype == KIPP_DT_F32) store_value<float>(p, t, f, v, partner, lane);
+                    else store_value<bf16>(p, t, f, v, partner, lane);
+                }
+            }
+        }
+        // nobody's shared memory may go away while a neighbour still reads it
+        asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                     "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols; long long ld; int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
+        h = h * 1000003u ^ (size_t)k.ld;   h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// Row-major bf16 [rows, cols] with leading dimension ld; box = [box_rows, 64].
+int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiled fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int TILE_T>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
+    using C = Cfg<TILE_T>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TILE_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    if (p.splits == 1) {
+        gemm_tc_kernel<TILE_T><<<grid, THREADS, C::SMEM, s>>>(mw, mx, p);
+        return kipp_launch_status();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = p.splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TILE_T>, mw, mx, p);
+    return e == cudaSuccess ? kipp_launch_status() : (int)e;
+}
+
+int pick_tile_t(int tokens) {
+    if (tokens <= 16) return 16;
+    if (tokens <= 32) return 32;
+    if (tokens <= 64) return 64;
+    if (tokens <= 128) return 128;
+    return 256;
+}
+}  // namespace
+
+// The token tile and the number of K splits (= cluster size, at most 8) the
+// kernel uses for a shape; want_splits == 0 lets it choose.
+extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_splits, int* tile_t_out,
+                                 int* splits_out) {
+    const int tile_t = pick_tile_t(tokens);
+    const int f_tiles = (features + TILE_F - 1) / TILE_F;
+    const int t_tiles = (tokens + tile_t - 1) / tile_t;
+    const int kb = (K + TILE_K - 1) / TILE_K;
+    int splits = want_splits;
+    if (splits <= 0) {
+        // aim at two CTAs per SM when the tiles alone do not fill the GPU; every
+        // split keeps at least 4 K blocks
+        const int tiles = f_tiles * t_tiles;
+        splits = 1;
+        if (tiles < 148) {
+            splits = (296 + tiles - 1) / tiles;
+            if (splits > kb / 4) splits = kb / 4;
+        }
+    }
+    if (splits > 8) splits = 8;
+    if (splits > kb) splits = kb;
+    if (splits < 1) splits = 1;
+    const int per = (kb + splits - 1) / splits;
+    splits = (kb + per - 1) / per;                     // no empty split
+    if (splits < 1) splits = 1;
+    *tile_t_out = tile_t;
+    *splits_out = splits;
+    return 0;
+}
+
+// C (+)= X W^T.  X [tokens, K] bf16 (ldx), W [features, K] bf16 (ldw), C float32
+// or bf16 (ldc).  Pointers 16-byte aligned, ldx and ldw multiples of 8.
+extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W, int tokens, int features,
+                            int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
+                            int* status, void* stream) {
+    if (tokens <= 0 || features <= 0) return 0;
+    if (K <= 0) return KIPP_ERR_ARG;
+    if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -3;
+    if (epilogue == EPI_ADD && out_dtype != KIPP_DT_F32) return KIPP_ERR_DTYPE;
+    if (epilogue == EPI_SWIGLU && (features & 1)) return KIPP_ERR_ARG;
+    if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
+    int tile_t, planned;
+    kipp_gemm_tc_plan(tokens, features, K, splits, &tile_t, &planned);
+    splits = planned;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, features, K, ldw, TILE_F);
+    if (rc) return rc;
+    rc = make_map(&mx, X, tokens, K, ldx, tile_t);
+    if (rc) return rc;
+    Params p;
+    p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
+    p.tokens = tokens; p.features = features; p.K = K; p.ldc = ldc;
+    const int kb = (K + TILE_K - 1) / TILE_K;
+    p.k_blocks_per_split = (kb + splits - 1) / splits;
+    p.splits = splits; p.status = status;
+    dim3 grid((tokens + tile_t - 1) / tile_t, (features + TILE_F - 1) / TILE_F, splits);
+    if (grid.y > 65535) return KIPP_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (tile_t) {
+    case 16: return launch<16>(mw, mx, p, grid, s);
+    case 32: return launch<32>(mw, mx, p, grid, s);
+    case 64: return launch<64>(mw, mx, p, grid, s);
+    case 128: return launch<128>(mw, mx, p, grid, s);
+    default: return launch<256>(mw, mx, p, grid, s);
+    }
+}

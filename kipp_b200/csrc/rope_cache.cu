@@ -46,7 +46,8 @@ __global__ void qk_norm_rope_write_kernel(
         dst = q_out + ((size_t)t * n_q + h) * head_dim;
     } else {
         const int e = entry_of_token[t];
-        const int page = block_table[(size_t)e * table_width + pos / page_size];
+        const int slot = pos / page_size;
+        const int page = slot < table_width ? block_table[(size_t)e * table_width + slot] : -1;
         if (page < 0) {                       // unmapped page: refuse, never write
             if (lane == 0) atomicExch(status, 2);
             return;

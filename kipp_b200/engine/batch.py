@@ -14,6 +14,9 @@ import numpy as np
 import torch
 
 
+ATTENTION_TILE = 64       # tokens per work item of the prefill attention kernel
+
+
 @dataclasses.dataclass
 class StepEntry:
     """One request's share of a step: its next ``tokens`` and the indices among
@@ -36,6 +39,12 @@ class StepMeta:
     logit_rows: Optional[torch.Tensor]  # int32 [R] token rows whose logits are wanted
     n_logit_rows: int
     block_tables: list                # per cache group: int32 [entries, width]
+    decode_rows: Optional[torch.Tensor] = None    # int32 [n]: entries that bring one token
+    n_decode: int = 0
+    prefill_work: Optional[torch.Tensor] = None   # int32 [items, 2]: (entry, first token) per 64-token tile
+    n_prefill_items: int = 0
+    all_work: Optional[torch.Tensor] = None       # the same over every entry (for kernels without a decode path)
+    n_all_items: int = 0
     # host copies for kernel choice
     q_lens: list = dataclasses.field(default_factory=list)
     kv_lens: list = dataclasses.field(default_factory=list)
@@ -101,9 +110,15 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
             if not 0 <= w < q_lens[i]:
                 raise ValueError(f"want index {w} is outside the entry's {q_lens[i]} tokens")
             rows.append(a + w)
-    parts = [token_ids, positions, entry_of_token, q_start,
+    decode_rows = [i for i, q in enumerate(q_lens) if q == 1]
+    prefill_work = [(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(0, q, ATTENTION_TILE)]
+    all_work = [(i, t) for i, q in enumerate(q_lens) for t in range(0, q, ATTENTION_TILE)]
+    fixed = [token_ids, positions, entry_of_token, q_start,
              np.asarray(starts, dtype=np.int32), np.asarray(slots, dtype=np.int32),
-             np.asarray(rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
+             np.asarray(rows, dtype=np.int32), np.asarray(decode_rows, dtype=np.int32),
+             np.asarray(prefill_work, dtype=np.int32).reshape(-1),
+             np.asarray(all_work, dtype=np.int32).reshape(-1)]
+    parts = fixed + [t.reshape(-1) for t in tables]
     # 4-int alignment of every section keeps 16-byte alignment for vector loads.
     offsets, total = [], 0
     for p in parts:
@@ -124,10 +139,14 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
     def sec(i):
         return dev[offsets[i]:offsets[i] + parts[i].size]
 
-    block_tables = [sec(7 + g).view(tables[g].shape) for g in range(len(tables))]
+    block_tables = [sec(len(fixed) + g).view(tables[g].shape) for g in range(len(tables))]
     return StepMeta(tokens=T, entries=n, token_ids=sec(0), positions=sec(1), entry_of_token=sec(2),
                     q_start=sec(3), context_len=sec(4), slots=sec(5),
                     logit_rows=sec(6) if rows else None, n_logit_rows=len(rows),
-                    block_tables=block_tables, q_lens=q_lens,
+                    block_tables=block_tables,
+                    decode_rows=sec(7) if decode_rows else None, n_decode=len(decode_rows),
+                    prefill_work=sec(8).view(-1, 2) if prefill_work else None,
+                    n_prefill_items=len(prefill_work),
+                    all_work=sec(9).view(-1, 2), n_all_items=len(all_work), q_lens=q_lens,
                     kv_lens=[s + q for s, q in zip(starts, q_lens)],
                     extra={"h2d_bytes": total * 4})

@@ -96,6 +96,7 @@ class Engine:
                            for cid, ss in state_specs.items()}
         self._staging = Staging()
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # -- construction ------------------------------------------------------------
     @classmethod
@@ -183,6 +184,7 @@ class Engine:
         rt = self.runtime
         with torch.cuda.device(rt.device):
             meta = pack_step(entries, starts, slots, tables, rt.device, self._staging)
+            self.last_h2d_bytes = meta.extra["h2d_bytes"]
             logits = self._forward(StepContext(self, meta))
         for e, s in zip(entries, starts):
             self.cache.advance(e.request, s + len(e.tokens))

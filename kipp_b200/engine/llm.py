@@ -107,12 +107,16 @@ class LLM:
         return [GenerationResult(r.id, r.prompt, list(r.output), r.finish_reason or "abort",
                                  r.preemptions) for r in requests]
 
-    def run(self, sched: Scheduler) -> None:
-        """Drive ``sched`` until no request is left: plan, step, sample, record."""
+    def run(self, sched: Scheduler, record_steps: bool = False) -> None:
+        """Drive ``sched`` until no request is left: plan, step, sample, record.
+        With ``record_steps`` every step's wall time (token ids on the host
+        before, sampled ids on the host after) goes to ``self.step_log``."""
         engine = self.engine
         steps = tokens = sampled_total = 0
+        self.step_log = []
         t0 = time.perf_counter()
         while sched.has_work():
+            t_step = time.perf_counter()
             plan = sched.schedule()
             if plan is None:
                 raise RuntimeError("requests are waiting but none can be admitted")
@@ -127,6 +131,14 @@ class LLM:
                 for r, s in zip(rs, states):
                     r.rng_state = s
             sched.complete(plan, sampled)
+            if record_steps:
+                if not sampled:
+                    torch.cuda.synchronize(engine.runtime.device)
+                self.step_log.append({
+                    "seconds": time.perf_counter() - t_step, "tokens": plan.tokens,
+                    "sampled": len(sampled),
+                    "decode_only": all(len(e.tokens) == 1 for e in plan.entries),
+                    "h2d_bytes": engine.last_h2d_bytes, "d2h_bytes": 4 * len(sampled)})
             steps += 1
             tokens += plan.tokens
             sampled_total += len(sampled)

@@ -1,10 +1,70 @@
-"""Choice among the bfloat16 attention kernels."""
+"""Launchers of the tensor-core attention kernels (bfloat16) and the choice
+between them and the CUDA-core kernel."""
 from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .ops import KernelError, _check, _fn, _ptr, _stream, c_float, c_int, c_void_p
+
+MAX_SPLITS = 32           # key splits of one decoded token
+SPLIT_KEYS_MIN = 256      # keys per split until MAX_SPLITS of them do not cover the context
+
+_scratch: dict = {}
+
+
+def supported(head_dim: int, n_q: int, n_kv: int) -> bool:
+    f = _fn("attention_mma", "kipp_attn_mma_supported", [c_int, c_int, c_int])
+    return bool(f(head_dim, n_q, n_kv))
+
+
+def decode_supported(head_dim: int, n_q: int, n_kv: int) -> bool:
+    f = _fn("attention_mma", "kipp_attn_decode_supported", [c_int, c_int, c_int])
+    return bool(f(head_dim, n_q, n_kv))
 
 
 def choose(meta, n_q, n_kv, head_dim, page_size) -> str:
-    return "simt"
+    return "mma" if supported(head_dim, n_q, n_kv) else "simt"
 
 
-def run(impl, *args) -> None:
-    raise NotImplementedError(impl)
+def decode_scratch(device: torch.device, n: int, n_q: int, head_dim: int) -> torch.Tensor:
+    """float32 scratch of the split-K decode kernel: partial outputs and
+    (max, sum) pairs of every split, kept per device and grown on demand."""
+    floats = n * n_q * MAX_SPLITS * (head_dim + 2)
+    key = (device.type, device.index)
+    cur = _scratch.get(key)
+    if cur is None or cur.numel() < floats:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("attention scratch must exist before a CUDA graph is captured")
+        cur = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[key] = cur
+    return cur
+
+
+def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv, head_dim, scale,
+        window, status) -> None:
+    if impl != "mma":
+        raise KernelError(f"unknown attention implementation {impl!r}")
+    if q.dtype != torch.bfloat16:
+        raise KernelError("attention_mma takes bfloat16")
+    use_decode = meta.n_decode > 0 and decode_supported(head_dim, n_q, n_kv)
+    work, items = (meta.prefill_work, meta.n_prefill_items) if use_decode else (meta.all_work, meta.n_all_items)
+    if items:
+        f = _fn("attention_mma", "kipp_attn_prefill_mma",
+                [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+        _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(meta.q_start),
+                 _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size, _ptr(work),
+                 items, n_q, n_kv, head_dim, float(scale), int(window or 0), _stream()),
+               "attn_prefill_mma")
+    if use_decode:
+        scratch = decode_scratch(q.device, meta.n_decode, n_q, head_dim)
+        f = _fn("attention_mma", "kipp_attn_decode_mma",
+                [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+        _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(meta.q_start),
+                 _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
+                 _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale),
+                 int(window or 0), MAX_SPLITS, SPLIT_KEYS_MIN, _ptr(scratch), _stream()),
+               "attn_decode_mma")

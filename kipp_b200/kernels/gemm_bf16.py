@@ -1,10 +1,60 @@
 """Choice among the bfloat16 matrix-product kernels."""
 from __future__ import annotations
 
+import ctypes
+
+import torch
+
+from .ops import EPILOGUES, KernelError, _check, _fn, _ptr, _stream, c_int, c_void_p, dtype_code
+
+c_ll = ctypes.c_longlong
+
+def plan(tokens: int, features: int, K: int, splits: int = 0):
+    """(token tile, K splits) the tensor-core kernel uses for a shape."""
+    f = _fn("gemm_tc", "kipp_gemm_tc_plan",
+            [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)])
+    tile, sp = c_int(), c_int()
+    f(tokens, features, K, splits, ctypes.byref(tile), ctypes.byref(sp))
+    return tile.value, sp.value
+
+
+def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes these operands (TMA needs 16-byte
+    aligned bases and row pitches)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
 
 def choose(M, N, K, a, w, out, epilogue) -> str:
-    return "simt"
+    return "tc" if tc_ok(a, w) else "simt"
 
 
-def run(impl, out, a, w, epilogue, M) -> None:
-    raise NotImplementedError(impl)
+def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None) -> None:
+    if impl != "tc":
+        raise KernelError(f"unknown gemm implementation {impl!r}")
+    if not tc_ok(a, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned bases and row pitches")
+    N, K = w.shape
+    if status is None:
+        status = _status(a.device)
+    f = _fn("gemm_tc", "kipp_gemm_tc",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int,
+             c_void_p, c_void_p])
+    _check(f(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
+             out.stride(0), EPILOGUES[epilogue], splits, _ptr(status), _stream()), "gemm_tc")
+
+
+_status_words: dict = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index)
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """int32[4]; element 1 is set when a tensor-core kernel gave up a wait."""
+    return _status(device)

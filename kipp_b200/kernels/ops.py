@@ -36,8 +36,18 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far in this process."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
     if code == 0:
+        _launches += 1
         return
     if code == -1:
         raise KernelError(f"{what}: the kernel refuses these sizes")

@@ -66,8 +66,8 @@ def from_bf16_bits(b):
 class SampleParams(ctypes.Structure):
     _fields_ = [("temperature", ctypes.c_float), ("top_p", ctypes.c_float),
                 ("top_k", ctypes.c_uint32), ("min_p", ctypes.c_float),
-                ("repetition_penalty", ctypes.c_float), ("presence_penalty", ctypes.c_float),
-                ("frequency_penalty", ctypes.c_float),
+                ("frequency_penalty", ctypes.c_float), ("presence_penalty", ctypes.c_float),
+                ("repetition_penalty", ctypes.c_float),
                 ("recent_tokens", ctypes.POINTER(ctypes.c_uint32)), ("recent_count", ctypes.c_size_t),
                 ("logit_bias_tokens", ctypes.POINTER(ctypes.c_uint32)),
                 ("logit_bias_values", FP), ("logit_bias_count", ctypes.c_size_t)]

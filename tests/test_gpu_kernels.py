@@ -1,0 +1,380 @@
+"""Each kernel alone against a plain float64 PyTorch reference of the same
+operation, at sizes other than the engine's, in float32 and bfloat16."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+from kipp_b200.engine.batch import StepEntry, pack_step
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from kipp_b200 import kernels
+    return kernels
+
+
+def status():
+    return torch.zeros(4, dtype=torch.int32, device=DEV)
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+# ------------------------------------------------------------------ embedding, norm
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(301, 72, generator=g).to(dtype).to(DEV)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, dtype=torch.float32, device=DEV)
+    st = status()
+    ops().embed_gather(out, table, ids, st)
+    assert torch.equal(out.cpu(), table.float().cpu()[ids.cpu().long()])
+    assert st.tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("size", [40, 100, 2560, 5000])
+def test_rmsnorm(size, out_dtype):
+    g = torch.Generator().manual_seed(size)
+    x = (torch.randn(7, size, generator=g) * 3).to(DEV)
+    for w_dtype in DTYPES:
+        w = (1 + 0.2 * torch.randn(size, generator=g)).to(w_dtype).to(DEV)
+        out = torch.empty(7, size, dtype=out_dtype, device=DEV)
+        ops().rmsnorm(out, x, w, 1e-5)
+        ref = P.plain_rmsnorm(x.cpu(), w.float().cpu(), 1e-5)
+        assert torch.allclose(out.double().cpu(), ref, **tol(out_dtype))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, size, dtype=out_dtype, device=DEV)
+    ops().rmsnorm(out, x, w, 1e-5, rows)
+    assert torch.allclose(out.double().cpu(), ref[[6, 0, 3]], **tol(out_dtype))
+
+
+# ------------------------------------------------------------------ matrix products
+def gemm_ref(a, w, epilogue, base):
+    p = a.double().cpu() @ w.double().cpu().t()
+    if epilogue == "swiglu":
+        return P.plain_silu(p[:, 0::2]) * p[:, 1::2]
+    return base.double().cpu() + p if epilogue == "add" else p
+
+
+@pytest.mark.parametrize("epilogue", ["store", "add", "swiglu"])
+@pytest.mark.parametrize("shape", [(1, 10, 24), (37, 130, 72), (64, 64, 16), (5, 1000, 136), (130, 66, 200)])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gemm_simt(dtype, shape, epilogue):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(dtype).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.2).to(dtype).to(DEV)
+    odt = torch.float32 if epilogue == "add" else dtype
+    out = torch.randn(M, N // 2 if epilogue == "swiglu" else N, generator=g).to(odt).to(DEV)
+    ref = gemm_ref(a, w, epilogue, out)
+    ops().gemm(out, a, w, epilogue, impl="simt")
+    assert torch.allclose(out.double().cpu(), ref, **tol(odt))
+
+
+@pytest.mark.parametrize("epilogue", ["store", "add", "swiglu"])
+@pytest.mark.parametrize("shape", [(1, 128, 64), (8, 256, 128), (17, 250, 192), (64, 1000, 136),
+                                   (100, 384, 2568), (300, 640, 520), (5, 2560, 1216)])
+def test_gemm_tensor_core(shape, epilogue):
+    """tcgen05 kernel: integer data must come out exactly (any wrong tile,
+    swizzle or split shows), random data within bfloat16 rounding; K splits of
+    1, a forced 3 and the cluster maximum 8."""
+    from kipp_b200.kernels import gemm_bf16
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M * 7 + N)
+    for integer in (True, False):
+        for splits in (0, 1, 3, 8):
+            if integer:
+                a = torch.randint(-3, 4, (M, K), generator=g).to(torch.bfloat16).to(DEV)
+                w = torch.randint(-2, 3, (N, K), generator=g).to(torch.bfloat16).to(DEV)
+            else:
+                a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+                w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+            odt = torch.float32 if (epilogue == "add" or integer) else torch.bfloat16
+            out = torch.randn(M, N // 2 if epilogue == "swiglu" else N, generator=g).to(odt).to(DEV)
+            ref = gemm_ref(a, w, epilogue, out)
+            gemm_bf16.run("tc", out, a, w, epilogue, M, splits=splits)
+            got = out.double().cpu()
+            if integer and epilogue != "swiglu":
+                assert torch.equal(got, ref.float().double()), (shape, splits)   # one float32 rounding
+            else:
+                scale = float(ref.abs().max())
+                assert float((got - ref).abs().max()) <= (1e-5 if odt == torch.float32 else 1e-2) * scale
+    assert gemm_bf16.status_word(torch.device(DEV)).tolist() == [0, 0, 0, 0]
+
+
+def test_gemm_refuses_what_it_cannot_take():
+    from kipp_b200.kernels import KernelError, gemm_bf16
+    a = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)          # K = 20: row pitch not 16-byte
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV)
+    assert not gemm_bf16.tc_ok(a, w)
+    with pytest.raises(KernelError):
+        gemm_bf16.run("tc", out, a, w, "store", 4)
+    ops().gemm(out, a, w, "store")                                     # the default path takes it (CUDA cores)
+    with pytest.raises(KernelError):
+        ops().gemm(out, a.cpu(), w, "store")
+
+
+# ------------------------------------------------------------------ norm + rotation + cache write
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [dict(D=16, nq=4, nkv=2, rot=16, norm=True, page=4),
+                                  dict(D=80, nq=3, nkv=3, rot=80, norm=True, page=16),
+                                  dict(D=128, nq=8, nkv=1, rot=128, norm=False, page=8),
+                                  dict(D=64, nq=2, nkv=2, rot=32, norm=True, page=16),
+                                  dict(D=256, nq=2, nkv=1, rot=0, norm=True, page=32)])
+def test_qk_norm_rope_write(case, dtype):
+    D, nq, nkv, rot, page = case["D"], case["nq"], case["nkv"], case["rot"], case["page"]
+    g = torch.Generator().manual_seed(D)
+    entries = [StepEntry("a", [0] * 5, []), StepEntry("b", [0] * 1, []), StepEntry("c", [0] * 19, [])]
+    starts = [13, 40, 0]
+    width = -(-45 // page)
+    n_pages = 3 * width
+    perm = torch.randperm(n_pages, generator=g).int().numpy().reshape(3, width)
+    meta = pack_step(entries, starts, [0, 1, 2], [perm.astype(np.int32)], torch.device(DEV))
+    T = meta.tokens
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, generator=g).to(dtype).to(DEV)
+    qw = (1 + 0.2 * torch.randn(D, generator=g)).to(DEV) if case["norm"] else None
+    kw = (1 + 0.2 * torch.randn(D, generator=g)).to(DEV) if case["norm"] else None
+    theta = 10000.0
+    inv = None
+    if rot:
+        i = torch.arange(rot // 2, dtype=torch.float32)
+        inv = torch.pow(torch.tensor(theta, dtype=torch.float64), (-(2.0 * i) / rot).double()).float().to(DEV)
+    q_out = torch.zeros(T, nq, D, dtype=dtype, device=DEV)
+    kp = torch.zeros(n_pages, nkv, page, D, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    st = status()
+    ops().qk_norm_rope_write(qkv, q_out, kp, vp, qw, kw, 1e-6, inv, rot, meta.positions,
+                             meta.entry_of_token, meta.block_tables[0], page, T, nq, nkv, D, True, st)
+    assert st.tolist() == [0, 0, 0, 0]
+    x = qkv.double().cpu().reshape(T, nq + 2 * nkv, D)
+    pos = meta.positions.cpu().tolist()
+
+    def transform(h, w):
+        if w is not None:
+            h = P.plain_rmsnorm(h, w.cpu(), 1e-6)
+        if rot:
+            h = torch.cat([P.plain_rope(h[..., :rot].float(), pos, theta), h[..., rot:].double()], -1)
+        return h
+    q_ref, k_ref, v_ref = transform(x[:, :nq], qw), transform(x[:, nq:nq + nkv], kw), x[:, nq + nkv:]
+    assert torch.allclose(q_out.double().cpu(), q_ref, **tol(dtype))
+    ent = meta.entry_of_token.cpu().tolist()
+    written = torch.zeros(n_pages, page, dtype=torch.bool)
+    for t in range(T):
+        pg, sl = int(perm[ent[t], pos[t] // page]), pos[t] % page
+        assert torch.allclose(kp[pg, :, sl].double().cpu(), k_ref[t], **tol(dtype)), t
+        assert torch.allclose(vp[pg, :, sl].double().cpu(), v_ref[t], **tol(dtype)), t
+        written[pg, sl] = True
+    assert float(kp.float().abs().sum(dim=(1, 3)).cpu()[~written].sum()) == 0.0    # nothing else touched
+    # a run that reads another run's cache writes nothing
+    kp2 = torch.zeros_like(kp)
+    ops().qk_norm_rope_write(qkv, q_out, kp2, kp2, qw, kw, 1e-6, inv, rot, meta.positions,
+                             meta.entry_of_token, meta.block_tables[0], page, T, nq, nkv, D, False, st)
+    assert float(kp2.float().abs().sum()) == 0.0
+
+
+# ------------------------------------------------------------------ attention
+def attention_case(seed, D, nq, nkv, page, layout, dtype, width=None):
+    """layout: list of (cached tokens, new tokens).  Random pages in a permuted
+    pool; returns everything the kernels and the reference need."""
+    g = torch.Generator().manual_seed(seed)
+    entries = [StepEntry(i, [0] * n, []) for i, (_, n) in enumerate(layout)]
+    starts = [c for c, _ in layout]
+    need = [-(-(c + n) // page) for c, n in layout]
+    width = width or max(need)
+    n_pages = sum(need) + 3
+    perm = torch.randperm(n_pages, generator=g).int().tolist()
+    table = np.full((len(layout), width), -1, dtype=np.int32)
+    at = 0
+    for i, k in enumerate(need):
+        table[i, :k] = perm[at:at + k]
+        at += k
+    meta = pack_step(entries, starts, list(range(len(layout))), [table], torch.device(DEV))
+    q = torch.randn(meta.tokens, nq, D, generator=g).to(dtype).to(DEV)
+    kp = torch.randn(n_pages, nkv, page, D, generator=g).to(dtype).to(DEV)
+    vp = torch.randn(n_pages, nkv, page, D, generator=g).to(dtype).to(DEV)
+    return meta, table, q, kp, vp
+
+
+def attention_ref(meta, table, q, kp, vp, layout, page, window, scale):
+    T, nq, D = q.shape
+    nkv = kp.shape[1]
+    out = torch.zeros(T, nq, D, dtype=torch.float64)
+    qc, kc, vc = q.double().cpu(), kp.double().cpu(), vp.double().cpu()
+    t = 0
+    for e, (ctx, n) in enumerate(layout):
+        total = ctx + n
+        pages = torch.tensor(table[e, :-(-total // page)].tolist())
+        keys = kc[pages].permute(0, 2, 1, 3).reshape(-1, nkv, D)[:total]
+        vals = vc[pages].permute(0, 2, 1, 3).reshape(-1, nkv, D)[:total]
+        for i in range(n):
+            pos = ctx + i
+            lo = 0 if not window else max(0, pos - window + 1)
+            for h in range(nq):
+                gk = h // (nq // nkv)
+                s = (keys[lo:pos + 1, gk] @ qc[t, h]) * scale
+                out[t, h] = P.plain_softmax(s) @ vals[lo:pos + 1, gk]
+            t += 1
+    return out
+
+
+LAYOUTS = [[(0, 70), (130, 1), (5, 2), (63, 66), (300, 1)],
+           [(0, 1), (1, 1), (15, 1), (16, 1), (255, 1), (256, 1), (257, 1), (700, 1)],
+           [(0, 200)], [(100, 3), (0, 64), (64, 64), (127, 2)]]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("shape", [dict(D=16, nq=4, nkv=2, page=16), dict(D=48, nq=6, nkv=3, page=8),
+                                   dict(D=128, nq=8, nkv=1, page=4), dict(D=256, nq=2, nkv=2, page=32)])
+def test_attention_simt(shape, window, dtype):
+    D, nq, nkv, page = shape["D"], shape["nq"], shape["nkv"], shape["page"]
+    for li, layout in enumerate(LAYOUTS[:2] + LAYOUTS[3:]):
+        meta, table, q, kp, vp = attention_case(li, D, nq, nkv, page, layout, dtype)
+        out = torch.zeros_like(q)
+        st = status()
+        ops().attention(out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D),
+                        window, st, impl="simt")
+        ref = attention_ref(meta, table, q, kp, vp, layout, page, window, 1 / math.sqrt(D))
+        assert st.tolist() == [0, 0, 0, 0]
+        assert torch.allclose(out.double().cpu(), ref, **tol(dtype)), (shape, li)
+
+
+@pytest.mark.parametrize("window", [None, 37, 300])
+@pytest.mark.parametrize("shape", [dict(D=64, nq=4, nkv=2, page=16), dict(D=128, nq=8, nkv=2, page=16),
+                                   dict(D=128, nq=16, nkv=1, page=8), dict(D=64, nq=3, nkv=3, page=32),
+                                   dict(D=128, nq=40, nkv=2, page=16)])
+def test_attention_tensor_core(shape, window):
+    """Prompt portions and single decoded tokens through the mma kernels (the
+    last shape has a group of 20 > 16: its decoded tokens go through the
+    portion kernel)."""
+    from kipp_b200.kernels import attention_bf16
+    D, nq, nkv, page = shape["D"], shape["nq"], shape["nkv"], shape["page"]
+    assert attention_bf16.supported(D, nq, nkv)
+    for li, layout in enumerate(LAYOUTS):
+        meta, table, q, kp, vp = attention_case(10 + li, D, nq, nkv, page, layout, torch.bfloat16)
+        out = torch.full_like(q, 9.0)
+        st = status()
+        ops().attention(out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D),
+                        window, st, impl="mma")
+        ref = attention_ref(meta, table, q, kp, vp, layout, page, window, 1 / math.sqrt(D))
+        assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2), (shape, li, window)
+
+
+@pytest.mark.parametrize("impl,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
+                                        ("mma", torch.bfloat16)])
+def test_attention_finds_one_far_key(impl, dtype):
+    """Random data would hide a wrong key among hundreds: here each query's
+    score is large for exactly one chosen key (the first key, page edges, the
+    window's edge, the token itself) and the values name their position."""
+    D, nq, nkv, page, window = 64, 4, 2, 16, 100
+    ctx, n = 419, 5                                  # a portion of 5 tokens and, below, one decoded token
+    for layout in ([(ctx, n)], [(ctx + n - 1, 1)]):
+        meta, table, q, kp, vp = attention_case(3, D, nq, nkv, page, layout, dtype)
+        total = layout[0][0] + layout[0][1]
+        kp.zero_(); vp.zero_(); q.zero_()
+        pages = table[0]
+        for pos in range(total):                     # key at pos: e_{pos % D} scaled; value: its position
+            kp[pages[pos // page], :, pos % page, pos % D] = 1.0
+            vp[pages[pos // page], :, pos % page, 0] = float(pos % 256)
+            vp[pages[pos // page], :, pos % page, 1] = float(pos // 256)
+        first = layout[0][0]                          # position of the first query
+        for win, targets in ((None, [0, 15, 16, 255, 256, first - 65, first - 1, "self"]),
+                             (window, ["edge", "edge+1", first - 64, "self"])):
+            for target in targets:
+                q.zero_()
+                want = []
+                for i in range(layout[0][1]):
+                    pos = layout[0][0] + i
+                    j = {"self": pos, "edge": pos - window + 1, "edge+1": pos - window + 2}.get(target, target)
+                    q[i, :, j % D] = 60.0
+                    want.append(j)
+                # keys j + k * D point the same way as key j: the wanted key alone is twice as long
+                for i, j in enumerate(want):
+                    kp[pages[j // page], :, j % page, j % D] = 2.0
+                out = torch.zeros_like(q)
+                ops().attention(out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1.0, win,
+                                status(), impl=impl)
+                got = out.float().cpu()
+                for i, j in enumerate(want):
+                    pos_read = got[i, :, 0] + 256 * got[i, :, 1]
+                    assert torch.allclose(pos_read, torch.full((nq,), float(j)), atol=0.6), (target, i, j, pos_read)
+                for j in want:
+                    kp[pages[j // page], :, j % page, j % D] = 1.0
+        # a key just outside the window must NOT be seen even when it is the strongest
+        q.zero_()
+        pos = layout[0][0] + layout[0][1] - 1
+        j = pos - window                               # one before the window's first key
+        q[-1, :, j % D] = 60.0
+        kp[pages[j // page], :, j % page, j % D] = 4.0
+        out = torch.zeros_like(q)
+        ops().attention(out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1.0, window, status(),
+                        impl=impl)
+        got = out.float().cpu()[-1]
+        assert (got[:, 0] + 256 * got[:, 1] - float(j)).abs().min() > 1.0
+        kp[pages[j // page], :, j % page, j % D] = 1.0
+
+
+# ------------------------------------------------------------------ sampling
+def test_argmax_first_maximum():
+    logits = torch.randn(5, 1000, generator=torch.Generator().manual_seed(1)).to(DEV)
+    logits[1, 7] = logits[1, 900] = 50.0
+    logits[2, :] = 0.25
+    out = ops().argmax_rows(logits).cpu().tolist()
+    assert out == [int(logits[0].argmax()), 7, 0, int(logits[3].argmax()), int(logits[4].argmax())]
+
+
+@pytest.mark.parametrize("vocab", [1000, 151936])
+def test_sample_rows_draws_the_plain_sampler_tokens(vocab):
+    from kipp_b200.kernels import sampling as ks
+    g = torch.Generator().manual_seed(vocab)
+    cases = [dict(temperature=0.0), dict(temperature=0.8), dict(temperature=1.3, top_k=5),
+             dict(temperature=0.7, top_p=0.6), dict(temperature=1.0, min_p=0.2),
+             dict(temperature=0.9, top_k=40, top_p=0.9, min_p=0.02), dict(temperature=0.25),
+             dict(temperature=5.0, top_p=0.95), dict(temperature=1.0, top_k=1), dict(temperature=2.0, top_k=vocab + 5)]
+    rows = len(cases)
+    logits = (torch.randn(rows, vocab, generator=g) * 2.5)
+    logits[:, 17] = logits[:, 200] = logits.max(dim=1).values - 0.25       # ties inside the candidates
+    dev = logits.to(DEV)
+    state = 99
+    for trial in range(12):
+        uni, want = [], []
+        for r, c in enumerate(cases):
+            tok, new_state = P.plain_sample(logits[r].numpy(), rng_state=state + r, **{"temperature": 0.0, **c})
+            _, u = P.uniform_unit(state + r)
+            uni.append(u)
+            want.append(tok)
+        f = lambda key, default, dt: torch.tensor([c.get(key, default) for c in cases], dtype=dt, device=DEV)
+        got = ks.sample_rows(dev, f("temperature", 0.0, torch.float32), f("top_k", 0, torch.int32),
+                             f("top_p", 1.0, torch.float32), f("min_p", 0.0, torch.float32),
+                             torch.tensor(uni, dtype=torch.float64, device=DEV)).cpu().tolist()
+        assert got == want, (trial, got, want)
+        state = state * 7 + 13
+
+
+def test_penalties_and_bias_match_the_reference_sampler():
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "operators.json")) as f:
+        gold = json.load(f)["penalties"]
+    from kipp_b200.sampling import SamplingParams
+    from kipp_b200.sampling.sampler import Sampler
+    logits = torch.tensor([gold["logits"], gold["logits"]], dtype=torch.float32, device=DEV)
+    sp = SamplingParams(repetition_penalty=gold["repetition"], presence_penalty=gold["presence"],
+                        frequency_penalty=gold["frequency"],
+                        logit_bias={int(k): v for k, v in gold["bias"].items()})
+    plain = SamplingParams()
+    states = [1, 1]
+    out = Sampler(DEV).sample(logits, [sp, plain], states, [gold["recent"], []]).cpu().tolist()
+    assert out[0] == gold["token"]                       # what kipp_sample_ex chose with the same settings
+    assert out[1] == int(np.argmax(np.asarray(gold["logits"], dtype=np.float32))) and out[0] != out[1]
+    assert states == [1, 1]                              # greedy leaves the generators alone
