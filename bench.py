@@ -202,7 +202,7 @@ def main() -> int:
             if i == warmup:
                 torch.cuda.synchronize(dev)
                 sampler = ClockSampler() if sample_clocks else None
-                launches0 = kops.launch_count()
+                launches0 = eng.kernel_launches()
                 a.record()
             logits = eng.step([StepEntry(r, [t], [0]) for r, t in zip(rids, next_tokens)])
             next_tokens = kernels.argmax_rows(logits).tolist()
@@ -210,7 +210,7 @@ def main() -> int:
         torch.cuda.synchronize(dev)
         clocks = sampler.stop() if sampler else None
         ms = a.elapsed_time(b) / steps
-        return ms, clocks, kops.launch_count() - launches0
+        return ms, clocks, eng.kernel_launches() - launches0
 
     headline_ctx = args.context - span
     rids = fill(B, headline_ctx, "head")
@@ -238,11 +238,15 @@ def main() -> int:
     # ---- end to end through the Python entry point: host token ids in and out --------
     from kipp_b200.engine.scheduler import Request
     sched = llm.new_scheduler()
-    e2e_ctx = min(headline_ctx, args.context - (K + 2))
+    # requests finish their prompts one after the other; each keeps decoding until
+    # all of them have decoded together for K steps
+    prefill_steps = B * (-(-(args.context - span) // PREFILL_TOKENS))
+    e2e_new = K + 4 + prefill_steps
+    e2e_ctx = args.context - e2e_new - 1
     for i in range(B):
-        sched.add(Request(id=("e2e", i), prompt=prompt(e2e_ctx), max_new_tokens=K + 1))
+        sched.add(Request(id=("e2e", i), prompt=prompt(e2e_ctx), max_new_tokens=e2e_new))
     llm.run(sched, record_steps=True)
-    dec = [s for s in llm.step_log if s["decode_only"]][1:]            # first decode step = warm-up
+    dec = [s for s in llm.step_log if s["decode_only"] and s["sampled"] == B][2:2 + K]
     e2e_s = sum(s["seconds"] for s in dec)
     e2e = {"value": round(sum(s["sampled"] for s in dec) / e2e_s, 1) if dec else None,
            "unit": "tokens/s",

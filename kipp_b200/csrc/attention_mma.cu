@@ -7,8 +7,9 @@
 // token may see, softmax with the maximum subtracted, weighted sum of values,
 // kv head = q head / group).  The split over keys with a final merge follows
 // the idea of the reference's Metal kernels (metal/kipp_kernels.metal:517-626,
-// 741-779): the split length depends only on the query's own context length,
-// so a token is reduced the same way in any batch.
+// 741-779).  The split length is a parameter of the step, read from device
+// memory so that a captured graph follows it; partial results are merged in
+// split order.
 //
 // Both kernels: keys and values are gathered page by page with cp.async into
 // shared memory (16-byte chunks, XOR-swizzled rows), scores and the weighted
@@ -66,23 +67,30 @@ template <int D> __device__ __forceinline__ uint32_t tile_offset(int row, int ch
 
 // Gathers TILE_KEYS rows of keys and of values, positions [j0, j0 + TILE_KEYS),
 // for kv head g into swizzled tiles.  Rows outside [lo, hi] are zero-filled
-// (their scores are masked; zero values keep 0 * v finite).
+// (their scores are masked; zero values keep 0 * v finite).  A thread copies
+// the same 16-byte chunk of every (THREADS / chunks-per-row)-th row, so it
+// looks a page up once per row.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_tile, uint32_t v_tile, const bf16* __restrict__ k_pages,
                                              const bf16* __restrict__ v_pages, const int* __restrict__ table,
                                              int table_width, int page_size, int n_kv, int g, int j0, int lo,
                                              int hi) {
     constexpr int CHUNKS = D / 8;                        // 16-byte chunks per row
-    for (int i = threadIdx.x; i < TILE_KEYS * CHUNKS; i += THREADS) {
-        const int row = i / CHUNKS, chunk = i % CHUNKS;
+    constexpr int ROWS_PER_PASS = THREADS / CHUNKS;
+    const int chunk = threadIdx.x % CHUNKS, row0 = threadIdx.x / CHUNKS;
+    const bool pow2 = (page_size & (page_size - 1)) == 0;
+    const int shift = 31 - __clz(page_size);
+#pragma unroll
+    for (int row = row0; row < TILE_KEYS; row += ROWS_PER_PASS) {
         const int j = j0 + row;
-        const bool valid = j >= lo && j <= hi;
         size_t src = 0;
         int bytes = 0;
-        if (valid) {
-            const int page = j / page_size < table_width ? table[j / page_size] : -1;
+        if (j >= lo && j <= hi) {
+            const int slot = pow2 ? (j >> shift) : (j / page_size);
+            const int within = pow2 ? (j & (page_size - 1)) : (j - slot * page_size);
+            const int page = slot < table_width ? __ldg(table + slot) : -1;
             if (page >= 0) {
-                src = (((size_t)page * n_kv + g) * page_size + (j % page_size)) * D + chunk * 8;
+                src = (((size_t)page * n_kv + g) * page_size + within) * D + chunk * 8;
                 bytes = 16;
             }
         }
@@ -268,13 +276,15 @@ struct DecodeParams {
     const int* rows;            // [n] entries that are single decoded tokens
     float* part_o;              // [n][n_q][max_splits][D]
     float* part_ml;             // [n][n_q][max_splits][2]  (max in log2 units, sum)
-    int table_width, page_size, n_q, n_kv, window, max_splits, split_keys_min;
+    const int* split_keys;      // device: keys per split of this step (a multiple of 64)
+    int table_width, page_size, n_q, n_kv, window, max_splits;
     float scale_log2;
 };
 
-// Keys per split for a context of kv_len keys: a function of kv_len alone.
+// Keys per split for a context of kv_len keys: the step's split length, or
+// longer when max_splits of them would not cover the context.
 __host__ __device__ __forceinline__ int decode_split_keys(int kv_len, int max_splits, int split_keys_min) {
-    int keys = split_keys_min;
+    int keys = split_keys_min < TILE_KEYS ? TILE_KEYS : split_keys_min / TILE_KEYS * TILE_KEYS;
     if ((long long)keys * max_splits < kv_len) {
         keys = (kv_len + max_splits - 1) / max_splits;
         keys = (keys + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS;
@@ -297,7 +307,7 @@ attn_decode_kernel(const DecodeParams p) {
     const int pos = p.context_len[entry];                  // position of the decoded token
     const int kv_len = pos + 1;
     const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int split_keys = decode_split_keys(kv_len, p.max_splits, p.split_keys_min);
+    const int split_keys = decode_split_keys(kv_len, p.max_splits, __ldg(p.split_keys));
     const int n_splits = (kv_len + split_keys - 1) / split_keys;
     if (split >= n_splits) return;
     const int lo = max(first_key, split * split_keys), hi = min(pos, (split + 1) * split_keys - 1);
@@ -439,11 +449,12 @@ attn_decode_kernel(const DecodeParams p) {
 __global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, const int* __restrict__ rows,
                                          const int* __restrict__ q_start, const int* __restrict__ context_len,
-                                         int n_q, int head_dim, int max_splits, int split_keys_min) {
+                                         int n_q, int head_dim, int max_splits,
+                                         const int* __restrict__ split_keys_ptr) {
     const int n = blockIdx.y, h = blockIdx.x;
     const int entry = rows[n];
     const int kv_len = context_len[entry] + 1;
-    const int split_keys = decode_split_keys(kv_len, max_splits, split_keys_min);
+    const int split_keys = decode_split_keys(kv_len, max_splits, __ldg(split_keys_ptr));
     const int n_splits = (kv_len + split_keys - 1) / split_keys;
     const float* ml = part_ml + ((size_t)n * n_q + h) * max_splits * 2;
     const float* po = part_o + ((size_t)n * n_q + h) * max_splits * head_dim;
@@ -529,11 +540,11 @@ extern "C" long long kipp_attn_decode_scratch_bytes(int n, int n_q, int head_dim
 extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
                                     const int* q_start, const int* context_len, const int* block_table,
                                     int table_width, int page_size, const int* rows, int n, int n_q, int n_kv,
-                                    int head_dim, float scale, int window, int max_splits, int split_keys_min,
-                                    float* scratch, void* stream) {
+                                    int head_dim, float scale, int window, int max_splits,
+                                    const int* split_keys, float* scratch, void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
-        max_splits > 65535 || split_keys_min <= 0 || split_keys_min % TILE_KEYS || scratch == nullptr)
+        max_splits > 65535 || split_keys == nullptr || scratch == nullptr)
         return KIPP_ERR_ARG;
     DecodeParams p;
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
@@ -541,12 +552,12 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     p.part_o = scratch;
     p.part_ml = scratch + (size_t)n * n_q * max_splits * head_dim;
     p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
-    p.max_splits = max_splits; p.split_keys_min = split_keys_min;
+    p.max_splits = max_splits; p.split_keys = split_keys;
     p.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
     if (rc) return rc;
     attn_decode_merge_kernel<<<dim3(n_q, n), head_dim >= 128 ? 128 : 64, 0, s>>>(
-        (bf16*)out, p.part_o, p.part_ml, rows, q_start, context_len, n_q, head_dim, max_splits, split_keys_min);
+        (bf16*)out, p.part_o, p.part_ml, rows, q_start, context_len, n_q, head_dim, max_splits, split_keys);
     return kipp_launch_status();
 }

@@ -273,13 +273,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = 0.f;
                 }
+                if (p.epilogue == EPI_ADD) {
+                    // all loads of the residual first, then the stores: the loads overlap
+                    float* cbase = reinterpret_cast<float*>(p.C) + f;
+                    float old[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int t = t0 + c + j;
-                    const float partner = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                    if (t < p.tokens) {
-                        if (p.out_dtype == KIPP_DT_F32) store_value<float>(p, t, f, v[j], partner, lane);
-                        else store_value<bf16>(p, t, f, v[j], partner, lane);
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c + j;
+                        old[j] = (t < p.tokens && f < p.features) ? cbase[(size_t)t * p.ldc] : 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c + j;
+                        if (t < p.tokens && f < p.features) cbase[(size_t)t * p.ldc] = old[j] + v[j];
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c + j;
+                        const float partner = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                        if (t < p.tokens) {
+                            if (p.out_dtype == KIPP_DT_F32) store_value<float>(p, t, f, v[j], partner, lane);
+                            else store_value<bf16>(p, t, f, v[j], partner, lane);
+                        }
                     }
                 }
             }
@@ -424,20 +440,24 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
     return e == cudaSuccess ? kipp_launch_status() : (int)e;
 }
 
-int pick_tile_t(int tokens) {
+// Token tile.  Measured on B200 at 2,048 tokens: 64-token tiles (two CTAs per SM,
+// one's epilogue under the other's MMAs) match or beat 256-token tiles except
+// for few features with a long K, where the wider tile re-reads less.
+int pick_tile_t(int tokens, int features) {
     if (tokens <= 16) return 16;
     if (tokens <= 32) return 32;
-    if (tokens <= 64) return 64;
-    if (tokens <= 128) return 128;
-    return 256;
+    if (tokens >= 1536 && features <= 8192) return 256;
+    return 64;
 }
 }  // namespace
 
 // The token tile and the number of K splits (= cluster size, at most 8) the
 // kernel uses for a shape; want_splits == 0 lets it choose.
-extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_splits, int* tile_t_out,
-                                 int* splits_out) {
-    const int tile_t = pick_tile_t(tokens);
+extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_splits, int want_tile,
+                                 int* tile_t_out, int* splits_out) {
+    int tile_t = pick_tile_t(tokens, features);
+    if (want_tile == 16 || want_tile == 32 || want_tile == 64 || want_tile == 128 || want_tile == 256)
+        tile_t = want_tile;
     const int f_tiles = (features + TILE_F - 1) / TILE_F;
     const int t_tiles = (tokens + tile_t - 1) / tile_t;
     const int kb = (K + TILE_K - 1) / TILE_K;
@@ -467,7 +487,7 @@ extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_split
 // or bf16 (ldc).  Pointers 16-byte aligned, ldx and ldw multiples of 8.
 extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W, int tokens, int features,
                             int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
-                            int* status, void* stream) {
+                            int want_tile, int* status, void* stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (K <= 0) return KIPP_ERR_ARG;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -3;
@@ -475,7 +495,7 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
     if (epilogue == EPI_SWIGLU && (features & 1)) return KIPP_ERR_ARG;
     if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
     int tile_t, planned;
-    kipp_gemm_tc_plan(tokens, features, K, splits, &tile_t, &planned);
+    kipp_gemm_tc_plan(tokens, features, K, splits, want_tile, &tile_t, &planned);
     splits = planned;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, W, features, K, ldw, TILE_F);

@@ -15,6 +15,20 @@ import torch
 
 
 ATTENTION_TILE = 64       # tokens per work item of the prefill attention kernel
+DECODE_TARGET_CTAS = 592  # decode attention aims at about two waves of CTAs on 148 SMs
+DECODE_MAX_SPLITS = 32
+DECODE_MIN_SPLIT = 256
+
+
+def decode_split_length(kv_lens: list, kv_heads_hint: int = 8) -> int:
+    """Keys per split for the decoded tokens of a step: few, long splits when
+    many (token, kv head) pairs already fill the GPU, many short ones when few."""
+    if not kv_lens:
+        return DECODE_MIN_SPLIT
+    pairs = len(kv_lens) * kv_heads_hint
+    splits = min(DECODE_MAX_SPLITS, max(1, DECODE_TARGET_CTAS // pairs))
+    keys = -(-max(kv_lens) // splits)
+    return max(DECODE_MIN_SPLIT, -(-keys // 64) * 64)
 
 
 @dataclasses.dataclass
@@ -45,6 +59,7 @@ class StepMeta:
     n_prefill_items: int = 0
     all_work: Optional[torch.Tensor] = None       # the same over every entry (for kernels without a decode path)
     n_all_items: int = 0
+    decode_split_keys: Optional[torch.Tensor] = None   # int32 [4]: keys per split of decoded tokens
     # host copies for kernel choice
     q_lens: list = dataclasses.field(default_factory=list)
     kv_lens: list = dataclasses.field(default_factory=list)
@@ -86,8 +101,20 @@ class Staging:
         ev.record()
 
 
+class StaticStep:
+    """Fixed host and device buffers for steps of one shape (a CUDA graph reads
+    the device buffer at the same addresses on every replay)."""
+
+    def __init__(self, n_ints: int, device: torch.device):
+        self.n_ints = n_ints
+        self.host = torch.empty(n_ints, dtype=torch.int32, pin_memory=True)
+        self.device = torch.zeros(n_ints, dtype=torch.int32, device=device)
+        self.meta: Optional[StepMeta] = None
+
+
 def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[np.ndarray],
-              device: torch.device, staging: Optional[Staging] = None) -> StepMeta:
+              device: torch.device, staging: Optional[Staging] = None,
+              static: Optional[StaticStep] = None) -> StepMeta:
     """Build the device metadata from host lists with one host-to-device copy.
 
     ``starts[i]`` is the number of tokens entry i has cached; ``tables[g]`` is
@@ -113,7 +140,9 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
     decode_rows = [i for i, q in enumerate(q_lens) if q == 1]
     prefill_work = [(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(0, q, ATTENTION_TILE)]
     all_work = [(i, t) for i, q in enumerate(q_lens) for t in range(0, q, ATTENTION_TILE)]
-    fixed = [token_ids, positions, entry_of_token, q_start,
+    split = np.zeros(4, dtype=np.int32)
+    split[0] = decode_split_length([starts[i] + 1 for i in decode_rows])
+    fixed = [split, token_ids, positions, entry_of_token, q_start,
              np.asarray(starts, dtype=np.int32), np.asarray(slots, dtype=np.int32),
              np.asarray(rows, dtype=np.int32), np.asarray(decode_rows, dtype=np.int32),
              np.asarray(prefill_work, dtype=np.int32).reshape(-1),
@@ -125,28 +154,52 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
         offsets.append(total)
         total += (p.size + 3) // 4 * 4
     total = max(total, 4)
-    if staging is None:
-        host, ring = torch.empty(total, dtype=torch.int32, pin_memory=True), None
+    if static is not None:
+        if static.n_ints != total:
+            raise ValueError("a static step must keep its shape")
+        hv = static.host.numpy()
+        for p, o in zip(parts, offsets):
+            hv[o:o + p.size] = p
+        static.device.copy_(static.host, non_blocking=True)
+        if static.meta is not None:            # same layout: the views stay valid
+            static.meta.q_lens = q_lens
+            static.meta.kv_lens = [s + q for s, q in zip(starts, q_lens)]
+            return static.meta
+        dev = static.device
     else:
-        host, ring = staging.get(total)
-    hv = host.numpy()
-    for p, o in zip(parts, offsets):
-        hv[o:o + p.size] = p
-    dev = host[:total].to(device, non_blocking=True)
-    if ring is not None:
-        staging.sent(ring)
+        if staging is None:
+            host, ring = torch.empty(total, dtype=torch.int32, pin_memory=True), None
+        else:
+            host, ring = staging.get(total)
+        hv = host.numpy()
+        for p, o in zip(parts, offsets):
+            hv[o:o + p.size] = p
+        dev = host[:total].to(device, non_blocking=True)
+        if ring is not None:
+            staging.sent(ring)
 
     def sec(i):
         return dev[offsets[i]:offsets[i] + parts[i].size]
 
     block_tables = [sec(len(fixed) + g).view(tables[g].shape) for g in range(len(tables))]
-    return StepMeta(tokens=T, entries=n, token_ids=sec(0), positions=sec(1), entry_of_token=sec(2),
-                    q_start=sec(3), context_len=sec(4), slots=sec(5),
-                    logit_rows=sec(6) if rows else None, n_logit_rows=len(rows),
+    meta = StepMeta(tokens=T, entries=n, decode_split_keys=sec(0), token_ids=sec(1), positions=sec(2),
+                    entry_of_token=sec(3), q_start=sec(4), context_len=sec(5), slots=sec(6),
+                    logit_rows=sec(7) if rows else None, n_logit_rows=len(rows),
                     block_tables=block_tables,
-                    decode_rows=sec(7) if decode_rows else None, n_decode=len(decode_rows),
-                    prefill_work=sec(8).view(-1, 2) if prefill_work else None,
+                    decode_rows=sec(8) if decode_rows else None, n_decode=len(decode_rows),
+                    prefill_work=sec(9).view(-1, 2) if prefill_work else None,
                     n_prefill_items=len(prefill_work),
-                    all_work=sec(9).view(-1, 2), n_all_items=len(all_work), q_lens=q_lens,
+                    all_work=sec(10).view(-1, 2), n_all_items=len(all_work), q_lens=q_lens,
                     kv_lens=[s + q for s, q in zip(starts, q_lens)],
                     extra={"h2d_bytes": total * 4})
+    if static is not None:
+        static.meta = meta
+    return meta
+
+
+def step_ints(n_entries: int, n_tokens: int, n_rows: int, n_decode: int, n_prefill_items: int,
+              n_all_items: int, table_ints: list[int]) -> int:
+    """Size in int32 of the packed buffer of a step of this shape."""
+    sizes = [4, n_tokens, n_tokens, n_tokens, n_entries + 1, n_entries, n_entries, n_rows, n_decode,
+             2 * n_prefill_items, 2 * n_all_items] + list(table_ints)
+    return max(sum((s + 3) // 4 * 4 for s in sizes), 4)

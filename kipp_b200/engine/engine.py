@@ -60,7 +60,7 @@ class Engine:
     def __init__(self, spec: ModelSpec, tensors: dict, *, dtype="bfloat16",
                  device: str | torch.device = "cuda:0", page_size: int = 16,
                  cache_tokens: int = 8192, max_requests: int = 64,
-                 max_batch_tokens: int = 8192):
+                 max_batch_tokens: int = 8192, cuda_graphs: bool = True):
         self.spec = spec
         self.runtime = Runtime(device, dtype)
         self.page_size = page_size
@@ -95,6 +95,12 @@ class Engine:
                                             device=rt.device)
                            for cid, ss in state_specs.items()}
         self._staging = Staging()
+        # decode steps replay a captured graph per batch size (bfloat16 path)
+        self.cuda_graphs = cuda_graphs and self.runtime.dtype == torch.bfloat16
+        self._graphs: dict = {}
+        self.last_forward_launches = 0
+        self.graph_replays = 0
+        self.graph_kernel_launches = 0
         self.steps_run = 0
         self.last_h2d_bytes = 0
 
@@ -183,9 +189,12 @@ class Engine:
         tables = [self.cache.block_table_rows(rids, gi) for gi in range(len(self.cache.groups))]
         rt = self.runtime
         with torch.cuda.device(rt.device):
-            meta = pack_step(entries, starts, slots, tables, rt.device, self._staging)
-            self.last_h2d_bytes = meta.extra["h2d_bytes"]
-            logits = self._forward(StepContext(self, meta))
+            if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+                logits = self._graph_step(entries, starts, slots, rids)
+            else:
+                meta = pack_step(entries, starts, slots, tables, rt.device, self._staging)
+                self.last_h2d_bytes = meta.extra["h2d_bytes"]
+                logits = self._forward(StepContext(self, meta))
         for e, s in zip(entries, starts):
             self.cache.advance(e.request, s + len(e.tokens))
         self.steps_run += 1
@@ -193,7 +202,39 @@ class Engine:
             rt.check_status()
         return logits
 
+    def _graph_step(self, entries, starts, slots, rids) -> torch.Tensor:
+        from .graphs import DecodeGraph
+        limit = self.spec.max_positions
+        widths = []
+        for g in self.cache.groups:
+            pages = g.pool.n_pages if limit is None else min(g.pool.n_pages, -(-limit // g.page_size))
+            widths.append(max(pages, 1))
+        tables = [self.cache.block_table_rows(rids, gi, width=w) for gi, w in enumerate(widths)]
+        graph = self._graphs.get(len(entries))
+        if graph is None:
+            if len(self._graphs) >= 16:
+                self._graphs.pop(next(iter(self._graphs)))
+            graph = self._graphs[len(entries)] = DecodeGraph(self, len(entries), widths)
+        logits = graph.run(entries, starts, slots, tables)
+        self.last_h2d_bytes = graph.static.n_ints * 4
+        self.graph_replays += 1
+        self.graph_kernel_launches += graph.launches
+        return logits
+
+    def kernel_launches(self) -> int:
+        """Kernels of this package run so far: launched directly or replayed in graphs."""
+        from ..kernels import ops as _kops
+        return _kops.launch_count() + self.graph_kernel_launches
+
     def _forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        from ..kernels import ops as _kops
+        launches0 = _kops.launch_count()
+        try:
+            return self._forward_impl(ctx)
+        finally:
+            self.last_forward_launches = _kops.launch_count() - launches0
+
+    def _forward_impl(self, ctx: StepContext) -> Optional[torch.Tensor]:
         spec = self.spec
         x = spec.embedding.forward(ctx)
         for run in spec.order:

@@ -1,0 +1,52 @@
+"""CUDA graphs for decode steps.
+
+A step in which every entry brings one token has the same kernels, grids and
+buffers whenever the number of entries is the same: only the contents of the
+metadata buffer differ.  Such a step is captured once per batch size and
+replayed; the host then pays for one copy of the metadata and one graph launch
+instead of some three hundred kernel launches.  (The reference launches 18
+kernels per layer and token from the host, src/cuda/kipp_cuda.cu:358-462.)
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import attention_bf16
+from .batch import StaticStep, StepMeta, pack_step, step_ints
+
+
+class DecodeGraph:
+    def __init__(self, engine, batch: int, table_widths: list[int]):
+        self.engine = engine
+        self.batch = batch
+        self.table_widths = table_widths
+        n = batch
+        ints = step_ints(n, n, n, n, 0, n, [n * w for w in table_widths])
+        self.static = StaticStep(ints, engine.runtime.device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.generation = None
+
+    def _generation(self):
+        return (self.engine.runtime.workspace.generation, attention_bf16.scratch_generation())
+
+    def run(self, entries, starts, slots, tables) -> torch.Tensor:
+        from .engine import StepContext
+        engine = self.engine
+        meta = pack_step(entries, starts, slots, tables, engine.runtime.device, static=self.static)
+        if self.graph is not None and self.generation != self._generation():
+            self.graph = None                       # a buffer moved since the capture
+        if self.graph is None:
+            ctx = StepContext(engine, meta)
+            engine._forward(ctx)                    # eager once: buffers, attributes, tensor maps
+            torch.cuda.synchronize(engine.runtime.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.logits = engine._forward(ctx)
+            self.graph = graph
+            self.generation = self._generation()
+            self.launches = engine.last_forward_launches
+        self.graph.replay()
+        return self.logits

@@ -28,6 +28,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._flat: dict[tuple[str, torch.dtype], torch.Tensor] = {}
+        self.generation = 0          # bumped whenever a buffer moves (captured graphs go stale)
 
     def buffer(self, key: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -35,8 +36,11 @@ class Workspace:
             n *= int(d)
         flat = self._flat.get((key, dtype))
         if flat is None or flat.numel() < n:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"workspace buffer {key!r} would be allocated inside a graph capture")
             flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._flat[(key, dtype)] = flat
+            self.generation += 1
         return flat[:n].view(shape)
 
     def bytes(self) -> int:

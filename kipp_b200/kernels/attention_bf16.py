@@ -8,10 +8,15 @@ import torch
 
 from .ops import KernelError, _check, _fn, _ptr, _stream, c_float, c_int, c_void_p
 
-MAX_SPLITS = 32           # key splits of one decoded token
-SPLIT_KEYS_MIN = 256      # keys per split until MAX_SPLITS of them do not cover the context
+MAX_SPLITS = 32           # key splits of one decoded token (engine.batch.DECODE_MAX_SPLITS)
 
 _scratch: dict = {}
+_generation = 0
+
+
+def scratch_generation() -> int:
+    """Changes whenever the decode scratch moved (captured graphs go stale)."""
+    return _generation
 
 
 def supported(head_dim: int, n_q: int, n_kv: int) -> bool:
@@ -37,8 +42,10 @@ def decode_scratch(device: torch.device, n: int, n_q: int, head_dim: int) -> tor
     if cur is None or cur.numel() < floats:
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("attention scratch must exist before a CUDA graph is captured")
+        global _generation
         cur = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
         _scratch[key] = cur
+        _generation += 1
     return cur
 
 
@@ -62,9 +69,9 @@ def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv,
         scratch = decode_scratch(q.device, meta.n_decode, n_q, head_dim)
         f = _fn("attention_mma", "kipp_attn_decode_mma",
                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p])
+                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
         _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(meta.q_start),
                  _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
                  _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale),
-                 int(window or 0), MAX_SPLITS, SPLIT_KEYS_MIN, _ptr(scratch), _stream()),
+                 int(window or 0), MAX_SPLITS, _ptr(meta.decode_split_keys), _ptr(scratch), _stream()),
                "attn_decode_mma")

@@ -9,12 +9,13 @@ from .ops import EPILOGUES, KernelError, _check, _fn, _ptr, _stream, c_int, c_vo
 
 c_ll = ctypes.c_longlong
 
-def plan(tokens: int, features: int, K: int, splits: int = 0):
+def plan(tokens: int, features: int, K: int, splits: int = 0, tile: int = 0):
     """(token tile, K splits) the tensor-core kernel uses for a shape."""
     f = _fn("gemm_tc", "kipp_gemm_tc_plan",
-            [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)])
-    tile, sp = c_int(), c_int()
-    f(tokens, features, K, splits, ctypes.byref(tile), ctypes.byref(sp))
+            [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)])
+    tile_out, sp = c_int(), c_int()
+    f(tokens, features, K, splits, tile, ctypes.byref(tile_out), ctypes.byref(sp))
+    tile = tile_out
     return tile.value, sp.value
 
 
@@ -30,7 +31,7 @@ def choose(M, N, K, a, w, out, epilogue) -> str:
     return "tc" if tc_ok(a, w) else "simt"
 
 
-def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None) -> None:
+def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 0) -> None:
     if impl != "tc":
         raise KernelError(f"unknown gemm implementation {impl!r}")
     if not tc_ok(a, w):
@@ -40,9 +41,9 @@ def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None) -> None:
         status = _status(a.device)
     f = _fn("gemm_tc", "kipp_gemm_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int,
-             c_void_p, c_void_p])
+             c_int, c_void_p, c_void_p])
     _check(f(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
-             out.stride(0), EPILOGUES[epilogue], splits, _ptr(status), _stream()), "gemm_tc")
+             out.stride(0), EPILOGUES[epilogue], splits, tile, _ptr(status), _stream()), "gemm_tc")
 
 
 _status_words: dict = {}

@@ -10,7 +10,7 @@ from tiny import nmse
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 97], "B": [1, 64, 100, 200], "C": [9, 70, 130, 41]}
+LENGTHS = {"A": [5, 17, 33, 97], "B": [1, 64, 100, 200], "C": [9, 70, 130, 41], "D": [3, 129, 260, 66]}
 PORTIONS = [7, 2, 19, 2, 48, 3, 2, 31, 64, 2, 5]
 
 
@@ -74,10 +74,10 @@ def build_trace(name: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_every_way_of_cutting_matches_the_plain_model(name, dtype):
     seqs, tr = build_trace(name)
-    page = {"A": 16, "B": 8, "C": 16}[name]
+    page = {"A": 16, "B": 8, "C": 16, "D": 32}[name]
     got = tr.collect(replay(name, dtype, tr.steps, max_tokens=tr.peak_tokens, page_size=page))
     total_pages_needed = sum(-(-len(t) // page) for t in seqs.values()) * 5
     assert total_pages_needed > 2 * tr.peak_tokens // page           # pages had to be used again

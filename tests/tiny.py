@@ -37,7 +37,18 @@ TINY_C = dict(
     torch_dtype="float32")
 TINY_C_INIT = dict(seed=7, sigma=0.04, norm_jitter=0.15)
 
-CONFIGS = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT)}
+# D has a head size the tensor-core attention kernels take (64), a group of 3
+# and one windowed layer.
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=777, hidden_size=192,
+    intermediate_size=320, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
+    head_dim=64, max_position_embeddings=1024, rope_theta=200000.0, rms_norm_eps=2e-6,
+    tie_word_embeddings=False, hidden_act="silu", attention_bias=False, initializer_range=0.05,
+    sliding_window=50, layer_types=["sliding_attention", "full_attention"], torch_dtype="float32")
+TINY_D_INIT = dict(seed=11, sigma=0.05, norm_jitter=0.1)
+
+CONFIGS = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT),
+           "D": (TINY_D, TINY_D_INIT)}
 
 
 def make_model_folder(folder: str, name: str, dtype=torch.float32) -> str:
