@@ -25,8 +25,11 @@ class ConfigError(ValueError):
 _MISSING = dataclasses.MISSING
 
 
-def _coerce(name: str, value: Any, annotation: str) -> Any:
-    """Check ``value`` against the (string) annotation of a field."""
+def _coerce(name: str, value: Any, annotation: Any) -> Any:
+    """Check ``value`` against the annotation of a field (a string under
+    ``from __future__ import annotations``, else the type itself)."""
+    if not isinstance(annotation, str):
+        annotation = getattr(annotation, "__name__", None) or str(annotation).replace("typing.", "")
     base = annotation.replace("Optional[", "").replace("]", "").strip()
     optional = annotation.startswith("Optional[") or "| None" in annotation
     base = base.replace("| None", "").strip()
@@ -87,7 +90,7 @@ class ModelConfig:
             keys = (field.name,) + tuple(cls.json_aliases.get(field.name, ()))
             present = [k for k in keys if k in data]
             if present:
-                values[field.name] = _coerce(present[0], data[present[0]], str(field.type))
+                values[field.name] = _coerce(present[0], data[present[0]], field.type)
             elif field.default is _MISSING and field.default_factory is _MISSING:
                 raise ConfigError(f"config.json lacks required key {field.name!r}")
         config = cls(**values)

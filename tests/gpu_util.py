@@ -122,3 +122,63 @@ def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = 
     e = nmse(got, want)
     assert e <= BOUND[dtype], f"{what}: NMSE {e:.3e} above {BOUND[dtype]:.0e}"
     assert torch.isfinite(got).all(), what
+
+
+# ---------------------------------------------------------------------------
+class PartHarness:
+    """Runs single parts the way the engine does: a runtime, a cache manager
+    and the step context a part sees, without a model around them."""
+
+    def __init__(self, dtype: str, cache_specs: dict, page_size: int = 8, n_pages: int = 64,
+                 state_specs: dict | None = None, max_requests: int = 4):
+        from kipp_b200.cache import CacheManager
+        from kipp_b200.engine.runtime import Runtime
+        self.runtime = Runtime("cuda:0", dtype)
+        self.cache = CacheManager(cache_specs, page_size, n_pages, max_requests)
+        rt = self.runtime
+        for g in self.cache.groups:
+            shape = (len(g.cache_ids), n_pages, g.spec.kv_heads, page_size, g.spec.head_dim)
+            g.k = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+            g.v = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+        self.states = {cid: torch.zeros((max_requests,) + tuple(s.shape), dtype=s.dtype, device=rt.device)
+                       for cid, s in (state_specs or {}).items()}
+
+    def context(self, layout: list):
+        """layout: [(request id, number of new tokens)].  Reserves pages; call
+        ``commit`` after the parts ran."""
+        from kipp_b200.engine.batch import StepEntry, pack_step
+        from kipp_b200.engine.engine import CacheView
+        for rid, _ in layout:
+            if rid not in self.cache:
+                self.cache.admit(rid)
+        starts = [self.cache.length(rid) for rid, _ in layout]
+        self.cache.reserve([(rid, s + n) for (rid, n), s in zip(layout, starts)])
+        rids = [rid for rid, _ in layout]
+        tables = [self.cache.block_table_rows(rids, gi) for gi in range(len(self.cache.groups))]
+        entries = [StepEntry(rid, [0] * n, []) for rid, n in layout]
+        meta = pack_step(entries, starts, [self.cache.slot(r) for r in rids], tables, self.runtime.device)
+        harness, rt = self, self.runtime
+        self._pending = [(rid, s + n) for (rid, n), s in zip(layout, starts)]
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        ctx.meta, ctx.device, ctx.dtype, ctx.ops = meta, rt.device, rt.dtype, rt.ops
+        ctx.workspace, ctx.status = rt.workspace, rt.status
+
+        def cache_view(run):
+            gi, j = harness.cache.group_of_cache[run.cache]
+            g = harness.cache.groups[gi]
+            return CacheView(g.k[j], g.v[j], meta.block_tables[gi], g.page_size)
+        ctx.cache_view = cache_view
+        ctx.state_view = lambda run: harness.states[run.cache]
+        return ctx
+
+    def commit(self) -> None:
+        for rid, n in self._pending:
+            self.cache.advance(rid, n)
+        self.runtime.check_status()
+
+
+def part_tol(dtype: str) -> dict:
+    return dict(rtol=1e-4, atol=1e-5) if dtype == "float32" else dict(rtol=3e-2, atol=3e-2)

@@ -1,0 +1,207 @@
+"""The engine in process: long decoding, the first tokens of a sequence,
+generation through the entry point (greedy and sampled), what happens when
+pages run out, graphs against plain launches."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+from gpu_util import (BOUND, assert_close, model_folder, plain_logits, plain_weights, random_tokens)
+from tiny import nmse
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def engine(name, dtype, **kw):
+    from kipp_b200.engine import Engine
+    opts = dict(dtype=dtype, page_size=16, cache_tokens=1024, max_requests=8, max_batch_tokens=512)
+    opts.update(kw)
+    return Engine.from_folder(model_folder(name), **opts)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_long_decoding(name, dtype):
+    """A short prompt and then 300 tokens one by one (given, not sampled), across
+    many pages and, in D, far past the window."""
+    from kipp_b200.engine import StepEntry
+    toks = random_tokens(name, 330, seed=3)
+    want = plain_logits(name, dtype, toks)
+    eng = engine(name, dtype, page_size=8)
+    rows = [eng.step([StepEntry("r", toks[:30], [29])], check=True).cpu().clone()]
+    for t in toks[30:]:
+        rows.append(eng.step([StepEntry("r", [t], [0])]).cpu().clone())
+    eng.runtime.check_status()
+    got = torch.cat(rows)
+    assert_close(got, want[29:], dtype, f"{name} long decode")
+    worst = max(nmse(got[i], want[29 + i]) for i in range(0, 301, 25))
+    assert worst <= BOUND[dtype]
+    if dtype == "bfloat16":
+        assert eng.graph_replays == 300              # the decode steps ran as captured graphs
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_of_a_sequence(dtype):
+    """Positions 0, 1, 2: one key, no history, each as a step of its own and
+    together."""
+    from kipp_b200.engine import StepEntry
+    toks = random_tokens("A", 3, seed=9)
+    want = plain_logits("A", dtype, toks)
+    eng = engine("A", dtype)
+    one = [eng.step([StepEntry("x", [t], [0])]).cpu().clone() for t in toks]
+    assert_close(torch.cat(one), want, dtype, "one by one")
+    both = eng.step([StepEntry("y", toks, [0, 1, 2])]).cpu()
+    assert_close(both, want, dtype, "together")
+    single = eng.step([StepEntry("z", toks[:1], [0])]).cpu()
+    assert_close(single, want[:1], dtype, "a prompt of one token")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_steps_equal_plain_launches(dtype):
+    from kipp_b200.engine import StepEntry
+    seqs = [random_tokens("D", n, seed=n) for n in (70, 9, 140)]
+    outs = []
+    for graphs in (True, False):
+        eng = engine("D", dtype, cuda_graphs=graphs)
+        eng.step([StepEntry(i, s[:-6], []) for i, s in enumerate(seqs)])
+        rows = []
+        for j in range(6, 0, -1):
+            rows.append(eng.step([StepEntry(i, [s[-j]], [0]) for i, s in enumerate(seqs)]).cpu().clone())
+        outs.append(torch.stack(rows))
+    assert torch.equal(outs[0], outs[1])             # same kernels, same order: bitwise
+
+
+def test_out_of_pages_leaves_every_request_unchanged():
+    from kipp_b200.cache import OutOfPages
+    from kipp_b200.engine import StepEntry
+    eng = engine("A", "float32", cache_tokens=64, page_size=16)       # 4 pages
+    a = random_tokens("A", 40, seed=1)
+    b = random_tokens("A", 30, seed=2)
+    la = eng.step([StepEntry("a", a[:20], [19])]).cpu().clone()
+    eng.step([StepEntry("b", b[:17], [])])
+    assert eng.cache.free_pages() == [0]
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("a", a[20:33], [0]), StepEntry("c", [1, 2, 3], [2])])
+    assert eng.length("a") == 20 and eng.length("b") == 17 and not eng.is_live("c")
+    eng.cache.check()
+    eng.finish("b")                                                    # pages come back and are used again
+    lb = eng.step([StepEntry("a", a[20:40], [19])]).cpu()
+    want = plain_logits("A", "float32", a)
+    assert_close(la, want[19:20], "float32")
+    assert_close(lb, want[39:40], "float32")
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+    with pytest.raises(ValueError, match="outside"):
+        eng.step([StepEntry("q", [256], [0])])
+    with pytest.raises(ValueError, match="max positions"):
+        eng.step([StepEntry("q", [1] * 129, [])])
+    assert not eng.is_live("q")
+
+
+def greedy_plain(name, dtype, prompt, steps):
+    cfg, w = plain_weights(name, dtype)
+    rounding = P.bf16_round if dtype == "bfloat16" else P.no_round
+    seq, gaps = list(prompt), []
+    for _ in range(steps):
+        logits = P.plain_forward(cfg, w, seq, rounding=rounding)[-1]
+        top = torch.topk(logits, 2).values
+        gaps.append(float(top[0] - top[1]))
+        seq.append(int(logits.argmax()))
+    return seq[len(prompt):], gaps
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(name, dtype):
+    """BASELINE's tiny workloads: A = prompts of 5/17/33 tokens, 8 greedy steps,
+    page 16; B = prompts of 1/64/100/200, portions of 48 mixed with decoding,
+    page 8."""
+    from kipp_b200.engine.llm import LLM
+    lengths = {"A": [5, 17, 33], "B": [1, 64, 100, 200]}[name]
+    prompts = [random_tokens(name, n, seed=20 + n) for n in lengths]
+    llm = LLM(model_folder(name), dtype=dtype, kv_block_size={"A": 16, "B": 8}[name], kv_tokens=640,
+              max_requests=4, max_batch_tokens=64, chunk=48)
+    out = llm.generate(prompts, decode=8)
+    assert llm.metrics["tokens_sampled"] == 8 * len(prompts)
+    for prompt, res in zip(prompts, out):
+        want, gaps = greedy_plain(name, dtype, prompt, 8)
+        assert res.finish_reason == "length" and len(res.tokens) == 8
+        for i, (g, w_) in enumerate(zip(res.tokens, want)):
+            if g != w_:
+                # only a near-tie may go the other way; the sequences part there
+                assert gaps[i] < (1e-4 if dtype == "float32" else 5e-2), (i, g, w_, gaps[i])
+                break
+    assert llm.engine.cache.free_pages() == [llm.engine.cache.groups[0].pool.n_pages]
+
+
+def test_sampled_generation_follows_the_plain_sampler():
+    """Temperature 0.8, seeded per request: with the engine's own float32 logits
+    the device sampler must draw what the plain sampler draws from them."""
+    from kipp_b200.engine import Request, StepEntry
+    from kipp_b200.engine.llm import LLM
+    from kipp_b200.sampling import SamplingParams
+    prompts = [random_tokens("B", n, seed=40 + n) for n in (1, 64, 100)]
+    llm = LLM(model_folder("B"), dtype="float32", kv_block_size=8, kv_tokens=1024, max_requests=4,
+              max_batch_tokens=64, chunk=48)
+    params = [SamplingParams(temperature=0.8, seed=5 + i, top_k=[0, 50, 0][i], top_p=[1.0, 1.0, 0.9][i])
+              for i in range(3)]
+    out = llm.generate(prompts, decode=10, sampling=params)
+    again = llm.generate(prompts, decode=10, sampling=params)
+    assert [r.tokens for r in out] == [r.tokens for r in again]            # seeded: reproducible
+    other = llm.generate(prompts, decode=10, sampling=[SamplingParams(temperature=0.8, seed=99 + i)
+                                                       for i in range(3)])
+    assert [r.tokens for r in out] != [r.tokens for r in other]
+    from kipp_b200.engine import Engine
+    eng = Engine.from_folder(model_folder("B"), dtype="float32", page_size=8, cache_tokens=512)
+    for i, (prompt, res, sp) in enumerate(zip(prompts, out, params)):
+        seq, state = list(prompt), sp.seed
+        logits = eng.step([StepEntry(("s", i), seq, [len(seq) - 1])]).cpu()[0]
+        for tok in res.tokens:
+            want, state = P.plain_sample(logits.numpy(), sp.temperature, state, top_k=sp.top_k, top_p=sp.top_p)
+            assert tok == want
+            logits = eng.step([StepEntry(("s", i), [tok], [0])]).cpu()[0]
+
+
+def test_preemption_recomputes_the_same_tokens():
+    """With too few pages for all requests the youngest is put back and
+    recomputed; greedy output must not change."""
+    from kipp_b200.engine.llm import LLM
+    prompts = [random_tokens("A", n, seed=60 + n) for n in (30, 28, 26)]
+    roomy = LLM(model_folder("A"), dtype="float32", kv_block_size=16, kv_tokens=512, max_requests=4,
+                max_batch_tokens=64)
+    want = [r.tokens for r in roomy.generate(prompts, decode=20)]
+    tight = LLM(model_folder("A"), dtype="float32", kv_block_size=16, kv_tokens=112, max_requests=4,
+                max_batch_tokens=64, policy="preempt")              # 7 pages; 3 x 50 tokens need 12
+    res = tight.generate(prompts, decode=20)
+    assert [r.tokens for r in res] == want
+    assert tight.metrics["preemptions"] >= 1 and sum(r.preemptions for r in res) >= 1
+    waits = LLM(model_folder("A"), dtype="float32", kv_block_size=16, kv_tokens=112, max_requests=4,
+                max_batch_tokens=64, policy="reserve")
+    assert [r.tokens for r in waits.generate(prompts, decode=20)] == want
+    assert waits.metrics["preemptions"] == 0
+
+
+def test_command_line(tmp_path):
+    import subprocess
+    import sys
+    import os
+    from gpu_util import ROOT
+    ids = random_tokens("A", 12, seed=5)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kipp"), "--model", model_folder("A"),
+                           "--prompt-ids", ",".join(map(str, ids)), "--decode", "6", "--dtype", "float32",
+                           "--top", "3"], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = proc.stdout.strip().splitlines()
+    assert lines[0].startswith("generated\t")
+    generated = [int(t) for t in lines[0].split("\t")[1].split()]
+    want, _ = greedy_plain("A", "float32", ids, 6)
+    assert generated == want
+    assert len(lines) == 4 and lines[1].startswith("1\t")
+    full = plain_logits("A", "float32", ids + generated)
+    assert int(lines[1].split("\t")[1]) == int(full[-1].argmax())
+    assert "KIPP_METRIC backend=cuda prefill_tokens=12" in proc.stderr and "decode_tokens=6" in proc.stderr
+    bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kipp"), "--model", model_folder("A"),
+                          "--prompt-ids", "1,2", "--decode", "2", "--temperature", "0.5", "--top-p", "0"],
+                         capture_output=True, text=True, timeout=300)
+    assert bad.returncode == 2 and "top_p" in bad.stderr
