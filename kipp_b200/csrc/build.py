@@ -71,9 +71,22 @@ def build_dir() -> str:
     raise BuildError(f"no writable build folder among {cands}")
 
 
+def _local_includes(name: str) -> tuple:
+    """Files of this folder that ``<name>.cu`` includes by name (one level)."""
+    out = []
+    with open(os.path.join(_HERE, name + ".cu"), "r", encoding="utf-8") as f:
+        for line in f:
+            line = line.strip()
+            if line.startswith('#include "'):
+                inc = line.split('"')[1]
+                if os.path.isfile(os.path.join(_HERE, inc)) and inc not in _HEADERS:
+                    out.append(inc)
+    return tuple(sorted(set(out)))
+
+
 def _digest(name: str, extra_flags: list[str]) -> str:
     h = hashlib.sha256()
-    for f in (name + ".cu",) + _HEADERS + tuple(sorted(
+    for f in (name + ".cu",) + _HEADERS + _local_includes(name) + tuple(sorted(
             x for x in os.listdir(_HERE) if x.endswith(".cuh") and x not in _HEADERS)):
         with open(os.path.join(_HERE, f), "rb") as fh:
             h.update(f.encode())

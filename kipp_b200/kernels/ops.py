@@ -55,6 +55,8 @@ def _check(code: int, what: str) -> None:
         raise KernelError(f"{what}: unsupported dtype combination")
     if code == -3:
         raise KernelError(f"{what}: a pointer or stride is not aligned as the kernel needs")
+    if code == -4:
+        raise KernelError(f"{what}: these sizes need more scratch than the library holds")
     raise KernelError(f"{what}: CUDA error {code}")
 
 
