@@ -27,6 +27,10 @@ namespace {
 constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
 constexpr int TILE_KEYS = 64;
+#ifndef KIPP_DECODE_STAGES
+#define KIPP_DECODE_STAGES 2
+#endif
+constexpr int DECODE_STAGES = KIPP_DECODE_STAGES;      // K/V tiles in flight per CTA
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -68,29 +72,46 @@ template <int D> __device__ __forceinline__ uint32_t tile_offset(int row, int ch
 // Gathers TILE_KEYS rows of keys and of values, positions [j0, j0 + TILE_KEYS),
 // for kv head g into swizzled tiles.  Rows outside [lo, hi] are zero-filled
 // (their scores are masked; zero values keep 0 * v finite).  A thread copies
-// the same 16-byte chunk of every (THREADS / chunks-per-row)-th row, so it
-// looks a page up once per row.
+// one 16-byte column of 8 consecutive rows (or of every 8th row when a row
+// holds 8 chunks); when the page size is a multiple of 8 those rows lie in
+// one page and the page is looked up once.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_tile, uint32_t v_tile, const bf16* __restrict__ k_pages,
                                              const bf16* __restrict__ v_pages, const int* __restrict__ table,
                                              int table_width, int page_size, int n_kv, int g, int j0, int lo,
                                              int hi) {
     constexpr int CHUNKS = D / 8;                        // 16-byte chunks per row
-    constexpr int ROWS_PER_PASS = THREADS / CHUNKS;
-    const int chunk = threadIdx.x % CHUNKS, row0 = threadIdx.x / CHUNKS;
-    const bool pow2 = (page_size & (page_size - 1)) == 0;
-    const int shift = 31 - __clz(page_size);
+    constexpr int GROUPS = THREADS / CHUNKS;             // threads along the rows
+    constexpr int ROWS = TILE_KEYS / GROUPS;             // consecutive rows per thread
+    const int chunk = threadIdx.x % CHUNKS, row0 = (threadIdx.x / CHUNKS) * ROWS;
+    if ((page_size & 7) == 0 && ROWS <= 8) {
+        const int j_first = j0 + row0;
+        const int slot = j_first / page_size;
+        const int within = j_first - slot * page_size;
+        const int page = (slot < table_width && j_first <= hi && j_first + ROWS - 1 >= lo)
+                             ? __ldg(table + slot) : -1;
+        const size_t base = (((size_t)max(page, 0) * n_kv + g) * page_size + within) * D + chunk * 8;
 #pragma unroll
-    for (int row = row0; row < TILE_KEYS; row += ROWS_PER_PASS) {
-        const int j = j0 + row;
+        for (int r = 0; r < ROWS; ++r) {
+            const int j = j_first + r;
+            const bool ok = page >= 0 && j >= lo && j <= hi;
+            const size_t src = ok ? base + (size_t)r * D : 0;
+            const uint32_t off = tile_offset<D>(row0 + r, chunk);
+            cp_async16(k_tile + off, k_pages + src, ok ? 16 : 0);
+            cp_async16(v_tile + off, v_pages + src, ok ? 16 : 0);
+        }
+        return;
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int row = row0 + r, j = j0 + row;
         size_t src = 0;
         int bytes = 0;
         if (j >= lo && j <= hi) {
-            const int slot = pow2 ? (j >> shift) : (j / page_size);
-            const int within = pow2 ? (j & (page_size - 1)) : (j - slot * page_size);
+            const int slot = j / page_size;
             const int page = slot < table_width ? __ldg(table + slot) : -1;
             if (page >= 0) {
-                src = (((size_t)page * n_kv + g) * page_size + within) * D + chunk * 8;
+                src = (((size_t)page * n_kv + g) * page_size + (j - slot * page_size)) * D + chunk * 8;
                 bytes = 16;
             }
         }
@@ -155,6 +176,8 @@ attn_prefill_kernel(const PrefillParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = TILE_KEYS * D * 2;
     const uint32_t k_base = smem_u32(smem), v_base = k_base + 2 * TILE_BYTES;    // [2 stages] each
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 2, t4 = lane & 3;
     const int entry = p.work[2 * blockIdx.x], tile_tok = p.work[2 * blockIdx.x + 1];
@@ -243,8 +266,10 @@ attn_prefill_kernel(const PrefillParams p) {
         l1 = l1 * c1 + sum1;
         m0 = mx0;
         m1 = mx1;
+        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {     // the maximum moved for some row
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+            for (int i = 0; i < D / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+        }
         pv_accumulate<D, 4>(o, pf, v_base + buf * TILE_BYTES, 0, lane);
         __syncthreads();
     }
@@ -297,8 +322,10 @@ __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TILE_BYTES = TILE_KEYS * D * 2;
-    constexpr int STAGES = 3;
+    constexpr int STAGES = DECODE_STAGES;
     const uint32_t k_base = smem_u32(smem), v_base = k_base + STAGES * TILE_BYTES;
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 2, t4 = lane & 3;
     const int n = blockIdx.z, entry = p.rows[n], g = blockIdx.y, split = blockIdx.x;
@@ -398,8 +425,10 @@ attn_decode_kernel(const DecodeParams p) {
         l1 = l1 * c1 + sum1;
         m0 = mx0;
         m1 = mx1;
+        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {     // the maximum moved for some row
 #pragma unroll
-        for (int d = 0; d < D / 8; ++d) { o[d][0] *= c0; o[d][1] *= c0; o[d][2] *= c1; o[d][3] *= c1; }
+            for (int d = 0; d < D / 8; ++d) { o[d][0] *= c0; o[d][1] *= c0; o[d][2] *= c1; o[d][3] *= c1; }
+        }
         pv_accumulate<D, 1>(o, pf, v_base + buf * TILE_BYTES, warp * 16, lane);
         __syncthreads();
     }
@@ -451,6 +480,8 @@ __global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __
                                          const int* __restrict__ q_start, const int* __restrict__ context_len,
                                          int n_q, int head_dim, int max_splits,
                                          const int* __restrict__ split_keys_ptr) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n = blockIdx.y, h = blockIdx.x;
     const int entry = rows[n];
     const int kv_len = context_len[entry] + 1;
@@ -485,12 +516,11 @@ template <int D> int launch_prefill(const PrefillParams& p, int items, cudaStrea
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_prefill_kernel<D><<<dim3(items, p.n_q), THREADS, SMEM, s>>>(p);
-    return kipp_launch_status();
+    return kipp_launch(attn_prefill_kernel<D>, dim3(items, p.n_q), dim3(THREADS), SMEM, s, 1, p);
 }
 
 template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s) {
-    constexpr int PIPE = 6 * TILE_KEYS * D * 2;
+    constexpr int PIPE = 2 * DECODE_STAGES * TILE_KEYS * D * 2;
     constexpr int MERGE = (2 * WARPS * 16 + WARPS * 16 * D) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
     static bool configured = false;
@@ -499,8 +529,7 @@ template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s)
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attn_decode_kernel<D><<<dim3(p.max_splits, p.n_kv, n), THREADS, SMEM, s>>>(p);
-    return kipp_launch_status();
+    return kipp_launch(attn_decode_kernel<D>, dim3(p.max_splits, p.n_kv, n), dim3(THREADS), SMEM, s, 1, p);
 }
 }  // namespace
 
@@ -557,7 +586,7 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     cudaStream_t s = (cudaStream_t)stream;
     int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
     if (rc) return rc;
-    attn_decode_merge_kernel<<<dim3(n_q, n), head_dim >= 128 ? 128 : 64, 0, s>>>(
-        (bf16*)out, p.part_o, p.part_ml, rows, q_start, context_len, n_q, head_dim, max_splits, split_keys);
-    return kipp_launch_status();
+    return kipp_launch(attn_decode_merge_kernel, dim3(n_q, n), dim3(head_dim >= 128 ? 128 : 64), 0, s, 1,
+                       (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, rows, q_start, context_len, n_q,
+                       head_dim, max_splits, split_keys);
 }

@@ -29,6 +29,8 @@ paged_attention_simt_kernel(T* __restrict__ out, const T* __restrict__ q,
                             int tokens, int n_q, int n_kv, int head_dim, float scale, int window,
                             int* __restrict__ status) {
     extern __shared__ float q_smem[];                 // [warps][head_dim]
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long wg = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
     if (wg >= (long long)tokens * n_q) return;
@@ -114,16 +116,14 @@ extern "C" int kipp_paged_attention_simt(
     if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
     const size_t smem = (size_t)warps * head_dim * sizeof(float);
     if (dtype == KIPP_DT_F32)
-        paged_attention_simt_kernel<float><<<(unsigned)blocks, warps * 32, smem, s>>>(
+        return kipp_launch(paged_attention_simt_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), smem, s, 1,
             (float*)out, (const float*)q, (const float*)k_pages, (const float*)v_pages, positions,
             entry_of_token, block_table, table_width, page_size, tokens, n_q, n_kv, head_dim, scale,
             window, status);
-    else if (dtype == KIPP_DT_BF16)
-        paged_attention_simt_kernel<bf16><<<(unsigned)blocks, warps * 32, smem, s>>>(
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(paged_attention_simt_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), smem, s, 1,
             (bf16*)out, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, positions,
             entry_of_token, block_table, table_width, page_size, tokens, n_q, n_kv, head_dim, scale,
             window, status);
-    else
-        return KIPP_ERR_DTYPE;
-    return kipp_launch_status();
+    return KIPP_ERR_DTYPE;
 }

@@ -52,6 +52,61 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return warp_sum(t);
 }
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of this package is launched with
+// the programmatic-stream-serialization attribute (unless KIPP_B200_PDL=0): its
+// blocks may be scheduled while the kernel before it in the stream drains, so
+// launch latency and each kernel's set-up hide behind the previous kernel's
+// tail.  The rule every kernel keeps: call pdl_wait() before the first access
+// to global memory that an earlier kernel may have written or may still read;
+// only set-up that touches nothing of the sort (barrier init, tensor-memory
+// allocation, loads of weights) may come before it.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool kipp_pdl_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("KIPP_B200_PDL");
+        cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return cached == 1;
+}
+
+// Launches `kernel` with the package's attributes; cluster_z > 1 makes the
+// grid's z dimension one thread-block cluster.
+template <typename... KArgs, typename... Args>
+static inline int kipp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_z, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (kipp_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return 0;
+}
+
 static inline int kipp_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;

@@ -10,6 +10,8 @@ template <typename TW>
 __global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                     const int* __restrict__ ids, int hidden, int vocab,
                                     int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     if (id < 0 || id >= vocab) {           // never read outside the table
@@ -29,12 +31,12 @@ extern "C" int kipp_embed_gather(float* out, const void* table, int table_dtype,
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == KIPP_DT_F32)
-        embed_gather_kernel<float><<<tokens, threads, 0, s>>>(out, (const float*)table, ids, hidden, vocab, status);
-    else if (table_dtype == KIPP_DT_BF16)
-        embed_gather_kernel<bf16><<<tokens, threads, 0, s>>>(out, (const bf16*)table, ids, hidden, vocab, status);
-    else
-        return KIPP_ERR_DTYPE;
-    return kipp_launch_status();
+        return kipp_launch(embed_gather_kernel<float>, dim3(tokens), dim3(threads), 0, s, 1, out,
+                           (const float*)table, ids, hidden, vocab, status);
+    if (table_dtype == KIPP_DT_BF16)
+        return kipp_launch(embed_gather_kernel<bf16>, dim3(tokens), dim3(threads), 0, s, 1, out,
+                           (const bf16*)table, ids, hidden, vocab, status);
+    return KIPP_ERR_DTYPE;
 }
 
 // y[r, i] = x[src(r), i] * rsqrt(mean(x[src(r), :]^2) + eps) * w[i]
@@ -45,6 +47,8 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
                                const void* __restrict__ w, int w_dtype, const int* __restrict__ rows,
                                int size, float eps) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* src = x + (size_t)(rows ? rows[r] : r) * size;
     float ss = 0.f;
@@ -59,18 +63,72 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
         dst[i] = from_f32<TO>(src[i] * scale * load_w(w, w_dtype, i));
 }
 
+// Vector path: size a multiple of 4 and at most 4096; each of 256 threads keeps
+// its float4 pieces of the row in registers, so the row is read once.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const void* __restrict__ w, int w_dtype,
+                   const int* __restrict__ rows, int size, float eps) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * size);
+    const int n4 = size >> 2;
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < n4) {
+            v[j] = src[i];
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)size + eps);
+    TO* dst = out + (size_t)r * size;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < n4) {
+            const size_t e = (size_t)i * 4;
+            const float a = v[j].x * scale * load_w(w, w_dtype, e), b = v[j].y * scale * load_w(w, w_dtype, e + 1);
+            const float c = v[j].z * scale * load_w(w, w_dtype, e + 2), d = v[j].w * scale * load_w(w, w_dtype, e + 3);
+            if (sizeof(TO) == 4) {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + e) = make_float4(a, b, c, d);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(dst) + e) = packed;
+            }
+        }
+    }
+}
+
 extern "C" int kipp_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype,
                             const int* rows, int n_rows, int size, float eps, void* stream) {
     if (n_rows <= 0) return 0;
     if (size <= 0) return KIPP_ERR_ARG;
     if (w_dtype != KIPP_DT_F32 && w_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (size % 4 == 0 && size <= 4096 && size >= 256 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        if (out_dtype == KIPP_DT_F32)
+            return kipp_launch(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(256), 0, s, 1, (float*)out, x, w,
+                               w_dtype, rows, size, eps);
+        if (out_dtype == KIPP_DT_BF16)
+            return kipp_launch(rmsnorm_vec_kernel<bf16>, dim3(n_rows), dim3(256), 0, s, 1, (bf16*)out, x, w,
+                               w_dtype, rows, size, eps);
+        return KIPP_ERR_DTYPE;
+    }
     int threads = size >= 2048 ? 512 : (size >= 512 ? 256 : 64);
     if (out_dtype == KIPP_DT_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, s>>>((float*)out, x, w, w_dtype, rows, size, eps);
-    else if (out_dtype == KIPP_DT_BF16)
-        rmsnorm_kernel<bf16><<<n_rows, threads, 0, s>>>((bf16*)out, x, w, w_dtype, rows, size, eps);
-    else
-        return KIPP_ERR_DTYPE;
-    return kipp_launch_status();
+        return kipp_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, 1, (float*)out, x, w, w_dtype,
+                           rows, size, eps);
+    if (out_dtype == KIPP_DT_BF16)
+        return kipp_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, 1, (bf16*)out, x, w, w_dtype,
+                           rows, size, eps);
+    return KIPP_ERR_DTYPE;
 }

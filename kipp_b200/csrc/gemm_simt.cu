@@ -29,6 +29,8 @@ gemm_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __restr
                  int M, int N, int K, int lda, int ldw, int ldc) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -98,19 +100,18 @@ int launch(void* C, const void* A, const void* W, int M, int N, int K, int lda, 
     if (grid.y > 65535) return KIPP_ERR_ARG;
     switch (epi) {
     case EPI_STORE:
-        gemm_simt_kernel<TA, TW, TC, EPI_STORE><<<grid, 256, 0, s>>>((TC*)C, (const TA*)A, (const TW*)W, M, N, K, lda, ldw, ldc);
-        break;
+        return kipp_launch(gemm_simt_kernel<TA, TW, TC, EPI_STORE>, grid, dim3(256), 0, s, 1, (TC*)C, (const TA*)A,
+                           (const TW*)W, M, N, K, lda, ldw, ldc);
     case EPI_ADD:
-        gemm_simt_kernel<TA, TW, TC, EPI_ADD><<<grid, 256, 0, s>>>((TC*)C, (const TA*)A, (const TW*)W, M, N, K, lda, ldw, ldc);
-        break;
+        return kipp_launch(gemm_simt_kernel<TA, TW, TC, EPI_ADD>, grid, dim3(256), 0, s, 1, (TC*)C, (const TA*)A,
+                           (const TW*)W, M, N, K, lda, ldw, ldc);
     case EPI_SWIGLU:
         if (N & 1) return KIPP_ERR_ARG;
-        gemm_simt_kernel<TA, TW, TC, EPI_SWIGLU><<<grid, 256, 0, s>>>((TC*)C, (const TA*)A, (const TW*)W, M, N, K, lda, ldw, ldc);
-        break;
+        return kipp_launch(gemm_simt_kernel<TA, TW, TC, EPI_SWIGLU>, grid, dim3(256), 0, s, 1, (TC*)C, (const TA*)A,
+                           (const TW*)W, M, N, K, lda, ldw, ldc);
     default:
         return KIPP_ERR_ARG;
     }
-    return kipp_launch_status();
 }
 }  // namespace
 

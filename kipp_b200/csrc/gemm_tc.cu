@@ -42,10 +42,10 @@
 
 namespace {
 
-constexpr int TILE_F = 128;          // features per CTA = MMA M
+constexpr int UMMA_M = 128;          // features per accumulator = MMA M (a CTA holds 1 or 2)
 constexpr int TILE_K = 64;           // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;         // TMA warp, MMA warp, 8 epilogue warps
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -147,15 +147,20 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
            | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-template <int TILE_T> struct Cfg {
+template <int TILE_T, int TILE_F> struct Cfg {
+    static constexpr int HALVES = TILE_F / UMMA_M;               // accumulators (128 features each)
     static constexpr int W_BYTES = TILE_F * TILE_K * 2;
     static constexpr int X_BYTES = TILE_T * TILE_K * 2;
     static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
     // stages: as many as fit in ~96 KB for narrow token tiles (two CTAs per
     // SM), ~192 KB for wide ones
-    static constexpr int STAGES = TILE_T >= 128 ? (192 * 1024) / STAGE_BYTES
-                                                : ((96 * 1024) / STAGE_BYTES > 8 ? 8 : (96 * 1024) / STAGE_BYTES);
-    static constexpr int TMEM_COLS = TILE_T < 32 ? 32 : TILE_T;
+    static constexpr int STAGES = (TILE_T >= 128 || TILE_F > 128)
+                                      ? (192 * 1024) / STAGE_BYTES
+                                      : ((96 * 1024) / STAGE_BYTES > 8 ? 8 : (96 * 1024) / STAGE_BYTES);
+    static constexpr int ACC_COLS = TILE_T * HALVES;
+    static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;   // 32, 64, 128, 256 or 512
+    // epilogue warp groups: two groups of four warps split the token columns
+    static constexpr int COL_GROUPS = TILE_T >= 32 ? 2 : 1;
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -170,27 +175,56 @@ struct Params {
     int* status;
 };
 
-// Epilogue of one value: thread holds feature f of token t.
-template <typename TC>
-__device__ __forceinline__ void store_value(const Params& p, int t, int f, float v, float partner, int lane) {
-    if (p.epilogue == EPI_SWIGLU) {
-        // gate rows are even, up rows odd; the even lane writes silu(g) * u
-        if ((lane & 1) == 0 && f + 1 < p.features) {
-            const float g = v, u = partner;
-            reinterpret_cast<TC*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = from_f32<TC>(g / (1.0f + __expf(-g)) * u);
+// Epilogue of 16 tokens (t_first .. + 15) of this thread's feature f.
+__device__ __forceinline__ void epilogue_chunk(const Params& p, const float* v, int t_first, int f, int lane) {
+    if (p.epilogue == EPI_ADD) {
+        // all loads of the residual first, then the stores: the loads overlap
+        float* cbase = reinterpret_cast<float*>(p.C) + f;
+        float old[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = t_first + j;
+            old[j] = (t < p.tokens && f < p.features) ? cbase[(size_t)t * p.ldc] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int t = t_first + j;
+            if (t < p.tokens && f < p.features) cbase[(size_t)t * p.ldc] = old[j] + v[j];
+        }
+    } else if (p.epilogue == EPI_SWIGLU) {
+        // gate rows are even, up rows odd: the even lane takes its neighbour's
+        // up value and writes silu(gate) * up
+        const bool writer = (lane & 1) == 0 && f + 1 < p.features;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float u = __shfl_xor_sync(0xffffffffu, v[j], 1);
+            const int t = t_first + j;
+            if (writer && t < p.tokens) {
+                const float r = __fdividef(v[j], 1.0f + __expf(-v[j])) * u;
+                if (p.out_dtype == KIPP_DT_F32) reinterpret_cast<float*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = r;
+                else reinterpret_cast<bf16*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = __float2bfloat16_rn(r);
+            }
         }
     } else if (f < p.features) {
-        TC* c = reinterpret_cast<TC*>(p.C) + (size_t)t * p.ldc + f;
-        if (p.epilogue == EPI_ADD) *c = from_f32<TC>(to_f32(*c) + v);
-        else *c = from_f32<TC>(v);
+        if (p.out_dtype == KIPP_DT_F32) {
+            float* c = reinterpret_cast<float*>(p.C) + f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (t_first + j < p.tokens) c[(size_t)(t_first + j) * p.ldc] = v[j];
+        } else {
+            bf16* c = reinterpret_cast<bf16*>(p.C) + f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (t_first + j < p.tokens) c[(size_t)(t_first + j) * p.ldc] = __float2bfloat16_rn(v[j]);
+        }
     }
 }
 
-template <int TILE_T>
+template <int TILE_T, int TILE_F>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const Params p) {
-    using C = Cfg<TILE_T>;
+    using C = Cfg<TILE_T, TILE_F>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
@@ -199,6 +233,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // token tiles vary fastest: CTAs that run together share a weight tile (L2)
     const int t0 = blockIdx.x * TILE_T;
@@ -224,10 +259,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            // Weights do not depend on the kernels before this one: the first
+            // ring of weight tiles is on its way before the dependency wait; the
+            // activation tiles follow after it.
+            const int ahead = min(n_kb, C::STAGES);
+            for (int i = 0; i < ahead; ++i) {
+                uint8_t* wt = tiles + (size_t)i * C::STAGE_BYTES;
+                mbar_expect_tx(&full[i], C::STAGE_BYTES);
+                tma_load_2d(wt, &map_w, &full[i], (kb_begin + i) * TILE_K, f0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i) {
+                uint8_t* xt = tiles + (size_t)i * C::STAGE_BYTES + C::W_BYTES;
+                tma_load_2d(xt, &map_x, &full[i], (kb_begin + i) * TILE_K, t0);
+            }
+            for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % C::STAGES;
                 const uint32_t ph = (i / C::STAGES) & 1;
-                if (i >= C::STAGES && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
                 uint8_t* wt = tiles + (size_t)s * C::STAGE_BYTES;
                 uint8_t* xt = wt + C::W_BYTES;
                 mbar_expect_tx(&full[s], C::STAGE_BYTES);
@@ -239,7 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(TILE_F, TILE_T);
+            constexpr uint32_t idesc = umma_idesc(UMMA_M, TILE_T);
             bool ok = true;
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % C::STAGES;
@@ -250,65 +299,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint64_t wd = umma_smem_desc(wa), xd = umma_smem_desc(wa + C::W_BYTES);
 #pragma unroll
                 for (int k = 0; k < TILE_K / UMMA_K; ++k) {
-                    // advance 16 elements = 32 bytes inside the swizzled row: +2 in the address field
-                    umma_bf16(tmem_base, wd + 2 * k, xd + 2 * k, idesc, (i | k) ? 1u : 0u);
+#pragma unroll
+                    for (int h = 0; h < C::HALVES; ++h) {
+                        // advance 16 elements = 32 bytes inside the swizzled row: +2 in the address
+                        // field; the second 128 features start 128 rows = 16 KB further: +1024
+                        umma_bf16(tmem_base + h * TILE_T, wd + 2 * k + h * 1024, xd + 2 * k, idesc,
+                                  (i | k) ? 1u : 0u);
+                    }
                 }
                 umma_commit(&empty[s]);            // stage reusable when these MMAs are done
             }
             if (ok) umma_commit(acc_ready);
         }
     } else {
-        // ---------------------------------------------------------------- epilogue warps 2..5
+        // ---------------------------------------------------------------- epilogue warps 2..9
         const int q = warp & 3;                    // tensor-memory lane quarter of this warp
-        const int f = f0 + q * 32 + lane;
+        const int cg = (warp - 2) >> 2;            // which share of the token columns
+        pdl_wait();                                // the epilogue reads and writes what earlier kernels made
         bool ok = n_kb > 0 ? mbar_wait(acc_ready, 0, abort_flag) : true;
         tcgen05_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
-        if (ok && p.splits == 1) {
+        constexpr int COLS_PER_GROUP = TILE_T / C::COL_GROUPS;
+        if (ok && cg < C::COL_GROUPS) {
+            if (p.splits == 1) {
 #pragma unroll 1
-            for (int c = 0; c < TILE_T; c += 16) {
-                float v[16];
-                if (n_kb > 0) tmem_ld16(taddr + c, v);
-                else {
+                for (int h = 0; h < C::HALVES; ++h) {
+                    const int f = f0 + h * UMMA_M + q * 32 + lane;
+#pragma unroll 1
+                    for (int c = cg * COLS_PER_GROUP; c < (cg + 1) * COLS_PER_GROUP; c += 16) {
+                        float v[16];
+                        if (n_kb > 0) tmem_ld16(taddr + h * TILE_T + c, v);
+                        else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                }
-                if (p.epilogue == EPI_ADD) {
-                    // all loads of the residual first, then the stores: the loads overlap
-                    float* cbase = reinterpret_cast<float*>(p.C) + f;
-                    float old[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c + j;
-                        old[j] = (t < p.tokens && f < p.features) ? cbase[(size_t)t * p.ldc] : 0.f;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c + j;
-                        if (t < p.tokens && f < p.features) cbase[(size_t)t * p.ldc] = old[j] + v[j];
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c + j;
-                        const float partner = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                        if (t < p.tokens) {
-                            if (p.out_dtype == KIPP_DT_F32) store_value<float>(p, t, f, v[j], partner, lane);
-                            else store_value<bf16>(p, t, f, v[j], partner, lane);
+                            for (int j = 0; j < 16; ++j) v[j] = 0.f;
                         }
+                        epilogue_chunk(p, v, t0 + c, f, lane);
                     }
                 }
-            }
-        } else if (ok) {
-            // partial sums of this split into this CTA's shared memory, [token][feature]
-            // (the pipeline stages are idle once the accumulator is complete)
-            float* red = reinterpret_cast<float*>(tiles) + q * 32 + lane;
+            } else {
+                // partial sums of this split into this CTA's shared memory, [token][feature]
+                // (the pipeline stages are idle once the accumulator is complete)
+                float* red = reinterpret_cast<float*>(tiles) + q * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < TILE_T; c += 16) {
-                float v[16];
-                tmem_ld16(taddr + c, v);
+                for (int c = cg * COLS_PER_GROUP; c < (cg + 1) * COLS_PER_GROUP; c += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c, v);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) red[(size_t)(c + j) * TILE_F] = v[j];
+                    for (int j = 0; j < 16; ++j) red[(size_t)(c + j) * UMMA_M] = v[j];
+                }
             }
         }
     }
@@ -318,7 +356,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // all threads of all CTAs of the cluster: partial sums are visible afterwards
         asm volatile("barrier.cluster.arrive.release.aligned;\n"
                      "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-        if (warp >= 2) {
+        if (warp >= 2 && warp < 6 && !*abort_flag) {
             const int q = warp & 3;
             const int f = f0 + q * 32 + lane;
             const int per = (TILE_T + p.splits - 1) / p.splits;       // tokens this CTA finishes
@@ -329,16 +367,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int s = 0; s < p.splits; ++s) {                    // fixed order
                     uint32_t remote;
                     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
-                                 : "r"(local + (uint32_t)(j * TILE_F * 4)), "r"(s));
+                                 : "r"(local + (uint32_t)(j * UMMA_M * 4)), "r"(s));
                     float part;
                     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(remote) : "memory");
                     v += part;
                 }
-                const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
                 const int t = t0 + j;
-                if (t < p.tokens) {
-                    if (p.out_dtype == KIPP_DT_F32) store_value<float>(p, t, f, v, partner, lane);
-                    else store_value<bf16>(p, t, f, v, partner, lane);
+                // one value per thread: the epilogue of a 16-token chunk with one live token
+                if (p.epilogue == EPI_SWIGLU) {
+                    const float u = __shfl_xor_sync(0xffffffffu, v, 1);
+                    if ((lane & 1) == 0 && f + 1 < p.features && t < p.tokens) {
+                        const float r = __fdividef(v, 1.0f + __expf(-v)) * u;
+                        if (p.out_dtype == KIPP_DT_F32) reinterpret_cast<float*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = r;
+                        else reinterpret_cast<bf16*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = __float2bfloat16_rn(r);
+                    }
+                } else if (t < p.tokens && f < p.features) {
+                    if (p.out_dtype == KIPP_DT_F32) {
+                        float* c = reinterpret_cast<float*>(p.C) + (size_t)t * p.ldc + f;
+                        *c = p.epilogue == EPI_ADD ? *c + v : v;
+                    } else {
+                        reinterpret_cast<bf16*>(p.C)[(size_t)t * p.ldc + f] = __float2bfloat16_rn(v);
+                    }
                 }
             }
         }
@@ -410,55 +459,46 @@ int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, long long ld
     return 0;
 }
 
-template <int TILE_T>
+template <int TILE_T, int TILE_F>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
-    using C = Cfg<TILE_T>;
+    using C = Cfg<TILE_T, TILE_F>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TILE_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)C::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TILE_T, TILE_F>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    if (p.splits == 1) {
-        gemm_tc_kernel<TILE_T><<<grid, THREADS, C::SMEM, s>>>(mw, mx, p);
-        return kipp_launch_status();
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = C::SMEM;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = p.splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TILE_T>, mw, mx, p);
-    return e == cudaSuccess ? kipp_launch_status() : (int)e;
+    return kipp_launch(gemm_tc_kernel<TILE_T, TILE_F>, grid, dim3(THREADS), C::SMEM, s, p.splits, mw, mx, p);
 }
 
-// Token tile.  Measured on B200 at 2,048 tokens: 64-token tiles (two CTAs per SM,
-// one's epilogue under the other's MMAs) match or beat 256-token tiles except
-// for few features with a long K, where the wider tile re-reads less.
-int pick_tile_t(int tokens, int features) {
-    if (tokens <= 16) return 16;
-    if (tokens <= 32) return 32;
-    if (tokens >= 1536 && features <= 8192) return 256;
-    return 64;
+// Tile choice, from measurements on B200: 128 features with a token tile of 16,
+// 32 or 64 (two CTAs per SM, one's epilogue under the other's MMAs), 256 tokens
+// from 1,024 tokens on.  256 features x 256 tokens per CTA (two accumulators,
+// all 512 tensor-memory columns) is built and selectable but measured no faster
+// than 128 x 256 here, so it is not chosen by default.
+void pick_tiles(int tokens, int features, int* tile_t, int* tile_f) {
+    *tile_f = 128;
+    if (tokens <= 16) *tile_t = 16;
+    else if (tokens <= 32) *tile_t = 32;
+    else if (tokens >= 1024) *tile_t = 256;
+    else *tile_t = 64;
 }
 }  // namespace
 
-// The token tile and the number of K splits (= cluster size, at most 8) the
-// kernel uses for a shape; want_splits == 0 lets it choose.
+// The token tile, feature tile and number of K splits (= cluster size, at most
+// 8) the kernel uses for a shape; a want_* of 0 lets it choose.
 extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_splits, int want_tile,
-                                 int* tile_t_out, int* splits_out) {
-    int tile_t = pick_tile_t(tokens, features);
-    if (want_tile == 16 || want_tile == 32 || want_tile == 64 || want_tile == 128 || want_tile == 256)
+                                 int want_tile_f, int* tile_t_out, int* tile_f_out, int* splits_out) {
+    int tile_t, tile_f;
+    pick_tiles(tokens, features, &tile_t, &tile_f);
+    if (want_tile == 16 || want_tile == 32 || want_tile == 64 || want_tile == 128 || want_tile == 256) {
         tile_t = want_tile;
-    const int f_tiles = (features + TILE_F - 1) / TILE_F;
+        if (tile_t != 256) tile_f = 128;
+    }
+    if (want_tile_f == 128) tile_f = 128;
+    if (want_tile_f == 256 && tile_t == 256) tile_f = 256;
+    const int f_tiles = (features + tile_f - 1) / tile_f;
     const int t_tiles = (tokens + tile_t - 1) / tile_t;
     const int kb = (K + TILE_K - 1) / TILE_K;
     int splits = want_splits;
@@ -472,6 +512,7 @@ extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_split
             if (splits > kb / 4) splits = kb / 4;
         }
     }
+    if (tile_f != 128) splits = 1;                     // the cluster reduction holds one accumulator
     if (splits > 8) splits = 8;
     if (splits > kb) splits = kb;
     if (splits < 1) splits = 1;
@@ -479,6 +520,7 @@ extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_split
     splits = (kb + per - 1) / per;                     // no empty split
     if (splits < 1) splits = 1;
     *tile_t_out = tile_t;
+    *tile_f_out = tile_f;
     *splits_out = splits;
     return 0;
 }
@@ -487,18 +529,18 @@ extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_split
 // or bf16 (ldc).  Pointers 16-byte aligned, ldx and ldw multiples of 8.
 extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W, int tokens, int features,
                             int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
-                            int want_tile, int* status, void* stream) {
+                            int want_tile, int want_tile_f, int* status, void* stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (K <= 0) return KIPP_ERR_ARG;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -3;
     if (epilogue == EPI_ADD && out_dtype != KIPP_DT_F32) return KIPP_ERR_DTYPE;
     if (epilogue == EPI_SWIGLU && (features & 1)) return KIPP_ERR_ARG;
     if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
-    int tile_t, planned;
-    kipp_gemm_tc_plan(tokens, features, K, splits, want_tile, &tile_t, &planned);
+    int tile_t, tile_f, planned;
+    kipp_gemm_tc_plan(tokens, features, K, splits, want_tile, want_tile_f, &tile_t, &tile_f, &planned);
     splits = planned;
     CUtensorMap mw, mx;
-    int rc = make_map(&mw, W, features, K, ldw, TILE_F);
+    int rc = make_map(&mw, W, features, K, ldw, tile_f);
     if (rc) return rc;
     rc = make_map(&mx, X, tokens, K, ldx, tile_t);
     if (rc) return rc;
@@ -508,14 +550,15 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
     const int kb = (K + TILE_K - 1) / TILE_K;
     p.k_blocks_per_split = (kb + splits - 1) / splits;
     p.splits = splits; p.status = status;
-    dim3 grid((tokens + tile_t - 1) / tile_t, (features + TILE_F - 1) / TILE_F, splits);
+    dim3 grid((tokens + tile_t - 1) / tile_t, (features + tile_f - 1) / tile_f, splits);
     if (grid.y > 65535) return KIPP_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
+    if (tile_f == 256) return launch<256, 256>(mw, mx, p, grid, s);
     switch (tile_t) {
-    case 16: return launch<16>(mw, mx, p, grid, s);
-    case 32: return launch<32>(mw, mx, p, grid, s);
-    case 64: return launch<64>(mw, mx, p, grid, s);
-    case 128: return launch<128>(mw, mx, p, grid, s);
-    default: return launch<256>(mw, mx, p, grid, s);
+    case 16: return launch<16, 128>(mw, mx, p, grid, s);
+    case 32: return launch<32, 128>(mw, mx, p, grid, s);
+    case 64: return launch<64, 128>(mw, mx, p, grid, s);
+    case 128: return launch<128, 128>(mw, mx, p, grid, s);
+    default: return launch<256, 128>(mw, mx, p, grid, s);
     }
 }

@@ -21,7 +21,24 @@
 namespace {
 constexpr int MAX_PER_LANE = 8;   // head_dim <= 512 (pairs: 256 per half / 32 lanes)
 
-template <typename T>
+__device__ __forceinline__ void load2(const float* p, float& a, float& b) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x; b = v.y;
+}
+__device__ __forceinline__ void load2(const bf16* p, float& a, float& b) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+    a = __low2float(v); b = __high2float(v);
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+__device__ __forceinline__ void store2(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// V = elements a lane handles side by side (2 when head_dim is a multiple of 4:
+// 4- or 8-byte loads and stores; else 1).
+template <typename T, int V>
 __global__ void qk_norm_rope_write_kernel(
     const T* __restrict__ qkv, int ld_qkv, T* __restrict__ q_out,
     T* __restrict__ k_pages, T* __restrict__ v_pages,
@@ -30,6 +47,8 @@ __global__ void qk_norm_rope_write_kernel(
     const int* __restrict__ positions, const int* __restrict__ entry_of_token,
     const int* __restrict__ block_table, int table_width, int page_size,
     int tokens, int n_q, int n_kv, int head_dim, int write_cache, int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int heads_total = n_q + 2 * n_kv;
@@ -58,21 +77,36 @@ __global__ void qk_norm_rope_write_kernel(
     }
 
     if (!is_q && !is_k) {                     // values: copy
-        for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+        if constexpr (V == 2) {
+            for (int i = 2 * lane; i < head_dim; i += 64) {
+                float a, b;
+                load2(src + i, a, b);
+                store2(dst + i, a, b);
+            }
+        } else {
+            for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+        }
         return;
     }
 
     const int half = head_dim / 2;
-    // Lane owns pairs (i, i + half) for i = lane, lane + 32, ...
-    float lo[MAX_PER_LANE], hi[MAX_PER_LANE];
+    // Lane owns pairs (i, i + half) for i = V * (lane + 32 j) + v.
+    constexpr int STEPS = MAX_PER_LANE / V;
+    float lo[STEPS][V], hi[STEPS][V];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < MAX_PER_LANE; ++j) {
-        const int i = lane + 32 * j;
+    for (int j = 0; j < STEPS; ++j) {
+        const int i = V * (lane + 32 * j);
         if (i < half) {
-            lo[j] = to_f32(src[i]);
-            hi[j] = to_f32(src[i + half]);
-            ss += lo[j] * lo[j] + hi[j] * hi[j];
+            if constexpr (V == 2) {
+                load2(src + i, lo[j][0], lo[j][1]);
+                load2(src + i + half, hi[j][0], hi[j][1]);
+            } else {
+                lo[j][0] = to_f32(src[i]);
+                hi[j][0] = to_f32(src[i + half]);
+            }
+#pragma unroll
+            for (int v = 0; v < V; ++v) ss += lo[j][v] * lo[j][v] + hi[j][v] * hi[j][v];
         }
     }
     const void* nw = is_q ? q_norm_w : k_norm_w;
@@ -80,11 +114,14 @@ __global__ void qk_norm_rope_write_kernel(
         ss = warp_sum(ss);
         const float scale = 1.0f / sqrtf(ss / (float)head_dim + eps);
 #pragma unroll
-        for (int j = 0; j < MAX_PER_LANE; ++j) {
-            const int i = lane + 32 * j;
+        for (int j = 0; j < STEPS; ++j) {
+            const int i = V * (lane + 32 * j);
             if (i < half) {
-                lo[j] = lo[j] * scale * load_w(nw, norm_dtype, i);
-                hi[j] = hi[j] * scale * load_w(nw, norm_dtype, i + half);
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    lo[j][v] = lo[j][v] * scale * load_w(nw, norm_dtype, i + v);
+                    hi[j][v] = hi[j][v] * scale * load_w(nw, norm_dtype, i + v + half);
+                }
             }
         }
     }
@@ -92,24 +129,33 @@ __global__ void qk_norm_rope_write_kernel(
     // With rotary_dim == head_dim a pair is exactly this lane's (lo, hi).
     if (inv_freq != nullptr && rotary_dim == head_dim) {
 #pragma unroll
-        for (int j = 0; j < MAX_PER_LANE; ++j) {
-            const int i = lane + 32 * j;
+        for (int j = 0; j < STEPS; ++j) {
+            const int i = V * (lane + 32 * j);
             if (i < half) {
-                const float angle = (float)pos * inv_freq[i];
-                const float c = cosf(angle), s = sinf(angle);
-                const float a = lo[j], b = hi[j];
-                lo[j] = a * c - b * s;
-                hi[j] = b * c + a * s;
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    const float angle = (float)pos * inv_freq[i + v];
+                    float s, c;
+                    sincosf(angle, &s, &c);
+                    const float a = lo[j][v], b = hi[j][v];
+                    lo[j][v] = a * c - b * s;
+                    hi[j][v] = b * c + a * s;
+                }
             }
         }
     }
     if (inv_freq == nullptr || rotary_dim == head_dim || rotary_dim == 0) {
 #pragma unroll
-        for (int j = 0; j < MAX_PER_LANE; ++j) {
-            const int i = lane + 32 * j;
+        for (int j = 0; j < STEPS; ++j) {
+            const int i = V * (lane + 32 * j);
             if (i < half) {
-                dst[i] = from_f32<T>(lo[j]);
-                dst[i + half] = from_f32<T>(hi[j]);
+                if constexpr (V == 2) {
+                    store2(dst + i, lo[j][0], lo[j][1]);
+                    store2(dst + i + half, hi[j][0], hi[j][1]);
+                } else {
+                    dst[i] = from_f32<T>(lo[j][0]);
+                    dst[i + half] = from_f32<T>(hi[j][0]);
+                }
             }
         }
         return;
@@ -119,11 +165,14 @@ __global__ void qk_norm_rope_write_kernel(
     __shared__ float stage[4][64 * MAX_PER_LANE];
     float* row = stage[threadIdx.x >> 5];
 #pragma unroll
-    for (int j = 0; j < MAX_PER_LANE; ++j) {
-        const int i = lane + 32 * j;
+    for (int j = 0; j < STEPS; ++j) {
+        const int i = V * (lane + 32 * j);
         if (i < half) {
-            row[i] = lo[j];
-            row[i + half] = hi[j];
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                row[i + v] = lo[j][v];
+                row[i + v + half] = hi[j][v];
+            }
         }
     }
     __syncwarp();
@@ -138,6 +187,22 @@ __global__ void qk_norm_rope_write_kernel(
         }
         dst[i] = from_f32<T>(v);
     }
+}
+
+template <typename T>
+int launch_rope(const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v_pages, const void* q_norm_w,
+                const void* k_norm_w, int norm_dtype, float eps, const float* inv_freq, int rotary_dim,
+                const int* positions, const int* entry_of_token, const int* block_table, int table_width,
+                int page_size, int tokens, int n_q, int n_kv, int head_dim, int write_cache, int* status,
+                unsigned blocks, int threads, cudaStream_t s) {
+    // adjacent elements side by side only when pairs of them stay inside one half
+    const bool two = head_dim % 4 == 0 && ld_qkv % 2 == 0 && ((uintptr_t)qkv & 7) == 0 &&
+                     ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0;
+    auto kernel = two ? qk_norm_rope_write_kernel<T, 2> : qk_norm_rope_write_kernel<T, 1>;
+    return kipp_launch(kernel, dim3(blocks), dim3(threads), 0, s, 1, (const T*)qkv, ld_qkv, (T*)q_out, (T*)k_pages,
+                       (T*)v_pages, q_norm_w, k_norm_w, norm_dtype, eps, inv_freq, rotary_dim, positions,
+                       entry_of_token, block_table, table_width, page_size, tokens, n_q, n_kv, head_dim,
+                       write_cache, status);
 }
 }  // namespace
 
@@ -158,16 +223,14 @@ extern "C" int kipp_qk_norm_rope_write(
     const long long blocks = (warps * 32 + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
     if (dtype == KIPP_DT_F32)
-        qk_norm_rope_write_kernel<float><<<(unsigned)blocks, threads, 0, s>>>(
-            (const float*)qkv, ld_qkv, (float*)q_out, (float*)k_pages, (float*)v_pages, q_norm_w,
-            k_norm_w, norm_dtype, eps, inv_freq, rotary_dim, positions, entry_of_token, block_table,
-            table_width, page_size, tokens, n_q, n_kv, head_dim, write_cache, status);
-    else if (dtype == KIPP_DT_BF16)
-        qk_norm_rope_write_kernel<bf16><<<(unsigned)blocks, threads, 0, s>>>(
-            (const bf16*)qkv, ld_qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, q_norm_w,
-            k_norm_w, norm_dtype, eps, inv_freq, rotary_dim, positions, entry_of_token, block_table,
-            table_width, page_size, tokens, n_q, n_kv, head_dim, write_cache, status);
-    else
-        return KIPP_ERR_DTYPE;
-    return kipp_launch_status();
+        return launch_rope<float>(qkv, ld_qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, norm_dtype, eps,
+                                  inv_freq, rotary_dim, positions, entry_of_token, block_table, table_width,
+                                  page_size, tokens, n_q, n_kv, head_dim, write_cache, status, (unsigned)blocks,
+                                  threads, s);
+    if (dtype == KIPP_DT_BF16)
+        return launch_rope<bf16>(qkv, ld_qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, norm_dtype, eps,
+                                 inv_freq, rotary_dim, positions, entry_of_token, block_table, table_width,
+                                 page_size, tokens, n_q, n_kv, head_dim, write_cache, status, (unsigned)blocks,
+                                 threads, s);
+    return KIPP_ERR_DTYPE;
 }

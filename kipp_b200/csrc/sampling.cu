@@ -204,6 +204,8 @@ __device__ void block_argmax(const float* v, int n, Shared& sh, float& best_v, i
 __global__ void __launch_bounds__(THREADS)
 argmax_rows_kernel(const float* __restrict__ logits, long long ld, int n, int* __restrict__ out) {
     __shared__ Shared sh;
+    pdl_launch_dependents();
+    pdl_wait();
     float bv; int bi;
     block_argmax(logits + (size_t)blockIdx.x * ld, n, sh, bv, bi);
     if (threadIdx.x == 0) out[blockIdx.x] = bi;
@@ -215,6 +217,8 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int n,
                    const float* __restrict__ top_p, const float* __restrict__ min_p,
                    const double* __restrict__ uniform, int* __restrict__ out) {
     __shared__ Shared sh;
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* v = logits + (size_t)r * ld;
     float best_v; int best_i;
@@ -310,6 +314,8 @@ __global__ void apply_penalties_kernel(float* __restrict__ logits, long long ld,
                                        const int* __restrict__ bias_tokens,
                                        const float* __restrict__ bias_values, int bias_width,
                                        const int* __restrict__ bias_count) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     float* v = logits + (size_t)r * ld;
     if (bias_tokens != nullptr && threadIdx.x == 0) {
@@ -348,8 +354,7 @@ extern "C" int kipp_argmax_rows(const float* logits, long long ld, int rows, int
                                 void* stream) {
     if (rows <= 0) return 0;
     if (n <= 0) return KIPP_ERR_ARG;
-    argmax_rows_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ld, n, out);
-    return kipp_launch_status();
+    return kipp_launch(argmax_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n, out);
 }
 
 extern "C" int kipp_sample_rows(const float* logits, long long ld, int rows, int n,
@@ -357,9 +362,8 @@ extern "C" int kipp_sample_rows(const float* logits, long long ld, int rows, int
                                 const float* min_p, const double* uniform, int* out, void* stream) {
     if (rows <= 0) return 0;
     if (n <= 0) return KIPP_ERR_ARG;
-    sample_rows_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(logits, ld, n, temperature, top_k,
-                                                                   top_p, min_p, uniform, out);
-    return kipp_launch_status();
+    return kipp_launch(sample_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n,
+                       temperature, top_k, top_p, min_p, uniform, out);
 }
 
 extern "C" int kipp_apply_penalties(float* logits, long long ld, int rows, int n, const int* recent,
@@ -370,8 +374,7 @@ extern "C" int kipp_apply_penalties(float* logits, long long ld, int rows, int n
                                     void* stream) {
     if (rows <= 0) return 0;
     if (n <= 0) return KIPP_ERR_ARG;
-    apply_penalties_kernel<<<rows, 64, 0, (cudaStream_t)stream>>>(
-        logits, ld, n, recent, recent_width, recent_count, repetition, presence, frequency,
-        bias_tokens, bias_values, bias_width, bias_count);
-    return kipp_launch_status();
+    return kipp_launch(apply_penalties_kernel, dim3(rows), dim3(64), 0, (cudaStream_t)stream, 1, logits, ld, n,
+                       recent, recent_width, recent_count, repetition, presence, frequency, bias_tokens,
+                       bias_values, bias_width, bias_count);
 }

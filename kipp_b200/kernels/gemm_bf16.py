@@ -9,14 +9,14 @@ from .ops import EPILOGUES, KernelError, _check, _fn, _ptr, _stream, c_int, c_vo
 
 c_ll = ctypes.c_longlong
 
-def plan(tokens: int, features: int, K: int, splits: int = 0, tile: int = 0):
-    """(token tile, K splits) the tensor-core kernel uses for a shape."""
+def plan(tokens: int, features: int, K: int, splits: int = 0, tile: int = 0, tile_f: int = 0):
+    """(token tile, feature tile, K splits) the tensor-core kernel uses for a shape."""
     f = _fn("gemm_tc", "kipp_gemm_tc_plan",
-            [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int)])
-    tile_out, sp = c_int(), c_int()
-    f(tokens, features, K, splits, tile, ctypes.byref(tile_out), ctypes.byref(sp))
-    tile = tile_out
-    return tile.value, sp.value
+            [c_int, c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int),
+             ctypes.POINTER(c_int)])
+    t, tf, sp = c_int(), c_int(), c_int()
+    f(tokens, features, K, splits, tile, tile_f, ctypes.byref(t), ctypes.byref(tf), ctypes.byref(sp))
+    return t.value, tf.value, sp.value
 
 
 def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -31,7 +31,7 @@ def choose(M, N, K, a, w, out, epilogue) -> str:
     return "tc" if tc_ok(a, w) else "simt"
 
 
-def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 0) -> None:
+def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 0, tile_f: int = 0) -> None:
     if impl != "tc":
         raise KernelError(f"unknown gemm implementation {impl!r}")
     if not tc_ok(a, w):
@@ -41,9 +41,9 @@ def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 
         status = _status(a.device)
     f = _fn("gemm_tc", "kipp_gemm_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int,
-             c_int, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
-             out.stride(0), EPILOGUES[epilogue], splits, tile, _ptr(status), _stream()), "gemm_tc")
+             out.stride(0), EPILOGUES[epilogue], splits, tile, tile_f, _ptr(status), _stream()), "gemm_tc")
 
 
 _status_words: dict = {}

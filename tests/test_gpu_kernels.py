@@ -41,7 +41,7 @@ def test_embed_gather(dtype):
 
 
 @pytest.mark.parametrize("out_dtype", DTYPES)
-@pytest.mark.parametrize("size", [40, 100, 2560, 5000])
+@pytest.mark.parametrize("size", [40, 100, 256, 1028, 2560, 4096, 5000])
 def test_rmsnorm(size, out_dtype):
     g = torch.Generator().manual_seed(size)
     x = (torch.randn(7, size, generator=g) * 3).to(DEV)
