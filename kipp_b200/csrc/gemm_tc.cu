@@ -402,6 +402,185 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------
+// Many tokens (prompt portions): the TOKENS are the M operand (128 per CTA) and
+// the features the N operand (TILE_N per CTA).  A thread of the epilogue then
+// owns one token row and gets consecutive features in consecutive registers,
+// so it writes 16-byte vectors and SwiGLU pairs sit in one thread: an eighth of
+// the instructions of the feature-per-thread epilogue above, which matters
+// because the epilogue is not hidden behind the next tile's MMAs.
+template <int TILE_N> struct CfgTok {
+    static constexpr int X_BYTES = UMMA_M * TILE_K * 2;          // 128 tokens
+    static constexpr int W_BYTES = TILE_N * TILE_K * 2;
+    static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
+    // 256 features: one CTA per SM with a deep ring; narrower: two CTAs per SM
+    static constexpr int STAGES = TILE_N > 160 ? (192 * 1024) / STAGE_BYTES : (100 * 1024) / STAGE_BYTES;
+    static constexpr int TMEM_COLS = TILE_N <= 32 ? 32 : TILE_N <= 64 ? 64 : TILE_N <= 128 ? 128 : 256;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+// 16 consecutive features [f, f + 16) of token t held by one thread.
+__device__ __forceinline__ void epilogue_row16(const Params& p, const float* v, int t, int f) {
+    if (t >= p.tokens || f >= p.features) return;
+    const bool full = f + 16 <= p.features;
+    if (p.epilogue == EPI_ADD) {
+        float* c = reinterpret_cast<float*>(p.C) + (size_t)t * p.ldc + f;
+        if (full && ((uintptr_t)c & 15) == 0) {
+            float4 old[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) old[i] = reinterpret_cast<float4*>(c)[i];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<float4*>(c)[i] = make_float4(old[i].x + v[4 * i], old[i].y + v[4 * i + 1],
+                                                              old[i].z + v[4 * i + 2], old[i].w + v[4 * i + 3]);
+        } else {
+            for (int i = 0; i < 16 && f + i < p.features; ++i) c[i] += v[i];
+        }
+    } else if (p.epilogue == EPI_SWIGLU) {
+        float r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) r[i] = __fdividef(v[2 * i], 1.0f + __expf(-v[2 * i])) * v[2 * i + 1];
+        const size_t at = (size_t)t * p.ldc + (f >> 1);
+        if (p.out_dtype == KIPP_DT_F32) {
+            float* c = reinterpret_cast<float*>(p.C) + at;
+            for (int i = 0; i < 8 && f + 2 * i + 1 < p.features; ++i) c[i] = r[i];
+        } else {
+            bf16* c = reinterpret_cast<bf16*>(p.C) + at;
+            if (full && ((uintptr_t)c & 15) == 0) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(r[0], r[1]), h1 = __floats2bfloat162_rn(r[2], r[3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(r[4], r[5]), h3 = __floats2bfloat162_rn(r[6], r[7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(c) = pk;
+            } else {
+                for (int i = 0; i < 8 && f + 2 * i + 1 < p.features; ++i) c[i] = __float2bfloat16_rn(r[i]);
+            }
+        }
+    } else if (p.out_dtype == KIPP_DT_F32) {
+        float* c = reinterpret_cast<float*>(p.C) + (size_t)t * p.ldc + f;
+        if (full && ((uintptr_t)c & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<float4*>(c)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+            for (int i = 0; i < 16 && f + i < p.features; ++i) c[i] = v[i];
+        }
+    } else {
+        bf16* c = reinterpret_cast<bf16*>(p.C) + (size_t)t * p.ldc + f;
+        if (full && ((uintptr_t)c & 15) == 0) {
+            uint4 pk[2];
+            uint32_t* w = reinterpret_cast<uint32_t*>(pk);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            reinterpret_cast<uint4*>(c)[0] = pk[0];
+            reinterpret_cast<uint4*>(c)[1] = pk[1];
+        } else {
+            for (int i = 0; i < 16 && f + i < p.features; ++i) c[i] = __float2bfloat16_rn(v[i]);
+        }
+    }
+}
+
+template <int TILE_N>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const Params p) {
+    using C = CfgTok<TILE_N>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_ready = empty + C::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * UMMA_M;            // token tiles fastest: neighbours share a weight tile
+    const int f0 = blockIdx.y * TILE_N;
+    const int n_kb = (p.K + TILE_K - 1) / TILE_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int ahead = min(n_kb, C::STAGES);
+            for (int i = 0; i < ahead; ++i) {          // weights first: they depend on no earlier kernel
+                mbar_expect_tx(&full[i], C::STAGE_BYTES);
+                tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + C::X_BYTES, &map_w, &full[i], i * TILE_K, f0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES, &map_x, &full[i], i * TILE_K, t0);
+            for (int i = ahead; i < n_kb; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+                uint8_t* xt = tiles + (size_t)s * C::STAGE_BYTES;
+                mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                tma_load_2d(xt, &map_x, &full[s], i * TILE_K, t0);
+                tma_load_2d(xt + C::X_BYTES, &map_w, &full[s], i * TILE_K, f0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(UMMA_M, TILE_N);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % C::STAGES;
+                const uint32_t ph = (i / C::STAGES) & 1;
+                if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t xa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+                const uint64_t xd = umma_smem_desc(xa), wd = umma_smem_desc(xa + C::X_BYTES);
+#pragma unroll
+                for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                    umma_bf16(tmem_base, xd + 2 * k, wd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(acc_ready);
+        }
+    } else {
+        const int q = warp & 3;                    // tensor-memory lane quarter = 32 tokens
+        const int cg = (warp - 2) >> 2;            // half of the feature columns
+        const int t = t0 + q * 32 + lane;
+        pdl_wait();
+        const bool ok = n_kb > 0 ? mbar_wait(acc_ready, 0, abort_flag) : true;
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+        constexpr int HALF = (TILE_N / 2 + 15) / 16 * 16;
+        if (ok) {
+#pragma unroll 1
+            for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
+                float v[16];
+                if (n_kb > 0) tmem_ld16(taddr + c, v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                }
+                epilogue_row16(p, v, t, f0 + c);
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
 // ------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -472,6 +651,19 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
     return kipp_launch(gemm_tc_kernel<TILE_T, TILE_F>, grid, dim3(THREADS), C::SMEM, s, p.splits, mw, mx, p);
 }
 
+template <int TILE_N>
+int launch_tokm(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
+    using C = CfgTok<TILE_N>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_tokm_kernel<TILE_N>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return kipp_launch(gemm_tc_tokm_kernel<TILE_N>, grid, dim3(THREADS), C::SMEM, s, 1, mw, mx, p);
+}
+
 // Tile choice, from measurements on B200: 128 features with a token tile of 16,
 // 32 or 64 (two CTAs per SM, one's epilogue under the other's MMAs), 256 tokens
 // from 1,024 tokens on.  256 features x 256 tokens per CTA (two accumulators,
@@ -536,6 +728,30 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
     if (epilogue == EPI_ADD && out_dtype != KIPP_DT_F32) return KIPP_ERR_DTYPE;
     if (epilogue == EPI_SWIGLU && (features & 1)) return KIPP_ERR_ARG;
     if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
+    // Prompt-sized batches: tokens as the M operand (want_tile_f < 0 forces it with
+    // the feature tile -want_tile_f).  Not for the float32 residual epilogue:
+    // there a thread per feature writes whole 128-byte lines per warp, a thread
+    // per token only 16 bytes of each line (measured 129 against 200 us at
+    // 2048 x 2560 x 9728).
+    if ((want_tile == 0 && want_tile_f == 0 && tokens >= 512 && epilogue != EPI_ADD) || want_tile_f < 0) {
+        int tile_n = want_tile_f < 0 ? -want_tile_f : 256;
+        if (tile_n != 128 && tile_n != 160 && tile_n != 256) return KIPP_ERR_ARG;
+        CUtensorMap mw, mx;
+        int rc = make_map(&mw, W, features, K, ldw, tile_n);
+        if (rc) return rc;
+        rc = make_map(&mx, X, tokens, K, ldx, UMMA_M);
+        if (rc) return rc;
+        Params p;
+        p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
+        p.tokens = tokens; p.features = features; p.K = K; p.ldc = ldc;
+        p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
+        dim3 grid((tokens + UMMA_M - 1) / UMMA_M, (features + tile_n - 1) / tile_n, 1);
+        if (grid.y > 65535) return KIPP_ERR_ARG;
+        cudaStream_t s = (cudaStream_t)stream;
+        if (tile_n == 128) return launch_tokm<128>(mw, mx, p, grid, s);
+        if (tile_n == 160) return launch_tokm<160>(mw, mx, p, grid, s);
+        return launch_tokm<256>(mw, mx, p, grid, s);
+    }
     int tile_t, tile_f, planned;
     kipp_gemm_tc_plan(tokens, features, K, splits, want_tile, want_tile_f, &tile_t, &tile_f, &planned);
     splits = planned;

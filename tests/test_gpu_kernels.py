@@ -111,6 +111,38 @@ def test_gemm_tensor_core(shape, epilogue):
     assert gemm_bf16.status_word(torch.device(DEV)).tolist() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("epilogue", ["store", "add", "swiglu"])
+@pytest.mark.parametrize("shape", [(600, 640, 520), (512, 1000, 136), (130, 250, 192), (1100, 2560, 320)])
+def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
+    """The orientation used for prompt-sized batches (tokens = MMA rows, a
+    thread of the epilogue owns a token and writes vectors), with feature tiles
+    of 128, 160 and 256 and ragged edges; integer data exactly."""
+    from kipp_b200.kernels import gemm_bf16
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + 3 * N)
+    for integer in (True, False):
+        for tile_f in (0, -128, -160, -256):
+            if tile_f == 0 and M < 512:
+                continue
+            if integer:
+                a = torch.randint(-3, 4, (M, K), generator=g).to(torch.bfloat16).to(DEV)
+                w = torch.randint(-2, 3, (N, K), generator=g).to(torch.bfloat16).to(DEV)
+            else:
+                a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+                w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
+            odt = torch.float32 if (epilogue == "add" or integer) else torch.bfloat16
+            out = torch.randn(M, N // 2 if epilogue == "swiglu" else N, generator=g).to(odt).to(DEV)
+            ref = gemm_ref(a, w, epilogue, out)
+            gemm_bf16.run("tc", out, a, w, epilogue, M, tile_f=tile_f)
+            got = out.double().cpu()
+            if integer and epilogue != "swiglu":
+                assert torch.equal(got, ref.float().double()), (shape, tile_f)
+            else:
+                scale = float(ref.abs().max())
+                assert float((got - ref).abs().max()) <= (1e-5 if odt == torch.float32 else 1e-2) * scale
+    assert gemm_bf16.status_word(torch.device(DEV)).tolist() == [0, 0, 0, 0]
+
+
 def test_gemm_refuses_what_it_cannot_take():
     from kipp_b200.kernels import KernelError, gemm_bf16
     a = torch.zeros(4, 20, dtype=torch.bfloat16, device=DEV)          # K = 20: row pitch not 16-byte
