@@ -42,6 +42,27 @@ class _RequestCache:
     # per group: first logical page that may still be mapped (pages before it
     # were given back by the window)
     first_live: list = dataclasses.field(default_factory=list)
+    # per group: int32 mirror of ``tables`` (grown by doubling) so that block
+    # tables of a step are copied, not converted from lists
+    mirrors: list = dataclasses.field(default_factory=list)
+
+    def set_page(self, group: int, logical: int, page: int) -> None:
+        table = self.tables[group]
+        while len(table) <= logical:
+            table.append(UNMAPPED)
+        table[logical] = page
+        mirror = self.mirrors[group]
+        if logical >= mirror.shape[0]:
+            grown = np.full(max(2 * mirror.shape[0], logical + 1, 16), UNMAPPED, dtype=np.int32)
+            grown[:mirror.shape[0]] = mirror
+            self.mirrors[group] = mirror = grown
+        mirror[logical] = page
+
+    def trim(self, group: int) -> None:
+        """Drop trailing unmapped entries (after a roll-back)."""
+        table = self.tables[group]
+        while table and table[-1] == UNMAPPED:
+            table.pop()
 
 
 class CacheGroup:
@@ -117,7 +138,9 @@ class CacheManager:
             raise ValueError(f"request {rid!r} is already live")
         slot = self.slots.alloc(rid)
         self._requests[rid] = _RequestCache(slot=slot, tables=[[] for _ in self.groups],
-                                            first_live=[0 for _ in self.groups])
+                                            first_live=[0 for _ in self.groups],
+                                            mirrors=[np.full(16, UNMAPPED, dtype=np.int32)
+                                                     for _ in self.groups])
         return slot
 
     def slot(self, rid) -> int:
@@ -159,25 +182,22 @@ class CacheManager:
                 for gi, g in enumerate(self.groups):
                     table = rc.tables[gi]
                     for lp in g.pages_for(rc.length, new_length):
-                        while len(table) <= lp:
-                            table.append(UNMAPPED)
-                        if table[lp] == UNMAPPED:
+                        if lp >= len(table) or table[lp] == UNMAPPED:
                             if lp < rc.first_live[gi]:
                                 raise RuntimeError("a page behind the window was asked for")
                             page = g.pool.alloc(rid)
-                            table[lp] = page
+                            rc.set_page(gi, lp, page)
                             taken.append((gi, rid, lp, page))
         except OutOfPages:
             for gi, rid, lp, page in reversed(taken):
                 self.groups[gi].pool.free(page, rid)
-                self._requests[rid].tables[gi][lp] = UNMAPPED
+                self._requests[rid].set_page(gi, lp, UNMAPPED)
             for rid, _ in wants:
                 rc = self._requests.get(rid)
                 if rc is None:
                     continue
-                for table in rc.tables:            # drop trailing holes the call made
-                    while table and table[-1] == UNMAPPED:
-                        table.pop()
+                for gi in range(len(self.groups)):  # drop trailing holes the call made
+                    rc.trim(gi)
             raise
 
     def advance(self, rid, new_length: int) -> None:
@@ -195,7 +215,7 @@ class CacheManager:
             for lp in range(rc.first_live[gi], min(keep_from, len(table))):
                 if table[lp] != UNMAPPED:
                     g.pool.free(table[lp], rid)
-                    table[lp] = UNMAPPED
+                    rc.set_page(gi, lp, UNMAPPED)
             rc.first_live[gi] = max(rc.first_live[gi], min(keep_from, len(table)))
 
     # -- views ----------------------------------------------------------------------
@@ -204,13 +224,14 @@ class CacheManager:
 
     def block_table_rows(self, rids: list, group: int, width: Optional[int] = None) -> np.ndarray:
         """int32 [len(rids), width] of physical pages, UNMAPPED where none."""
-        tables = [self._requests[r].tables[group] for r in rids]
+        reqs = [self._requests[r] for r in rids]
+        lens = [len(rc.tables[group]) for rc in reqs]
         if width is None:
-            width = max([len(t) for t in tables] + [1])
+            width = max(lens + [1])
         out = np.full((len(rids), width), UNMAPPED, dtype=np.int32)
-        for i, t in enumerate(tables):
-            if t:
-                out[i, :len(t)] = t
+        for i, (rc, n) in enumerate(zip(reqs, lens)):
+            if n:
+                out[i, :n] = rc.mirrors[group][:n]
         return out
 
     def pages_held(self, rid) -> list[int]:
@@ -233,6 +254,10 @@ class CacheManager:
                     seen[page] = rid
                     if g.pool.owner(page) != rid:
                         raise AssertionError(f"page {page} of group {gi}: table and pool disagree")
+            for rid, rc in self._requests.items():
+                n = len(rc.tables[gi])
+                if rc.mirrors[gi][:n].tolist() != rc.tables[gi]:
+                    raise AssertionError(f"group {gi}: the int32 mirror of {rid!r}'s table is stale")
             if len(seen) != g.pool.used_pages:
                 raise AssertionError(f"group {gi}: {g.pool.used_pages - len(seen)} pages are lost")
         self.slots.check()

@@ -186,12 +186,12 @@ class Engine:
             raise
         rids = [e.request for e in entries]
         slots = [self.cache.slot(r) for r in rids]
-        tables = [self.cache.block_table_rows(rids, gi) for gi in range(len(self.cache.groups))]
         rt = self.runtime
         with torch.cuda.device(rt.device):
             if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
                 logits = self._graph_step(entries, starts, slots, rids)
             else:
+                tables = [self.cache.block_table_rows(rids, gi) for gi in range(len(self.cache.groups))]
                 meta = pack_step(entries, starts, slots, tables, rt.device, self._staging)
                 self.last_h2d_bytes = meta.extra["h2d_bytes"]
                 logits = self._forward(StepContext(self, meta))
