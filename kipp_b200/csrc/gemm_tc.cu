@@ -356,22 +356,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // all threads of all CTAs of the cluster: partial sums are visible afterwards
         asm volatile("barrier.cluster.arrive.release.aligned;\n"
                      "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-        if (warp >= 2 && warp < 6 && !*abort_flag) {
+        if (warp >= 2 && !*abort_flag) {
             const int q = warp & 3;
+            const int cg = (warp - 2) >> 2;                             // two warp groups share the tokens
             const int f = f0 + q * 32 + lane;
             const int per = (TILE_T + p.splits - 1) / p.splits;       // tokens this CTA finishes
             const int j0 = split * per, j1 = min(TILE_T, j0 + per);
             const uint32_t local = smem_u32(reinterpret_cast<float*>(tiles) + q * 32 + lane);
-            for (int j = j0; j < j1; ++j) {
-                float v = 0.f;
-                for (int s = 0; s < p.splits; ++s) {                    // fixed order
-                    uint32_t remote;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
-                                 : "r"(local + (uint32_t)(j * UMMA_M * 4)), "r"(s));
-                    float part;
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part) : "r"(remote) : "memory");
-                    v += part;
+            // this CTA's view of every split's partial tile (at most 8 splits)
+            uint32_t remote[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[s]) : "r"(local),
+                             "r"(s < p.splits ? s : 0));
+            for (int j = j0 + cg; j < j1; j += 2) {
+                // all loads of a token first (they overlap), then the sum in split order
+                float part[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    part[s] = 0.f;
+                    if (s < p.splits)
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[s])
+                                     : "r"(remote[s] + (uint32_t)(j * UMMA_M * 4)) : "memory");
                 }
+                float v = 0.f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) v += part[s];              // absent splits add zero
                 const int t = t0 + j;
                 // one value per thread: the epilogue of a 16-token chunk with one live token
                 if (p.epilogue == EPI_SWIGLU) {
@@ -695,12 +705,14 @@ extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_split
     const int kb = (K + TILE_K - 1) / TILE_K;
     int splits = want_splits;
     if (splits <= 0) {
-        // aim at two CTAs per SM when the tiles alone do not fill the GPU; every
-        // split keeps at least 4 K blocks
+        // Few tiles: split K so that tiles x splits comes close to, but stays
+        // under, what is resident at once with clusters (measured: 48 tiles run
+        // fastest with 5 splits = 240 CTAs, slower with 6 = 288; 20 tiles with 8).
+        // Every split keeps at least 4 K blocks.
         const int tiles = f_tiles * t_tiles;
         splits = 1;
-        if (tiles < 148) {
-            splits = (296 + tiles - 1) / tiles;
+        if (tiles <= 128) {
+            splits = 256 / tiles;
             if (splits > kb / 4) splits = kb / 4;
         }
     }
