@@ -301,6 +301,7 @@ struct DecodeParams {
     const int* rows;            // [n] entries that are single decoded tokens
     float* part_o;              // [n][n_q][max_splits][D]
     float* part_ml;             // [n][n_q][max_splits][2]  (max in log2 units, sum)
+    bf16* out;                  // [tokens][n_q][D]: written here when a token has one split
     const int* split_keys;      // device: keys per split of this step (a multiple of 64)
     int table_width, page_size, n_q, n_kv, window, max_splits;
     float scale_log2;
@@ -466,6 +467,11 @@ attn_decode_kernel(const DecodeParams p) {
             l += w_l[w * 16 + row] * c;
             acc += w_o[((size_t)w * 16 + row) * D + d] * c;
         }
+        if (n_splits == 1) {
+            // nothing to merge: this is the token's result
+            p.out[((size_t)tok * p.n_q + g * group + row) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+            continue;
+        }
         my_o[row * head_stride_o + d] = acc;
         if (d == 0) {
             my_ml[row * head_stride_ml] = m;
@@ -487,6 +493,7 @@ __global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __
     const int kv_len = context_len[entry] + 1;
     const int split_keys = decode_split_keys(kv_len, max_splits, __ldg(split_keys_ptr));
     const int n_splits = (kv_len + split_keys - 1) / split_keys;
+    if (n_splits == 1) return;                     // the split kernel wrote the result itself
     const float* ml = part_ml + ((size_t)n * n_q + h) * max_splits * 2;
     const float* po = part_o + ((size_t)n * n_q + h) * max_splits * head_dim;
     float m = -INFINITY;
@@ -579,6 +586,7 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
     p.q_start = q_start; p.context_len = context_len; p.block_table = block_table; p.rows = rows;
     p.part_o = scratch;
+    p.out = (bf16*)out;
     p.part_ml = scratch + (size_t)n * n_q * max_splits * head_dim;
     p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
     p.max_splits = max_splits; p.split_keys = split_keys;

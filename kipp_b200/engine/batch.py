@@ -15,19 +15,29 @@ import torch
 
 
 ATTENTION_TILE = 64       # tokens per work item of the prefill attention kernel
-DECODE_TARGET_CTAS = 592  # decode attention aims at about two waves of CTAs on 148 SMs
+DECODE_RESIDENT_CTAS = 444  # decode-attention CTAs resident at once: 3 per SM on 148 SMs
 DECODE_MAX_SPLITS = 32
 DECODE_MIN_SPLIT = 256
 
 
 def decode_split_length(kv_lens: list, kv_heads_hint: int = 8) -> int:
-    """Keys per split for the decoded tokens of a step: few, long splits when
-    many (token, kv head) pairs already fill the GPU, many short ones when few."""
+    """Keys per split for the decoded tokens of a step.  The number of splits is
+    the one whose CTAs (tokens x kv heads x splits) fill whole waves of resident
+    CTAs best, with a small price per split for its fixed cost and the merge."""
     if not kv_lens:
         return DECODE_MIN_SPLIT
     pairs = len(kv_lens) * kv_heads_hint
-    splits = min(DECODE_MAX_SPLITS, max(1, DECODE_TARGET_CTAS // pairs))
-    keys = -(-max(kv_lens) // splits)
+    longest = max(kv_lens)
+    best, best_score = 1, -1.0
+    for splits in range(1, DECODE_MAX_SPLITS + 1):
+        if splits > 1 and longest // splits < DECODE_MIN_SPLIT:
+            break
+        ctas = pairs * splits
+        waves = -(-ctas // DECODE_RESIDENT_CTAS)
+        score = ctas / (waves * DECODE_RESIDENT_CTAS) - 0.015 * splits
+        if score > best_score + 1e-9:
+            best, best_score = splits, score
+    keys = -(-longest // best)
     return max(DECODE_MIN_SPLIT, -(-keys // 64) * 64)
 
 
