@@ -496,22 +496,38 @@ __global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __
     if (n_splits == 1) return;                     // the split kernel wrote the result itself
     const float* ml = part_ml + ((size_t)n * n_q + h) * max_splits * 2;
     const float* po = part_o + ((size_t)n * n_q + h) * max_splits * head_dim;
-    float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ml[2 * s]);
-    float l = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float ms = ml[2 * s];
-        l += (ms == -INFINITY) ? 0.f : ml[2 * s + 1] * exp2f(ms - m);
+    // weights of the splits first (all loads at once), then the weighted sum
+    __shared__ float weight[64];                   // max_splits <= 64 checked by the launcher
+    __shared__ float inv_sum;
+    if (threadIdx.x < 32) {
+        float m[2], l[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int s = threadIdx.x + 32 * i;
+            m[i] = s < n_splits ? ml[2 * s] : -INFINITY;
+            l[i] = s < n_splits ? ml[2 * s + 1] : 0.f;
+        }
+        const float mx = warp_max(fmaxf(m[0], m[1]));
+        float total = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int s = threadIdx.x + 32 * i;
+            const float w = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - mx);
+            if (s < 64) weight[s] = w;
+            total += l[i] * w;
+        }
+        // sum in split order would need a serial loop; lanes hold splits s and s + 32,
+        // a fixed tree over lanes keeps the order the same for every token
+        total = warp_sum(total);
+        if (threadIdx.x == 0) inv_sum = total > 0.f ? 1.f / total : 0.f;
     }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    __syncthreads();
     bf16* dst = out + ((size_t)q_start[entry] * n_q + h) * head_dim;
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = ml[2 * s];
-            if (ms != -INFINITY) acc += po[(size_t)s * head_dim + d] * exp2f(ms - m);
-        }
-        dst[d] = __float2bfloat16_rn(acc * inv);
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) acc += po[(size_t)s * head_dim + d] * weight[s];
+        dst[d] = __float2bfloat16_rn(acc * inv_sum);
     }
 }
 
@@ -580,7 +596,7 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
                                     const int* split_keys, float* scratch, void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
-        max_splits > 65535 || split_keys == nullptr || scratch == nullptr)
+        max_splits > 64 || split_keys == nullptr || scratch == nullptr)
         return KIPP_ERR_ARG;
     DecodeParams p;
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;

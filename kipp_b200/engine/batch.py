@@ -17,7 +17,7 @@ import torch
 ATTENTION_TILE = 64       # tokens per work item of the prefill attention kernel
 DECODE_RESIDENT_CTAS = 444  # decode-attention CTAs resident at once: 3 per SM on 148 SMs
 DECODE_MAX_SPLITS = 32
-DECODE_MIN_SPLIT = 256
+DECODE_MIN_SPLIT = 128
 
 
 def decode_split_length(kv_lens: list, kv_heads_hint: int = 8) -> int:

@@ -204,17 +204,21 @@ class Engine:
 
     def _graph_step(self, entries, starts, slots, rids) -> torch.Tensor:
         from .graphs import DecodeGraph
+        # table width: what the longest entry needs, rounded up to 64 pages so that a
+        # captured graph serves many steps and little is copied for short contexts
         limit = self.spec.max_positions
         widths = []
-        for g in self.cache.groups:
-            pages = g.pool.n_pages if limit is None else min(g.pool.n_pages, -(-limit // g.page_size))
-            widths.append(max(pages, 1))
+        for gi, g in enumerate(self.cache.groups):
+            cap = g.pool.n_pages if limit is None else min(g.pool.n_pages, -(-limit // g.page_size))
+            need = max(len(self.cache.table(r, gi)) for r in rids)
+            widths.append(max(1, min(max(cap, need), -(-(need + 1) // 64) * 64)))
         tables = [self.cache.block_table_rows(rids, gi, width=w) for gi, w in enumerate(widths)]
-        graph = self._graphs.get(len(entries))
+        key = (len(entries), tuple(widths))
+        graph = self._graphs.get(key)
         if graph is None:
-            if len(self._graphs) >= 16:
+            if len(self._graphs) >= 24:
                 self._graphs.pop(next(iter(self._graphs)))
-            graph = self._graphs[len(entries)] = DecodeGraph(self, len(entries), widths)
+            graph = self._graphs[key] = DecodeGraph(self, len(entries), widths)
         logits = graph.run(entries, starts, slots, tables)
         self.last_h2d_bytes = graph.static.n_ints * 4
         self.graph_replays += 1
