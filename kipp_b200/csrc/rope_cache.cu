@@ -9,6 +9,11 @@
 // (i, i + rot/2), angle = position * theta^(-2i/rot)), and the cache row
 // src/kipp.c:2806-2811 (keys stored after norm and rotation).
 //
+// The cosines and sines do not depend on the head or the layer: rope_table_kernel
+// makes them once per step, [token][pair] -> (cos, sin), and every layer's
+// launch reads them (full-range cosf/sinf for 40 heads x 36 layers per token
+// were most of this kernel's instructions).
+//
 // One warp handles one (token, head).  Heads [0, Nq) are queries, [Nq, Nq+Nkv)
 // keys, the rest values.  All arithmetic is float32; cosf/sinf are the full
 // range-reduced versions.
@@ -43,7 +48,7 @@ __global__ void qk_norm_rope_write_kernel(
     const T* __restrict__ qkv, int ld_qkv, T* __restrict__ q_out,
     T* __restrict__ k_pages, T* __restrict__ v_pages,
     const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_dtype, float eps,
-    const float* __restrict__ inv_freq, int rotary_dim,
+    const float2* __restrict__ cos_sin, int rotary_dim,
     const int* __restrict__ positions, const int* __restrict__ entry_of_token,
     const int* __restrict__ block_table, int table_width, int page_size,
     int tokens, int n_q, int n_kv, int head_dim, int write_cache, int* __restrict__ status) {
@@ -127,16 +132,16 @@ __global__ void qk_norm_rope_write_kernel(
     }
     // Rotation of the first rotary_dim dims, pairs (i, i + rotary_dim/2).
     // With rotary_dim == head_dim a pair is exactly this lane's (lo, hi).
-    if (inv_freq != nullptr && rotary_dim == head_dim) {
+    if (cos_sin != nullptr && rotary_dim == head_dim) {
+        const float2* cs_row = cos_sin + (size_t)t * half;
 #pragma unroll
         for (int j = 0; j < STEPS; ++j) {
             const int i = V * (lane + 32 * j);
             if (i < half) {
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
-                    const float angle = (float)pos * inv_freq[i + v];
-                    float s, c;
-                    sincosf(angle, &s, &c);
+                    const float2 cs = cs_row[i + v];
+                    const float c = cs.x, s = cs.y;
                     const float a = lo[j][v], b = hi[j][v];
                     lo[j][v] = a * c - b * s;
                     hi[j][v] = b * c + a * s;
@@ -144,7 +149,7 @@ __global__ void qk_norm_rope_write_kernel(
             }
         }
     }
-    if (inv_freq == nullptr || rotary_dim == head_dim || rotary_dim == 0) {
+    if (cos_sin == nullptr || rotary_dim == head_dim || rotary_dim == 0) {
 #pragma unroll
         for (int j = 0; j < STEPS; ++j) {
             const int i = V * (lane + 32 * j);
@@ -181,8 +186,8 @@ __global__ void qk_norm_rope_write_kernel(
         float v = row[i];
         if (i < rotary_dim) {
             const int p = i < rh ? i : i - rh;
-            const float angle = (float)pos * inv_freq[p];
-            const float c = cosf(angle), s = sinf(angle);
+            const float2 cs = cos_sin[(size_t)t * rh + p];
+            const float c = cs.x, s = cs.y;
             v = i < rh ? row[i] * c - row[i + rh] * s : row[i] * c + row[i - rh] * s;
         }
         dst[i] = from_f32<T>(v);
@@ -191,7 +196,7 @@ __global__ void qk_norm_rope_write_kernel(
 
 template <typename T>
 int launch_rope(const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v_pages, const void* q_norm_w,
-                const void* k_norm_w, int norm_dtype, float eps, const float* inv_freq, int rotary_dim,
+                const void* k_norm_w, int norm_dtype, float eps, const float2* cos_sin, int rotary_dim,
                 const int* positions, const int* entry_of_token, const int* block_table, int table_width,
                 int page_size, int tokens, int n_q, int n_kv, int head_dim, int write_cache, int* status,
                 unsigned blocks, int threads, cudaStream_t s) {
@@ -200,16 +205,40 @@ int launch_rope(const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v
                      ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0;
     auto kernel = two ? qk_norm_rope_write_kernel<T, 2> : qk_norm_rope_write_kernel<T, 1>;
     return kipp_launch(kernel, dim3(blocks), dim3(threads), 0, s, 1, (const T*)qkv, ld_qkv, (T*)q_out, (T*)k_pages,
-                       (T*)v_pages, q_norm_w, k_norm_w, norm_dtype, eps, inv_freq, rotary_dim, positions,
+                       (T*)v_pages, q_norm_w, k_norm_w, norm_dtype, eps, cos_sin, rotary_dim, positions,
                        entry_of_token, block_table, table_width, page_size, tokens, n_q, n_kv, head_dim,
                        write_cache, status);
 }
+// (cos, sin) of position * inv_freq[i] for every token of the step and every
+// rotated pair: float32 angle as the reference forms it ((float)position *
+// frequency, src/kipp.c:2374), full-range cosf/sinf.
+__global__ void rope_table_kernel(float2* __restrict__ out, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int tokens, int half) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= tokens * half) return;
+    const int t = i / half, k = i - t * half;
+    const float angle = (float)positions[t] * inv_freq[k];
+    float s, c;
+    sincosf(angle, &s, &c);
+    out[i] = make_float2(c, s);
+}
 }  // namespace
+
+extern "C" int kipp_rope_table(void* out, const int* positions, const float* inv_freq, int tokens, int half,
+                               void* stream) {
+    if (tokens <= 0 || half <= 0) return 0;
+    const long long n = (long long)tokens * half;
+    if (n > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return kipp_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       (float2*)out, positions, inv_freq, tokens, half);
+}
 
 extern "C" int kipp_qk_norm_rope_write(
     const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v_pages, int dtype,
     const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
-    const float* inv_freq, int rotary_dim, const int* positions, const int* entry_of_token,
+    const void* cos_sin, int rotary_dim, const int* positions, const int* entry_of_token,
     const int* block_table, int table_width, int page_size, int tokens, int n_q, int n_kv,
     int head_dim, int write_cache, int* status, void* stream) {
     if (tokens <= 0) return 0;
@@ -224,12 +253,12 @@ extern "C" int kipp_qk_norm_rope_write(
     if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
     if (dtype == KIPP_DT_F32)
         return launch_rope<float>(qkv, ld_qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, norm_dtype, eps,
-                                  inv_freq, rotary_dim, positions, entry_of_token, block_table, table_width,
+                                  (const float2*)cos_sin, rotary_dim, positions, entry_of_token, block_table, table_width,
                                   page_size, tokens, n_q, n_kv, head_dim, write_cache, status, (unsigned)blocks,
                                   threads, s);
     if (dtype == KIPP_DT_BF16)
         return launch_rope<bf16>(qkv, ld_qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, norm_dtype, eps,
-                                 inv_freq, rotary_dim, positions, entry_of_token, block_table, table_width,
+                                 (const float2*)cos_sin, rotary_dim, positions, entry_of_token, block_table, table_width,
                                  page_size, tokens, n_q, n_kv, head_dim, write_cache, status, (unsigned)blocks,
                                  threads, s);
     return KIPP_ERR_DTYPE;

@@ -44,6 +44,7 @@ class StepContext:
         self.ops = rt.ops
         self.workspace = rt.workspace
         self.status = rt.status
+        self.step_cache: dict = {}       # what parts share within ONE forward pass (e.g. rotary tables)
 
     def cache_view(self, run: LayerRun) -> CacheView:
         gi, j = self.engine.cache.group_of_cache[run.cache]

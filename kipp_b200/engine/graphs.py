@@ -39,12 +39,12 @@ class DecodeGraph:
         if self.graph is not None and self.generation != self._generation():
             self.graph = None                       # a buffer moved since the capture
         if self.graph is None:
-            ctx = StepContext(engine, meta)
-            engine._forward(ctx)                    # eager once: buffers, attributes, tensor maps
+            engine._forward(StepContext(engine, meta))      # eager once: buffers, attributes, tensor maps
             torch.cuda.synchronize(engine.runtime.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                self.logits = engine._forward(ctx)
+                # a fresh context: what a forward pass computes once per step must be in the graph
+                self.logits = engine._forward(StepContext(engine, meta))
             self.graph = graph
             self.generation = self._generation()
             self.launches = engine.last_forward_launches

@@ -6,7 +6,7 @@ tensor that is not on a CUDA device, a size a kernel refuses, or a library
 that cannot be built raises.
 """
 from .ops import (KernelError, argmax_rows, attention, embed_gather, gemm, qk_norm_rope_write,
-                  rmsnorm, sample_rows, dtype_code)
+                  rmsnorm, rope_table, sample_rows, dtype_code)
 
 __all__ = ["KernelError", "argmax_rows", "attention", "embed_gather", "gemm",
-           "qk_norm_rope_write", "rmsnorm", "sample_rows", "dtype_code"]
+           "qk_norm_rope_write", "rmsnorm", "rope_table", "sample_rows", "dtype_code"]

@@ -155,15 +155,32 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: str = "s
         gemm_bf16.run(impl, out, a, w, epilogue, M)
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, tokens: int,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [tokens, len(inv_freq), 2]: (cos, sin) of position * inv_freq, made
+    once per step and read by every layer's rotation."""
+    _int32(positions, "positions")
+    if inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous():
+        raise KernelError("rope_table: inv_freq must be contiguous float32")
+    half = inv_freq.numel()
+    if out is None:
+        out = torch.empty((tokens, half, 2), dtype=torch.float32, device=positions.device)
+    f = _fn("rope_cache", "kipp_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(positions), _ptr(inv_freq), tokens, half, _stream()), "rope_table")
+    return out
+
+
 def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional[torch.Tensor],
                        v_pages: Optional[torch.Tensor], q_norm_w: Optional[torch.Tensor],
                        k_norm_w: Optional[torch.Tensor], eps: float,
                        inv_freq: Optional[torch.Tensor], rotary_dim: int,
                        positions: torch.Tensor, entry_of_token: torch.Tensor,
                        block_table: torch.Tensor, page_size: int, tokens: int, n_q: int, n_kv: int,
-                       head_dim: int, write_cache: bool, status: torch.Tensor) -> None:
+                       head_dim: int, write_cache: bool, status: torch.Tensor,
+                       cos_sin: Optional[torch.Tensor] = None) -> None:
     """Per-head RMSNorm of q and k, rotation, q to ``q_out`` [T, n_q, D], k and v
-    into pages [page, n_kv, page_size, D] through ``block_table`` [entries, width]."""
+    into pages [page, n_kv, page_size, D] through ``block_table`` [entries, width].
+    ``cos_sin`` is the step's ``rope_table``; without it the table is made here."""
     if qkv.stride(1) != 1 or qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
         raise KernelError("qk_norm_rope_write: qkv has the wrong width")
     if q_out.dtype != qkv.dtype or not q_out.is_contiguous():
@@ -182,13 +199,17 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_out: torch.Tensor, k_pages: Optional
         norm_dtype = dtype_code(q_norm_w.dtype)
     if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() * 2 != rotary_dim):
         raise KernelError("qk_norm_rope_write: inv_freq must be float32 [rotary_dim / 2]")
+    if inv_freq is not None and rotary_dim > 0 and cos_sin is None:
+        cos_sin = rope_table(positions, inv_freq, tokens)
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or cos_sin.numel() < tokens * rotary_dim):
+        raise KernelError("qk_norm_rope_write: cos_sin must be float32 [tokens, rotary_dim / 2, 2]")
     f = _fn("rope_cache", "kipp_qk_norm_rope_write",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float,
              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
              c_int, c_void_p, c_void_p])
     _check(f(_ptr(qkv), qkv.stride(0), _ptr(q_out), _ptr(k_pages), _ptr(v_pages),
              dtype_code(qkv.dtype), _ptr(q_norm_w), _ptr(k_norm_w), norm_dtype, float(eps),
-             _ptr(inv_freq), rotary_dim if inv_freq is not None else 0, _ptr(positions),
+             _ptr(cos_sin), rotary_dim if cos_sin is not None else 0, _ptr(positions),
              _ptr(entry_of_token), _ptr(block_table), block_table.shape[1], page_size, tokens, n_q,
              n_kv, head_dim, 1 if write_cache else 0, _ptr(status), _stream()),
            "qk_norm_rope_write")

@@ -78,12 +78,24 @@ class AttentionMixer(Mixer):
         ops.gemm(qkv, h, self.w_qkv, "store", m=T)
         cache = ctx.cache_view(run)                      # pages of this run's cache id
         q = ws.buffer("q", (T, self.num_heads, self.head_dim), ctx.dtype)
+        inv_freq = self.position.inv_freq(ctx.device)
+        cos_sin = None
+        if inv_freq is not None:
+            # the step's (cos, sin) table: the same for every layer that rotates alike
+            tables = ctx.step_cache.setdefault("rope_tables", {})
+            key = (self.position.table_key(), T)
+            cos_sin = tables.get(key)
+            if cos_sin is None:
+                cos_sin = ws.buffer(f"rope_table_{len(tables)}", (T, inv_freq.numel(), 2), torch.float32)
+                ops.rope_table(ctx.meta.positions, inv_freq, T, out=cos_sin)
+                tables[key] = cos_sin
         ops.qk_norm_rope_write(
             qkv, q, cache.k_pages, cache.v_pages, self.q_norm, self.k_norm,
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
-            self.position.inv_freq(ctx.device), self.position.rotary_dim,
+            inv_freq, self.position.rotary_dim,
             ctx.meta.positions, ctx.meta.entry_of_token, cache.block_table, cache.page_size, T,
-            self.num_heads, self.num_kv_heads, self.head_dim, run.writes_cache, ctx.status)
+            self.num_heads, self.num_kv_heads, self.head_dim, run.writes_cache, ctx.status,
+            cos_sin=cos_sin)
         attn = ws.buffer("attn_out", (T, self.q_dim), ctx.dtype)
         ops.attention(attn.view(T, self.num_heads, self.head_dim), q, cache.k_pages, cache.v_pages,
                       ctx.meta, cache.block_table, cache.page_size, self.num_heads,

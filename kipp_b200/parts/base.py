@@ -78,6 +78,10 @@ class PositionEncoding(Part):
         """float32 ``[rotary_dim // 2]``: angle of pair i at position p is p * inv_freq[i]."""
         return None
 
+    def table_key(self):
+        """Encodings with equal keys rotate alike and share a step's (cos, sin) table."""
+        return id(self)
+
 
 class Mixer(Part):
     def cache_spec(self) -> Optional[PagedKVSpec]:

@@ -30,6 +30,9 @@ class RotaryEncoding(PositionEncoding):
         theta = torch.tensor(self.theta, dtype=torch.float32).double()
         return torch.pow(theta, exponent).float()
 
+    def table_key(self):
+        return ("rotary", self.theta, self.rotary_dim)
+
     def inv_freq(self, device) -> Optional[torch.Tensor]:
         if self.rotary_dim == 0:
             return None

@@ -165,6 +165,7 @@ class PartHarness:
         ctx = Ctx()
         ctx.meta, ctx.device, ctx.dtype, ctx.ops = meta, rt.device, rt.dtype, rt.ops
         ctx.workspace, ctx.status = rt.workspace, rt.status
+        ctx.step_cache = {}
 
         def cache_view(run):
             gi, j = harness.cache.group_of_cache[run.cache]
