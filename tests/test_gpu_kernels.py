@@ -162,13 +162,17 @@ def test_gemm_refuses_what_it_cannot_take():
                                   dict(D=80, nq=3, nkv=3, rot=80, norm=True, page=16),
                                   dict(D=128, nq=8, nkv=1, rot=128, norm=False, page=8),
                                   dict(D=64, nq=2, nkv=2, rot=32, norm=True, page=16),
-                                  dict(D=256, nq=2, nkv=1, rot=0, norm=True, page=32)])
+                                  dict(D=256, nq=2, nkv=1, rot=0, norm=True, page=32),
+                                  dict(D=128, nq=9, nkv=3, rot=128, norm=True, page=16, long=290),
+                                  dict(D=48, nq=5, nkv=5, rot=16, norm=True, page=8, long=260)])
 def test_qk_norm_rope_write(case, dtype):
+    """The last two cases have many tokens: several heads per warp."""
     D, nq, nkv, rot, page = case["D"], case["nq"], case["nkv"], case["rot"], case["page"]
     g = torch.Generator().manual_seed(D)
-    entries = [StepEntry("a", [0] * 5, []), StepEntry("b", [0] * 1, []), StepEntry("c", [0] * 19, [])]
+    n_long = case.get("long", 19)
+    entries = [StepEntry("a", [0] * 5, []), StepEntry("b", [0] * 1, []), StepEntry("c", [0] * n_long, [])]
     starts = [13, 40, 0]
-    width = -(-45 // page)
+    width = -(-max(45, n_long + 1) // page)
     n_pages = 3 * width
     perm = torch.randperm(n_pages, generator=g).int().numpy().reshape(3, width)
     meta = pack_step(entries, starts, [0, 1, 2], [perm.astype(np.int32)], torch.device(DEV))
