@@ -46,7 +46,7 @@ constexpr int UMMA_M = 128;          // features per accumulator = MMA M (a CTA 
 constexpr int TILE_K = 64;           // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 320;         // TMA warp, MMA warp, 8 epilogue warps
-constexpr unsigned SPIN_LIMIT = 1u << 24;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // ~1 s: a wait that long has failed
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -70,11 +70,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false after SPIN_LIMIT polls (or when another role gave up).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+    // Bounded by time, not by polls (a poll may itself block for a while): about
+    // a second of SM clocks, or at once when another thread of the CTA gave up.
+    const long long t0 = clock64();
+    for (unsigned i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
+        }
     }
     *abort_flag = 1;
     return false;

@@ -69,6 +69,8 @@ class StepMeta:
     n_prefill_items: int = 0
     all_work: Optional[torch.Tensor] = None       # the same over every entry (for kernels without a decode path)
     n_all_items: int = 0
+    prefill_work128: Optional[torch.Tensor] = None   # (entry, first token) per 128-token tile, entries of > 1 token
+    n_prefill_items128: int = 0
     decode_split_keys: Optional[torch.Tensor] = None   # int32 [4]: keys per split of decoded tokens
     # host copies for kernel choice
     q_lens: list = dataclasses.field(default_factory=list)
@@ -150,13 +152,15 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
     decode_rows = [i for i, q in enumerate(q_lens) if q == 1]
     prefill_work = [(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(0, q, ATTENTION_TILE)]
     all_work = [(i, t) for i, q in enumerate(q_lens) for t in range(0, q, ATTENTION_TILE)]
+    work128 = [(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(0, q, 2 * ATTENTION_TILE)]
     split = np.zeros(4, dtype=np.int32)
     split[0] = decode_split_length([starts[i] + 1 for i in decode_rows])
     fixed = [split, token_ids, positions, entry_of_token, q_start,
              np.asarray(starts, dtype=np.int32), np.asarray(slots, dtype=np.int32),
              np.asarray(rows, dtype=np.int32), np.asarray(decode_rows, dtype=np.int32),
              np.asarray(prefill_work, dtype=np.int32).reshape(-1),
-             np.asarray(all_work, dtype=np.int32).reshape(-1)]
+             np.asarray(all_work, dtype=np.int32).reshape(-1),
+             np.asarray(work128, dtype=np.int32).reshape(-1)]
     parts = fixed + [t.reshape(-1) for t in tables]
     # 4-int alignment of every section keeps 16-byte alignment for vector loads.
     offsets, total = [], 0
@@ -199,7 +203,9 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
                     decode_rows=sec(8) if decode_rows else None, n_decode=len(decode_rows),
                     prefill_work=sec(9).view(-1, 2) if prefill_work else None,
                     n_prefill_items=len(prefill_work),
-                    all_work=sec(10).view(-1, 2), n_all_items=len(all_work), q_lens=q_lens,
+                    all_work=sec(10).view(-1, 2), n_all_items=len(all_work),
+                    prefill_work128=sec(11).view(-1, 2) if work128 else None, n_prefill_items128=len(work128),
+                    q_lens=q_lens,
                     kv_lens=[s + q for s, q in zip(starts, q_lens)],
                     extra={"h2d_bytes": total * 4})
     if static is not None:
@@ -208,8 +214,8 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
 
 
 def step_ints(n_entries: int, n_tokens: int, n_rows: int, n_decode: int, n_prefill_items: int,
-              n_all_items: int, table_ints: list[int]) -> int:
+              n_all_items: int, table_ints: list[int], n_prefill_items128: int = 0) -> int:
     """Size in int32 of the packed buffer of a step of this shape."""
     sizes = [4, n_tokens, n_tokens, n_tokens, n_entries + 1, n_entries, n_entries, n_rows, n_decode,
-             2 * n_prefill_items, 2 * n_all_items] + list(table_ints)
+             2 * n_prefill_items, 2 * n_all_items, 2 * n_prefill_items128] + list(table_ints)
     return max(sum((s + 3) // 4 * 4 for s in sizes), 4)

@@ -29,6 +29,27 @@ def decode_supported(head_dim: int, n_q: int, n_kv: int) -> bool:
     return bool(f(head_dim, n_q, n_kv))
 
 
+def prefill_tc_supported(head_dim: int, n_q: int, n_kv: int) -> bool:
+    f = _fn("attention_tc", "kipp_attn_prefill_tc_supported", [c_int, c_int, c_int])
+    return bool(f(head_dim, n_q, n_kv))
+
+
+PREFILL_TC = True           # prompt portions on tcgen05 where the sizes allow
+PREFILL_TC_MIN_TOKENS = 64  # shorter portions waste a 128-row tile: they stay on mma.sync
+
+
+def prefill_tc(out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv, head_dim, scale,
+               window, status) -> None:
+    """Portions of more than one token through the tcgen05 kernel (128-token tiles)."""
+    f = _fn("attention_tc", "kipp_attn_prefill_tc",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(meta.q_start), _ptr(meta.context_len),
+             _ptr(block_table), block_table.shape[1], page_size, _ptr(meta.prefill_work128),
+             meta.n_prefill_items128, n_q, n_kv, head_dim, float(scale), int(window or 0),
+             _ptr(status), _stream()), "attn_prefill_tc")
+
+
 def choose(meta, n_q, n_kv, head_dim, page_size) -> str:
     return "mma" if supported(head_dim, n_q, n_kv) else "simt"
 
@@ -57,7 +78,13 @@ def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv,
         raise KernelError("attention_mma takes bfloat16")
     use_decode = meta.n_decode > 0 and decode_supported(head_dim, n_q, n_kv)
     work, items = (meta.prefill_work, meta.n_prefill_items) if use_decode else (meta.all_work, meta.n_all_items)
-    if items:
+    longest = max((n for n in meta.q_lens if n > 1), default=0)
+    if (PREFILL_TC and meta.n_prefill_items128 and longest >= PREFILL_TC_MIN_TOKENS
+            and (use_decode or meta.n_decode == 0) and prefill_tc_supported(head_dim, n_q, n_kv)
+            and all(t.data_ptr() % 16 == 0 for t in (out, q, k_pages, v_pages))):
+        prefill_tc(out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv, head_dim, scale, window,
+                   status)
+    elif items:
         f = _fn("attention_mma", "kipp_attn_prefill_mma",
                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                  c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])

@@ -290,9 +290,10 @@ def test_attention_simt(shape, window, dtype):
                                    dict(D=128, nq=16, nkv=1, page=8), dict(D=64, nq=3, nkv=3, page=32),
                                    dict(D=128, nq=40, nkv=2, page=16)])
 def test_attention_tensor_core(shape, window):
-    """Prompt portions and single decoded tokens through the mma kernels (the
-    last shape has a group of 20 > 16: its decoded tokens go through the
-    portion kernel)."""
+    """Prompt portions and single decoded tokens through the tensor-core kernels:
+    portions of 64 tokens and more through tcgen05, shorter ones and decoded
+    tokens through mma.sync (the last shape has a group of 20 > 16: everything
+    goes through the mma.sync portion kernel); then the same with tcgen05 off."""
     from kipp_b200.kernels import attention_bf16
     D, nq, nkv, page = shape["D"], shape["nq"], shape["nkv"], shape["page"]
     assert attention_bf16.supported(D, nq, nkv)
@@ -304,6 +305,15 @@ def test_attention_tensor_core(shape, window):
                         window, st, impl="mma")
         ref = attention_ref(meta, table, q, kp, vp, layout, page, window, 1 / math.sqrt(D))
         assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2), (shape, li, window)
+        assert st.tolist() == [0, 0, 0, 0]
+        attention_bf16.PREFILL_TC = False
+        try:
+            out2 = torch.full_like(q, 9.0)
+            ops().attention(out2, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D),
+                            window, st, impl="mma")
+        finally:
+            attention_bf16.PREFILL_TC = True
+        assert torch.allclose(out2.double().cpu(), ref, rtol=2e-2, atol=2e-2), (shape, li, window)
 
 
 @pytest.mark.parametrize("impl,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
@@ -312,9 +322,9 @@ def test_attention_finds_one_far_key(impl, dtype):
     """Random data would hide a wrong key among hundreds: here each query's
     score is large for exactly one chosen key (the first key, page edges, the
     window's edge, the token itself) and the values name their position."""
-    D, nq, nkv, page, window = 64, 4, 2, 16, 100
-    ctx, n = 419, 5                                  # a portion of 5 tokens and, below, one decoded token
-    for layout in ([(ctx, n)], [(ctx + n - 1, 1)]):
+    D, nq, nkv, page, window = 128, 4, 2, 16, 100      # D > the longest portion: key directions stay unique
+    ctx, n = 419, 5                                  # a portion of 5 tokens, one decoded token, a portion of 70
+    for layout in ([(ctx, n)], [(ctx + n - 1, 1)], [(ctx, 70)]):
         meta, table, q, kp, vp = attention_case(3, D, nq, nkv, page, layout, dtype)
         total = layout[0][0] + layout[0][1]
         kp.zero_(); vp.zero_(); q.zero_()
@@ -325,13 +335,14 @@ def test_attention_finds_one_far_key(impl, dtype):
             vp[pages[pos // page], :, pos % page, 1] = float(pos // 256)
         first = layout[0][0]                          # position of the first query
         for win, targets in ((None, [0, 15, 16, 255, 256, first - 65, first - 1, "self"]),
-                             (window, ["edge", "edge+1", first - 64, "self"])):
+                             (window, ["edge", "edge+1", "mid", "self"])):
             for target in targets:
                 q.zero_()
                 want = []
                 for i in range(layout[0][1]):
                     pos = layout[0][0] + i
-                    j = {"self": pos, "edge": pos - window + 1, "edge+1": pos - window + 2}.get(target, target)
+                    j = {"self": pos, "edge": pos - window + 1, "edge+1": pos - window + 2,
+                         "mid": pos - window // 2}.get(target, target)
                     q[i, :, j % D] = 60.0
                     want.append(j)
                 # keys j + k * D point the same way as key j: the wanted key alone is twice as long
