@@ -59,6 +59,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -428,8 +431,8 @@ template <int TILE_N> struct CfgTok {
     static constexpr int X_BYTES = UMMA_M * TILE_K * 2;          // 128 tokens
     static constexpr int W_BYTES = TILE_N * TILE_K * 2;
     static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
-    // 256 features: one CTA per SM with a deep ring; narrower: two CTAs per SM
-    static constexpr int STAGES = TILE_N > 160 ? (192 * 1024) / STAGE_BYTES : (100 * 1024) / STAGE_BYTES;
+    // persistent kernel, one CTA per SM: the ring takes what shared memory there is
+    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
     static constexpr int TMEM_COLS = TILE_N <= 32 ? 32 : TILE_N <= 64 ? 64 : TILE_N <= 128 ? 128 : 256;
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
 };
@@ -499,6 +502,10 @@ __device__ __forceinline__ void epilogue_row16(const Params& p, const float* v, 
     }
 }
 
+// Persistent: one CTA per SM walks over the tiles (token tiles fastest, so CTAs
+// that run together share a weight tile in L2).  Two accumulators in tensor
+// memory: while the epilogue warps drain tile i, the MMA warp already works on
+// tile i + 1, and the TMA warp streams on without a break between tiles.
 template <int TILE_N>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -508,92 +515,120 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
     uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_ready = empty + C::STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    uint64_t* acc_full = empty + C::STAGES;        // [2]
+    uint64_t* acc_empty = acc_full + 2;            // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.x * UMMA_M;            // token tiles fastest: neighbours share a weight tile
-    const int f0 = blockIdx.y * TILE_N;
     const int n_kb = (p.K + TILE_K - 1) / TILE_K;
+    const int m_tiles = (p.tokens + UMMA_M - 1) / UMMA_M;
+    const int n_tiles = (p.features + TILE_N - 1) / TILE_N;
+    const int total_tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    if (warp == 1) tmem_alloc(tmem_slot, 2 * C::TMEM_COLS);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0 && (int)blockIdx.x < total_tiles) {
+            // Weights depend on no earlier kernel: the first ring of weight tiles of
+            // this CTA's first tile is requested before the dependency wait, the
+            // activations after it.
+            const int first = blockIdx.x;
             const int ahead = min(n_kb, C::STAGES);
-            for (int i = 0; i < ahead; ++i) {          // weights first: they depend on no earlier kernel
-                mbar_expect_tx(&full[i], C::STAGE_BYTES);
-                tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + C::X_BYTES, &map_w, &full[i], i * TILE_K, f0);
+            {
+                const int t0 = (first % m_tiles) * UMMA_M, f0 = (first / m_tiles) * TILE_N;
+                for (int i = 0; i < ahead; ++i) {
+                    mbar_expect_tx(&full[i], C::STAGE_BYTES);
+                    tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + C::X_BYTES, &map_w, &full[i], i * TILE_K, f0);
+                }
+                pdl_wait();
+                for (int i = 0; i < ahead; ++i)
+                    tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES, &map_x, &full[i], i * TILE_K, t0);
             }
-            pdl_wait();
-            for (int i = 0; i < ahead; ++i)
-                tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES, &map_x, &full[i], i * TILE_K, t0);
-            for (int i = ahead; i < n_kb; ++i) {
-                const int s = i % C::STAGES;
-                const uint32_t ph = (i / C::STAGES) & 1;
-                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-                uint8_t* xt = tiles + (size_t)s * C::STAGE_BYTES;
-                mbar_expect_tx(&full[s], C::STAGE_BYTES);
-                tma_load_2d(xt, &map_x, &full[s], i * TILE_K, t0);
-                tma_load_2d(xt + C::X_BYTES, &map_w, &full[s], i * TILE_K, f0);
+            int it = ahead;                                 // K blocks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = first; tile < total_tiles && ok; tile += gridDim.x) {
+                const int t0 = (tile % m_tiles) * UMMA_M, f0 = (tile / m_tiles) * TILE_N;
+                for (int i = (tile == first ? ahead : 0); i < n_kb; ++i, ++it) {
+                    const int s = it % C::STAGES;
+                    if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* xt = tiles + (size_t)s * C::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    tma_load_2d(xt, &map_x, &full[s], i * TILE_K, t0);
+                    tma_load_2d(xt + C::X_BYTES, &map_w, &full[s], i * TILE_K, f0);
+                }
             }
         }
     } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(UMMA_M, TILE_N);
+            int it = 0, tile_iter = 0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % C::STAGES;
-                const uint32_t ph = (i / C::STAGES) & 1;
-                if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_iter) {
+                const int b = tile_iter & 1, use = tile_iter >> 1;
+                if (tile_iter >= 2 && !mbar_wait(&acc_empty[b], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
-                const uint32_t xa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
-                const uint64_t xd = umma_smem_desc(xa), wd = umma_smem_desc(xa + C::X_BYTES);
+                const uint32_t acc = tmem_base + b * C::TMEM_COLS;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % C::STAGES;
+                    if (!mbar_wait(&full[s], (it / C::STAGES) & 1, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t xa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+                    const uint64_t xd = umma_smem_desc(xa), wd = umma_smem_desc(xa + C::X_BYTES);
 #pragma unroll
-                for (int k = 0; k < TILE_K / UMMA_K; ++k)
-                    umma_bf16(tmem_base, xd + 2 * k, wd + 2 * k, idesc, (i | k) ? 1u : 0u);
-                umma_commit(&empty[s]);
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                        umma_bf16(acc, xd + 2 * k, wd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[b]);
             }
-            if (ok) umma_commit(acc_ready);
         }
     } else {
+        // ---------------------------------------------------------------- epilogue warps 2..9
         const int q = warp & 3;                    // tensor-memory lane quarter = 32 tokens
         const int cg = (warp - 2) >> 2;            // half of the feature columns
-        const int t = t0 + q * 32 + lane;
         pdl_wait();
-        const bool ok = n_kb > 0 ? mbar_wait(acc_ready, 0, abort_flag) : true;
-        tcgen05_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
         constexpr int HALF = (TILE_N / 2 + 15) / 16 * 16;
-        if (ok) {
+        int tile_iter = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_iter) {
+            const int b = tile_iter & 1, use = tile_iter >> 1;
+            const int t = (tile % m_tiles) * UMMA_M + q * 32 + lane, f0 = (tile / m_tiles) * TILE_N;
+            if (ok && !mbar_wait(&acc_full[b], use & 1, abort_flag)) ok = false;
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + b * C::TMEM_COLS + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
             for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
                 float v[16];
-                if (n_kb > 0) tmem_ld16(taddr + c, v);
-                else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                }
-                epilogue_row16(p, v, t, f0 + c);
+                tmem_ld16(taddr + c, v);
+                if (ok) epilogue_row16(p, v, t, f0 + c);
             }
+            // this warp has read its part of the accumulator: hand it back
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);
         }
     }
     tcgen05_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
-    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * C::TMEM_COLS);
 }
 
 // ------------------------------------------------------------------------ host side
@@ -676,7 +711,16 @@ int launch_tokm(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, d
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return kipp_launch(gemm_tc_tokm_kernel<TILE_N>, grid, dim3(THREADS), C::SMEM, s, 1, mw, mx, p);
+    // persistent: at most one CTA per SM
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int total = (int)(grid.x * grid.y);
+    return kipp_launch(gemm_tc_tokm_kernel<TILE_N>, dim3(total < sms ? total : sms), dim3(THREADS), C::SMEM, s, 1, mw,
+                       mx, p);
 }
 
 // Tile choice, from measurements on B200: 128 features with a token tile of 16,
