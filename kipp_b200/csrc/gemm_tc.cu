@@ -24,13 +24,20 @@
 // epilogue for them.  No global scratch, no atomics, and the order of the sum
 // is fixed.
 //
-// Warp roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor
-// memory and issues the MMAs, warps 2-5 run the epilogue (warp w reads the
-// tensor-memory lanes 32*(w%4) .. +31).  Every mbarrier wait gives up after a
-// bounded number of polls, records it in `status[1]` and lets the CTA drain and
-// free its tensor memory.
+// Warp roles (320 threads): warp 0 issues TMA loads, warp 1 allocates tensor
+// memory and issues the MMAs, warps 2-9 run the epilogue (warp w reads the
+// tensor-memory lanes 32*(w%4) .. +31, half of the columns each).  Every
+// mbarrier wait gives up after about a second, records it in `status[1]` and
+// lets the CTA drain and free its tensor memory.
 //
-// No cluster, no multicast: every CTA fetches its own tiles.
+// Prompt-sized batches (512 tokens and more) take a second kernel with the
+// operands the other way round: 128 TOKENS are the M operand and 128 to 256
+// features the N operand, one persistent CTA per SM walks over the tiles with
+// two accumulators in tensor memory (the epilogue of a tile runs under the MMAs
+// of the next), and the residual add leaves as reducing TMA stores.  The
+// feature tile is chosen so that the rounds of tiles over the SMs are full.
+//
+// No multicast: every CTA fetches its own tiles.
 #include "common.cuh"
 #include <cuda.h>
 #include <mutex>
@@ -93,6 +100,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// Adds a float32 box from shared memory into global memory (the adds happen at
+// the L2; nothing is read back).  Tracked by the thread's bulk-group.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the sources of all earlier bulk-groups of this thread have been read
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all earlier bulk-groups of this thread are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// makes this thread's ordinary shared-memory writes visible to the TMA unit
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
                  "r"(cols)
@@ -427,14 +448,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // so it writes 16-byte vectors and SwiGLU pairs sit in one thread: an eighth of
 // the instructions of the feature-per-thread epilogue above, which matters
 // because the epilogue is not hidden behind the next tile's MMAs.
-template <int TILE_N> struct CfgTok {
+constexpr int TOKM_TILE_FIXED = 64;              // fixed part of a tile's time, in feature columns
+constexpr int RED_BOX = 32;                     // the residual add goes out in boxes of 32 tokens x 32 features
+constexpr int RED_BYTES = RED_BOX * RED_BOX * 4;
+template <int TILE_N, bool REDUCE> struct CfgTok {
     static constexpr int X_BYTES = UMMA_M * TILE_K * 2;          // 128 tokens
     static constexpr int W_BYTES = TILE_N * TILE_K * 2;
     static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
+    static constexpr int STAGING = REDUCE ? 8 * RED_BYTES : 0;   // one box per epilogue warp
     // persistent kernel, one CTA per SM: the ring takes what shared memory there is
-    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
-    static constexpr int TMEM_COLS = TILE_N <= 32 ? 32 : TILE_N <= 64 ? 64 : TILE_N <= 128 ? 128 : 256;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int BUDGET = 227 * 1024 - 1024 - 256 - STAGING;
+    static constexpr int STAGES = BUDGET / STAGE_BYTES > 8 ? 8 : BUDGET / STAGE_BYTES;
+    static constexpr int TMEM_COLS = TILE_N <= 128 ? 128 : 256;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING + 1024 + 256;
 };
 
 // 16 consecutive features [f, f + 16) of token t held by one thread.
@@ -506,14 +532,25 @@ __device__ __forceinline__ void epilogue_row16(const Params& p, const float* v, 
 // that run together share a weight tile in L2).  Two accumulators in tensor
 // memory: while the epilogue warps drain tile i, the MMA warp already works on
 // tile i + 1, and the TMA warp streams on without a break between tiles.
-template <int TILE_N>
+//
+// REDUCE (the float32 residual add): a thread per token would touch 16 bytes of
+// 32 different lines per store.  Instead each epilogue warp puts 32 tokens x 32
+// features of the product into shared memory (128-byte swizzle, so the row-wise
+// writes spread over the banks) and hands the box to the TMA unit as a reducing
+// store: the sum is formed at the L2, whole lines at a time, and the old value
+// never travels to the SM.  One add per element, so the result does not depend
+// on timing.  `map_c` covers exactly [tokens, features]: what lies outside is
+// dropped by the unit.
+template <int TILE_N, bool REDUCE>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    const Params p) {
-    using C = CfgTok<TILE_N>;
+                    const __grid_constant__ CUtensorMap map_c, const Params p) {
+    using C = CfgTok<TILE_N, REDUCE>;
+    static_assert(TILE_N % RED_BOX == 0 && TILE_N >= 2 * RED_BOX && TILE_N <= 256, "feature tile");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
+    uint8_t* staging = tiles + (size_t)C::STAGES * C::STAGE_BYTES;        // 1024-byte aligned
+    uint64_t* full = (uint64_t*)(staging + C::STAGING);
     uint64_t* empty = full + C::STAGES;
     uint64_t* acc_full = empty + C::STAGES;        // [2]
     uint64_t* acc_empty = acc_full + 2;            // [2]
@@ -605,25 +642,49 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int cg = (warp - 2) >> 2;            // half of the feature columns
         pdl_wait();
         constexpr int HALF = (TILE_N / 2 + 15) / 16 * 16;
+        uint8_t* box = staging + (size_t)(warp - 2) * RED_BYTES;
         int tile_iter = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_iter) {
             const int b = tile_iter & 1, use = tile_iter >> 1;
-            const int t = (tile % m_tiles) * UMMA_M + q * 32 + lane, f0 = (tile / m_tiles) * TILE_N;
+            const int t_warp = (tile % m_tiles) * UMMA_M + q * 32, f0 = (tile / m_tiles) * TILE_N;
+            const int t = t_warp + lane;
             if (ok && !mbar_wait(&acc_full[b], use & 1, abort_flag)) ok = false;
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + b * C::TMEM_COLS + ((uint32_t)(q * 32) << 16);
+            if constexpr (REDUCE) {
 #pragma unroll 1
-            for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
-                float v[16];
-                tmem_ld16(taddr + c, v);
-                if (ok) epilogue_row16(p, v, t, f0 + c);
+                for (int c = cg * RED_BOX; c < TILE_N; c += 2 * RED_BOX) {
+                    float v[32];
+                    tmem_ld16(taddr + c, v);
+                    tmem_ld16(taddr + c + 16, v + 16);
+                    if (lane == 0) bulk_wait_read();        // the unit has read the previous box
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0 && ok && t_warp < p.tokens && f0 + c < p.features) {
+                        tma_reduce_add_2d(&map_c, box, f0 + c, t_warp);
+                        bulk_commit();
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c, v);
+                    if (ok) epilogue_row16(p, v, t, f0 + c);
+                }
             }
             // this warp has read its part of the accumulator: hand it back
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[b]);
         }
+        if (REDUCE && lane == 0) bulk_wait_all();
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -651,7 +712,7 @@ EncodeTiled encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; int rows, cols; long long ld; int box_rows;
+    const void* ptr; int rows, cols; long long ld; int box_rows;   // box_rows < 0: float32 box for the reducing store
     bool operator==(const MapKey& o) const {
         return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
     }
@@ -666,20 +727,23 @@ struct MapHash {
 };
 
 // Row-major bf16 [rows, cols] with leading dimension ld; box = [box_rows, 64].
-int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, long long ld, int box_rows) {
+// f32_box: row-major float32 instead, box = [RED_BOX, RED_BOX].
+int make_map(CUtensorMap* out, const void* ptr, int rows, int cols, long long ld, int box_rows,
+             bool f32_box = false) {
     static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
     static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
+    MapKey key{ptr, rows, cols, ld, f32_box ? -RED_BOX : box_rows};
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return 0; }
     EncodeTiled fn = encode_fn();
     if (!fn) return (int)cudaErrorNotSupported;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (f32_box ? 4 : 2)};
+    cuuint32_t box[2] = {(cuuint32_t)(f32_box ? RED_BOX : TILE_K), (cuuint32_t)(f32_box ? RED_BOX : box_rows)};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+    CUresult r = fn(out, f32_box ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return 1000 + (int)r;
@@ -701,26 +765,61 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
     return kipp_launch(gemm_tc_kernel<TILE_T, TILE_F>, grid, dim3(THREADS), C::SMEM, s, p.splits, mw, mx, p);
 }
 
-template <int TILE_N>
-int launch_tokm(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
-    using C = CfgTok<TILE_N>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_tokm_kernel<TILE_N>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    // persistent: at most one CTA per SM
+int sm_count() {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
-    const int total = (int)(grid.x * grid.y);
-    return kipp_launch(gemm_tc_tokm_kernel<TILE_N>, dim3(total < sms ? total : sms), dim3(THREADS), C::SMEM, s, 1, mw,
-                       mx, p);
+    return sms;
+}
+
+template <int TILE_N, bool REDUCE>
+int launch_tokm(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, const Params& p, int total,
+                cudaStream_t s) {
+    using C = CfgTok<TILE_N, REDUCE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_tokm_kernel<TILE_N, REDUCE>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    // persistent: at most one CTA per SM
+    const int sms = sm_count();
+    return kipp_launch(gemm_tc_tokm_kernel<TILE_N, REDUCE>, dim3(total < sms ? total : sms), dim3(THREADS), C::SMEM,
+                       s, 1, mw, mx, mc, p);
+}
+template <bool REDUCE>
+int launch_tokm_n(int tile_n, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, const Params& p,
+                  int total, cudaStream_t s) {
+    switch (tile_n) {
+    case 128: return launch_tokm<128, REDUCE>(mw, mx, mc, p, total, s);
+    case 160: return launch_tokm<160, REDUCE>(mw, mx, mc, p, total, s);
+    case 192: return launch_tokm<192, REDUCE>(mw, mx, mc, p, total, s);
+    case 224: return launch_tokm<224, REDUCE>(mw, mx, mc, p, total, s);
+    case 256: return launch_tokm<256, REDUCE>(mw, mx, mc, p, total, s);
+    }
+    return KIPP_ERR_ARG;
+}
+
+// Feature tile of the persistent kernel: the CTAs take the tiles in rounds, so
+// the cost is rounds x (time of a tile); a tile's time grows with its width
+// plus a fixed part.  For 2,048 tokens x 2,560 features, 256 wide gives 160
+// tiles = two rounds of which the second is nearly empty; 160 wide gives 256
+// tiles = two well-filled rounds of shorter tiles.
+int pick_tile_n(int tokens, int features) {
+    const int sms = sm_count();
+    const int m_tiles = (tokens + UMMA_M - 1) / UMMA_M;
+    int best = 256;
+    long long best_cost = -1;
+    for (int n = 256; n >= 128; n -= 32) {
+        const long long tiles = (long long)m_tiles * ((features + n - 1) / n);
+        const long long cost = ((tiles + sms - 1) / sms) * (n + TOKM_TILE_FIXED);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = n; }
+    }
+    return best;
 }
 
 // Tile choice, from measurements on B200: 128 features with a token tile of 16,
@@ -790,28 +889,32 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
     if (epilogue == EPI_SWIGLU && (features & 1)) return KIPP_ERR_ARG;
     if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
     // Prompt-sized batches: tokens as the M operand (want_tile_f < 0 forces it with
-    // the feature tile -want_tile_f).  Not for the float32 residual epilogue:
-    // there a thread per feature writes whole 128-byte lines per warp, a thread
-    // per token only 16 bytes of each line (measured 129 against 200 us at
-    // 2048 x 2560 x 9728).
-    if ((want_tile == 0 && want_tile_f == 0 && tokens >= 512 && epilogue != EPI_ADD) || want_tile_f < 0) {
-        int tile_n = want_tile_f < 0 ? -want_tile_f : 256;
-        if (tile_n != 128 && tile_n != 160 && tile_n != 256) return KIPP_ERR_ARG;
-        CUtensorMap mw, mx;
+    // the feature tile -want_tile_f).  The residual add needs a tensor map over C.
+    const bool c_map_ok = epilogue != EPI_ADD || (ldc % 4 == 0 && ((uintptr_t)C & 15) == 0);
+    if ((want_tile == 0 && want_tile_f == 0 && tokens >= 512 && c_map_ok) || want_tile_f < 0) {
+        const bool reduce = epilogue == EPI_ADD && c_map_ok;     // else a thread per token adds in place
+        const int tile_n = want_tile_f < 0 ? -want_tile_f : pick_tile_n(tokens, features);
+        if (tile_n < 128 || tile_n > 256 || tile_n % 32) return KIPP_ERR_ARG;
+        CUtensorMap mw, mx, mc;
         int rc = make_map(&mw, W, features, K, ldw, tile_n);
         if (rc) return rc;
         rc = make_map(&mx, X, tokens, K, ldx, UMMA_M);
         if (rc) return rc;
+        if (reduce) {
+            rc = make_map(&mc, C, tokens, features, ldc, RED_BOX, true);
+            if (rc) return rc;
+        } else {
+            mc = mw;                                    // unused
+        }
         Params p;
         p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
         p.tokens = tokens; p.features = features; p.K = K; p.ldc = ldc;
         p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
-        dim3 grid((tokens + UMMA_M - 1) / UMMA_M, (features + tile_n - 1) / tile_n, 1);
-        if (grid.y > 65535) return KIPP_ERR_ARG;
+        const long long total = (long long)((tokens + UMMA_M - 1) / UMMA_M) * ((features + tile_n - 1) / tile_n);
+        if (total > 0x7fffffffLL) return KIPP_ERR_ARG;
         cudaStream_t s = (cudaStream_t)stream;
-        if (tile_n == 128) return launch_tokm<128>(mw, mx, p, grid, s);
-        if (tile_n == 160) return launch_tokm<160>(mw, mx, p, grid, s);
-        return launch_tokm<256>(mw, mx, p, grid, s);
+        return reduce ? launch_tokm_n<true>(tile_n, mw, mx, mc, p, (int)total, s)
+                      : launch_tokm_n<false>(tile_n, mw, mx, mc, p, (int)total, s);
     }
     int tile_t, tile_f, planned;
     kipp_gemm_tc_plan(tokens, features, K, splits, want_tile, want_tile_f, &tile_t, &tile_f, &planned);

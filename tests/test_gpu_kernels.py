@@ -114,14 +114,16 @@ def test_gemm_tensor_core(shape, epilogue):
 @pytest.mark.parametrize("epilogue", ["store", "add", "swiglu"])
 @pytest.mark.parametrize("shape", [(600, 640, 520), (512, 1000, 136), (130, 250, 192), (1100, 2560, 320)])
 def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
-    """The orientation used for prompt-sized batches (tokens = MMA rows, a
-    thread of the epilogue owns a token and writes vectors), with feature tiles
-    of 128, 160 and 256 and ragged edges; integer data exactly."""
+    """The orientation used for prompt-sized batches (tokens = MMA rows; a
+    thread of the epilogue owns a token and writes vectors, the residual add
+    leaves as reducing TMA stores where the output's pitch allows a tensor map,
+    in place otherwise), with every feature tile and ragged edges; the output
+    also as a slice of a wider buffer; integer data exactly."""
     from kipp_b200.kernels import gemm_bf16
     M, N, K = shape
     g = torch.Generator().manual_seed(M + 3 * N)
     for integer in (True, False):
-        for tile_f in (0, -128, -160, -256):
+        for tile_f in (0, -128, -160, -192, -224, -256):
             if tile_f == 0 and M < 512:
                 continue
             if integer:
@@ -131,10 +133,17 @@ def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
                 a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
                 w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16).to(DEV)
             odt = torch.float32 if (epilogue == "add" or integer) else torch.bfloat16
-            out = torch.randn(M, N // 2 if epilogue == "swiglu" else N, generator=g).to(odt).to(DEV)
+            n_out = N // 2 if epilogue == "swiglu" else N
+            wide = torch.randn(M + 1, n_out + 8, generator=g).to(odt).to(DEV)
+            out = wide[:M, 4:4 + n_out] if tile_f in (-160, -224) else wide[:M, :n_out].contiguous()
+            before = wide.clone()
             ref = gemm_ref(a, w, epilogue, out)
             gemm_bf16.run("tc", out, a, w, epilogue, M, tile_f=tile_f)
             got = out.double().cpu()
+            if not out.is_contiguous():                     # nothing beside the slice is touched
+                after = wide.clone()
+                after[:M, 4:4 + n_out] = before[:M, 4:4 + n_out]
+                assert torch.equal(after, before), (shape, tile_f)
             if integer and epilogue != "swiglu":
                 assert torch.equal(got, ref.float().double()), (shape, tile_f)
             else:
