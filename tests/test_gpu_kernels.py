@@ -173,9 +173,15 @@ def test_gemm_refuses_what_it_cannot_take():
                                   dict(D=64, nq=2, nkv=2, rot=32, norm=True, page=16),
                                   dict(D=256, nq=2, nkv=1, rot=0, norm=True, page=32),
                                   dict(D=128, nq=9, nkv=3, rot=128, norm=True, page=16, long=290),
-                                  dict(D=48, nq=5, nkv=5, rot=16, norm=True, page=8, long=260)])
+                                  dict(D=48, nq=5, nkv=5, rot=16, norm=True, page=8, long=260),
+                                  dict(D=64, nq=5, nkv=2, rot=64, norm=True, page=8, long=130, w16=True),
+                                  dict(D=256, nq=3, nkv=2, rot=256, norm=True, page=16, long=70, w16=True)])
 def test_qk_norm_rope_write(case, dtype):
-    """The last two cases have many tokens: several heads per warp."""
+    """Cases with `long` have many tokens: several heads per warp.  In bfloat16
+    the head sizes 64, 128 and 256 with a full or no rotation take the
+    16-byte-vector kernel (head counts that leave a warp's last heads empty or
+    put a key and a value head into one warp); `w16` has the norm weights in
+    bfloat16 as checkpoints store them."""
     D, nq, nkv, rot, page = case["D"], case["nq"], case["nkv"], case["rot"], case["page"]
     g = torch.Generator().manual_seed(D)
     n_long = case.get("long", 19)
@@ -187,8 +193,9 @@ def test_qk_norm_rope_write(case, dtype):
     meta = pack_step(entries, starts, [0, 1, 2], [perm.astype(np.int32)], torch.device(DEV))
     T = meta.tokens
     qkv = torch.randn(T, (nq + 2 * nkv) * D, generator=g).to(dtype).to(DEV)
-    qw = (1 + 0.2 * torch.randn(D, generator=g)).to(DEV) if case["norm"] else None
-    kw = (1 + 0.2 * torch.randn(D, generator=g)).to(DEV) if case["norm"] else None
+    wdt = torch.bfloat16 if case.get("w16") else torch.float32
+    qw = (1 + 0.2 * torch.randn(D, generator=g)).to(wdt).to(DEV) if case["norm"] else None
+    kw = (1 + 0.2 * torch.randn(D, generator=g)).to(wdt).to(DEV) if case["norm"] else None
     theta = 10000.0
     inv = None
     if rot:
