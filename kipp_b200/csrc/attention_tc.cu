@@ -6,30 +6,45 @@
 // src/kipp.c:2882-2922 (scores (q.k)/sqrt(D) over the keys a token may see,
 // softmax with the maximum subtracted, weighted sum of values).
 //
-// One CTA = 128 consecutive tokens of one entry x one query head, 128 threads;
-// thread r owns query row r: it reads the row's 64 scores of a key tile from
-// tensor memory, so maximum, exponentials and sum need no exchange between
-// threads.  Per tile of 64 keys:
-//   1. keys and values are gathered page by page with cp.async into swizzled
-//      shared-memory tiles (double-buffered: the next tile is in flight);
-//   2. one thread issues S = Q K^T (128 x 64 x D) into tensor memory;
-//   3. every thread: scale, mask, running maximum, p = 2^(s - m) -> bfloat16
-//      into the shared-memory P tile; if some row's maximum moved, the output
-//      accumulator in tensor memory is rescaled (tcgen05.ld / st);
-//   4. one thread issues O += P V (128 x D x 64), V as an MN-major operand.
-// Two CTAs fit an SM (112 KB shared memory, 256 tensor-memory columns each),
-// so one's softmax runs under the other's MMAs.  All arithmetic outside the
-// MMAs is float32.  Every mbarrier wait is bounded; on a time-out status[1] is
-// set and the CTA drains and frees its tensor memory.
+// One CTA = 128 consecutive tokens of one entry x one query head, 10 warps:
+//   warps 0-7  softmax: threads r and r + 128 share query row r, each takes 32 of
+//              a tile's 64 keys (scores straight from tensor memory, lane = row)
+//              and half of the output columns;
+//   warp 8     gathers the key and value tiles page by page with TMA (one box
+//              per lane, 128-byte swizzle) into a two-stage ring;
+//   warp 9     one thread issues the products.
+// Per tile of 64 keys: S = Q K^T (128 x 64 x D) into one of two score buffers in
+// tensor memory; the softmax threads scale, mask, take the running maximum
+// (exchanged between the two threads of a row through shared memory), form
+// p = 2^(s - m) and put it, as bfloat16, over the scores it came from; if some
+// row's maximum moved, the output accumulator in tensor memory is rescaled;
+// O += P V (128 x D x 64) takes P from tensor memory and V as an MN-major
+// shared-memory operand.  The products run ahead of the softmax: S of tile
+// i + 1 is computed while tile i is in the softmax, O += P V of tile i while
+// tile i + 1 is.  Everything is handed over through mbarriers; every wait is
+// bounded in time, and on a time-out status[1] is set and the CTA drains and
+// frees its tensor memory.  Two CTAs fit an SM (98 KB shared memory, 256
+// tensor-memory columns each).  All arithmetic outside the MMAs is float32.
 //
-// Sizes: head_dim 64 or 128.  Cache layout of a layer: [page][kv_head][slot][D].
+// Keys beyond a row's limits are masked after the product, so whole pages are
+// fetched; rows of a tile without a page are fetched from beyond the end of the
+// pool, where the TMA unit fills zeros.  A masked value row is multiplied by a
+// weight of exactly zero: the pool must hold finite numbers everywhere (it is
+// created zeroed and only ever holds keys and values).
+//
+// Sizes: head_dim 64 or 128; page size 8, 16, 32 or a multiple of 64.  Cache
+// layout of a layer: [page][kv_head][slot][D].
 #include "common.cuh"
+#include <cuda.h>
 #include <math.h>
+#include <mutex>
+#include <unordered_map>
 
 namespace {
 constexpr int BM = 128;            // query rows per CTA = MMA M
 constexpr int BN = 64;             // keys per tile
-constexpr int THREADS = 128;
+constexpr int SOFTMAX_THREADS = 256;  // two threads per query row: each half of a tile's keys
+constexpr int THREADS = 320;          // + the TMA warp and the MMA warp
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // ~1 s: a wait that long has failed
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -63,6 +78,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
     *abort_flag = 1;
     return false;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
@@ -117,6 +145,26 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
           "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
         : "memory");
 }
+// 16 columns of raw 32-bit words (pairs of bfloat16) into this thread's lane.
+__device__ __forceinline__ void tmem_st16_words(uint32_t taddr, const uint32_t* w) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
+          "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15])
+        : "memory");
+}
+// Barrier among `count` threads (whole warps) that all name `id` (1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// D (+)= A B with A in tensor memory (lane = row, a column = two bfloat16 of K) and B in shared memory.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 // 2^x, single instruction (flushes denormals to zero: such weights do not matter in a sum of weights <= 1)
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -153,6 +201,8 @@ struct Params {
     const int* q_start; const int* context_len; const int* block_table;
     const int* work;            // [items][2] = (entry, first token of the tile within the entry)
     int table_width, page_size, n_q, n_kv, window;
+    int box_rows;               // rows of one TMA box = min(page_size, 64)
+    int rows_total;             // pages x kv heads x page_size: a row coordinate from here on reads zeros
     float scale_log2;
     uint32_t v_lbo, v_sbo;      // descriptor strides of the MN-major value tile
     int* status;
@@ -162,257 +212,329 @@ template <int D> struct Cfg {
     static constexpr int HALVES = D / 64;
     static constexpr int Q_BYTES = BM * D * 2;
     static constexpr int KV_BYTES = BN * D * 2;       // one of K or V, one stage
-    static constexpr int P_BYTES = BM * BN * 2;
-    static constexpr int TMEM_COLS = D == 128 ? 256 : 128;      // S (64) + O (D), power of two
+    static constexpr int XCHG_BYTES = 2 * 2 * BM * 4;  // row maxima of the two halves, two parities
+    static constexpr int TMEM_COLS = 256;                       // two score buffers (64 each) + O (D), power of two
     // 114,816 bytes at head_dim 128: two CTAs (plus the 1 KB the system keeps per CTA) fit in 227 KB
-    static constexpr size_t SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 128;
+    static constexpr size_t SMEM = Q_BYTES + 4 * KV_BYTES + XCHG_BYTES + 128;   // 14 barriers, 2 words
 };
 
-// Gathers BN rows of keys and of values, positions [j0, j0 + BN), kv head g.
 template <int D>
-__device__ __forceinline__ void load_kv(uint32_t k_tile, uint32_t v_tile, const bf16* __restrict__ k_pages,
-                                        const bf16* __restrict__ v_pages, const int* __restrict__ table,
-                                        int table_width, int page_size, int n_kv, int g, int j0, int lo, int hi) {
-    constexpr int CHUNKS = D / 8;                        // 16-byte chunks per row
-    constexpr int GROUPS = THREADS / CHUNKS;
-    constexpr int ROWS = BN / GROUPS;                    // consecutive rows per thread
-    const int chunk = threadIdx.x % CHUNKS, row0 = (threadIdx.x / CHUNKS) * ROWS;
-    if ((page_size & 7) == 0 && ROWS <= 8) {
-        // the thread's rows are consecutive and start at a multiple of ROWS: one page
-        const int j_first = j0 + row0;
-        const int slot = j_first / page_size;
-        const int page = (slot < table_width && j_first <= hi && j_first + ROWS - 1 >= lo) ? __ldg(table + slot) : -1;
-        const size_t base = (((size_t)max(page, 0) * n_kv + g) * page_size + (j_first - slot * page_size)) * D +
-                            chunk * 8;
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const int j = j_first + r;
-            const bool in = page >= 0 && j >= lo && j <= hi;
-            const uint32_t off = tile_off<BN>(chunk >> 3, row0 + r, chunk & 7);
-            cp_async16(k_tile + off, k_pages + (in ? base + (size_t)r * D : 0), in ? 16 : 0);
-            cp_async16(v_tile + off, v_pages + (in ? base + (size_t)r * D : 0), in ? 16 : 0);
-        }
-        return;
-    }
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-        const int row = row0 + r, j = j0 + row;
-        size_t src = 0;
-        int bytes = 0;
-        if (j >= lo && j <= hi) {
-            const int slot = j / page_size;
-            const int page = slot < table_width ? __ldg(table + slot) : -1;
-            if (page >= 0) {
-                src = (((size_t)page * n_kv + g) * page_size + (j - slot * page_size)) * D + chunk * 8;
-                bytes = 16;
-            }
-        }
-        const uint32_t off = tile_off<BN>(chunk >> 3, row, chunk & 7);
-        cp_async16(k_tile + off, k_pages + src, bytes);
-        cp_async16(v_tile + off, v_pages + src, bytes);
-    }
-}
-
-template <int D>
-__global__ void __launch_bounds__(THREADS)
-attn_prefill_tc_kernel(const Params p) {
+__global__ void __launch_bounds__(THREADS, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const Params p) {
     using C = Cfg<D>;
     extern __shared__ __align__(1024) uint8_t smem[];     // swizzled tiles need 1024-byte alignment
     const uint32_t q_tile = smem_u32(smem);
     const uint32_t k_tiles = q_tile + C::Q_BYTES;                  // [2 stages]
     const uint32_t v_tiles = k_tiles + 2 * C::KV_BYTES;            // [2 stages]
-    const uint32_t p_tile = v_tiles + 2 * C::KV_BYTES;
-    uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + C::Q_BYTES + 4 * C::KV_BYTES + C::P_BYTES);
-    uint64_t* bar_o = bar_s + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+    float* xchg = reinterpret_cast<float*>(smem + C::Q_BYTES + 4 * C::KV_BYTES);      // [parity][half][row]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::Q_BYTES + 4 * C::KV_BYTES + C::XCHG_BYTES);
+    uint64_t* q_full = bars;            // the query tile is in shared memory            (256 arrivals)
+    uint64_t* k_full = bars + 1;        // [2] a key stage has landed                    (1 + bytes)
+    uint64_t* k_empty = bars + 3;       // [2] its S product has read it                 (1, by commit)
+    uint64_t* v_full = bars + 5;        // [2]
+    uint64_t* v_empty = bars + 7;       // [2] its O product has read it
+    uint64_t* s_full = bars + 9;        // [2] a score buffer holds S of a tile          (1, by commit)
+    uint64_t* p_full = bars + 11;       // [2] it holds the tile's weights, O is rescaled (8 = softmax warps)
+    uint64_t* o_done = bars + 13;       // O += P V of a tile is complete                 (1, by commit)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
+        mbar_init(q_full, SOFTMAX_THREADS);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
+            mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
+            mbar_init(&s_full[b], 1); mbar_init(&p_full[b], SOFTMAX_THREADS / 32);
+        }
+        mbar_init(o_done, 1);
         *abort_flag = (q_tile & 1023u) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + BN;      // columns [0, 64) and [64, 64 + D)
+    // columns: two score buffers [0, 64) and [64, 128) (the weights of a tile, as pairs
+    // of bfloat16, overwrite the first 32 columns of its scores), output [128, 128 + D)
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BN;
     pdl_wait();
 
     const int entry = p.work[2 * blockIdx.x], tile_tok = p.work[2 * blockIdx.x + 1];
     const int h = blockIdx.y, g = h / (p.n_q / p.n_kv);
     const int qs = p.q_start[entry], q_len = p.q_start[entry + 1] - qs;
     const int ctx = p.context_len[entry];
-    const int* table = p.block_table + (size_t)entry * p.table_width;
-
-    // ---- the query tile: rows beyond the entry are zero
-    {
-        constexpr int CHUNKS = D / 8;
-        for (int i = threadIdx.x; i < BM * CHUNKS; i += THREADS) {
-            const int row = i / CHUNKS, chunk = i % CHUNKS;
-            const int tok = tile_tok + row;
-            const bool live = tok < q_len;
-            const bf16* src = p.q + ((size_t)(qs + (live ? tok : 0)) * p.n_q + h) * D + chunk * 8;
-            cp_async16(q_tile + tile_off<BM>(chunk >> 3, row, chunk & 7), src, live ? 16 : 0);
-        }
-    }
     // keys the tile may see: from the first token's window start to the last token
-    const int row = threadIdx.x;                           // this thread's query row
-    const int tok = tile_tok + row;
-    const bool live = tok < q_len;
-    const int pos = ctx + tok;
-    const int lo_row = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int tile_first = ctx + tile_tok, tile_last = ctx + min(tile_tok + BM - 1, q_len - 1);
     const int lo = p.window > 0 ? max(0, tile_first - p.window + 1) : 0, hi = tile_last;
     const int first_tile = lo / BN, last_tile = hi / BN;
+    const int n_tiles = last_tile - first_tile + 1;
 
-    load_kv<D>(k_tiles, v_tiles, p.k_pages, p.v_pages, table, p.table_width, p.page_size, p.n_kv, g,
-               first_tile * BN, lo, hi);
-    cp_async_commit();
-
-    float m_run = -INFINITY, l_run = 0.f;
-    bool ok = true;
-    uint32_t phase = 0;
-    constexpr uint32_t IDESC_S = idesc(BM, BN, 0);
-    constexpr uint32_t IDESC_O = idesc(BM, D, 1);
-    const uint32_t t_lane = (uint32_t)(warp * 32) << 16;   // this warp's tensor-memory lanes
-
-    // (a failed wait does not leave the loop: every thread must meet every barrier;
-    // once the abort flag is up the remaining waits return at once)
-    for (int kt = first_tile; kt <= last_tile; ++kt) {
-        const int buf = (kt - first_tile) & 1;
-        const uint32_t k_tile = k_tiles + buf * C::KV_BYTES, v_tile = v_tiles + buf * C::KV_BYTES;
-        // 1. this tile's keys and values (and, the first time, the queries) have landed
-        cp_async_wait<0>();
-        fence_async_proxy();                               // cp.async wrote; the tensor core reads
-        __syncthreads();
-        // 2. S = Q K^T
-        if (threadIdx.x == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int hh = 0; hh < C::HALVES; ++hh) {
-                const uint64_t qd = smem_desc(q_tile + hh * (BM * 128), 0, 1024);
-                const uint64_t kd = smem_desc(k_tile + hh * (BN * 128), 0, 1024);
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    umma_bf16(tmem_s, qd + 2 * k, kd + 2 * k, IDESC_S, (hh | k) ? 1u : 0u);
+    if (warp == 8) {
+        // ------------------------------------------------------------ TMA producer
+        // Lane l fetches box l of a tile: rows [rb * box_rows, + box_rows) of the
+        // 64-column half `half`; the rows of a box lie in one page.
+        const int* table = p.block_table + (size_t)entry * p.table_width;
+        const int rb = lane / C::HALVES, half = lane % C::HALVES;
+        const bool has_box = rb * p.box_rows < BN;
+        const uint32_t dst_off = (uint32_t)(half * (BN * 128) + rb * p.box_rows * 128);
+        bool ok = true;
+        for (int i = 0; i < n_tiles; ++i) {
+            const int kt = first_tile + i, b = i & 1, use = i >> 1;
+            int row_coord = p.rows_total;                  // beyond the pool: zeros
+            if (has_box) {
+                const int j = kt * BN + rb * p.box_rows;
+                const int slot = j / p.page_size;
+                const int page = (j <= hi && slot < p.table_width) ? __ldg(table + slot) : -1;
+                if (page >= 0) row_coord = (page * p.n_kv + g) * p.page_size + (j - slot * p.page_size);
             }
-            umma_commit(bar_s);
+            if (i >= 2 && ok && !mbar_wait(&k_empty[b], (use - 1) & 1, abort_flag)) ok = false;
+            if (lane == 0) mbar_expect_tx(&k_full[b], C::KV_BYTES);
+            __syncwarp();
+            if (has_box && ok) tma_load_2d(k_tiles + b * C::KV_BYTES + dst_off, &map_k, &k_full[b], half * 64, row_coord);
+            if (i >= 2 && ok && !mbar_wait(&v_empty[b], (use - 1) & 1, abort_flag)) ok = false;
+            if (lane == 0) mbar_expect_tx(&v_full[b], C::KV_BYTES);
+            __syncwarp();
+            if (has_box && ok) tma_load_2d(v_tiles + b * C::KV_BYTES + dst_off, &map_v, &v_full[b], half * 64, row_coord);
         }
-        // the next tile's keys and values travel meanwhile
-        if (kt < last_tile) {
-            load_kv<D>(k_tiles + (buf ^ 1) * C::KV_BYTES, v_tiles + (buf ^ 1) * C::KV_BYTES, p.k_pages, p.v_pages,
-                       table, p.table_width, p.page_size, p.n_kv, g, (kt + 1) * BN, lo, hi);
-        }
-        cp_async_commit();
-        // 3. softmax of this thread's row
-        if (!mbar_wait(bar_s, phase, abort_flag)) { if (ok) atomicMax(&p.status[2], 1); ok = false; }
-        tc_fence_after();
-        float s[BN];
-        tmem_ld32(tmem_s + t_lane, s);
-        tmem_ld32(tmem_s + t_lane + 32, s + 32);
-        const int j0 = kt * BN;
-        // Masking only where the tile crosses a row's limits (the diagonal, a
-        // window's edge, rows beyond the entry): decided per warp.
-        if (!__all_sync(0xffffffffu, live && j0 + BN - 1 <= pos && j0 >= lo_row)) {
+    } else if (warp == 9) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = idesc(BM, BN, 0);
+            constexpr uint32_t IDESC_O = idesc(BM, D, 1);
+            bool ok = true;
+            // S(tile) = Q K^T into score buffer b from key stage b
+            auto issue_scores = [&](int b, uint32_t parity) {
+                if (ok && !mbar_wait(&k_full[b], parity, abort_flag)) ok = false;
+                tc_fence_after();
 #pragma unroll
-            for (int j = 0; j < BN; ++j) {
-                const int key = j0 + j;
-                if (!(live && key >= lo_row && key <= pos)) s[j] = -INFINITY;
+                for (int hh = 0; hh < C::HALVES; ++hh) {
+                    const uint64_t qd = smem_desc(q_tile + hh * (BM * 128), 0, 1024);
+                    const uint64_t kd = smem_desc(k_tiles + b * C::KV_BYTES + hh * (BN * 128), 0, 1024);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_s + b * BN, qd + 2 * k, kd + 2 * k, IDESC_S, (hh | k) ? 1u : 0u);
+                }
+                umma_commit(&s_full[b]);
+                umma_commit(&k_empty[b]);
+            };
+            if (!mbar_wait(q_full, 0, abort_flag)) ok = false;
+            issue_scores(0, 0);
+            if (n_tiles > 1) issue_scores(1, 0);
+            for (int i = 0; i < n_tiles; ++i) {
+                const int b = i & 1, use = i >> 1;
+                // the tile's weights are in its score buffer, O is rescaled, its values have landed
+                if (ok && !mbar_wait(&p_full[b], use & 1, abort_flag)) ok = false;
+                if (ok && !mbar_wait(&v_full[b], use & 1, abort_flag)) ok = false;
+                tc_fence_after();
+                const uint64_t vd = smem_desc(v_tiles + b * C::KV_BYTES, p.v_lbo, p.v_sbo);
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k)
+                    // 16 keys further: 8 columns of P; 16 rows = 2048 bytes in the value tile
+                    umma_bf16_a_tmem(tmem_o, tmem_s + b * BN + 8 * k, vd + 128 * k, IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&v_empty[b]);
+                umma_commit(o_done);
+                if (i + 2 < n_tiles) {
+                    // S of the tile after next goes where this tile's weights are: not before they are read
+                    if (ok && !mbar_wait(o_done, i & 1, abort_flag)) ok = false;
+                    issue_scores(b, ((i + 2) >> 1) & 1);
+                }
             }
         }
-        float raw = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < BN; ++j) raw = fmaxf(raw, s[j]);
-        const float mx = fmaxf(m_run, raw * p.scale_log2);          // scale > 0: the maximum commutes
-        const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mx);
-        const float neg_base = (mx == -INFINITY) ? 0.f : -mx;
-        float sum = 0.f;
-        uint32_t packed[BN / 2];
-#pragma unroll
-        for (int j = 0; j < BN; j += 2) {
-            const float p0 = fast_exp2(fmaf(s[j], p.scale_log2, neg_base));
-            const float p1 = fast_exp2(fmaf(s[j + 1], p.scale_log2, neg_base));
-            sum += p0 + p1;
-            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-            packed[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
-        }
-        l_run = l_run * corr + sum;
-        m_run = mx;
-        // P tile: this thread's row, 8 chunks of 8 keys
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ softmax warps 0-7
+        // the query tile: rows beyond the entry are zero
         {
-            uint8_t* p_row = smem + (p_tile - q_tile);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint4 v4 = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-                *reinterpret_cast<uint4*>(p_row + tile_off<BM>(0, row, c)) = v4;
+            constexpr int CHUNKS = D / 8;
+            for (int i = threadIdx.x; i < BM * CHUNKS; i += SOFTMAX_THREADS) {
+                const int r = i / CHUNKS, chunk = i % CHUNKS;
+                const int tk = tile_tok + r;
+                const bool there = tk < q_len;
+                const bf16* src = p.q + ((size_t)(qs + (there ? tk : 0)) * p.n_q + h) * D + chunk * 8;
+                cp_async16(q_tile + tile_off<BM>(chunk >> 3, r, chunk & 7), src, there ? 16 : 0);
             }
+            cp_async_commit();
+            cp_async_wait<0>();
+            fence_async_proxy();                           // cp.async wrote; the tensor core reads
+            mbar_arrive(q_full);
         }
-        // rescale the output accumulator when some row of the warp moved its maximum
-        if (kt > first_tile && __any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
-                float o[32];
-                tmem_ld32(tmem_o + t_lane + c, o);
+        // Threads r and r + 128 share query row r.  Warps w and w + 4 hold the same 32
+        // rows (a warp reaches the tensor-memory lanes 32 (w % 4) .. + 31).
+        const int row = threadIdx.x & (BM - 1), ch = threadIdx.x >> 7;
+        const int tok = tile_tok + row;
+        const bool live = tok < q_len;
+        const int pos = ctx + tok;
+        const int lo_row = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const uint32_t t_lane = (uint32_t)((warp & 3) * 32) << 16;   // this warp's tensor-memory lanes
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        // (A failed wait does not leave the loop: every thread must meet every barrier;
+        // once the abort flag is up the remaining waits return at once.)
+        for (int i = 0; i < n_tiles; ++i) {
+            const int kt = first_tile + i, b = i & 1, use = i >> 1;
+            const uint32_t tmem_sb = tmem_s + b * BN;
+            if (!mbar_wait(&s_full[b], use & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 1); ok = false; }
+            tc_fence_after();
+            constexpr int HB = BN / 2;                     // keys per thread
+            float s[HB];
+            tmem_ld32(tmem_sb + t_lane + ch * HB, s);
+            const int j0 = kt * BN + ch * HB;
+            // Masking only where the tile crosses a row's limits (the diagonal, a
+            // window's edge, rows beyond the entry): decided per warp.
+            if (!__all_sync(0xffffffffu, live && j0 + HB - 1 <= pos && j0 >= lo_row)) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[i] *= corr;
-                tmem_st32(tmem_o + t_lane + c, o);
+                for (int j = 0; j < HB; ++j) {
+                    const int key = j0 + j;
+                    if (!(live && key >= lo_row && key <= pos)) s[j] = -INFINITY;
+                }
+            }
+            float raw = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < HB; ++j) raw = fmaxf(raw, s[j]);
+            // the row's maximum over both halves: through shared memory, between the two warps of the row
+            {
+                float* xb = xchg + b * (2 * BM);
+                xb[ch * BM + row] = raw;
+                named_barrier(1 + (warp & 3), 64);
+                raw = fmaxf(raw, xb[(ch ^ 1) * BM + row]);
+            }
+            const float mx = fmaxf(m_run, raw * p.scale_log2);      // scale > 0: the maximum commutes
+            const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mx);
+            const float neg_base = (mx == -INFINITY) ? 0.f : -mx;
+            float sum = 0.f;
+            uint32_t packed[HB / 2];
+#pragma unroll
+            for (int j = 0; j < HB; j += 2) {
+                const float p0 = fast_exp2(fmaf(s[j], p.scale_log2, neg_base));
+                const float p1 = fast_exp2(fmaf(s[j + 1], p.scale_log2, neg_base));
+                sum += p0 + p1;
+                __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                packed[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            l_run = l_run * corr + sum;                    // this thread's half of the row's sum
+            m_run = mx;
+            // O += P V of the tile before is complete: the output may be rescaled
+            if (i > 0) {
+                if (!mbar_wait(o_done, (i - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
+                tc_fence_after();
+            }
+            // The weights of this thread's keys go over the scores they came from (both
+            // threads of the row have read theirs: they met at the barrier above).
+            tmem_st16_words(tmem_sb + t_lane + ch * (HB / 2), packed);
+            // rescale the output accumulator when some row of the warp moved its maximum
+            // (this thread: its half of the columns)
+            if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                for (int c = ch * (D / 2); c < (ch + 1) * (D / 2); c += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_o + t_lane + c, o);
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) o[k] *= corr;
+                    tmem_st32(tmem_o + t_lane + c, o);
+                }
             }
             tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[b]);
         }
-        fence_async_proxy();                               // P was written with ordinary stores
-        tc_fence_before();
-        __syncthreads();
-        // 4. O += P V
-        if (threadIdx.x == 0) {
-            tc_fence_after();
-            const uint64_t pd = smem_desc(p_tile, 0, 1024);
-            const uint64_t vd = smem_desc(v_tile, p.v_lbo, p.v_sbo);
-#pragma unroll
-            for (int k = 0; k < BN / 16; ++k)
-                // 16 keys further: 32 bytes in a P row; 16 rows = 2048 bytes in the value tile
-                umma_bf16(tmem_o, pd + 2 * k, vd + 128 * k, IDESC_O, (kt > first_tile || k > 0) ? 1u : 0u);
-            umma_commit(bar_o);
-        }
-        if (!mbar_wait(bar_o, phase, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
+        if (!mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
         tc_fence_after();
-        phase ^= 1;
-    }
-    cp_async_wait<0>();
 
-    // ---- result: o / l, this thread's row.  The tensor-memory loads are warp-wide
-    // (.sync.aligned): every thread of the warp runs them, whether its row exists or not.
-    {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        // ---- result: o / l, this thread's half of its row's columns.  The tensor-memory
+        // loads are warp-wide (.sync.aligned): every thread of the warp runs them, whether
+        // its row exists or not.
+        float* xl = xchg + (n_tiles & 1) * (2 * BM);       // not the buffer the last tile's maxima went through
+        xl[ch * BM + row] = l_run;
+        named_barrier(1 + (warp & 3), 64);
+        const float l_row = l_run + xl[(ch ^ 1) * BM + row];
+        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
         bf16* dst = p.out + ((size_t)(qs + (live ? tok : 0)) * p.n_q + h) * D;
 #pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
+        for (int c = ch * (D / 2); c < (ch + 1) * (D / 2); c += 32) {
             float o[32];
             tmem_ld32(tmem_o + t_lane + c, o);
             if (ok && live) {
                 uint4 pk[4];
                 uint32_t* w = reinterpret_cast<uint32_t*>(pk);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
-                    w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                for (int k = 0; k < 16; ++k) {
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(o[2 * k] * inv, o[2 * k + 1] * inv);
+                    w[k] = *reinterpret_cast<uint32_t*>(&h2);
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(dst + c)[i] = pk[i];
+                for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(dst + c)[k] = pk[k];
             }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
-    if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
-template <int D> int launch(const Params& p, int items, cudaStream_t s) {
+// ------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)ptr;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows; int cols, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows;
+    }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols; h = h * 1000003u ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+// The pool of one layer as a matrix bf16 [rows, D] (a row = one key or value of
+// one kv head); box = [box_rows, 64 columns], 128-byte swizzle, zeros outside.
+int pool_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiled fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int items, cudaStream_t s) {
     using C = Cfg<D>;
     static bool configured = false;
     if (!configured) {
@@ -421,7 +543,7 @@ template <int D> int launch(const Params& p, int items, cudaStream_t s) {
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(items, p.n_q), dim3(THREADS), C::SMEM, s, 1, p);
+    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(items, p.n_q), dim3(THREADS), C::SMEM, s, 1, mk, mv, p);
 }
 }  // namespace
 
@@ -429,21 +551,33 @@ extern "C" int kipp_attn_prefill_tc_supported(int head_dim, int n_q, int n_kv) {
     return (head_dim == 64 || head_dim == 128) && n_kv > 0 && n_q % n_kv == 0;
 }
 
+// Page sizes the kernel takes: a TMA box holds min(page_size, 64) rows of one page,
+// in whole 8-row swizzle groups.
+extern "C" int kipp_attn_prefill_tc_page_ok(int page_size) {
+    return page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0);
+}
+
 // Prompt portions: `work` lists (entry, first token) of every 128-token tile.
+// k_pages and v_pages: one layer's pool, bf16 [n_pages][n_kv][page_size][head_dim].
 extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_pages, const void* v_pages,
-                                    const int* q_start, const int* context_len, const int* block_table,
-                                    int table_width, int page_size, const int* work, int items, int n_q,
-                                    int n_kv, int head_dim, float scale, int window, int* status,
-                                    void* stream) {
+                                    int n_pages, const int* q_start, const int* context_len,
+                                    const int* block_table, int table_width, int page_size, const int* work,
+                                    int items, int n_q, int n_kv, int head_dim, float scale, int window,
+                                    int* status, void* stream) {
     if (items <= 0) return 0;
-    if (!kipp_attn_prefill_tc_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || status == nullptr)
+    if (!kipp_attn_prefill_tc_supported(head_dim, n_q, n_kv) || !kipp_attn_prefill_tc_page_ok(page_size) ||
+        n_pages <= 0 || window < 0 || status == nullptr)
         return KIPP_ERR_ARG;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 15))
         return -3;
+    const long long rows = (long long)n_pages * n_kv * page_size;
+    if (rows + BN > 0x7fffffffLL) return KIPP_ERR_ARG;
     Params p;
     p.out = (bf16*)out; p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
     p.q_start = q_start; p.context_len = context_len; p.block_table = block_table; p.work = work;
     p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
+    p.box_rows = page_size < BN ? page_size : BN;
+    p.rows_total = (int)rows;
     p.scale_log2 = scale * 1.4426950408889634f;
     // The value tile is the MN-major operand of O += P V: leading offset = the next
     // 64-column half of the tile, stride offset = the next 8 keys (checked against
@@ -451,6 +585,11 @@ extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_page
     p.v_lbo = (uint32_t)(BN * 128);
     p.v_sbo = 1024u;
     p.status = status;
+    CUtensorMap mk, mv;
+    int rc = pool_map(&mk, k_pages, rows, head_dim, p.box_rows);
+    if (rc) return rc;
+    rc = pool_map(&mv, v_pages, rows, head_dim, p.box_rows);
+    if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 64 ? launch<64>(p, items, s) : launch<128>(p, items, s);
+    return head_dim == 64 ? launch<64>(mk, mv, p, items, s) : launch<128>(mk, mv, p, items, s);
 }

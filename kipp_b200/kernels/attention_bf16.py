@@ -29,9 +29,15 @@ def decode_supported(head_dim: int, n_q: int, n_kv: int) -> bool:
     return bool(f(head_dim, n_q, n_kv))
 
 
-def prefill_tc_supported(head_dim: int, n_q: int, n_kv: int) -> bool:
+def prefill_tc_supported(head_dim: int, n_q: int, n_kv: int, page_size: int = 0) -> bool:
+    """Whether the tcgen05 portion kernel takes these sizes (with a page size:
+    also whether its TMA boxes fit the pages)."""
     f = _fn("attention_tc", "kipp_attn_prefill_tc_supported", [c_int, c_int, c_int])
-    return bool(f(head_dim, n_q, n_kv))
+    if not f(head_dim, n_q, n_kv):
+        return False
+    if page_size:
+        return bool(_fn("attention_tc", "kipp_attn_prefill_tc_page_ok", [c_int])(page_size))
+    return True
 
 
 PREFILL_TC = True           # prompt portions on tcgen05 where the sizes allow
@@ -41,13 +47,16 @@ PREFILL_TC_MIN_TOKENS = 64  # shorter portions waste a 128-row tile: they stay o
 def prefill_tc(out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv, head_dim, scale,
                window, status) -> None:
     """Portions of more than one token through the tcgen05 kernel (128-token tiles)."""
+    if not (k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape
+            and tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)):
+        raise KernelError("attn_prefill_tc: pages must be contiguous [pages, n_kv, page_size, head_dim]")
     f = _fn("attention_tc", "kipp_attn_prefill_tc",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
              c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(meta.q_start), _ptr(meta.context_len),
-             _ptr(block_table), block_table.shape[1], page_size, _ptr(meta.prefill_work128),
-             meta.n_prefill_items128, n_q, n_kv, head_dim, float(scale), int(window or 0),
-             _ptr(status), _stream()), "attn_prefill_tc")
+    _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(meta.q_start),
+             _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
+             _ptr(meta.prefill_work128), meta.n_prefill_items128, n_q, n_kv, head_dim, float(scale),
+             int(window or 0), _ptr(status), _stream()), "attn_prefill_tc")
 
 
 def choose(meta, n_q, n_kv, head_dim, page_size) -> str:
@@ -80,7 +89,7 @@ def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv,
     work, items = (meta.prefill_work, meta.n_prefill_items) if use_decode else (meta.all_work, meta.n_all_items)
     longest = max((n for n in meta.q_lens if n > 1), default=0)
     if (PREFILL_TC and meta.n_prefill_items128 and longest >= PREFILL_TC_MIN_TOKENS
-            and (use_decode or meta.n_decode == 0) and prefill_tc_supported(head_dim, n_q, n_kv)
+            and (use_decode or meta.n_decode == 0) and prefill_tc_supported(head_dim, n_q, n_kv, page_size)
             and all(t.data_ptr() % 16 == 0 for t in (out, q, k_pages, v_pages))):
         prefill_tc(out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv, head_dim, scale, window,
                    status)

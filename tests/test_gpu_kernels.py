@@ -304,12 +304,14 @@ def test_attention_simt(shape, window, dtype):
 @pytest.mark.parametrize("window", [None, 37, 300])
 @pytest.mark.parametrize("shape", [dict(D=64, nq=4, nkv=2, page=16), dict(D=128, nq=8, nkv=2, page=16),
                                    dict(D=128, nq=16, nkv=1, page=8), dict(D=64, nq=3, nkv=3, page=32),
-                                   dict(D=128, nq=40, nkv=2, page=16)])
+                                   dict(D=128, nq=40, nkv=2, page=16), dict(D=128, nq=4, nkv=2, page=64),
+                                   dict(D=64, nq=2, nkv=1, page=128), dict(D=128, nq=2, nkv=2, page=4)])
 def test_attention_tensor_core(shape, window):
     """Prompt portions and single decoded tokens through the tensor-core kernels:
     portions of 64 tokens and more through tcgen05, shorter ones and decoded
-    tokens through mma.sync (the last shape has a group of 20 > 16: everything
-    goes through the mma.sync portion kernel); then the same with tcgen05 off."""
+    tokens through mma.sync (a group of 20 > 16 and a page of 4 slots go through
+    the mma.sync portion kernel throughout; pages of 64 and 128 slots hold a whole
+    key tile); then the same with tcgen05 off."""
     from kipp_b200.kernels import attention_bf16
     D, nq, nkv, page = shape["D"], shape["nq"], shape["nkv"], shape["page"]
     assert attention_bf16.supported(D, nq, nkv)
