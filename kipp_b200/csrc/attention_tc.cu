@@ -263,8 +263,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BN;
     pdl_wait();
 
-    const int entry = p.work[2 * blockIdx.x], tile_tok = p.work[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, g = h / (p.n_q / p.n_kv);
+    // Grid (heads, tiles), the last tile of the list first: within an entry the later
+    // tiles see more keys, and the long ones should not be the last to start; the
+    // heads of a tile, which share its keys and values, start together.
+    const int item = gridDim.y - 1 - blockIdx.y;
+    const int entry = p.work[2 * item], tile_tok = p.work[2 * item + 1];
+    const int h = blockIdx.x, g = h / (p.n_q / p.n_kv);
     const int qs = p.q_start[entry], q_len = p.q_start[entry + 1] - qs;
     const int ctx = p.context_len[entry];
     // keys the tile may see: from the first token's window start to the last token
@@ -543,7 +547,7 @@ template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(items, p.n_q), dim3(THREADS), C::SMEM, s, 1, mk, mv, p);
+    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, p);
 }
 }  // namespace
 
@@ -565,6 +569,7 @@ extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_page
                                     int items, int n_q, int n_kv, int head_dim, float scale, int window,
                                     int* status, void* stream) {
     if (items <= 0) return 0;
+    if (items > 65535) return KIPP_ERR_ARG;
     if (!kipp_attn_prefill_tc_supported(head_dim, n_q, n_kv) || !kipp_attn_prefill_tc_page_ok(page_size) ||
         n_pages <= 0 || window < 0 || status == nullptr)
         return KIPP_ERR_ARG;

@@ -9,6 +9,8 @@ kernels per layer and token from the host, src/cuda/kipp_cuda.cu:358-462.)
 """
 from __future__ import annotations
 
+import gc
+
 from typing import Optional
 
 import torch
@@ -42,9 +44,19 @@ class DecodeGraph:
             engine._forward(StepContext(engine, meta))      # eager once: buffers, attributes, tensor maps
             torch.cuda.synchronize(engine.runtime.device)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                # a fresh context: what a forward pass computes once per step must be in the graph
-                self.logits = engine._forward(StepContext(engine, meta))
+            # No garbage collection inside the capture: collecting an engine that is
+            # no longer used destroys its graphs, which CUDA forbids while any stream
+            # captures and which would invalidate this capture.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    # a fresh context: what a forward pass computes once per step must be in the graph
+                    self.logits = engine._forward(StepContext(engine, meta))
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.graph = graph
             self.generation = self._generation()
             self.launches = engine.last_forward_launches
