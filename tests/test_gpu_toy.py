@@ -1,6 +1,8 @@
 """Generality of the parts: a toy mixer with state of its own, a layer that is
-run twice and a layer that reads another layer's cache are defined HERE,
-registered, built and stepped without a change to the framework's files."""
+run twice, a layer that reads another layer's cache, a feed-forward with
+routing, a scaled partial rotation and positions learned at the embedding are
+defined HERE, registered, built and stepped without a change to the
+framework's files."""
 import dataclasses
 import math
 import os
@@ -193,3 +195,237 @@ def test_toy_architecture_with_state_repeated_layer_and_shared_cache(tmp_path, s
         assert eng.cache.slots.free_slots == 3
     finally:
         unregister_architecture("ToyStateLM")
+
+
+# ---------------------------------------------------------------------------------------
+# A feed-forward with routing, a rotation of another kind and a position encoding that is
+# not a rotation at all: toy parts again, defined here, beside the framework's attention.
+def _register_routed():
+    from kipp_b200.config import register_architecture, unregister_architecture
+    from kipp_b200.config.base import ModelConfig
+    from kipp_b200.models.spec import LayerRun, ModelSpec
+    from kipp_b200.parts import (AttentionMixer, FeedForward, NoPositionEncoding, OutputHead, PositionEncoding,
+                                 PreNormBlock, RMSNorm, SwiGLUFeedForward, TokenEmbedding)
+    from kipp_b200.weights import TensorSpec
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyRoutedConfig(ModelConfig):
+        vocab_size: int = 61
+        hidden_size: int = 40
+        num_experts: int = 5
+        experts_per_token: int = 2
+        expert_size: int = 24
+        intermediate_size: int = 56
+        max_positions: int = 96
+        rotary_dim: int = 8
+        rope_theta: float = 500.0
+        rope_scale: float = 4.0
+        rms_norm_eps: float = 1e-5
+        initializer_range: float = 0.3
+
+    class RoutedFeedForward(FeedForward):
+        """Router logits and softmax in float32, the experts_per_token largest
+        probabilities renormalised, each chosen expert a SwiGLU of its own.
+        Plain torch calls: a test double, not a kernel."""
+
+        def __init__(self, hidden, experts, top_k, size):
+            self.hidden, self.experts, self.top_k, self.size = hidden, experts, top_k, size
+
+        def tensor_specs(self, prefix):
+            e, h, s = self.experts, self.hidden, self.size
+            return [TensorSpec(prefix + "router.weight", (e, h)), TensorSpec(prefix + "experts.gate", (e, s, h)),
+                    TensorSpec(prefix + "experts.up", (e, s, h)), TensorSpec(prefix + "experts.down", (e, h, s))]
+
+        def bind(self, tensors, prefix, runtime):
+            get = lambda n: tensors[prefix + n].to(runtime.device).float()
+            self.router, self.gate, self.up, self.down = (get("router.weight"), get("experts.gate"),
+                                                          get("experts.up"), get("experts.down"))
+
+        def forward(self, ctx, h, residual):
+            T = ctx.meta.tokens
+            x = h[:T].float()
+            prob = torch.softmax(x @ self.router.t(), dim=-1)
+            top, idx = torch.topk(prob, self.top_k, dim=-1)
+            top = top / top.sum(-1, keepdim=True)
+            for e in range(self.experts):
+                rows, slot = (idx == e).nonzero(as_tuple=True)
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows]
+                act = torch.nn.functional.silu(xe @ self.gate[e].t()) * (xe @ self.up[e].t())
+                residual[:T].index_add_(0, rows, (act @ self.down[e].t()) * top[rows, slot, None])
+
+    class ScaledPartialRotary(PositionEncoding):
+        """The first rotary_dim dims of a head rotate, with frequencies divided
+        by a scale (positions stretched): another table than the dense layer's."""
+
+        def __init__(self, rotary_dim, theta, scale):
+            self.rotary_dim, self.theta, self.scale = rotary_dim, theta, scale
+            self._dev = {}
+
+        def frequencies(self):
+            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            return (self.theta ** (-2.0 * i / self.rotary_dim) / self.scale).float()
+
+        def table_key(self):
+            return ("toy-scaled", self.theta, self.rotary_dim, self.scale)
+
+        def inv_freq(self, device):
+            if str(device) not in self._dev:
+                self._dev[str(device)] = self.frequencies().to(device)
+            return self._dev[str(device)]
+
+    class LearnedPositionEmbedding(TokenEmbedding):
+        """x_t = E[id_t] + P[position_t]: positions enter at the bottom, not in the mixer."""
+
+        def __init__(self, vocab, hidden, max_positions):
+            super().__init__(vocab, hidden)
+            self.max_positions = max_positions
+
+        def tensor_specs(self, prefix):
+            return super().tensor_specs(prefix) + [
+                TensorSpec("model.embed_positions.weight", (self.max_positions, self.hidden_size))]
+
+        def bind(self, tensors, prefix, runtime):
+            super().bind(tensors, prefix, runtime)
+            self.positions = tensors["model.embed_positions.weight"].to(runtime.device).float()
+
+        def forward(self, ctx):
+            x = super().forward(ctx)
+            T = ctx.meta.tokens
+            x[:T] += self.positions[ctx.meta.positions[:T].long()]
+            return x
+
+    def build(c):
+        emb = LearnedPositionEmbedding(c.vocab_size, c.hidden_size, c.max_positions)
+        norm = lambda: RMSNorm(c.hidden_size, c.rms_norm_eps)
+        rotary = ScaledPartialRotary(c.rotary_dim, c.rope_theta, c.rope_scale)
+        layers = [
+            ("model.layers.0.", PreNormBlock(
+                norm(), AttentionMixer(c.hidden_size, 4, 2, 16, NoPositionEncoding(), qk_norm_eps=c.rms_norm_eps),
+                norm(), RoutedFeedForward(c.hidden_size, c.num_experts, c.experts_per_token, c.expert_size))),
+            ("model.layers.1.", PreNormBlock(
+                norm(), AttentionMixer(c.hidden_size, 6, 3, 16, rotary, qk_norm_eps=c.rms_norm_eps),
+                norm(), SwiGLUFeedForward(c.hidden_size, c.intermediate_size))),
+        ]
+        return ModelSpec(config=c, hidden_size=c.hidden_size, vocab_size=c.vocab_size, embedding=emb,
+                         layers=layers, order=[LayerRun(0, cache=0), LayerRun(1, cache=1)],
+                         final_norm=("model.norm.", norm()),
+                         head=("lm_head.", OutputHead(c.vocab_size, c.hidden_size, tied_to=emb)),
+                         max_positions=c.max_positions)
+
+    unregister_architecture("ToyRoutedLM")
+    register_architecture("ToyRoutedLM", ToyRoutedConfig, build)
+    return ToyRoutedConfig, ScaledPartialRotary
+
+
+def plain_routed(cfg, w, tokens, inv_freq):
+    """Whole sequence, float64.  Returns the logits and, per token, the gap
+    between the last chosen and the first rejected router probability."""
+    T = len(tokens)
+    eps = cfg.rms_norm_eps
+    x = P.plain_embedding(w["model.embed_tokens.weight"], tokens) + w["model.embed_positions.weight"][:T].double()
+
+    def attention(x, pre, heads, kv_heads, rotate):
+        n = P.plain_rmsnorm(x, w[pre + "input_layernorm.weight"], eps)
+        q = P.plain_linear(n, w[pre + "self_attn.q_proj.weight"]).reshape(T, heads, 16)
+        k = P.plain_linear(n, w[pre + "self_attn.k_proj.weight"]).reshape(T, kv_heads, 16)
+        v = P.plain_linear(n, w[pre + "self_attn.v_proj.weight"]).reshape(T, kv_heads, 16)
+        q = P.plain_head_norm(q, w[pre + "self_attn.q_norm.weight"], eps)
+        k = P.plain_head_norm(k, w[pre + "self_attn.k_norm.weight"], eps)
+        if rotate:
+            rot = cfg.rotary_dim
+            # angle = float32(position) * float32(frequency), as the kernel forms it
+            angle = (torch.arange(T, dtype=torch.float32)[:, None] * inv_freq[None, :]).double()[:, None, :]
+
+            def turn(h):
+                lo, hi = h[..., :rot // 2], h[..., rot // 2:rot]
+                return torch.cat([lo * torch.cos(angle) - hi * torch.sin(angle),
+                                  hi * torch.cos(angle) + lo * torch.sin(angle), h[..., rot:]], -1)
+            q, k = turn(q), turn(k)
+        a = P.plain_attention(q, k, v).reshape(T, heads * 16)
+        return x + P.plain_linear(a, w[pre + "self_attn.o_proj.weight"])
+
+    x = attention(x, "model.layers.0.", 4, 2, False)
+    pre = "model.layers.0."
+    n = P.plain_rmsnorm(x, w[pre + "post_attention_layernorm.weight"], eps)
+    prob = torch.softmax(P.plain_linear(n, w[pre + "mlp.router.weight"]), dim=-1)
+    ranked = torch.sort(prob, dim=-1, descending=True)
+    k_top = cfg.experts_per_token
+    gaps = ranked.values[:, k_top - 1] - ranked.values[:, k_top]
+    out = torch.zeros_like(x)
+    for t in range(T):
+        chosen = ranked.indices[t, :k_top]
+        share = prob[t, chosen] / prob[t, chosen].sum()
+        for e, s in zip(chosen.tolist(), share):
+            act = P.plain_silu(P.plain_linear(n[t], w[pre + "mlp.experts.gate"][e])) * \
+                P.plain_linear(n[t], w[pre + "mlp.experts.up"][e])
+            out[t] += s * P.plain_linear(act, w[pre + "mlp.experts.down"][e])
+    x = x + out
+    x = attention(x, "model.layers.1.", 6, 3, True)
+    pre = "model.layers.1."
+    n = P.plain_rmsnorm(x, w[pre + "post_attention_layernorm.weight"], eps)
+    x = x + P.plain_feed_forward(n, w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"],
+                                 w[pre + "mlp.down_proj.weight"])
+    n = P.plain_rmsnorm(x, w["model.norm.weight"], eps)
+    return P.plain_linear(n, w["model.embed_tokens.weight"]), gaps
+
+
+def test_toy_routed_feed_forward_and_other_position_encodings(tmp_path):
+    """Layer by layer different parts: a routed feed-forward under an attention
+    without rotation (positions are learned vectors added at the embedding),
+    then the dense feed-forward under an attention with a scaled, partial
+    rotation.  Whole sequences and mixed portions against the plain model."""
+    ToyRoutedConfig, ScaledPartialRotary = _register_routed()
+    from kipp_b200.config import load_config, unregister_architecture
+    from kipp_b200.engine import Engine, StepEntry
+    from kipp_b200.weights import write_random_model
+    from tiny import read_weights
+    try:
+        cfg = ToyRoutedConfig(architecture="ToyRoutedLM")
+        folder = write_random_model(str(tmp_path / "routed"), cfg, seed=7, sigma=cfg.initializer_range)
+        assert load_config(folder) == cfg
+        w = read_weights(folder)
+        inv_freq = ScaledPartialRotary(cfg.rotary_dim, cfg.rope_theta, cfg.rope_scale).frequencies()
+        eng = Engine.from_folder(folder, dtype="float32", page_size=8, cache_tokens=160, max_requests=3)
+        assert [len(g.cache_ids) for g in eng.cache.groups] == [1, 1]     # 2 and 3 kv heads: pages of their own
+        g = torch.Generator().manual_seed(3)
+        seqs = {r: torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
+                for r, n in (("a", 40), ("b", 23), ("c", 9))}
+        want = {r: plain_routed(cfg, w, s, inv_freq) for r, s in seqs.items()}
+        # a token whose router choice hangs on less than float32 can tell is not compared
+        sure = {r: (gaps > 1e-5) for r, (_, gaps) in want.items()}
+        assert sum(int(s.sum()) for s in sure.values()) >= 0.9 * sum(len(s) for s in seqs.values())
+        got = eng.step([StepEntry("a", seqs["a"], list(range(40)))], check=True).cpu()
+        first_unsure = int((~sure["a"]).nonzero()[0]) if (~sure["a"]).any() else 40
+        assert nmse(got[:first_unsure], want["a"][0][:first_unsure]) < 1e-10
+        eng.finish("a")
+        cuts = {"a": [3, 20, 1, 1, 15], "b": [22, 1], "c": [2, 2, 5]}
+        at = {r: 0 for r in seqs}
+        live = ["a", "b", "c"]
+        rows = {}
+        while live:
+            entries = []
+            for r in live:
+                n = cuts[r].pop(0)
+                entries.append(StepEntry(r, seqs[r][at[r]:at[r] + n], list(range(n))))
+            out = eng.step(entries, check=True).cpu()
+            k = 0
+            for e in entries:
+                for i in range(len(e.tokens)):
+                    rows[(e.request, at[e.request] + i)] = out[k]
+                    k += 1
+                at[e.request] += len(e.tokens)
+            for r in list(live):
+                if not cuts[r]:
+                    live.remove(r)
+                    eng.finish(r)
+        checked = 0
+        for (r, pos), row in rows.items():
+            if bool(sure[r][:pos + 1].all()):          # an unsure choice changes every later position
+                assert nmse(row, want[r][0][pos]) < 1e-10, (r, pos)
+                checked += 1
+        assert checked >= 0.6 * len(rows)
+        eng.cache.check()
+    finally:
+        unregister_architecture("ToyRoutedLM")
