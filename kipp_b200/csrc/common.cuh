@@ -76,11 +76,11 @@ static inline bool kipp_pdl_enabled() {
     return cached == 1;
 }
 
-// Launches `kernel` with the package's attributes; cluster_z > 1 makes the
-// grid's z dimension one thread-block cluster.
+// Launches `kernel` with the package's attributes; a cluster of more than one
+// CTA makes thread-block clusters of that shape.
 template <typename... KArgs, typename... Args>
-static inline int kipp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              int cluster_z, Args&&... args) {
+static inline int kipp_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, dim3 cluster, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -93,11 +93,11 @@ static inline int kipp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_z > 1) {
+    if (cluster.x * cluster.y * cluster.z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     cfg.attrs = attr;
@@ -105,6 +105,14 @@ static inline int kipp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
     return 0;
+}
+
+// cluster_z > 1 makes the grid's z dimension one thread-block cluster.
+template <typename... KArgs, typename... Args>
+static inline int kipp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_z, Args&&... args) {
+    return kipp_launch_cluster(kernel, grid, block, smem, stream, dim3(1, 1, cluster_z > 1 ? cluster_z : 1),
+                               static_cast<Args&&>(args)...);
 }
 
 static inline int kipp_launch_status() {

@@ -36,6 +36,9 @@
 // two accumulators in tensor memory (the epilogue of a tile runs under the MMAs
 // of the next), and the residual add leaves as reducing TMA stores.  The
 // feature tile is chosen so that the rounds of tiles over the SMs are full.
+// From 1,024 tokens on, store and SwiGLU products take a third kernel of the
+// same build in which a PAIR of CTAs shares one MMA (cta_group::2, 256 tokens
+// per tile, each CTA holding half of the weight tile).
 //
 // No multicast: every CTA fetches its own tiles.
 #include "common.cuh"
@@ -136,6 +139,67 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                      smem_u32(bar))
                  : "memory");
+}
+// ---- a pair of CTAs (a cluster of two) on one MMA: cta_group::2 forms
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Arrives on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+// The address, in the cluster's shared window, of `bar` at the same offset in CTA `rank`.
+__device__ __forceinline__ uint32_t mbar_in_cta(uint64_t* bar, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
+    return remote;
+}
+// TMA load into this CTA's shared memory whose bytes are counted on a barrier of either
+// CTA of the pair (`bar_cluster_addr` from mbar_in_cta).  No multicast: every CTA
+// fetches what it holds.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+// Both CTAs of the pair run these (one warp each): the columns are taken in both.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[256 x N] (+)= A[256 x 16] B[N x 16]^T: 128 rows of A and D and N/2 rows of B live
+// in each CTA, at the same shared- and tensor-memory addresses.  Issued by one thread
+// of the pair's first CTA.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` (same offset) in both CTAs when all MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+        : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -528,6 +592,42 @@ __device__ __forceinline__ void epilogue_row16(const Params& p, const float* v, 
     }
 }
 
+// Epilogue of one 128-token x TILE_N tile by one warp: its 32 tokens (tensor-memory
+// lanes of `taddr`), its share `cg` (0 or 1) of the feature columns.
+template <int TILE_N, bool REDUCE>
+__device__ __forceinline__ void tokm_epilogue_tile(const Params& p, const CUtensorMap* map_c, uint32_t taddr,
+                                                   uint8_t* box, int t_warp, int f0, int cg, int lane, bool ok) {
+    constexpr int HALF = (TILE_N / 2 + 15) / 16 * 16;
+    const int t = t_warp + lane;
+    if constexpr (REDUCE) {
+#pragma unroll 1
+        for (int c = cg * RED_BOX; c < TILE_N; c += 2 * RED_BOX) {
+            float v[32];
+            tmem_ld16(taddr + c, v);
+            tmem_ld16(taddr + c + 16, v + 16);
+            if (lane == 0) bulk_wait_read();        // the unit has read the previous box
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && ok && t_warp < p.tokens && f0 + c < p.features) {
+                tma_reduce_add_2d(map_c, box, f0 + c, t_warp);
+                bulk_commit();
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
+            float v[16];
+            tmem_ld16(taddr + c, v);
+            if (ok) epilogue_row16(p, v, t, f0 + c);
+        }
+    }
+}
+
 // Persistent: one CTA per SM walks over the tiles (token tiles fastest, so CTAs
 // that run together share a weight tile in L2).  Two accumulators in tensor
 // memory: while the epilogue warps drain tile i, the MMA warp already works on
@@ -641,44 +741,16 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int q = warp & 3;                    // tensor-memory lane quarter = 32 tokens
         const int cg = (warp - 2) >> 2;            // half of the feature columns
         pdl_wait();
-        constexpr int HALF = (TILE_N / 2 + 15) / 16 * 16;
         uint8_t* box = staging + (size_t)(warp - 2) * RED_BYTES;
         int tile_iter = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tile_iter) {
             const int b = tile_iter & 1, use = tile_iter >> 1;
             const int t_warp = (tile % m_tiles) * UMMA_M + q * 32, f0 = (tile / m_tiles) * TILE_N;
-            const int t = t_warp + lane;
             if (ok && !mbar_wait(&acc_full[b], use & 1, abort_flag)) ok = false;
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + b * C::TMEM_COLS + ((uint32_t)(q * 32) << 16);
-            if constexpr (REDUCE) {
-#pragma unroll 1
-                for (int c = cg * RED_BOX; c < TILE_N; c += 2 * RED_BOX) {
-                    float v[32];
-                    tmem_ld16(taddr + c, v);
-                    tmem_ld16(taddr + c + 16, v + 16);
-                    if (lane == 0) bulk_wait_read();        // the unit has read the previous box
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<float4*>(box + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                            make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0 && ok && t_warp < p.tokens && f0 + c < p.features) {
-                        tma_reduce_add_2d(&map_c, box, f0 + c, t_warp);
-                        bulk_commit();
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + c, v);
-                    if (ok) epilogue_row16(p, v, t, f0 + c);
-                }
-            }
+            tokm_epilogue_tile<TILE_N, REDUCE>(p, &map_c, taddr, box, t_warp, f0, cg, lane, ok);
             // this warp has read its part of the accumulator: hand it back
             tcgen05_fence_before();
             __syncwarp();
@@ -690,6 +762,172 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
     if (warp == 1) tmem_dealloc(tmem_base, 2 * C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------
+// The same work with a PAIR of CTAs on one MMA (cta_group::2): a tile is 256 tokens x
+// TILE_N features; CTA r of the pair holds tokens [128 r, 128 r + 128) and the
+// weight rows [r TILE_N/2, (r + 1) TILE_N/2) of the tile, and gets the accumulator
+// of its 128 tokens in its own tensor memory.  Each SM then writes and reads half
+// of the weight tile instead of all of it: a 128 x 256 x 64 block costs 64 KB of
+// shared-memory traffic per 512 tensor cycles instead of 96 KB, under the 128 B/cycle
+// the shared memory gives (the one-CTA kernel is capped near 68 % by that).
+//
+// Hand-overs.  Every CTA fills its own ring by TMA, but the bytes of both are counted
+// on full[s] of the first CTA (armed there with twice a stage's bytes): its MMA
+// thread waits for that one barrier, issues the MMAs and commits to empty[s] in
+// both CTAs; after a tile it commits to acc_full[b] in both.  The epilogue warps of
+// both CTAs arrive on acc_empty[b] of the first CTA (16 arrivals).  A cluster
+// barrier stands after the barrier set-up and before the tensor memory is given
+// back.  (A first version let a thread of the second CTA relay "my stage is full"
+// to the first: one relay per K block took about a microsecond, three times the
+// MMAs of the block.)
+template <int TILE_N, bool REDUCE> struct CfgPair {
+    static constexpr int HALF_N = TILE_N / 2;                    // weight rows per CTA
+    static constexpr int X_BYTES = UMMA_M * TILE_K * 2;
+    static constexpr int W_BYTES = HALF_N * TILE_K * 2;
+    static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
+    static constexpr int STAGING = REDUCE ? 8 * RED_BYTES : 0;
+    static constexpr int BUDGET = 227 * 1024 - 1024 - 512 - STAGING;
+    static constexpr int STAGES = BUDGET / STAGE_BYTES > 8 ? 8 : BUDGET / STAGE_BYTES;
+    static constexpr int TMEM_COLS = TILE_N <= 128 ? 128 : 256;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING + 1024 + 512;
+};
+
+template <int TILE_N, bool REDUCE>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_c, const Params p) {
+    using C = CfgPair<TILE_N, REDUCE>;
+    static_assert(TILE_N % RED_BOX == 0 && TILE_N >= 2 * RED_BOX && TILE_N <= 256, "feature tile");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* staging = tiles + (size_t)C::STAGES * C::STAGE_BYTES;        // 1024-byte aligned
+    uint64_t* full = (uint64_t*)(staging + C::STAGING);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_full = empty + C::STAGES;        // [2]
+    uint64_t* acc_empty = acc_full + 2;            // [2], used in the first CTA only
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_kb = (p.K + TILE_K - 1) / TILE_K;
+    const int m_tiles = (p.tokens + 2 * UMMA_M - 1) / (2 * UMMA_M);
+    const int n_tiles = (p.features + TILE_N - 1) / TILE_N;
+    const int total_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(&full[s], 1); mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 16); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, 2 * C::TMEM_COLS);
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                             // the other CTA's barriers exist before anyone arrives on them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        if (lane == 0 && pair < total_tiles) {
+            const int ahead = min(n_kb, C::STAGES);
+            {
+                const int f0 = (pair / m_tiles) * TILE_N + (int)rank * C::HALF_N;
+                const int t0 = (pair % m_tiles) * (2 * UMMA_M) + (int)rank * UMMA_M;
+                for (int i = 0; i < ahead; ++i) {
+                    if (rank == 0) mbar_expect_tx(&full[i], 2 * C::STAGE_BYTES);
+                    tma_load_2d_pair(tiles + (size_t)i * C::STAGE_BYTES + C::X_BYTES, &map_w, mbar_in_cta(&full[i], 0),
+                                     i * TILE_K, f0);
+                }
+                pdl_wait();
+                for (int i = 0; i < ahead; ++i)
+                    tma_load_2d_pair(tiles + (size_t)i * C::STAGE_BYTES, &map_x, mbar_in_cta(&full[i], 0), i * TILE_K,
+                                     t0);
+            }
+            int it = ahead;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+                const int f0 = (tile / m_tiles) * TILE_N + (int)rank * C::HALF_N;
+                const int t0 = (tile % m_tiles) * (2 * UMMA_M) + (int)rank * UMMA_M;
+                for (int i = (tile == pair ? ahead : 0); i < n_kb; ++i, ++it) {
+                    const int s = it % C::STAGES;
+                    if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* xt = tiles + (size_t)s * C::STAGE_BYTES;
+                    const uint32_t bar = mbar_in_cta(&full[s], 0);
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * C::STAGE_BYTES);
+                    tma_load_2d_pair(xt, &map_x, bar, i * TILE_K, t0);
+                    tma_load_2d_pair(xt + C::X_BYTES, &map_w, bar, i * TILE_K, f0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ------------------------------------------------------------ MMA issuer (first CTA)
+            constexpr uint32_t idesc = umma_idesc(2 * UMMA_M, TILE_N);
+            int it = 0, tile_iter = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++tile_iter) {
+                const int b = tile_iter & 1, use = tile_iter >> 1;
+                if (tile_iter >= 2 && !mbar_wait(&acc_empty[b], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t acc = tmem_base + b * C::TMEM_COLS;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1;
+                    if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t xa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+                    const uint64_t xd = umma_smem_desc(xa), wd = umma_smem_desc(xa + C::X_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
+                        umma_bf16_pair(acc, xd + 2 * k, wd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);
+                }
+                if (ok) umma_commit_pair(&acc_full[b]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- epilogue warps 2..9 (both CTAs)
+        const int q = warp & 3;                    // tensor-memory lane quarter = 32 tokens
+        const int cg = (warp - 2) >> 2;            // half of the feature columns
+        pdl_wait();
+        uint8_t* box = staging + (size_t)(warp - 2) * RED_BYTES;
+        int tile_iter = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles; tile += n_pairs, ++tile_iter) {
+            const int b = tile_iter & 1, use = tile_iter >> 1;
+            const int t_warp = (tile % m_tiles) * (2 * UMMA_M) + (int)rank * UMMA_M + q * 32;
+            const int f0 = (tile / m_tiles) * TILE_N;
+            if (ok && !mbar_wait(&acc_full[b], use & 1, abort_flag)) ok = false;
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + b * C::TMEM_COLS + ((uint32_t)(q * 32) << 16);
+            tokm_epilogue_tile<TILE_N, REDUCE>(p, &map_c, taddr, box, t_warp, f0, cg, lane, ok);
+            // this warp has read its part of the accumulator: hand it back to the first CTA
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(&acc_empty[b]);
+                else mbar_arrive_remote(&acc_empty[b], 0);
+            }
+        }
+        if (REDUCE && lane == 0) bulk_wait_all();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
+    cluster_sync_all();                             // no MMA of the pair is in flight, no arrival under way
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 2 * C::TMEM_COLS);
 }
 
 // ------------------------------------------------------------------------ host side
@@ -804,19 +1042,51 @@ int launch_tokm_n(int tile_n, const CUtensorMap& mw, const CUtensorMap& mx, cons
     return KIPP_ERR_ARG;
 }
 
+template <int TILE_N, bool REDUCE>
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, const Params& p, int total,
+                cudaStream_t s) {
+    using C = CfgPair<TILE_N, REDUCE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TILE_N, REDUCE>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    // persistent: at most one pair of CTAs per pair of SMs
+    const int pairs = sm_count() / 2;
+    // the two CTAs of an MMA pair are neighbours along x
+    return kipp_launch_cluster(gemm_tc_pair_kernel<TILE_N, REDUCE>, dim3(2 * (total < pairs ? total : pairs)),
+                               dim3(THREADS), C::SMEM, s, dim3(2, 1, 1), mw, mx, mc, p);
+}
+template <bool REDUCE>
+int launch_pair_n(int tile_n, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, const Params& p,
+                  int total, cudaStream_t s) {
+    switch (tile_n) {
+    case 128: return launch_pair<128, REDUCE>(mw, mx, mc, p, total, s);
+    case 160: return launch_pair<160, REDUCE>(mw, mx, mc, p, total, s);
+    case 192: return launch_pair<192, REDUCE>(mw, mx, mc, p, total, s);
+    case 224: return launch_pair<224, REDUCE>(mw, mx, mc, p, total, s);
+    case 256: return launch_pair<256, REDUCE>(mw, mx, mc, p, total, s);
+    }
+    return KIPP_ERR_ARG;
+}
+
 // Feature tile of the persistent kernel: the CTAs take the tiles in rounds, so
 // the cost is rounds x (time of a tile); a tile's time grows with its width
 // plus a fixed part.  For 2,048 tokens x 2,560 features, 256 wide gives 160
 // tiles = two rounds of which the second is nearly empty; 160 wide gives 256
 // tiles = two well-filled rounds of shorter tiles.
-int pick_tile_n(int tokens, int features) {
-    const int sms = sm_count();
-    const int m_tiles = (tokens + UMMA_M - 1) / UMMA_M;
+// `pair`: tiles of 256 tokens, taken in rounds by the pairs of SMs.
+int pick_tile_n(int tokens, int features, bool pair = false) {
+    const int units = pair ? sm_count() / 2 : sm_count();
+    const int rows = pair ? 2 * UMMA_M : UMMA_M;
+    const int m_tiles = (tokens + rows - 1) / rows;
     int best = 256;
     long long best_cost = -1;
     for (int n = 256; n >= 128; n -= 32) {
         const long long tiles = (long long)m_tiles * ((features + n - 1) / n);
-        const long long cost = ((tiles + sms - 1) / sms) * (n + TOKM_TILE_FIXED);
+        const long long cost = ((tiles + units - 1) / units) * (n + TOKM_TILE_FIXED);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = n; }
     }
     return best;
@@ -893,10 +1163,17 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
     const bool c_map_ok = epilogue != EPI_ADD || (ldc % 4 == 0 && ((uintptr_t)C & 15) == 0);
     if ((want_tile == 0 && want_tile_f == 0 && tokens >= 512 && c_map_ok) || want_tile_f < 0) {
         const bool reduce = epilogue == EPI_ADD && c_map_ok;     // else a thread per token adds in place
-        const int tile_n = want_tile_f < 0 ? -want_tile_f : pick_tile_n(tokens, features);
+        // want_tile_f: -N = one CTA per tile, -(1000 + N) = a pair of CTAs per 256-token tile
+        // By default: the pair kernel from 1,024 tokens on, except for the residual
+        // add (measured 8-12 % faster for store and SwiGLU at 1,024 and 2,048 tokens,
+        // no faster for the add, whose 2,560-feature shapes are bound by the rounds).
+        const bool pair = want_tile_f < 0 ? want_tile_f <= -1000 : (tokens >= 1024 && epilogue != EPI_ADD);
+        const int tile_n = want_tile_f <= -1000 ? -want_tile_f - 1000
+                           : want_tile_f < 0    ? -want_tile_f
+                                                : pick_tile_n(tokens, features, pair);
         if (tile_n < 128 || tile_n > 256 || tile_n % 32) return KIPP_ERR_ARG;
         CUtensorMap mw, mx, mc;
-        int rc = make_map(&mw, W, features, K, ldw, tile_n);
+        int rc = make_map(&mw, W, features, K, ldw, pair ? tile_n / 2 : tile_n);
         if (rc) return rc;
         rc = make_map(&mx, X, tokens, K, ldx, UMMA_M);
         if (rc) return rc;
@@ -910,9 +1187,13 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
         p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
         p.tokens = tokens; p.features = features; p.K = K; p.ldc = ldc;
         p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
-        const long long total = (long long)((tokens + UMMA_M - 1) / UMMA_M) * ((features + tile_n - 1) / tile_n);
+        const int rows = pair ? 2 * UMMA_M : UMMA_M;
+        const long long total = (long long)((tokens + rows - 1) / rows) * ((features + tile_n - 1) / tile_n);
         if (total > 0x7fffffffLL) return KIPP_ERR_ARG;
         cudaStream_t s = (cudaStream_t)stream;
+        if (pair)
+            return reduce ? launch_pair_n<true>(tile_n, mw, mx, mc, p, (int)total, s)
+                          : launch_pair_n<false>(tile_n, mw, mx, mc, p, (int)total, s);
         return reduce ? launch_tokm_n<true>(tile_n, mw, mx, mc, p, (int)total, s)
                       : launch_tokm_n<false>(tile_n, mw, mx, mc, p, (int)total, s);
     }

@@ -112,18 +112,20 @@ def test_gemm_tensor_core(shape, epilogue):
 
 
 @pytest.mark.parametrize("epilogue", ["store", "add", "swiglu"])
-@pytest.mark.parametrize("shape", [(600, 640, 520), (512, 1000, 136), (130, 250, 192), (1100, 2560, 320)])
+@pytest.mark.parametrize("shape", [(600, 640, 520), (512, 1000, 136), (130, 250, 192), (1100, 2560, 320),
+                                   (1024, 384, 4160)])
 def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
     """The orientation used for prompt-sized batches (tokens = MMA rows; a
     thread of the epilogue owns a token and writes vectors, the residual add
     leaves as reducing TMA stores where the output's pitch allows a tensor map,
-    in place otherwise), with every feature tile and ragged edges; the output
-    also as a slice of a wider buffer; integer data exactly."""
+    in place otherwise), with every feature tile and ragged edges, by one CTA per
+    128-token tile and (-1000 - tile) by a pair of CTAs on one MMA per 256-token
+    tile; the output also as a slice of a wider buffer; integer data exactly."""
     from kipp_b200.kernels import gemm_bf16
     M, N, K = shape
     g = torch.Generator().manual_seed(M + 3 * N)
     for integer in (True, False):
-        for tile_f in (0, -128, -160, -192, -224, -256):
+        for tile_f in (0, -128, -160, -192, -224, -256, -1128, -1160, -1192, -1224, -1256):
             if tile_f == 0 and M < 512:
                 continue
             if integer:
@@ -135,7 +137,7 @@ def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
             odt = torch.float32 if (epilogue == "add" or integer) else torch.bfloat16
             n_out = N // 2 if epilogue == "swiglu" else N
             wide = torch.randn(M + 1, n_out + 8, generator=g).to(odt).to(DEV)
-            out = wide[:M, 4:4 + n_out] if tile_f in (-160, -224) else wide[:M, :n_out].contiguous()
+            out = wide[:M, 4:4 + n_out] if tile_f in (-160, -224, -1192) else wide[:M, :n_out].contiguous()
             before = wide.clone()
             ref = gemm_ref(a, w, epilogue, out)
             gemm_bf16.run("tc", out, a, w, epilogue, M, tile_f=tile_f)
