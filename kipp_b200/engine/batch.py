@@ -119,9 +119,10 @@ class StaticStep:
 
     def __init__(self, n_ints: int, device: torch.device):
         self.n_ints = n_ints
-        self.host = torch.empty(n_ints, dtype=torch.int32, pin_memory=True)
+        self.host = torch.zeros(n_ints, dtype=torch.int32, pin_memory=True)
         self.device = torch.zeros(n_ints, dtype=torch.int32, device=device)
         self.meta: Optional[StepMeta] = None
+        self.offsets: list[int] = []          # of the sections of the packed buffer, once packed
 
 
 def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[np.ndarray],
@@ -175,6 +176,7 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
         for p, o in zip(parts, offsets):
             hv[o:o + p.size] = p
         static.device.copy_(static.host, non_blocking=True)
+        static.offsets = offsets
         if static.meta is not None:            # same layout: the views stay valid
             static.meta.q_lens = q_lens
             static.meta.kv_lens = [s + q for s, q in zip(starts, q_lens)]
@@ -210,6 +212,33 @@ def pack_step(entries: list, starts: list[int], slots: list[int], tables: list[n
                     extra={"h2d_bytes": total * 4})
     if static is not None:
         static.meta = meta
+    return meta
+
+
+def pack_decode(static: StaticStep, tokens: list[int], starts: list[int], slots: list[int],
+                tables: list[np.ndarray]) -> StepMeta:
+    """The same as :func:`pack_step` for a step in which every entry brings one
+    token and wants its logits, into a static step that :func:`pack_step` has
+    filled once for that many entries: the sections that depend only on the
+    number of entries (token-to-entry map, row lists, work lists) are left as
+    they are; token ids, positions, context lengths, slots, the split length
+    and the block tables are written."""
+    meta, o = static.meta, static.offsets
+    n = len(tokens)
+    if meta is None or meta.entries != n or meta.tokens != n or meta.n_decode != n:
+        raise ValueError("pack_decode needs a static step packed for as many one-token entries")
+    hv = static.host.numpy()
+    kv_lens = [s + 1 for s in starts]
+    hv[o[0]] = decode_split_length(kv_lens)
+    hv[o[1]:o[1] + n] = tokens
+    hv[o[2]:o[2] + n] = starts
+    hv[o[5]:o[5] + n] = starts
+    hv[o[6]:o[6] + n] = slots
+    for g, t in enumerate(tables):
+        at = o[12 + g]
+        hv[at:at + t.size] = t.reshape(-1)
+    static.device.copy_(static.host, non_blocking=True)
+    meta.kv_lens = kv_lens
     return meta
 
 

@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 
 from ..kernels import attention_bf16
-from .batch import StaticStep, StepMeta, pack_step, step_ints
+from .batch import StaticStep, StepMeta, pack_decode, pack_step, step_ints
 
 
 class DecodeGraph:
@@ -37,7 +37,10 @@ class DecodeGraph:
     def run(self, entries, starts, slots, tables) -> torch.Tensor:
         from .engine import StepContext
         engine = self.engine
-        meta = pack_step(entries, starts, slots, tables, engine.runtime.device, static=self.static)
+        if self.static.meta is None:
+            meta = pack_step(entries, starts, slots, tables, engine.runtime.device, static=self.static)
+        else:
+            meta = pack_decode(self.static, [e.tokens[0] for e in entries], starts, slots, tables)
         if self.graph is not None and self.generation != self._generation():
             self.graph = None                       # a buffer moved since the capture
         if self.graph is None:

@@ -205,3 +205,35 @@ def test_command_line(tmp_path):
                           "--prompt-ids", "1,2", "--decode", "2", "--temperature", "0.5", "--top-p", "0"],
                          capture_output=True, text=True, timeout=300)
     assert bad.returncode == 2 and "top_p" in bad.stderr
+
+
+def test_decode_metadata_fast_path_equals_the_general_packing():
+    """pack_decode rewrites only what changes between decode steps of one shape;
+    the buffer must equal what pack_step builds from scratch."""
+    import numpy as np
+    from kipp_b200.engine.batch import StaticStep, StepEntry, pack_decode, pack_step, step_ints
+    dev = torch.device("cuda:0")
+    n, widths = 5, [8, 3]
+    ints = step_ints(n, n, n, n, 0, n, [n * w for w in widths])
+    rng = np.random.default_rng(0)
+
+    def random_step():
+        tokens = rng.integers(0, 1000, n).tolist()
+        starts = rng.integers(0, 3000, n).tolist()
+        slots = rng.permutation(16)[:n].tolist()
+        tables = [rng.integers(-1, 500, (n, w)).astype(np.int32) for w in widths]
+        return tokens, starts, slots, tables
+
+    fast, plain = StaticStep(ints, dev), StaticStep(ints, dev)
+    tokens, starts, slots, tables = random_step()
+    pack_step([StepEntry(i, [t], [0]) for i, t in enumerate(tokens)], starts, slots, tables, dev, static=fast)
+    for _ in range(4):
+        tokens, starts, slots, tables = random_step()
+        meta = pack_decode(fast, tokens, starts, slots, tables)
+        ref = pack_step([StepEntry(i, [t], [0]) for i, t in enumerate(tokens)], starts, slots, tables, dev,
+                        static=plain)
+        torch.cuda.synchronize()
+        assert torch.equal(fast.host, plain.host) and torch.equal(fast.device, plain.device)
+        assert meta.kv_lens == ref.kv_lens and meta.q_lens == ref.q_lens
+    with pytest.raises(ValueError):
+        pack_decode(fast, tokens[:-1], starts[:-1], slots[:-1], [t[:-1] for t in tables])
