@@ -329,7 +329,12 @@ attn_decode_kernel(const DecodeParams p) {
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 2, t4 = lane & 3;
-    const int n = blockIdx.z, entry = p.rows[n], g = blockIdx.y, split = blockIdx.x;
+    // Grid (kv heads, tokens, splits): the splits are the slowest dimension, so the CTAs
+    // that have work come first in launch order and all start at once; those of
+    // splits a step does not use come after and leave at once.  (With the splits as
+    // x, 1,664 of 2,048 CTAs of a batch-8 step were empty ones interleaved with the
+    // working ones, and the last working CTA started microseconds late.)
+    const int n = blockIdx.y, entry = p.rows[n], g = blockIdx.x, split = blockIdx.z;
     const int group = p.n_q / p.n_kv;
     const int tok = p.q_start[entry];
     const int pos = p.context_len[entry];                  // position of the decoded token
@@ -552,7 +557,8 @@ template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s)
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return kipp_launch(attn_decode_kernel<D>, dim3(p.max_splits, p.n_kv, n), dim3(THREADS), SMEM, s, 1, p);
+    if (n > 65535) return KIPP_ERR_ARG;
+    return kipp_launch(attn_decode_kernel<D>, dim3(p.n_kv, n, p.max_splits), dim3(THREADS), SMEM, s, 1, p);
 }
 }  // namespace
 
