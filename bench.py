@@ -22,13 +22,11 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN3_4B = dict(
-    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=2560,
-    intermediate_size=9728, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
-    head_dim=128, max_position_embeddings=8192, rope_theta=1000000.0, rms_norm_eps=1e-6,
-    tie_word_embeddings=True, hidden_act="silu", attention_bias=False, initializer_range=0.02,
-    torch_dtype="bfloat16")
-WEIGHT_SEED = 2
+from kipp_b200.config.presets import load_preset  # noqa: E402
+
+# BASELINE.json configs[2] (Qwen3-4B-shaped): the sizes and the weight seed are the preset's
+QWEN3_4B, _INIT_4B = load_preset("qwen3-4b")
+WEIGHT_SEED = int(_INIT_4B["seed"])
 CONTEXT = 8192            # BASELINE.json configs[2]: context length 8192
 POINT_PROMPT = 2048       # ... decode at batch 1/8/64 with 2,048-token prompts
 PREFILL_TOKENS = 2048

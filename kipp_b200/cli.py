@@ -21,9 +21,11 @@ import time
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="kipp", description="Qwen3 dense inference on one B200")
     ap.add_argument("--model", help="folder with config.json and *.safetensors")
-    ap.add_argument("--random", metavar="CONFIG.json",
-                    help="instead of --model: a config.json to fill with random weights from --weights-seed")
-    ap.add_argument("--weights-seed", type=int, default=0)
+    ap.add_argument("--random", metavar="PRESET|CONFIG.json",
+                    help="instead of --model: a preset name (tiny-a, tiny-b, qwen3-4b, qwen3-8b, qwen3-32b) or a "
+                         "config.json, filled with random weights")
+    ap.add_argument("--weights-seed", type=int, default=None,
+                    help="seed of the random weights (default: the preset's, else 0)")
     prompt = ap.add_mutually_exclusive_group(required=True)
     prompt.add_argument("--prompt-ids", help="comma-separated token ids")
     prompt.add_argument("--prompt-file", help="file of little-endian uint32 token ids")
@@ -74,12 +76,25 @@ def main(argv=None) -> int:
     from .sampling.params import SamplingParams
     from .sampling.sampler import Sampler
 
+    init = {}
     if args.model is not None:
         config = load_config(args.model)
     else:
         import json
-        with open(args.random) as f:
-            config = config_from_dict(json.load(f))
+        from .config.presets import load_preset, preset_names
+        if args.random in preset_names():
+            cfg_dict, init = load_preset(args.random)
+            config = config_from_dict(cfg_dict)
+        else:
+            try:
+                with open(args.random) as f:
+                    config = config_from_dict(json.load(f))
+            except FileNotFoundError:
+                print(f"kipp: --random {args.random}: neither a preset ({', '.join(preset_names())}) nor a file",
+                      file=sys.stderr)
+                return 2
+        if args.weights_seed is None:
+            args.weights_seed = int(init.get("seed", 0))
     tokens = _prompt_tokens(args, config.vocab_size)
     if not tokens:
         print("kipp: the prompt is empty", file=sys.stderr)
@@ -93,7 +108,8 @@ def main(argv=None) -> int:
                 cache_tokens=capacity + args.kv_block_size, max_requests=1,
                 max_batch_tokens=max(args.chunk, 1))
     engine = (Engine.from_folder(args.model, **opts) if args.model is not None
-              else Engine.from_config(config, args.weights_seed, **opts))
+              else Engine.from_config(config, args.weights_seed, sigma=init.get("sigma"),
+                                      norm_jitter=init.get("norm_jitter", 0.1), **opts))
     sampler = Sampler(engine.runtime.device)
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                             min_p=args.min_p, seed=args.seed or 1)

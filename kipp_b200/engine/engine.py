@@ -68,6 +68,7 @@ class Engine:
         self.max_requests = max_requests
         self.max_batch_tokens = max_batch_tokens
         rt = self.runtime
+        self._check_device_memory(cache_tokens)
         with torch.cuda.device(rt.device):
             # -- weights -------------------------------------------------------
             spec.embedding.bind(tensors, spec.embedding_prefix, rt)
@@ -104,6 +105,34 @@ class Engine:
         self.graph_kernel_launches = 0
         self.steps_run = 0
         self.last_h2d_bytes = 0
+
+    def _check_device_memory(self, cache_tokens: int) -> None:
+        """Refuse before anything is uploaded when weights and cache cannot fit
+        (the reference does the same before its one allocation,
+        src/cuda/kipp_cuda.cu:542-561)."""
+        rt, spec = self.runtime, self.spec
+        es = torch.empty((), dtype=rt.dtype).element_size()
+        weights = 0
+        for ts in spec.tensor_specs():
+            if ts.optional and ts.alias_of is not None:
+                continue
+            n = 1
+            for d in ts.shape:
+                n *= d
+            weights += n * es
+        cache = 0
+        seen = set()
+        for run in spec.order:
+            cs = spec.layers[run.layer][1].mixer.cache_spec()
+            if cs is not None and run.cache not in seen:
+                seen.add(run.cache)
+                pages = max(1, -(-cache_tokens // self.page_size))
+                cache += 2 * pages * self.page_size * cs.kv_heads * cs.head_dim * es
+        need = weights + cache
+        free, _total = torch.cuda.mem_get_info(rt.device)
+        if need > free:
+            raise MemoryError(f"the model needs about {need:,} device bytes ({weights:,} of weights, {cache:,} of "
+                              f"cache for {cache_tokens:,} tokens) but only {free:,} are free on {rt.device}")
 
     # -- construction ------------------------------------------------------------
     @classmethod

@@ -96,3 +96,22 @@ def test_registry_takes_another_architecture():
     finally:
         unregister_architecture("ToyForTests")
     assert "Qwen3ForCausalLM" in registered_architectures()
+
+
+def test_presets_are_data_and_valid():
+    """Every preset file parses into a valid typed configuration; the benchmark
+    preset has the sizes BASELINE.json configs[2] names."""
+    from kipp_b200.config import config_from_dict, load_preset, preset_names
+    names = preset_names()
+    assert {"tiny-a", "tiny-b", "qwen3-4b", "qwen3-8b", "qwen3-32b"} <= set(names)
+    for name in names:
+        cfg_dict, init = load_preset(name)
+        cfg = config_from_dict(cfg_dict)
+        assert cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        assert init["seed"] >= 0 and init["sigma"] > 0
+    cfg = config_from_dict(load_preset("qwen3-4b")[0])
+    assert (cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+            cfg.head_dim, cfg.intermediate_size, cfg.vocab_size) == (36, 2560, 32, 8, 128, 9728, 151936)
+    assert cfg.tie_word_embeddings and load_preset("qwen3-4b")[1]["seed"] == 2
+    with pytest.raises(KeyError):
+        load_preset("no-such-model")

@@ -237,3 +237,15 @@ def test_decode_metadata_fast_path_equals_the_general_packing():
         assert meta.kv_lens == ref.kv_lens and meta.q_lens == ref.q_lens
     with pytest.raises(ValueError):
         pack_decode(fast, tokens[:-1], starts[:-1], slots[:-1], [t[:-1] for t in tables])
+
+
+def test_refuses_a_model_that_cannot_fit_before_uploading_anything():
+    """Weights plus cache are checked against the free device memory first."""
+    from kipp_b200.config import config_from_dict, load_preset
+    from kipp_b200.engine import Engine
+    cfg_dict, init = load_preset("qwen3-32b")
+    before = torch.cuda.memory_allocated()
+    with pytest.raises(MemoryError, match="device bytes"):
+        Engine.from_config(config_from_dict(cfg_dict), init["seed"], dtype="bfloat16", page_size=16,
+                           cache_tokens=4_000_000, max_requests=4)
+    assert torch.cuda.memory_allocated() == before
