@@ -39,9 +39,14 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--min-p", type=float, default=0.0, help="min prob vs top, 0 <= F <= 1 (0 = off)")
     ap.add_argument("--seed", type=int, default=1, help="nonzero sampling seed (default 1)")
     ap.add_argument("--top", type=int, default=10, help="final top-N logits to print (default 10)")
-    ap.add_argument("--ctx", type=int, default=None, help="session capacity in tokens (default prompt + decode)")
+    ap.add_argument("--ctx", "--max-context", dest="ctx", type=int, default=None,
+                    help="session capacity in tokens (default prompt + decode)")
     ap.add_argument("--kv-block-size", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--kv-blocks", type=int, default=None,
+                    help="pages of the cache pool (default: what the capacity needs)")
     ap.add_argument("--chunk", type=int, default=2048, help="largest prompt portion of one step")
+    ap.add_argument("--max-batch-tokens", type=int, default=None,
+                    help="tokens one step may hold (default: --chunk); sizes the activation buffers")
     ap.add_argument("--stop-token", type=int, action="append", default=None,
                     help="token id that ends decoding (default: the config's eos_token_id)")
     ap.add_argument("--device", default="cuda:0")
@@ -104,9 +109,21 @@ def main(argv=None) -> int:
         print(f"kipp: prompt ({len(tokens)}) + decode ({args.decode}) exceeds --ctx {capacity}",
               file=sys.stderr)
         return 2
+    if args.max_batch_tokens is not None and args.max_batch_tokens < 1:
+        print("kipp: --max-batch-tokens must be positive", file=sys.stderr)
+        return 2
+    if args.max_batch_tokens is not None:
+        args.chunk = min(args.chunk, args.max_batch_tokens)
+    cache_tokens = capacity + args.kv_block_size
+    if args.kv_blocks is not None:
+        cache_tokens = args.kv_blocks * args.kv_block_size
+        if cache_tokens < capacity:
+            print(f"kipp: --kv-blocks {args.kv_blocks} x {args.kv_block_size} tokens cannot hold {capacity}",
+                  file=sys.stderr)
+            return 2
     opts = dict(dtype=args.dtype, device=args.device, page_size=args.kv_block_size,
-                cache_tokens=capacity + args.kv_block_size, max_requests=1,
-                max_batch_tokens=max(args.chunk, 1))
+                cache_tokens=cache_tokens, max_requests=1,
+                max_batch_tokens=max(args.max_batch_tokens or args.chunk, 1))
     engine = (Engine.from_folder(args.model, **opts) if args.model is not None
               else Engine.from_config(config, args.weights_seed, sigma=init.get("sigma"),
                                       norm_jitter=init.get("norm_jitter", 0.1), **opts))
