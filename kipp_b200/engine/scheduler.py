@@ -64,6 +64,16 @@ class Request:
     def all_tokens(self) -> list:
         return self.prompt + self.output
 
+    def tokens_between(self, a: int, b: int) -> list:
+        """Tokens [a, b) of prompt + output, without building the whole list
+        (a decoding request asks for one token every step)."""
+        n = len(self.prompt)
+        if b <= n:
+            return self.prompt[a:b]
+        if a >= n:
+            return self.output[a - n:b - n]
+        return self.prompt[a:] + self.output[:b - n]
+
     @property
     def pending(self) -> int:
         """Tokens known but not yet in the cache."""
@@ -184,7 +194,7 @@ class Scheduler:
         # decoding requests first: one token each
         for r in self.running:
             if r.pending == 1 and r.fed >= len(r.prompt) and budget > 0:
-                entries.append(StepEntry(r.id, [r.all_tokens[r.fed]], [0]))
+                entries.append(StepEntry(r.id, r.tokens_between(r.fed, r.fed + 1), [0]))
                 requests.append(r)
                 sampled.append(len(entries) - 1)
                 budget -= 1
@@ -197,7 +207,7 @@ class Scheduler:
             n = min(r.pending, self.chunk_size, budget)
             if n <= 0:
                 continue
-            toks = r.all_tokens[r.fed:r.fed + n]
+            toks = r.tokens_between(r.fed, r.fed + n)
             last = r.fed + n == len(r.prompt) + len(r.output)
             want = [n - 1] if last and len(r.output) < r.max_new_tokens else []
             entries.append(StepEntry(r.id, toks, want))
