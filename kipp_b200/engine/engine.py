@@ -100,6 +100,7 @@ class Engine:
         # decode steps replay a captured graph per batch size (bfloat16 path)
         self.cuda_graphs = cuda_graphs and self.runtime.dtype == torch.bfloat16
         self._graphs: dict = {}
+        self._shapes_seen: set = set()
         self.last_forward_launches = 0
         self.graph_replays = 0
         self.graph_kernel_launches = 0
@@ -220,6 +221,11 @@ class Engine:
         with torch.cuda.device(rt.device):
             if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
                 logits = self._graph_step(entries, starts, slots, rids)
+            elif self.cuda_graphs and self._shape_repeats(entries):
+                # e.g. the 2,048-token chunks of long prompts: the second step of a shape
+                # is captured, later ones replayed (the host then launches one graph
+                # instead of nine kernels per layer)
+                logits = self._graph_step(entries, starts, slots, rids, bucket=512, decode=False)
             else:
                 tables = [self.cache.block_table_rows(rids, gi) for gi in range(len(self.cache.groups))]
                 meta = pack_step(entries, starts, slots, tables, rt.device, self._staging)
@@ -232,23 +238,43 @@ class Engine:
             rt.check_status()
         return logits
 
-    def _graph_step(self, entries, starts, slots, rids) -> torch.Tensor:
+    def _shape_repeats(self, entries) -> bool:
+        """Whether a step of this shape (tokens and wanted rows per entry) has been
+        run before; only repeating shapes are worth a capture."""
+        sig = tuple((len(e.tokens), len(e.want)) for e in entries)
+        seen = self._shapes_seen
+        if sig in seen:
+            return True
+        if len(seen) >= 512:
+            seen.clear()
+        seen.add(sig)
+        return False
+
+    def _graph_step(self, entries, starts, slots, rids, bucket: int = 64, decode: bool = True) -> torch.Tensor:
         from .graphs import DecodeGraph
-        # table width: what the longest entry needs, rounded up to 64 pages so that a
-        # captured graph serves many steps and little is copied for short contexts
+        # table width: what the longest entry needs, rounded up to `bucket` pages so that
+        # a captured graph serves many steps and little is copied for short contexts
         limit = self.spec.max_positions
         widths = []
         for gi, g in enumerate(self.cache.groups):
             cap = g.pool.n_pages if limit is None else min(g.pool.n_pages, -(-limit // g.page_size))
             need = max(len(self.cache.table(r, gi)) for r in rids)
-            widths.append(max(1, min(max(cap, need), -(-(need + 1) // 64) * 64)))
+            widths.append(max(1, min(max(cap, need), -(-(need + 1) // bucket) * bucket)))
         tables = [self.cache.block_table_rows(rids, gi, width=w) for gi, w in enumerate(widths)]
-        key = (len(entries), tuple(widths))
+        if decode:
+            key = (len(entries), tuple(widths))
+        else:
+            key = (tuple((len(e.tokens), len(e.want)) for e in entries), tuple(widths))
         graph = self._graphs.get(key)
         if graph is None:
             if len(self._graphs) >= 24:
                 self._graphs.pop(next(iter(self._graphs)))
-            graph = self._graphs[key] = DecodeGraph(self, len(entries), widths)
+            if decode:
+                graph = DecodeGraph(self, len(entries), widths)
+            else:
+                graph = DecodeGraph(self, len(entries), widths, [len(e.tokens) for e in entries],
+                                    [len(e.want) for e in entries])
+            self._graphs[key] = graph
         logits = graph.run(entries, starts, slots, tables)
         self.last_h2d_bytes = graph.static.n_ints * 4
         self.graph_replays += 1

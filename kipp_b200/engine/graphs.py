@@ -16,16 +16,29 @@ from typing import Optional
 import torch
 
 from ..kernels import attention_bf16
-from .batch import StaticStep, StepMeta, pack_decode, pack_step, step_ints
+from .batch import ATTENTION_TILE, StaticStep, StepMeta, pack_decode, pack_step, step_ints
 
 
 class DecodeGraph:
-    def __init__(self, engine, batch: int, table_widths: list[int]):
+    """The captured forward pass of steps of one shape: the same number of tokens
+    and wanted rows per entry and the same block-table widths.  Built for decode
+    steps (every entry one token); prompt portions of a repeating shape (the
+    chunks of long prompts) use it too."""
+
+    def __init__(self, engine, batch: int, table_widths: list[int], q_lens: Optional[list[int]] = None,
+                 wants: Optional[list[int]] = None):
         self.engine = engine
         self.batch = batch
         self.table_widths = table_widths
         n = batch
-        ints = step_ints(n, n, n, n, 0, n, [n * w for w in table_widths])
+        q_lens = [1] * n if q_lens is None else list(q_lens)
+        wants = [1] * n if wants is None else list(wants)
+        self.decode_only = all(q == 1 for q in q_lens) and all(w == 1 for w in wants)
+        tile = ATTENTION_TILE
+        ints = step_ints(n, sum(q_lens), sum(wants), sum(1 for q in q_lens if q == 1),
+                         sum(-(-q // tile) for q in q_lens if q > 1), sum(-(-q // tile) for q in q_lens),
+                         [n * w for w in table_widths],
+                         sum(-(-q // (2 * tile)) for q in q_lens if q > 1))
         self.static = StaticStep(ints, engine.runtime.device)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
@@ -37,7 +50,7 @@ class DecodeGraph:
     def run(self, entries, starts, slots, tables) -> torch.Tensor:
         from .engine import StepContext
         engine = self.engine
-        if self.static.meta is None:
+        if self.static.meta is None or not self.decode_only:
             meta = pack_step(entries, starts, slots, tables, engine.runtime.device, static=self.static)
         else:
             meta = pack_decode(self.static, [e.tokens[0] for e in entries], starts, slots, tables)

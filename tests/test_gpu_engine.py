@@ -249,3 +249,37 @@ def test_refuses_a_model_that_cannot_fit_before_uploading_anything():
         Engine.from_config(config_from_dict(cfg_dict), init["seed"], dtype="bfloat16", page_size=16,
                            cache_tokens=4_000_000, max_requests=4)
     assert torch.cuda.memory_allocated() == before
+
+
+def test_repeating_prompt_shapes_replay_a_graph_with_the_eager_results():
+    """Portions of a shape seen before are captured and then replayed; the logits
+    must be exactly those of an engine without graphs, at other contexts, other
+    tokens and other pages than the capture saw."""
+    from kipp_b200.engine import Engine, StepEntry
+    folder = model_folder("D")
+    opts = dict(dtype="bfloat16", page_size=16, cache_tokens=1024, max_requests=4, max_batch_tokens=256)
+    with_graphs = Engine.from_folder(folder, **opts)
+    eager = Engine.from_folder(folder, cuda_graphs=False, **opts)
+    seqs = {r: random_tokens("D", 70 * 3 + 5, seed=60 + i) for i, r in enumerate("abc")}
+    replays0 = with_graphs.graph_replays
+    for r, seq in seqs.items():                          # the same cuts for every request
+        at = 0
+        for n in (70, 70, 70, 5):
+            entry = [StepEntry(r, seq[at:at + n], [0, n - 1])]
+            got = with_graphs.step(entry, check=True).clone()
+            want = eager.step(entry, check=True)
+            assert torch.equal(got, want), (r, at)
+            at += n
+    # two requests beside each other, shapes repeating from step to step
+    for eng in (with_graphs, eager):
+        for r in "abc":
+            eng.finish(r)
+    outs = []
+    for eng in (with_graphs, eager):
+        rows = []
+        for k in range(3):
+            rows.append(eng.step([StepEntry("x", seqs["a"][40 * k:40 * k + 40], [39]),
+                                  StepEntry("y", seqs["b"][33 * k:33 * k + 33], [])], check=True).clone())
+        outs.append(torch.cat(rows))
+    assert torch.equal(outs[0], outs[1])
+    assert with_graphs.graph_replays - replays0 >= 8 and eager.graph_replays == 0
