@@ -100,7 +100,7 @@ class Engine:
         # decode steps replay a captured graph per batch size (bfloat16 path)
         self.cuda_graphs = cuda_graphs and self.runtime.dtype == torch.bfloat16
         self._graphs: dict = {}
-        self._shapes_seen: set = set()
+        self._shapes_seen: dict = {}
         self.last_forward_launches = 0
         self.graph_replays = 0
         self.graph_kernel_launches = 0
@@ -222,7 +222,7 @@ class Engine:
             if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
                 logits = self._graph_step(entries, starts, slots, rids)
             elif self.cuda_graphs and self._shape_repeats(entries):
-                # e.g. the 2,048-token chunks of long prompts: the second step of a shape
+                # e.g. the 2,048-token chunks of long prompts: the third step of a shape
                 # is captured, later ones replayed (the host then launches one graph
                 # instead of nine kernels per layer)
                 logits = self._graph_step(entries, starts, slots, rids, bucket=512, decode=False)
@@ -239,15 +239,16 @@ class Engine:
         return logits
 
     def _shape_repeats(self, entries) -> bool:
-        """Whether a step of this shape (tokens and wanted rows per entry) has been
-        run before; only repeating shapes are worth a capture."""
+        """Whether steps of this shape (tokens and wanted rows per entry) have been
+        run twice before: only shapes that keep coming back are worth a capture."""
         sig = tuple((len(e.tokens), len(e.want)) for e in entries)
         seen = self._shapes_seen
-        if sig in seen:
+        n = seen.get(sig, 0)
+        if n >= 2:
             return True
         if len(seen) >= 512:
             seen.clear()
-        seen.add(sig)
+        seen[sig] = n + 1
         return False
 
     def _graph_step(self, entries, starts, slots, rids, bucket: int = 64, decode: bool = True) -> torch.Tensor:
@@ -265,16 +266,16 @@ class Engine:
             key = (len(entries), tuple(widths))
         else:
             key = (tuple((len(e.tokens), len(e.want)) for e in entries), tuple(widths))
-        graph = self._graphs.get(key)
+        graph = self._graphs.pop(key, None)               # re-inserted below: the dict is kept in order of use
         if graph is None:
             if len(self._graphs) >= 24:
-                self._graphs.pop(next(iter(self._graphs)))
+                self._graphs.pop(next(iter(self._graphs)))   # the least recently used
             if decode:
                 graph = DecodeGraph(self, len(entries), widths)
             else:
                 graph = DecodeGraph(self, len(entries), widths, [len(e.tokens) for e in entries],
                                     [len(e.want) for e in entries])
-            self._graphs[key] = graph
+        self._graphs[key] = graph
         logits = graph.run(entries, starts, slots, tables)
         self.last_h2d_bytes = graph.static.n_ints * 4
         self.graph_replays += 1
