@@ -101,6 +101,9 @@ class Engine:
         self.cuda_graphs = cuda_graphs and self.runtime.dtype == torch.bfloat16
         self._graphs: dict = {}
         self._shapes_seen: dict = {}
+        self._last_decode_graph = None
+        self._burst_host = None
+        self._burst_events: list = []
         self.last_forward_launches = 0
         self.graph_replays = 0
         self.graph_kernel_launches = 0
@@ -238,6 +241,87 @@ class Engine:
             rt.check_status()
         return logits
 
+    def decode_burst(self, requests: list, tokens: list[int], steps: int) -> torch.Tensor:
+        """Greedy decoding of ``steps`` tokens for every request without the host in
+        the loop.  ``tokens[i]`` is the next token of ``requests[i]`` (its logits
+        give the first new token).  Returns int32 ``[steps, len(requests)]`` on
+        the device: row k holds the tokens chosen at step k.  Each step's argmax
+        is fed to the next step on the device; the host only prepares positions
+        and launches, so nothing waits for a copy back.  Pages for all steps are
+        taken first (``OutOfPages`` leaves every request as it was).  Callers
+        that must look at every token (stop tokens, sampling with penalties)
+        use :meth:`step`."""
+        from ..kernels import sampling as _sampling
+        from .batch import decode_split_length
+        n = len(requests)
+        if n == 0 or steps <= 0:
+            return torch.empty((0, n), dtype=torch.int32, device=self.runtime.device)
+        if len(tokens) != n:
+            raise ValueError("one next token per request")
+        rt = self.runtime
+        for r in requests:
+            if r not in self.cache:
+                raise ValueError(f"decode_burst: request {r!r} is not live (feed its prompt with step())")
+        starts = [self.cache.length(r) for r in requests]
+        limit = self.spec.max_positions
+        if limit is not None and max(starts) + steps > limit:
+            raise ValueError(f"a request would pass max positions {limit}")
+        # the pages of all steps are mapped first: all or nothing, and the block tables
+        # then stay as they are from step to step
+        self.cache.reserve([(r, s + steps) for r, s in zip(requests, starts)])
+        ring = torch.empty((steps, n), dtype=torch.int32, device=rt.device)
+        if not self.cuda_graphs:
+            # no graphs (the 32-bit path): the same tokens, one step at a time
+            cur = list(tokens)
+            for k in range(steps):
+                logits = self.step([StepEntry(r, [t], [0]) for r, t in zip(requests, cur)])
+                _sampling.argmax_rows(logits, out=ring[k])
+                cur = ring[k].tolist()
+            return ring
+        # step 0 through the ordinary path (it captures the graph if need be)
+        with torch.cuda.device(rt.device):
+            logits = self.step([StepEntry(r, [t], [0]) for r, t in zip(requests, tokens)])
+            _sampling.argmax_rows(logits, out=ring[0])
+            graph = self._last_decode_graph
+            if steps > 1 and (graph is None or graph.graph is None or graph.batch != n):
+                raise RuntimeError("decode_burst: the decode graph is missing")
+            if steps > 1:
+                o, static = graph.static.offsets, graph.static
+                # A ring of pinned rows, one per step in flight; a row is rewritten only
+                # after the copy that read it has run (an event per row).
+                depth = 16
+                host = self._burst_host
+                if host is None or host.shape[1] != static.n_ints:
+                    host = self._burst_host = torch.empty((depth, static.n_ints), dtype=torch.int32,
+                                                          pin_memory=True)
+                    self._burst_events = [None] * depth
+                template = static.host
+                token_section = static.device[o[1]:o[1] + n]
+                for k in range(1, steps):
+                    i = k % depth
+                    if self._burst_events[i] is not None:
+                        self._burst_events[i].synchronize()
+                    row = host[i]
+                    row.copy_(template)
+                    hv = row.numpy()
+                    at = [s + k for s in starts]
+                    hv[o[0]] = decode_split_length([a + 1 for a in at])
+                    hv[o[2]:o[2] + n] = at
+                    hv[o[5]:o[5] + n] = at
+                    static.device.copy_(row, non_blocking=True)
+                    if self._burst_events[i] is None:
+                        self._burst_events[i] = torch.cuda.Event()
+                    self._burst_events[i].record()
+                    token_section.copy_(ring[k - 1], non_blocking=True)
+                    graph.graph.replay()
+                    _sampling.argmax_rows(graph.logits, out=ring[k])
+                for r, s in zip(requests, starts):
+                    self.cache.advance(r, s + steps)
+                self.steps_run += steps - 1
+                self.graph_replays += steps - 1
+                self.graph_kernel_launches += (steps - 1) * graph.launches
+        return ring
+
     def _shape_repeats(self, entries) -> bool:
         """Whether steps of this shape (tokens and wanted rows per entry) have been
         run twice before: only shapes that keep coming back are worth a capture."""
@@ -276,6 +360,8 @@ class Engine:
                 graph = DecodeGraph(self, len(entries), widths, [len(e.tokens) for e in entries],
                                     [len(e.want) for e in entries])
         self._graphs[key] = graph
+        if decode:
+            self._last_decode_graph = graph
         logits = graph.run(entries, starts, slots, tables)
         self.last_h2d_bytes = graph.static.n_ints * 4
         self.graph_replays += 1

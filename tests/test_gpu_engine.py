@@ -283,3 +283,42 @@ def test_repeating_prompt_shapes_replay_a_graph_with_the_eager_results():
         outs.append(torch.cat(rows))
     assert torch.equal(outs[0], outs[1])
     assert with_graphs.graph_replays - replays0 >= 4 and eager.graph_replays == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_burst_gives_the_tokens_of_greedy_steps(dtype):
+    """Several greedy steps with the tokens fed back on the device: the same
+    tokens as step() + argmax with the host in between, pages for all steps
+    taken first, lengths advanced; a burst that cannot get its pages changes
+    nothing."""
+    from kipp_b200.cache import OutOfPages
+    from kipp_b200.engine import Engine, StepEntry
+    from kipp_b200.kernels import argmax_rows
+    folder = model_folder("B")
+    opts = dict(dtype=dtype, page_size=8, cache_tokens=400, max_requests=4, max_batch_tokens=128)
+    a, b = Engine.from_folder(folder, **opts), Engine.from_folder(folder, **opts)
+    prompts = {r: random_tokens("B", n, seed=70 + n) for r, n in (("x", 37), ("y", 9), ("z", 64))}
+    firsts = {}
+    for eng in (a, b):
+        for r, p in prompts.items():
+            firsts[r] = int(argmax_rows(eng.step([StepEntry(r, p, [len(p) - 1])], check=True))[0])
+    rids = list(prompts)
+    steps = 21
+    ring = a.decode_burst(rids, [firsts[r] for r in rids], steps).cpu()
+    cur = [firsts[r] for r in rids]
+    for k in range(steps):
+        cur = argmax_rows(b.step([StepEntry(r, [t], [0]) for r, t in zip(rids, cur)], check=True)).tolist()
+        assert ring[k].tolist() == cur, k
+    a.runtime.check_status()
+    assert [a.length(r) for r in rids] == [b.length(r) for r in rids]
+    a.cache.check()
+    # a second burst goes on from there, and one that cannot fit leaves everything as it was
+    ring2 = a.decode_burst(rids, ring[-1].tolist(), 3).cpu()
+    for k in range(3):
+        cur = argmax_rows(b.step([StepEntry(r, [t], [0]) for r, t in zip(rids, cur)], check=True)).tolist()
+        assert ring2[k].tolist() == cur
+    lengths, free = [a.length(r) for r in rids], a.cache.free_pages()
+    with pytest.raises(OutOfPages):
+        a.decode_burst(rids, ring2[-1].tolist(), 200)
+    assert [a.length(r) for r in rids] == lengths and a.cache.free_pages() == free
+    a.cache.check()
