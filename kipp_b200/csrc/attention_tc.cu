@@ -197,7 +197,7 @@ template <int ROWS> __device__ __forceinline__ uint32_t tile_off(int half, int r
 }
 
 struct Params {
-    bf16* out; const bf16* q; const bf16* k_pages; const bf16* v_pages;
+    bf16* out; const bf16* q;   // keys and values come through the tensor maps
     const int* q_start; const int* context_len; const int* block_table;
     const int* work;            // [items][2] = (entry, first token of the tile within the entry)
     int table_width, page_size, n_q, n_kv, window;
@@ -214,7 +214,7 @@ template <int D> struct Cfg {
     static constexpr int KV_BYTES = BN * D * 2;       // one of K or V, one stage
     static constexpr int XCHG_BYTES = 2 * 2 * BM * 4;  // row maxima of the two halves, two parities
     static constexpr int TMEM_COLS = 256;                       // two score buffers (64 each) + O (D), power of two
-    // 114,816 bytes at head_dim 128: two CTAs (plus the 1 KB the system keeps per CTA) fit in 227 KB
+    // 100,480 bytes at head_dim 128: two CTAs (plus the 1 KB the system keeps per CTA) fit in 227 KB
     static constexpr size_t SMEM = Q_BYTES + 4 * KV_BYTES + XCHG_BYTES + 128;   // 14 barriers, 2 words
 };
 
@@ -578,7 +578,7 @@ extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_page
     const long long rows = (long long)n_pages * n_kv * page_size;
     if (rows + BN > 0x7fffffffLL) return KIPP_ERR_ARG;
     Params p;
-    p.out = (bf16*)out; p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+    p.out = (bf16*)out; p.q = (const bf16*)q;
     p.q_start = q_start; p.context_len = context_len; p.block_table = block_table; p.work = work;
     p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
     p.box_rows = page_size < BN ? page_size : BN;
