@@ -218,6 +218,37 @@ class CacheManager:
                     rc.set_page(gi, lp, UNMAPPED)
             rc.first_live[gi] = max(rc.first_live[gi], min(keep_from, len(table)))
 
+    def truncate(self, rid, new_length: int) -> None:
+        """Forget the positions from ``new_length`` on: pages that hold none of the
+        remaining positions go back to their pools (the reference's session
+        truncate gives back the blocks past ceil(length / block),
+        src/kipp.c:3755-3768; its reset is a truncate to 0).  A window group can
+        only be cut back to where the pages it still holds cover what the next
+        token may see; else the call is refused and nothing changes."""
+        rc = self._requests[rid]
+        if new_length < 0 or new_length > rc.length:
+            raise ValueError(f"truncate to {new_length} is outside 0..{rc.length}")
+        for gi, g in enumerate(self.groups):
+            if g.window is None or new_length == 0:
+                continue
+            first_page = g.first_needed_position(new_length) // g.page_size
+            if first_page < rc.first_live[gi]:
+                raise ValueError(f"request {rid!r} cannot be cut back to {new_length}: the window of cache "
+                                 f"group {gi} has already given back pages it would need")
+        for gi, g in enumerate(self.groups):
+            table = rc.tables[gi]
+            keep = -(-new_length // g.page_size)              # pages with positions below new_length
+            for lp in range(keep, len(table)):
+                if table[lp] != UNMAPPED:
+                    g.pool.free(table[lp], rid)
+                    rc.set_page(gi, lp, UNMAPPED)
+            del table[keep:]
+            if new_length == 0:
+                rc.first_live[gi] = 0
+            else:
+                rc.first_live[gi] = min(rc.first_live[gi], keep)
+        rc.length = new_length
+
     # -- views ----------------------------------------------------------------------
     def table(self, rid, group: int) -> list[int]:
         return self._requests[rid].tables[group]

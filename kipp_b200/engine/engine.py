@@ -172,6 +172,22 @@ class Engine:
         """The request is over: its pages and its slot are given back."""
         self.cache.release(rid)
 
+    def truncate(self, rid, new_length: int) -> None:
+        """Cut a live request back to its first ``new_length`` tokens; the pages
+        beyond go back.  A model whose mixers keep state per request can only be
+        cut back to nothing (the state is then cleared): a state cannot be unwound."""
+        if self.states and new_length != 0:
+            raise ValueError("a model with per-request state can only be reset (truncate to 0)")
+        self.cache.truncate(rid, new_length)
+        if new_length == 0:
+            slot = self.cache.slot(rid)
+            for st in self.states.values():
+                st[slot].zero_()
+
+    def reset(self, rid) -> None:
+        """The request keeps its slot and starts again from an empty context."""
+        self.truncate(rid, 0)
+
     def length(self, rid) -> int:
         return self.cache.length(rid)
 

@@ -113,6 +113,17 @@ def test_random_orders_keep_the_invariants(seed):
         elif action < 0.40 and lengths:
             rid = rng.choice(sorted(lengths))
             m.release(rid); del lengths[rid]
+        elif action < 0.50 and lengths:
+            # cut a request back: to nothing always works; to some length only while the
+            # window group still holds what the next token would see
+            rid = rng.choice(sorted(lengths))
+            to = rng.choice([0, 0, rng.randint(0, lengths[rid])])
+            held = [m.pages_held(rid), m.free_pages()]
+            try:
+                m.truncate(rid, to)
+                lengths[rid] = to
+            except ValueError:
+                assert to > 0 and [m.pages_held(rid), m.free_pages()] == held
         elif lengths:
             batch = rng.sample(sorted(lengths), rng.randint(1, len(lengths)))
             wants = [(r, lengths[r] + rng.choice([1, 1, 1, 2, 5, 13])) for r in batch]
@@ -144,3 +155,35 @@ def test_random_orders_keep_the_invariants(seed):
     m.check()
     assert m.free_pages() == [24, 10] and m.slots.free_slots == 4
     assert reused                                               # pages were used again
+
+
+def test_truncate_gives_back_the_pages_past_the_new_length():
+    m = CacheManager({0: FULL, 1: FULL}, page_size=4, pages_per_group={FULL: 8}, max_requests=2)
+    m.admit("a")
+    m.reserve([("a", 21)]); m.advance("a", 21)
+    assert m.pages_held("a")[0] == 6
+    m.truncate("a", 9)                                      # pages 0..2 stay
+    assert m.length("a") == 9 and m.pages_held("a")[0] == 3 and m.free_pages()[0] == 5
+    m.check()
+    m.reserve([("a", 10)]); m.advance("a", 10)              # goes on from there
+    with pytest.raises(ValueError):
+        m.truncate("a", 11)
+    m.truncate("a", 0)
+    assert m.pages_held("a") == [0] and m.free_pages() == [8]
+    m.reserve([("a", 3)]); m.advance("a", 3)
+    m.check()
+    # a window that has given pages back cannot be cut back into them
+    w = CacheManager({0: FULL, 1: WIN}, page_size=4, pages_per_group={FULL: 8, WIN: 8}, max_requests=2)
+    w.admit("b")
+    w.reserve([("b", 30)]); w.advance("b", 30)
+    assert w.pages_held("b")[1] < 8                         # the window let go of early pages
+    held, free = w.pages_held("b"), w.free_pages()
+    with pytest.raises(ValueError, match="window"):
+        w.truncate("b", 5)
+    assert w.length("b") == 30 and w.pages_held("b") == held and w.free_pages() == free
+    w.truncate("b", 29)                                     # its window still lies in held pages
+    w.check()
+    w.truncate("b", 0)
+    assert w.free_pages() == [8, 8]
+    w.reserve([("b", 6)]); w.advance("b", 6)
+    w.check()

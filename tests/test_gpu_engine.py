@@ -322,3 +322,26 @@ def test_decode_burst_gives_the_tokens_of_greedy_steps(dtype):
         a.decode_burst(rids, ring2[-1].tolist(), 200)
     assert [a.length(r) for r in rids] == lengths and a.cache.free_pages() == free
     a.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_truncate_and_reset_continue_like_a_fresh_request(dtype):
+    """A request cut back to 23 tokens and fed other tokens gives what a new
+    request with those tokens gives; the pages beyond the cut are free again."""
+    from kipp_b200.engine import Engine, StepEntry
+    folder = model_folder("B")
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=8, cache_tokens=256, max_requests=3,
+                             max_batch_tokens=128)
+    first, other = random_tokens("B", 50, seed=81), random_tokens("B", 30, seed=82)
+    eng.step([StepEntry("s", first, [])], check=True)
+    held = eng.cache.pages_held("s")[0]
+    eng.truncate("s", 23)
+    assert eng.length("s") == 23 and eng.cache.pages_held("s")[0] == 3 < held
+    got = eng.step([StepEntry("s", other, [0, 29])], check=True).clone()
+    want = eng.step([StepEntry("fresh", first[:23] + other, [23, 52])], check=True)
+    assert nmse(got, want) < (1e-12 if dtype == "float32" else 1e-5)
+    eng.reset("s")
+    assert eng.length("s") == 0 and eng.cache.pages_held("s") == [0]
+    again = eng.step([StepEntry("s", first[:23] + other, [23, 52])], check=True)
+    assert nmse(again, want) < 1e-12                        # the same kernels on the same tokens
+    eng.cache.check()
