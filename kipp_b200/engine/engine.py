@@ -410,6 +410,22 @@ class Engine:
         return spec.head[1].forward(ctx, h, meta.n_logit_rows)
 
     # -- accounting -----------------------------------------------------------------
+    def info(self) -> dict:
+        """What is loaded and what it may hold (the reference's kipp_model_info and
+        kipp_session_info in one, src/kipp.h:109-145, 172-200)."""
+        cfg = self.spec.config
+        groups = [{"caches": len(g.cache_ids), "kv_heads": g.spec.kv_heads, "head_dim": g.spec.head_dim,
+                   "window": g.spec.window, "pages": g.pool.n_pages, "free_pages": g.pool.free_pages}
+                  for g in self.cache.groups]
+        return {"architecture": getattr(cfg, "architecture", None), "dtype": str(self.runtime.dtype),
+                "device": str(self.runtime.device), "layers": len(self.spec.layers),
+                "runs": len(self.spec.order), "hidden_size": self.spec.hidden_size,
+                "vocab_size": self.spec.vocab_size, "max_positions": self.spec.max_positions,
+                "weight_bytes": self.weight_bytes(), "cache_bytes_per_token": self.cache_bytes_per_token(),
+                "page_size": self.page_size, "cache_groups": groups, "max_requests": self.max_requests,
+                "max_batch_tokens": self.max_batch_tokens,
+                "live_requests": {r: self.cache.length(r) for r in self.cache.live_requests()}}
+
     def weight_bytes(self) -> int:
         """Bytes of weights one step reads (each weight once)."""
         spec = self.spec

@@ -340,6 +340,9 @@ def test_truncate_and_reset_continue_like_a_fresh_request(dtype):
     got = eng.step([StepEntry("s", other, [0, 29])], check=True).clone()
     want = eng.step([StepEntry("fresh", first[:23] + other, [23, 52])], check=True)
     assert nmse(got, want) < (1e-12 if dtype == "float32" else 1e-5)
+    info = eng.info()
+    assert info["live_requests"] == {"s": 53, "fresh": 53} and info["cache_groups"][0]["pages"] == 32
+    assert info["layers"] == 3 and info["vocab_size"] == 1000 and info["weight_bytes"] > 0
     eng.reset("s")
     assert eng.length("s") == 0 and eng.cache.pages_held("s") == [0]
     again = eng.step([StepEntry("s", first[:23] + other, [23, 52])], check=True)
