@@ -34,7 +34,7 @@ def _random_config(rng: random.Random) -> tuple[dict, int, int]:
     return cfg, rng.choice([8, 16, 32, 64, 128]), rng.choice([1030, 1100, 1300, 1536])
 
 
-@pytest.mark.parametrize("seed", [101, 202, 303, 304])
+@pytest.mark.parametrize("seed", [101, 202, 303, 110, 155, 214])
 def test_random_configuration_against_the_plain_model(tmp_path, seed):
     from kipp_b200.config import config_from_dict
     from kipp_b200.engine import Engine, StepEntry
