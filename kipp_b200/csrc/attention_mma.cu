@@ -531,7 +531,12 @@ __global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float acc = 0.f;
 #pragma unroll 4
-        for (int s = 0; s < n_splits; ++s) acc += po[(size_t)s * head_dim + d] * weight[s];
+        for (int s = 0; s < n_splits; ++s) {
+            // a split with no key in reach (wholly behind a window) has weight 0 and wrote no
+            // partial output: what lies in the scratch there is not read (0 x garbage may be NaN)
+            const float w = weight[s];
+            if (w != 0.f) acc += po[(size_t)s * head_dim + d] * w;
+        }
         dst[d] = __float2bfloat16_rn(acc * inv_sum);
     }
 }

@@ -321,6 +321,9 @@ def test_attention_tensor_core(shape, window):
         meta, table, q, kp, vp = attention_case(10 + li, D, nq, nkv, page, layout, torch.bfloat16)
         out = torch.full_like(q, 9.0)
         st = status()
+        # whatever lies in the split-K scratch must not matter: a split wholly behind a
+        # window writes no partial output, and 0 x NaN would be NaN
+        attention_bf16.decode_scratch(torch.device(DEV), meta.tokens, nq, D).fill_(float("nan"))
         ops().attention(out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D),
                         window, st, impl="mma")
         ref = attention_ref(meta, table, q, kp, vp, layout, page, window, 1 / math.sqrt(D))
