@@ -305,7 +305,43 @@ struct DecodeParams {
     const int* split_keys;      // device: keys per split of this step (a multiple of 64)
     int table_width, page_size, n_q, n_kv, window, max_splits;
     float scale_log2;
+    // Fused form (qkv != nullptr): queries, the new key and the new value come raw out of
+    // the q/k/v projection; the kernel does the per-head norm and the rotation itself and
+    // puts the new key and value into the cache (what qk_norm_rope_write_kernel does in a
+    // launch of its own, src/kipp.c:2480-2512 and 2806-2811 for the formulas).
+    const bf16* qkv; int ld_qkv;
+    const void* q_norm_w; const void* k_norm_w; int norm_dtype; float eps;
+    const float2* cos_sin;      // [token][D / 2] (cos, sin), or nullptr: no rotation
+    bf16* k_write; bf16* v_write;   // the pools, writable; nullptr: this run does not write its cache
+    int* status;
 };
+
+// The per-head norm and the rotation of one head vector, one warp: lane l holds
+// elements l, l + 32, ...; element e < D/2 pairs with e + D/2, which the same lane
+// holds.  Returns the values in x.
+template <int D>
+__device__ __forceinline__ void warp_norm_rope(float (&x)[D / 32], const void* norm_w, int norm_dtype, float eps,
+                                               const float2* cs_row, int lane) {
+    constexpr int NE = D / 32;
+    if (norm_w != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < NE; ++j) ss += x[j] * x[j];
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int j = 0; j < NE; ++j) x[j] = x[j] * scale * load_w(norm_w, norm_dtype, lane + 32 * j);
+    }
+    if (cs_row != nullptr) {
+#pragma unroll
+        for (int j = 0; j < NE / 2; ++j) {
+            const float2 cs = cs_row[lane + 32 * j];
+            const float a = x[j], b = x[j + NE / 2];
+            x[j] = a * cs.x - b * cs.y;
+            x[j + NE / 2] = b * cs.x + a * cs.y;
+        }
+    }
+}
 
 // Keys per split for a context of kv_len keys: the step's split length, or
 // longer when max_splits of them would not cover the context.
@@ -358,7 +394,53 @@ attn_decode_kernel(const DecodeParams p) {
     }
     // rows g4 and g4 + 8 = heads of the group (zero rows beyond it)
     uint32_t qf[D / 16][4];
-    {
+    if (p.qkv != nullptr) {
+        // Fused form: norm and rotation of the group's queries here, a warp per head, into
+        // shared memory (the tiles are not in use yet); the split that holds the token's
+        // own position also makes the new key and value and puts them into the cache.
+        constexpr int NE = D / 32;
+        bf16* q_s = reinterpret_cast<bf16*>(smem);                 // [16][D]
+        const bf16* raw = p.qkv + (size_t)tok * p.ld_qkv;
+        const float2* cs_row = p.cos_sin != nullptr ? p.cos_sin + (size_t)tok * (D / 2) : nullptr;
+        for (int hh = warp; hh < group; hh += WARPS) {
+            float x[NE];
+#pragma unroll
+            for (int j = 0; j < NE; ++j) x[j] = __bfloat162float(raw[(size_t)(g * group + hh) * D + lane + 32 * j]);
+            warp_norm_rope<D>(x, p.q_norm_w, p.norm_dtype, p.eps, cs_row, lane);
+#pragma unroll
+            for (int j = 0; j < NE; ++j) q_s[hh * D + lane + 32 * j] = __float2bfloat16_rn(x[j]);
+        }
+        if (split == n_splits - 1 && p.k_write != nullptr && warp < 2) {
+            const int slot = pos / p.page_size;
+            const int page = slot < p.table_width ? table[slot] : -1;
+            if (page < 0) {                                        // unmapped page: refuse, never write
+                if (lane == 0) atomicExch(p.status, 2);
+            } else {
+                const size_t at = (((size_t)page * p.n_kv + g) * p.page_size + (pos - slot * p.page_size)) * D;
+                float x[NE];
+                const bf16* src = raw + (size_t)(p.n_q + (warp == 0 ? 0 : p.n_kv) + g) * D;
+#pragma unroll
+                for (int j = 0; j < NE; ++j) x[j] = __bfloat162float(src[lane + 32 * j]);
+                if (warp == 0) warp_norm_rope<D>(x, p.k_norm_w, p.norm_dtype, p.eps, cs_row, lane);
+                bf16* dst = (warp == 0 ? p.k_write : p.v_write) + at;
+#pragma unroll
+                for (int j = 0; j < NE; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(x[j]);
+            }
+            __threadfence();                                       // before this CTA gathers that page
+        }
+        __syncthreads();
+        const bool v0 = g4 < group, v1 = g4 + 8 < group;
+        const bf16* q0 = q_s + min(g4, group - 1) * D;
+        const bf16* q1 = q_s + min(g4 + 8, group - 1) * D;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qf[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 2 * t4) : 0u;
+            qf[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 2 * t4) : 0u;
+            qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t4) : 0u;
+            qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t4) : 0u;
+        }
+        __syncthreads();                                           // the tiles may now be loaded over q_s
+    } else {
         const bf16* q0 = p.q + ((size_t)tok * p.n_q + g * group + min(g4, group - 1)) * D;
         const bf16* q1 = p.q + ((size_t)tok * p.n_q + g * group + min(g4 + 8, group - 1)) * D;
         const bool v0 = g4 < group, v1 = g4 + 8 < group;
@@ -618,6 +700,49 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
     p.max_splits = max_splits; p.split_keys = split_keys;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.qkv = nullptr; p.ld_qkv = 0; p.q_norm_w = p.k_norm_w = nullptr; p.norm_dtype = 0; p.eps = 0.f;
+    p.cos_sin = nullptr; p.k_write = p.v_write = nullptr; p.status = nullptr;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
+    if (rc) return rc;
+    return kipp_launch(attn_decode_merge_kernel, dim3(n_q, n), dim3(head_dim >= 128 ? 128 : 64), 0, s, 1,
+                       (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, rows, q_start, context_len, n_q,
+                       head_dim, max_splits, split_keys);
+}
+
+// The same for a step of decoded tokens only, taking the raw output of the q/k/v
+// projection [tokens, (n_q + 2 n_kv) * head_dim]: per-head norm (weights or nullptr),
+// rotation by the step's (cos, sin) table (or nullptr) and the write of the new key and
+// value into the pools (write_cache) happen inside the attention kernel.
+extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long ld_qkv, void* k_pages,
+                                          void* v_pages, const void* q_norm_w, const void* k_norm_w,
+                                          int norm_dtype, float eps, const void* cos_sin, int write_cache,
+                                          const int* q_start, const int* context_len, const int* block_table,
+                                          int table_width, int page_size, const int* rows, int n, int n_q,
+                                          int n_kv, int head_dim, float scale, int window, int max_splits,
+                                          const int* split_keys, float* scratch, int* status, void* stream) {
+    if (n <= 0) return 0;
+    if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
+        max_splits > 64 || split_keys == nullptr || scratch == nullptr || status == nullptr || qkv == nullptr ||
+        ld_qkv < (long long)(n_q + 2 * n_kv) * head_dim || ld_qkv > 0x7fffffffLL ||
+        (q_norm_w == nullptr) != (k_norm_w == nullptr))
+        return KIPP_ERR_ARG;
+    if (q_norm_w != nullptr && norm_dtype != KIPP_DT_F32 && norm_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
+    DecodeParams p;
+    p.q = nullptr; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
+    p.q_start = q_start; p.context_len = context_len; p.block_table = block_table; p.rows = rows;
+    p.part_o = scratch;
+    p.out = (bf16*)out;
+    p.part_ml = scratch + (size_t)n * n_q * max_splits * head_dim;
+    p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
+    p.max_splits = max_splits; p.split_keys = split_keys;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.qkv = (const bf16*)qkv; p.ld_qkv = (int)ld_qkv;
+    p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.norm_dtype = norm_dtype; p.eps = eps;
+    p.cos_sin = (const float2*)cos_sin;
+    p.k_write = write_cache ? (bf16*)k_pages : nullptr;
+    p.v_write = write_cache ? (bf16*)v_pages : nullptr;
+    p.status = status;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
     if (rc) return rc;

@@ -111,3 +111,36 @@ def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv,
                  _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale),
                  int(window or 0), MAX_SPLITS, _ptr(meta.decode_split_keys), _ptr(scratch), _stream()),
                "attn_decode_mma")
+
+
+def decode_fused_ok(meta, q_dtype, n_q: int, n_kv: int, head_dim: int, rotary_dim: int) -> bool:
+    """Whether a step can take :func:`decode_fused`: decoded tokens only, bfloat16,
+    a head size and group the split-K kernel takes, the whole head rotated or none of it."""
+    return (q_dtype == torch.bfloat16 and meta.n_decode == meta.entries == meta.tokens and meta.n_decode > 0
+            and rotary_dim in (0, head_dim) and decode_supported(head_dim, n_q, n_kv))
+
+
+def decode_fused(out, qkv, k_pages, v_pages, q_norm_w, k_norm_w, eps, cos_sin, write_cache: bool, meta,
+                 block_table, page_size, n_q, n_kv, head_dim, scale, window, status) -> None:
+    """Attention of a step of decoded tokens straight from the raw q/k/v projection:
+    the per-head norm, the rotation and the write of the new key and value happen in
+    the attention kernel (no launch of their own)."""
+    from .ops import dtype_code
+    if qkv.dtype != torch.bfloat16 or qkv.stride(1) != 1 or qkv.shape[1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError("decode_fused: qkv must be bfloat16 [tokens, (n_q + 2 n_kv) * head_dim]")
+    if (q_norm_w is None) != (k_norm_w is None):
+        raise KernelError("decode_fused: q and k norm weights must come together")
+    norm_dtype = dtype_code(q_norm_w.dtype) if q_norm_w is not None else 0
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous()):
+        raise KernelError("decode_fused: cos_sin must be contiguous float32 [tokens, head_dim / 2, 2]")
+    scratch = decode_scratch(qkv.device, meta.n_decode, n_q, head_dim)
+    f = _fn("attention_mma", "kipp_attn_decode_mma_fused",
+            [c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
+             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+             c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(out), _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(q_norm_w), _ptr(k_norm_w),
+             norm_dtype, float(eps), _ptr(cos_sin), 1 if write_cache else 0, _ptr(meta.q_start),
+             _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
+             _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale), int(window or 0),
+             MAX_SPLITS, _ptr(meta.decode_split_keys), _ptr(scratch), _ptr(status), _stream()),
+           "attn_decode_mma_fused")

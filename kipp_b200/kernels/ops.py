@@ -244,6 +244,29 @@ def attention(out: torch.Tensor, q: torch.Tensor, k_pages: torch.Tensor, v_pages
                            head_dim, scale, window, status)
 
 
+def attention_decode_fused_ok(meta, dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int,
+                              rotary_dim: int) -> bool:
+    """Whether :func:`attention_decode_fused` takes this step (decoded tokens only, bfloat16,
+    sizes of the split-K kernel, the whole head rotated or none of it)."""
+    if dtype != torch.bfloat16:
+        return False
+    from . import attention_bf16
+    return attention_bf16.decode_fused_ok(meta, dtype, n_q, n_kv, head_dim, rotary_dim)
+
+
+def attention_decode_fused(out: torch.Tensor, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                           cos_sin: Optional[torch.Tensor], write_cache: bool, meta, block_table: torch.Tensor,
+                           page_size: int, n_q: int, n_kv: int, head_dim: int, scale: float,
+                           window: Optional[int], status: torch.Tensor) -> None:
+    """``qk_norm_rope_write`` and ``attention`` of a step of decoded tokens in one pair of
+    launches: the attention kernel normalises and rotates the raw queries and the new key
+    itself and writes the new key and value into the pages."""
+    from . import attention_bf16
+    attention_bf16.decode_fused(out, qkv, k_pages, v_pages, q_norm_w, k_norm_w, eps, cos_sin, write_cache, meta,
+                                block_table, page_size, n_q, n_kv, head_dim, scale, window, status)
+
+
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """First index of each row's maximum (strict '>' as src/kipp.c:3459-3464)."""
     from . import sampling

@@ -89,15 +89,26 @@ class AttentionMixer(Mixer):
                 cos_sin = ws.buffer(f"rope_table_{len(tables)}", (T, inv_freq.numel(), 2), torch.float32)
                 ops.rope_table(ctx.meta.positions, inv_freq, T, out=cos_sin)
                 tables[key] = cos_sin
-        ops.qk_norm_rope_write(
-            qkv, q, cache.k_pages, cache.v_pages, self.q_norm, self.k_norm,
-            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
-            inv_freq, self.position.rotary_dim,
-            ctx.meta.positions, ctx.meta.entry_of_token, cache.block_table, cache.page_size, T,
-            self.num_heads, self.num_kv_heads, self.head_dim, run.writes_cache, ctx.status,
-            cos_sin=cos_sin)
         attn = ws.buffer("attn_out", (T, self.q_dim), ctx.dtype)
-        ops.attention(attn.view(T, self.num_heads, self.head_dim), q, cache.k_pages, cache.v_pages,
-                      ctx.meta, cache.block_table, cache.page_size, self.num_heads,
-                      self.num_kv_heads, self.head_dim, self.scale, self.window, ctx.status)
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        fused_ok = getattr(ops, "attention_decode_fused_ok", None)
+        if fused_ok is not None and fused_ok(ctx.meta, ctx.dtype, self.num_heads, self.num_kv_heads,
+                                             self.head_dim, self.position.rotary_dim):
+            # decoded tokens only: norm, rotation and the cache write happen inside the
+            # attention kernel, straight from the projection's output
+            ops.attention_decode_fused(
+                attn.view(T, self.num_heads, self.head_dim), qkv, cache.k_pages, cache.v_pages,
+                self.q_norm, self.k_norm, eps, cos_sin, run.writes_cache, ctx.meta, cache.block_table,
+                cache.page_size, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
+                ctx.status)
+        else:
+            ops.qk_norm_rope_write(
+                qkv, q, cache.k_pages, cache.v_pages, self.q_norm, self.k_norm, eps,
+                inv_freq, self.position.rotary_dim,
+                ctx.meta.positions, ctx.meta.entry_of_token, cache.block_table, cache.page_size, T,
+                self.num_heads, self.num_kv_heads, self.head_dim, run.writes_cache, ctx.status,
+                cos_sin=cos_sin)
+            ops.attention(attn.view(T, self.num_heads, self.head_dim), q, cache.k_pages, cache.v_pages,
+                          ctx.meta, cache.block_table, cache.page_size, self.num_heads,
+                          self.num_kv_heads, self.head_dim, self.scale, self.window, ctx.status)
         ops.gemm(residual, attn, self.w_o, "add", m=T)

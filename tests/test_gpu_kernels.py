@@ -448,3 +448,59 @@ def test_penalties_and_bias_match_the_reference_sampler():
     assert out[0] == gold["token"]                       # what kipp_sample_ex chose with the same settings
     assert out[1] == int(np.argmax(np.asarray(gold["logits"], dtype=np.float32))) and out[0] != out[1]
     assert states == [1, 1]                              # greedy leaves the generators alone
+
+
+@pytest.mark.parametrize("case", [dict(D=128, nq=8, nkv=2, page=16, rot=True, norm=True, w16=True, window=None),
+                                  dict(D=64, nq=6, nkv=3, page=8, rot=True, norm=True, w16=False, window=90),
+                                  dict(D=128, nq=5, nkv=1, page=32, rot=False, norm=True, w16=True, window=None),
+                                  dict(D=64, nq=16, nkv=1, page=16, rot=True, norm=False, w16=False, window=None)])
+def test_decode_attention_fused_with_norm_rotation_and_cache_write(case):
+    """A step of decoded tokens: the attention kernel that normalises, rotates and
+    writes the new key and value itself against the two separate launches, on
+    the same raw projection output; outputs and caches must agree (the norm's
+    sum runs in another order: rounding only), and a run that does not write
+    its cache leaves the pages alone."""
+    from kipp_b200.kernels import attention_bf16
+    D, nq, nkv, page, window = case["D"], case["nq"], case["nkv"], case["page"], case["window"]
+    layout = [(700, 1), (15, 1), (16, 1), (255, 1), (1023, 1), (0, 1), (129, 1)]
+    meta, table, _, kp, vp = attention_case(77, D, nq, nkv, page, layout, torch.bfloat16)
+    T = meta.tokens
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, generator=g).to(torch.bfloat16).to(DEV)
+    wdt = torch.bfloat16 if case["w16"] else torch.float32
+    qw = (1 + 0.2 * torch.randn(D, generator=g)).to(wdt).to(DEV) if case["norm"] else None
+    kw = (1 + 0.2 * torch.randn(D, generator=g)).to(wdt).to(DEV) if case["norm"] else None
+    rot = D if case["rot"] else 0
+    inv = cos_sin = None
+    if rot:
+        i = torch.arange(D // 2, dtype=torch.float32)
+        inv = torch.pow(torch.tensor(1e4, dtype=torch.float64), (-(2.0 * i) / D).double()).float().to(DEV)
+        cos_sin = ops().rope_table(meta.positions, inv, T)
+    assert attention_bf16.decode_fused_ok(meta, torch.bfloat16, nq, nkv, D, rot)
+    st = status()
+    # separate launches
+    k1, v1 = kp.clone(), vp.clone()
+    q = torch.zeros(T, nq, D, dtype=torch.bfloat16, device=DEV)
+    ops().qk_norm_rope_write(qkv, q, k1, v1, qw, kw, 1e-6, inv, rot, meta.positions, meta.entry_of_token,
+                             meta.block_tables[0], page, T, nq, nkv, D, True, st, cos_sin=cos_sin)
+    want = torch.zeros_like(q)
+    ops().attention(want, q, k1, v1, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D), window, st,
+                    impl="mma")
+    # one launch
+    k2, v2 = kp.clone(), vp.clone()
+    got = torch.full_like(q, 7.0)
+    attention_bf16.decode_scratch(torch.device(DEV), T, nq, D).fill_(float("nan"))
+    ops().attention_decode_fused(got, qkv, k2, v2, qw, kw, 1e-6, cos_sin, True, meta, meta.block_tables[0], page,
+                                 nq, nkv, D, 1 / math.sqrt(D), window, st)
+    assert st.tolist() == [0, 0, 0, 0]
+    assert torch.equal(v1, v2)
+    assert torch.allclose(k1.float(), k2.float(), rtol=1e-2, atol=1e-2)
+    assert float((k1.float() - kp.float()).abs().sum()) > 0          # keys were written
+    assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    # reading another run's cache: nothing is written
+    k3, v3 = k1.clone(), v1.clone()
+    got3 = torch.zeros_like(q)
+    ops().attention_decode_fused(got3, qkv, k3, v3, qw, kw, 1e-6, cos_sin, False, meta, meta.block_tables[0],
+                                 page, nq, nkv, D, 1 / math.sqrt(D), window, st)
+    assert torch.equal(k3, k1) and torch.equal(v3, v1)
+    assert torch.allclose(got3.float(), want.float(), rtol=2e-2, atol=2e-2)
