@@ -12,6 +12,7 @@ bfloat16 weights made on the device; prompts are seeded random token ids.  A
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -51,47 +52,66 @@ def peaks() -> tuple[dict, str]:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi clocks and throttle reasons while the timed region runs.  It is
+    started before the warm-up (nvidia-smi needs a moment to come up); each sample
+    carries nvidia-smi's own timestamp, and only samples between mark_start() and
+    mark_end() count.  A timed region shorter than the sampling period may hold
+    none: then the samples of the warm-up just before it (the same load) stand
+    in, and "window" says so."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int = 0):
         self.proc = None
+        self.t_begin = datetime.datetime.now()
+        self.t_start = self.t_end = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
 
+    def mark_start(self) -> None:
+        self.t_start = datetime.datetime.now()
+
+    def mark_end(self) -> None:
+        self.t_end = datetime.datetime.now()
+
     def stop(self) -> dict:
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.06)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        samples = []
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0])); mx.append(float(parts[1]))
+                when = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                samples.append((when, float(parts[1]), float(parts[2]),
+                                [n for n, v in zip(self.NAMES, parts[3:7]) if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+        t0, t1 = self.t_start or self.t_begin, self.t_end or datetime.datetime.now()
+        window = "timed region"
+        chosen = [x for x in samples if t0 <= x[0] <= t1]
+        if not chosen:
+            window = "warm-up and timed region (the timed region is shorter than the sampling period)"
+            chosen = [x for x in samples if self.t_begin <= x[0] <= t1]
+        sm = [x[1] for x in chosen]
         return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "sm_max_mhz": max(x[2] for x in chosen) if chosen else None,
+                "reasons": sorted({r for x in chosen for r in x[3]}), "samples": len(chosen), "window": window}
 
 
 def reference_arm() -> int:
@@ -196,15 +216,19 @@ def main() -> int:
         end-to-end figure below has the host in every step.)"""
         next_tokens = prompt(len(rids))
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler() if sample_clocks else None
         ring = eng.decode_burst(rids, next_tokens, warmup)
         next_tokens = ring[-1].tolist()
         torch.cuda.synchronize(dev)
-        sampler = ClockSampler() if sample_clocks else None
         launches0 = eng.kernel_launches()
+        if sampler:
+            sampler.mark_start()
         a.record()
         ring = eng.decode_burst(rids, next_tokens, steps)
         b.record()
         torch.cuda.synchronize(dev)
+        if sampler:
+            sampler.mark_end()
         clocks = sampler.stop() if sampler else None
         assert ring.shape[0] == steps and int(ring.min()) >= 0
         ms = a.elapsed_time(b) / steps

@@ -43,6 +43,7 @@
 namespace {
 constexpr int BM = 128;            // query rows per CTA = MMA M
 constexpr int BN = 64;             // keys per tile
+constexpr float RESCALE_SLACK = 8.f;   // log2 of the largest weight a stale running maximum may give
 constexpr int SOFTMAX_THREADS = 256;  // two threads per query row: each half of a tile's keys
 constexpr int THREADS = 320;          // + the TMA warp and the MMA warp
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // ~1 s: a wait that long has failed
@@ -215,7 +216,7 @@ template <int D> struct Cfg {
     static constexpr int XCHG_BYTES = 2 * 2 * BM * 4;  // row maxima of the two halves, two parities
     static constexpr int TMEM_COLS = 256;                       // two score buffers (64 each) + O (D), power of two
     // 100,480 bytes at head_dim 128: two CTAs (plus the 1 KB the system keeps per CTA) fit in 227 KB
-    static constexpr size_t SMEM = Q_BYTES + 4 * KV_BYTES + XCHG_BYTES + 128;   // 14 barriers, 2 words
+    static constexpr size_t SMEM = Q_BYTES + 4 * KV_BYTES + XCHG_BYTES + 144;   // 15 barriers, 2 words
 };
 
 template <int D>
@@ -237,7 +238,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* s_full = bars + 9;        // [2] a score buffer holds S of a tile          (1, by commit)
     uint64_t* p_full = bars + 11;       // [2] it holds the tile's weights, O is rescaled (8 = softmax warps)
     uint64_t* o_done = bars + 13;       // O += P V of a tile is complete                 (1, by commit)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+    uint64_t* o_final = bars + 14;      // the last O += P V is complete                  (1, by commit)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     pdl_launch_dependents();
@@ -250,6 +252,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             mbar_init(&s_full[b], 1); mbar_init(&p_full[b], SOFTMAX_THREADS / 32);
         }
         mbar_init(o_done, 1);
+        mbar_init(o_final, 1);
         *abort_flag = (q_tile & 1023u) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -341,6 +344,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     umma_bf16_a_tmem(tmem_o, tmem_s + b * BN + 8 * k, vd + 128 * k, IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&v_empty[b]);
                 umma_commit(o_done);
+                if (i == n_tiles - 1) umma_commit(o_final);
                 if (i + 2 < n_tiles) {
                     // S of the tile after next goes where this tile's weights are: not before they are read
                     if (ok && !mbar_wait(o_done, i & 1, abort_flag)) ok = false;
@@ -406,8 +410,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 named_barrier(1 + (warp & 3), 64);
                 raw = fmaxf(raw, xb[(ch ^ 1) * BM + row]);
             }
-            const float mx = fmaxf(m_run, raw * p.scale_log2);      // scale > 0: the maximum commutes
-            const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - mx);
+            // The running maximum only has to bound the exponents: it moves when the
+            // tile's maximum exceeds it by more than RESCALE_SLACK (weights up to
+            // 2^RESCALE_SLACK, far inside bfloat16 and the fp32 sums); numerator and
+            // denominator carry the same reference, so the quotient is unchanged.
+            const float cand = raw * p.scale_log2;                  // scale > 0: the maximum commutes
+            const float mx = (cand > m_run + RESCALE_SLACK || m_run == -INFINITY) ? fmaxf(m_run, cand) : m_run;
+            const float corr = (m_run == -INFINITY) ? 0.f : (mx == m_run ? 1.f : fast_exp2(m_run - mx));
             const float neg_base = (mx == -INFINITY) ? 0.f : -mx;
             float sum = 0.f;
             uint32_t packed[HB / 2];
@@ -421,17 +430,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             l_run = l_run * corr + sum;                    // this thread's half of the row's sum
             m_run = mx;
-            // O += P V of the tile before is complete: the output may be rescaled
-            if (i > 0) {
-                if (!mbar_wait(o_done, (i - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
-                tc_fence_after();
-            }
             // The weights of this thread's keys go over the scores they came from (both
-            // threads of the row have read theirs: they met at the barrier above).
+            // threads of the row have read theirs: they met at the barrier above; the
+            // product that read the buffer's earlier weights was complete before these
+            // scores were issued).
             tmem_st16_words(tmem_sb + t_lane + ch * (HB / 2), packed);
             // rescale the output accumulator when some row of the warp moved its maximum
-            // (this thread: its half of the columns)
+            // (this thread: its half of the columns), once O += P V of the tile before
+            // is complete.  The parity is unambiguous: tile i - 2's product was complete
+            // before this tile's scores were issued, and tile i's is not issued yet.
             if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+                if (!mbar_wait(o_done, (i - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
+                tc_fence_after();
 #pragma unroll 1
                 for (int c = ch * (D / 2); c < (ch + 1) * (D / 2); c += 32) {
                     float o[32];
@@ -446,7 +456,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
         }
-        if (!mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
+        // (a barrier of its own: a warp that skipped the waits above may be two phases
+        // behind o_done, where a parity says nothing)
+        if (!mbar_wait(o_final, 0, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
         tc_fence_after();
 
         // ---- result: o / l, this thread's half of its row's columns.  The tensor-memory

@@ -394,6 +394,29 @@ def test_attention_finds_one_far_key(impl, dtype):
         kp[pages[j // page], :, j % page, j % D] = 1.0
 
 
+@pytest.mark.parametrize("rate", [0.02, 0.07, 0.3, -0.07])
+def test_attention_scores_that_climb(rate):
+    """Scores that rise (or fall) steadily with the key's position: the running
+    maximum of the prompt kernel drifts by a few units per key tile, so tiles are
+    added under a maximum that is not their own before the output is rescaled;
+    with random scores the maximum settles in the first tiles and this path sleeps."""
+    D, nq, nkv, page = 128, 4, 2, 16
+    for layout in ([(0, 700)], [(300, 150), (0, 64)]):
+        meta, table, q, kp, vp = attention_case(21, D, nq, nkv, page, layout, torch.bfloat16)
+        kp.mul_(0.1)
+        q.mul_(0.1)
+        q[:, :, 5] = 1.0
+        for r, (ctx, n) in enumerate(layout):
+            for pos in range(ctx + n):
+                kp[table[r][pos // page], :, pos % page, 5] = rate * pos      # score = rate * pos in natural-log units
+        out = torch.zeros_like(q)
+        st = status()
+        ops().attention(out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1.0, None, st, impl="mma")
+        ref = attention_ref(meta, table, q, kp, vp, layout, page, None, 1.0)
+        assert st.tolist() == [0, 0, 0, 0]
+        assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2), (rate, layout)
+
+
 # ------------------------------------------------------------------ sampling
 def test_argmax_first_maximum():
     logits = torch.randn(5, 1000, generator=torch.Generator().manual_seed(1)).to(DEV)
