@@ -216,7 +216,7 @@ template <int D> struct Cfg {
     static constexpr int XCHG_BYTES = 2 * 2 * BM * 4;  // row maxima of the two halves, two parities
     static constexpr int TMEM_COLS = 256;                       // two score buffers (64 each) + O (D), power of two
     // 100,480 bytes at head_dim 128: two CTAs (plus the 1 KB the system keeps per CTA) fit in 227 KB
-    static constexpr size_t SMEM = Q_BYTES + 4 * KV_BYTES + XCHG_BYTES + 144;   // 15 barriers, 2 words
+    static constexpr size_t SMEM = Q_BYTES + 4 * KV_BYTES + XCHG_BYTES + 144;   // 16 barriers, 2 words
 };
 
 template <int D>
@@ -235,11 +235,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* k_empty = bars + 3;       // [2] its S product has read it                 (1, by commit)
     uint64_t* v_full = bars + 5;        // [2]
     uint64_t* v_empty = bars + 7;       // [2] its O product has read it
-    uint64_t* s_full = bars + 9;        // [2] a score buffer holds S of a tile          (1, by commit)
-    uint64_t* p_full = bars + 11;       // [2] it holds the tile's weights, O is rescaled (8 = softmax warps)
-    uint64_t* o_done = bars + 13;       // O += P V of a tile is complete                 (1, by commit)
-    uint64_t* o_final = bars + 14;      // the last O += P V is complete                  (1, by commit)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint64_t* s_full = bars + 9;        // the score buffer holds S of a tile             (1, by commit)
+    uint64_t* s_free = bars + 10;       // every softmax warp has its scores in registers (8 = softmax warps)
+    uint64_t* p_full = bars + 11;       // [2] a weight buffer holds a tile's weights, O is rescaled (8)
+    uint64_t* p_empty = bars + 13;      // [2] O += P V has read it (and is complete)     (1, by commit)
+    uint64_t* o_final = bars + 15;      // the last O += P V is complete                  (1, by commit)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     pdl_launch_dependents();
@@ -249,9 +250,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int b = 0; b < 2; ++b) {
             mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
             mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
-            mbar_init(&s_full[b], 1); mbar_init(&p_full[b], SOFTMAX_THREADS / 32);
+            mbar_init(&p_full[b], SOFTMAX_THREADS / 32); mbar_init(&p_empty[b], 1);
         }
-        mbar_init(o_done, 1);
+        mbar_init(s_full, 1); mbar_init(s_free, SOFTMAX_THREADS / 32);
         mbar_init(o_final, 1);
         *abort_flag = (q_tile & 1023u) ? 1 : 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -261,9 +262,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // columns: two score buffers [0, 64) and [64, 128) (the weights of a tile, as pairs
-    // of bfloat16, overwrite the first 32 columns of its scores), output [128, 128 + D)
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BN;
+    // columns: scores [0, 64); two weight buffers [64, 96) and [96, 128) (pairs of
+    // bfloat16); output [128, 128 + D)
+    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base + BN, tmem_o = tmem_base + 2 * BN;
     pdl_wait();
 
     // Grid (heads, tiles), the last tile of the list first: within an entry the later
@@ -313,9 +314,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             constexpr uint32_t IDESC_S = idesc(BM, BN, 0);
             constexpr uint32_t IDESC_O = idesc(BM, D, 1);
             bool ok = true;
-            // S(tile) = Q K^T into score buffer b from key stage b
-            auto issue_scores = [&](int b, uint32_t parity) {
-                if (ok && !mbar_wait(&k_full[b], parity, abort_flag)) ok = false;
+            // S(tile i) = Q K^T into the score buffer from key stage i & 1
+            auto issue_scores = [&](int i) {
+                const int b = i & 1;
+                if (ok && !mbar_wait(&k_full[b], (i >> 1) & 1, abort_flag)) ok = false;
                 tc_fence_after();
 #pragma unroll
                 for (int hh = 0; hh < C::HALVES; ++hh) {
@@ -323,17 +325,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     const uint64_t kd = smem_desc(k_tiles + b * C::KV_BYTES + hh * (BN * 128), 0, 1024);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_s + b * BN, qd + 2 * k, kd + 2 * k, IDESC_S, (hh | k) ? 1u : 0u);
+                        umma_bf16(tmem_s, qd + 2 * k, kd + 2 * k, IDESC_S, (hh | k) ? 1u : 0u);
                 }
-                umma_commit(&s_full[b]);
+                umma_commit(s_full);
                 umma_commit(&k_empty[b]);
             };
             if (!mbar_wait(q_full, 0, abort_flag)) ok = false;
-            issue_scores(0, 0);
-            if (n_tiles > 1) issue_scores(1, 0);
+            issue_scores(0);
             for (int i = 0; i < n_tiles; ++i) {
                 const int b = i & 1, use = i >> 1;
-                // the tile's weights are in its score buffer, O is rescaled, its values have landed
+                // S of the next tile as soon as the softmax warps hold this tile's scores
+                // in registers: it runs while they work on them
+                if (i + 1 < n_tiles) {
+                    if (ok && !mbar_wait(s_free, i & 1, abort_flag)) ok = false;
+                    issue_scores(i + 1);
+                }
+                // the tile's weights are in weight buffer b, O is rescaled, its values have landed
                 if (ok && !mbar_wait(&p_full[b], use & 1, abort_flag)) ok = false;
                 if (ok && !mbar_wait(&v_full[b], use & 1, abort_flag)) ok = false;
                 tc_fence_after();
@@ -341,15 +348,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)
                     // 16 keys further: 8 columns of P; 16 rows = 2048 bytes in the value tile
-                    umma_bf16_a_tmem(tmem_o, tmem_s + b * BN + 8 * k, vd + 128 * k, IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16_a_tmem(tmem_o, tmem_p + b * (BN / 2) + 8 * k, vd + 128 * k, IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&v_empty[b]);
-                umma_commit(o_done);
+                umma_commit(&p_empty[b]);
                 if (i == n_tiles - 1) umma_commit(o_final);
-                if (i + 2 < n_tiles) {
-                    // S of the tile after next goes where this tile's weights are: not before they are read
-                    if (ok && !mbar_wait(o_done, i & 1, abort_flag)) ok = false;
-                    issue_scores(b, ((i + 2) >> 1) & 1);
-                }
             }
         }
         __syncwarp();
@@ -384,12 +386,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         // once the abort flag is up the remaining waits return at once.)
         for (int i = 0; i < n_tiles; ++i) {
             const int kt = first_tile + i, b = i & 1, use = i >> 1;
-            const uint32_t tmem_sb = tmem_s + b * BN;
-            if (!mbar_wait(&s_full[b], use & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 1); ok = false; }
+            if (!mbar_wait(s_full, i & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 1); ok = false; }
             tc_fence_after();
             constexpr int HB = BN / 2;                     // keys per thread
             float s[HB];
-            tmem_ld32(tmem_sb + t_lane + ch * HB, s);
+            tmem_ld32(tmem_s + t_lane + ch * HB, s);
+            // the scores are in registers: the buffer may take the next tile's
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);
             const int j0 = kt * BN + ch * HB;
             // Masking only where the tile crosses a row's limits (the diagonal, a
             // window's edge, rows beyond the entry): decided per warp.
@@ -430,17 +435,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             l_run = l_run * corr + sum;                    // this thread's half of the row's sum
             m_run = mx;
-            // The weights of this thread's keys go over the scores they came from (both
-            // threads of the row have read theirs: they met at the barrier above; the
-            // product that read the buffer's earlier weights was complete before these
-            // scores were issued).
-            tmem_st16_words(tmem_sb + t_lane + ch * (HB / 2), packed);
+            // The weights of this thread's keys go to weight buffer b, once the product
+            // that read its earlier weights (tile i - 2) is complete.
+            if (i >= 2) {
+                if (!mbar_wait(&p_empty[b], (use - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
+                tc_fence_after();
+            }
+            tmem_st16_words(tmem_p + b * (BN / 2) + t_lane + ch * (HB / 2), packed);
             // rescale the output accumulator when some row of the warp moved its maximum
             // (this thread: its half of the columns), once O += P V of the tile before
-            // is complete.  The parity is unambiguous: tile i - 2's product was complete
-            // before this tile's scores were issued, and tile i's is not issued yet.
+            // is complete: that is the latest product on the other weight buffer (the one
+            // before it there was waited for in the iteration before this one).
             if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-                if (!mbar_wait(o_done, (i - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
+                if (!mbar_wait(&p_empty[b ^ 1], ((i - 1) >> 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = ch * (D / 2); c < (ch + 1) * (D / 2); c += 32) {
@@ -456,8 +463,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
         }
-        // (a barrier of its own: a warp that skipped the waits above may be two phases
-        // behind o_done, where a parity says nothing)
         if (!mbar_wait(o_final, 0, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
         tc_fence_after();
 
@@ -484,320 +489,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(dst + c)[k] = pk[k];
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
-    if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
-}
-
-// ------------------------------------------------------------------ wide kernel
-// head_dim 128, long prompts.  One CTA per SM = 256 consecutive tokens of one entry
-// x one query head, as two query tiles of 128 rows, and key tiles of 128 keys:
-//   warps 0-3 / 4-7  softmax of query tile 0 / 1: one thread per query row holds the
-//                    tile's 128 scores in registers (no exchange between threads);
-//   warp 8           TMA gather of key and value tiles (shared by both query tiles);
-//   warp 9           one thread issues the products of both query tiles.
-// Tensor memory (512 columns): S of tile 0, S of tile 1, O of tile 0, O of tile 1;
-// the weights of a key tile overwrite the first 64 columns of its scores.  Per
-// query tile the chain S -> softmax -> O += P V -> next S is serial (S of the next
-// key tile is issued once O += P V has read the weights it would overwrite); the
-// two query tiles alternate, so one is in the softmax while the other's products
-// run.  A 128-key S product reads its operands from shared memory at 128 bytes a
-// cycle, which the 64-key one of the kernel above exceeds (192).
-constexpr int WN = 128;                               // keys per tile
-struct CfgW {
-    static constexpr int D = 128;
-    static constexpr int Q_BYTES = BM * D * 2;        // one query tile
-    static constexpr int KV_BYTES = WN * D * 2;       // one of K or V, one stage
-    static constexpr int TMEM_COLS = 512;
-    static constexpr size_t SMEM = 2 * Q_BYTES + 4 * KV_BYTES + 256;   // 18 barriers, 2 words
-};
-
-// 128 columns of this thread's lane in one instruction; the wait is part of the same statement,
-// so no use of the registers can be scheduled in front of it.
-__device__ __forceinline__ void tmem_ld128(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x128.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
-        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,"
-        "%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63,"
-        "%64,%65,%66,%67,%68,%69,%70,%71,%72,%73,%74,%75,%76,%77,%78,%79,"
-        "%80,%81,%82,%83,%84,%85,%86,%87,%88,%89,%90,%91,%92,%93,%94,%95,"
-        "%96,%97,%98,%99,%100,%101,%102,%103,%104,%105,%106,%107,%108,%109,%110,%111,"
-        "%112,%113,%114,%115,%116,%117,%118,%119,%120,%121,%122,%123,%124,%125,%126,%127}, [%128];\n"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
-          "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
-          "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
-          "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
-          "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]),
-          "=r"(r[64]), "=r"(r[65]), "=r"(r[66]), "=r"(r[67]), "=r"(r[68]), "=r"(r[69]), "=r"(r[70]), "=r"(r[71]),
-          "=r"(r[72]), "=r"(r[73]), "=r"(r[74]), "=r"(r[75]), "=r"(r[76]), "=r"(r[77]), "=r"(r[78]), "=r"(r[79]),
-          "=r"(r[80]), "=r"(r[81]), "=r"(r[82]), "=r"(r[83]), "=r"(r[84]), "=r"(r[85]), "=r"(r[86]), "=r"(r[87]),
-          "=r"(r[88]), "=r"(r[89]), "=r"(r[90]), "=r"(r[91]), "=r"(r[92]), "=r"(r[93]), "=r"(r[94]), "=r"(r[95]),
-          "=r"(r[96]), "=r"(r[97]), "=r"(r[98]), "=r"(r[99]), "=r"(r[100]), "=r"(r[101]), "=r"(r[102]), "=r"(r[103]),
-          "=r"(r[104]), "=r"(r[105]), "=r"(r[106]), "=r"(r[107]), "=r"(r[108]), "=r"(r[109]), "=r"(r[110]), "=r"(r[111]),
-          "=r"(r[112]), "=r"(r[113]), "=r"(r[114]), "=r"(r[115]), "=r"(r[116]), "=r"(r[117]), "=r"(r[118]), "=r"(r[119]),
-          "=r"(r[120]), "=r"(r[121]), "=r"(r[122]), "=r"(r[123]), "=r"(r[124]), "=r"(r[125]), "=r"(r[126]), "=r"(r[127])
-        : "r"(taddr) : "memory");
-}
-__global__ void __launch_bounds__(THREADS, 1)
-attn_prefill_tc_wide_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                            const Params p) {
-    using C = CfgW;
-    constexpr int D = C::D;
-    pdl_launch_dependents();
-    // The work list names 128-token tiles; a CTA takes an even tile and the one after
-    // it.  (The lists of the step come by a copy that is complete before any kernel
-    // of the step starts; what the kernel before this one wrote is read after the
-    // dependency wait below.)
-    const int item = gridDim.y - 1 - blockIdx.y;
-    const int entry = p.work[2 * item], tile_tok = p.work[2 * item + 1];
-    if (tile_tok & 255) return;
-
-    extern __shared__ __align__(1024) uint8_t smem[];
-    const uint32_t q_tiles = smem_u32(smem);                         // [2 query tiles]
-    const uint32_t k_tiles = q_tiles + 2 * C::Q_BYTES;               // [2 stages]
-    const uint32_t v_tiles = k_tiles + 2 * C::KV_BYTES;              // [2 stages]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * C::Q_BYTES + 4 * C::KV_BYTES);
-    uint64_t* q_full = bars;            // [2] a query tile is in shared memory          (128 arrivals)
-    uint64_t* k_full = bars + 2;        // [2] a key stage has landed                    (1 + bytes)
-    uint64_t* k_empty = bars + 4;       // [2] the S products that use it are complete   (1, by commit)
-    uint64_t* v_full = bars + 6;        // [2]
-    uint64_t* v_empty = bars + 8;       // [2]
-    uint64_t* s_full = bars + 10;       // [query tile] S of a key tile is complete      (1, by commit)
-    uint64_t* p_full = bars + 12;       // [query tile] weights stored, O rescaled       (4 = its warps)
-    uint64_t* o_done = bars + 14;       // [query tile] O += P V complete (the MMA thread waits) (1, by commit)
-    uint64_t* o_final = bars + 16;      // [query tile] the last O += P V is complete    (1, by commit)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&q_full[b], 128);
-            mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
-            mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
-            mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4);
-            mbar_init(&o_done[b], 1); mbar_init(&o_final[b], 1);
-        }
-        *abort_flag = (q_tiles & 1023u) ? 1 : 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();
-
-    const int h = blockIdx.x, g = h / (p.n_q / p.n_kv);
-    const int qs = p.q_start[entry], q_len = p.q_start[entry + 1] - qs;
-    const int ctx = p.context_len[entry];
-    // key tiles of each query tile: from the window start of its first row to its last row
-    int first[2], n_t[2];
-    int hi_all = 0;
-#pragma unroll
-    for (int qt = 0; qt < 2; ++qt) {
-        const int tok0 = tile_tok + qt * BM;
-        const int t_first = ctx + tok0, t_last = ctx + min(tok0 + BM - 1, q_len - 1);
-        const int lo = p.window > 0 ? max(0, t_first - p.window + 1) : 0;
-        first[qt] = lo / WN;
-        n_t[qt] = tok0 < q_len ? t_last / WN - first[qt] + 1 : 0;
-        if (tok0 < q_len) hi_all = t_last;
-    }
-    const int kt_min = first[0];
-    const int kt_max = hi_all / WN;
-
-    if (warp == 8) {
-        // ------------------------------------------------------------ TMA producer
-        const int* table = p.block_table + (size_t)entry * p.table_width;
-        const int rb = lane >> 1, half = lane & 1;
-        const bool has_box = rb * p.box_rows < WN;
-        const uint32_t dst_off = (uint32_t)(half * (WN * 128) + rb * p.box_rows * 128);
-        bool ok = true;
-        for (int kt = kt_min; kt <= kt_max; ++kt) {
-            const int i = kt - kt_min, b = i & 1, use = i >> 1;
-            int row_coord = p.rows_total;                  // beyond the pool: zeros
-            if (has_box) {
-                const int j = kt * WN + rb * p.box_rows;
-                const int slot = j / p.page_size;
-                const int page = (j <= hi_all && slot < p.table_width) ? __ldg(table + slot) : -1;
-                if (page >= 0) row_coord = (page * p.n_kv + g) * p.page_size + (j - slot * p.page_size);
-            }
-            if (i >= 2 && ok && !mbar_wait(&k_empty[b], (use - 1) & 1, abort_flag)) ok = false;
-            if (lane == 0) mbar_expect_tx(&k_full[b], C::KV_BYTES);
-            __syncwarp();
-            if (has_box && ok) tma_load_2d(k_tiles + b * C::KV_BYTES + dst_off, &map_k, &k_full[b], half * 64, row_coord);
-            if (i >= 2 && ok && !mbar_wait(&v_empty[b], (use - 1) & 1, abort_flag)) ok = false;
-            if (lane == 0) mbar_expect_tx(&v_full[b], C::KV_BYTES);
-            __syncwarp();
-            if (has_box && ok) tma_load_2d(v_tiles + b * C::KV_BYTES + dst_off, &map_v, &v_full[b], half * 64, row_coord);
-        }
-    } else if (warp == 9) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t IDESC_S = idesc(BM, WN, 0);
-            constexpr uint32_t IDESC_O = idesc(BM, D, 1);
-            bool ok = true;
-            // the query tile that issues last among the users of key tile kt
-            auto last_user = [&](int kt) { return (n_t[1] > 0 && kt >= first[1] && kt < first[1] + n_t[1]) ? 1 : 0; };
-            auto issue_scores = [&](int qt, int kt) {
-                const int i = kt - kt_min, b = i & 1, use = i >> 1;
-                if (ok && !mbar_wait(&k_full[b], use & 1, abort_flag)) ok = false;
-                tc_fence_after();
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const uint64_t qd = smem_desc(q_tiles + qt * C::Q_BYTES + hh * (BM * 128), 0, 1024);
-                    const uint64_t kd = smem_desc(k_tiles + b * C::KV_BYTES + hh * (WN * 128), 0, 1024);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_base + qt * WN, qd + 2 * k, kd + 2 * k, IDESC_S, (hh | k) ? 1u : 0u);
-                }
-                umma_commit(&s_full[qt]);
-                if (qt == last_user(kt)) umma_commit(&k_empty[b]);
-            };
-            if (!mbar_wait(&q_full[0], 0, abort_flag)) ok = false;
-            if (n_t[1] > 0 && !mbar_wait(&q_full[1], 0, abort_flag)) ok = false;
-            issue_scores(0, kt_min);
-            for (int kt = kt_min; kt <= kt_max; ++kt) {
-                if (n_t[1] > 0 && first[1] == kt) issue_scores(1, kt);       // query tile 1 joins here
-                const int b = (kt - kt_min) & 1, use = (kt - kt_min) >> 1;
-#pragma unroll
-                for (int qt = 0; qt < 2; ++qt) {
-                    const int i = kt - first[qt];
-                    if (i < 0 || i >= n_t[qt]) continue;
-                    // the tile's weights are over its scores, O is rescaled, its values have landed
-                    if (ok && !mbar_wait(&p_full[qt], i & 1, abort_flag)) ok = false;
-                    if (ok && !mbar_wait(&v_full[b], use & 1, abort_flag)) ok = false;
-                    tc_fence_after();
-                    const uint64_t vd = smem_desc(v_tiles + b * C::KV_BYTES, (uint32_t)(WN * 128), 1024);
-#pragma unroll
-                    for (int k = 0; k < WN / 16; ++k)
-                        umma_bf16_a_tmem(tmem_base + 2 * WN + qt * D, tmem_base + qt * WN + 8 * k, vd + 128 * k,
-                                         IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
-                    if (qt == last_user(kt)) umma_commit(&v_empty[b]);
-                    if (i == n_t[qt] - 1) {
-                        umma_commit(&o_final[qt]);
-                    } else {
-                        // S of the next key tile goes where these weights are: not before they are read
-                        umma_commit(&o_done[qt]);
-                        if (ok && !mbar_wait(&o_done[qt], i & 1, abort_flag)) ok = false;
-                        issue_scores(qt, kt + 1);
-                    }
-                }
-            }
-        }
-        __syncwarp();
-    } else {
-        // ------------------------------------------------------------ softmax warps
-        const int qt = warp >> 2;
-        const int row = threadIdx.x & (BM - 1);
-        const int tok = tile_tok + qt * BM + row;
-        const bool live = tok < q_len;
-        {
-            constexpr int CHUNKS = D / 8;
-            for (int i = row; i < BM * CHUNKS; i += BM) {
-                const int r = i / CHUNKS, chunk = i % CHUNKS;
-                const int tk = tile_tok + qt * BM + r;
-                const bool there = tk < q_len;
-                const bf16* src = p.q + ((size_t)(qs + (there ? tk : 0)) * p.n_q + h) * D + chunk * 8;
-                cp_async16(q_tiles + qt * C::Q_BYTES + tile_off<BM>(chunk >> 3, r, chunk & 7), src, there ? 16 : 0);
-            }
-            cp_async_commit();
-            cp_async_wait<0>();
-            fence_async_proxy();
-            mbar_arrive(&q_full[qt]);
-        }
-        const int pos = ctx + tok;
-        const int lo_row = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-        const uint32_t t_lane = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tmem_sq = tmem_base + qt * WN + t_lane;
-        const uint32_t tmem_oq = tmem_base + 2 * WN + qt * D + t_lane;
-        float m_run = -INFINITY, l_run = 0.f;
-        bool ok = true;
-        const int n_mine = n_t[qt];
-        for (int i = 0; i < n_mine; ++i) {
-            const int kt = first[qt] + i;
-            if (!mbar_wait(&s_full[qt], i & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 1); ok = false; }
-            tc_fence_after();
-            uint32_t sr[WN];
-            tmem_ld128(tmem_sq, sr);
-            const int j0 = kt * WN;
-            if (!__all_sync(0xffffffffu, live && j0 + WN - 1 <= pos && j0 >= lo_row)) {
-#pragma unroll
-                for (int j = 0; j < WN; ++j) {
-                    const int key = j0 + j;
-                    if (!(live && key >= lo_row && key <= pos)) sr[j] = 0xff800000u;   // -inf
-                }
-            }
-            float raw = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < WN; ++j) raw = fmaxf(raw, __uint_as_float(sr[j]));
-            const float cand = raw * p.scale_log2;
-            const float mx = (cand > m_run + RESCALE_SLACK || m_run == -INFINITY) ? fmaxf(m_run, cand) : m_run;
-            const float corr = (m_run == -INFINITY) ? 0.f : (mx == m_run ? 1.f : fast_exp2(m_run - mx));
-            const float neg_base = (mx == -INFINITY) ? 0.f : -mx;
-            // O += P V of the key tile before completed before these scores were issued:
-            // the output may be rescaled at once
-            if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll 1
-                for (int c = 0; c < D; c += 32) {
-                    float o[32];
-                    tmem_ld32(tmem_oq + c, o);
-#pragma unroll
-                    for (int k = 0; k < 32; ++k) o[k] *= corr;
-                    tmem_st32(tmem_oq + c, o);
-                }
-            }
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < WN / 32; ++c) {
-                uint32_t packed[16];
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c * 32 + j]), p.scale_log2, neg_base));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c * 32 + j + 1]), p.scale_log2, neg_base));
-                    sum += p0 + p1;
-                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                    packed[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
-                }
-                tmem_st16_words(tmem_sq + c * 16, packed);
-            }
-            l_run = l_run * corr + sum;
-            m_run = mx;
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[qt]);
-        }
-        if (n_mine > 0) {
-            if (!mbar_wait(&o_final[qt], 0, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
-            tc_fence_after();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            bf16* dst = p.out + ((size_t)(qs + (live ? tok : 0)) * p.n_q + h) * D;
-#pragma unroll 1
-            for (int c = 0; c < D; c += 32) {
-                float o[32];
-                tmem_ld32(tmem_oq + c, o);
-                if (ok && live) {
-                    uint4 pk[4];
-                    uint32_t* w = reinterpret_cast<uint32_t*>(pk);
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(o[2 * k] * inv, o[2 * k + 1] * inv);
-                        w[k] = *reinterpret_cast<uint32_t*>(&h2);
-                    }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(dst + c)[k] = pk[k];
-                }
             }
         }
     }
@@ -875,16 +566,6 @@ template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const 
     }
     return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, p);
 }
-int launch_wide(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int items, cudaStream_t s) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)CfgW::SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    return kipp_launch(attn_prefill_tc_wide_kernel, dim3(p.n_q, items), dim3(THREADS), CfgW::SMEM, s, 1, mk, mv, p);
-}
 }  // namespace
 
 extern "C" int kipp_attn_prefill_tc_supported(int head_dim, int n_q, int n_kv) {
@@ -897,12 +578,13 @@ extern "C" int kipp_attn_prefill_tc_page_ok(int page_size) {
     return page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0);
 }
 
-namespace {
-int prefill_tc(bool wide, void* out, const void* q, const void* k_pages, const void* v_pages,
-               int n_pages, const int* q_start, const int* context_len,
-               const int* block_table, int table_width, int page_size, const int* work,
-               int items, int n_q, int n_kv, int head_dim, float scale, int window,
-               int* status, void* stream) {
+// Prompt portions: `work` lists (entry, first token) of every 128-token tile.
+// k_pages and v_pages: one layer's pool, bf16 [n_pages][n_kv][page_size][head_dim].
+extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_pages, const void* v_pages,
+                                    int n_pages, const int* q_start, const int* context_len,
+                                    const int* block_table, int table_width, int page_size, const int* work,
+                                    int items, int n_q, int n_kv, int head_dim, float scale, int window,
+                                    int* status, void* stream) {
     if (items <= 0) return 0;
     if (items > 65535) return KIPP_ERR_ARG;
     if (!kipp_attn_prefill_tc_supported(head_dim, n_q, n_kv) || !kipp_attn_prefill_tc_page_ok(page_size) ||
@@ -931,29 +613,5 @@ int prefill_tc(bool wide, void* out, const void* q, const void* k_pages, const v
     rc = pool_map(&mv, v_pages, rows, head_dim, p.box_rows);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (wide) return launch_wide(mk, mv, p, items, s);
     return head_dim == 64 ? launch<64>(mk, mv, p, items, s) : launch<128>(mk, mv, p, items, s);
-}
-}  // namespace
-
-// Prompt portions: `work` lists (entry, first token) of every 128-token tile.
-// k_pages and v_pages: one layer's pool, bf16 [n_pages][n_kv][page_size][head_dim].
-extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_pages, const void* v_pages,
-                                    int n_pages, const int* q_start, const int* context_len,
-                                    const int* block_table, int table_width, int page_size, const int* work,
-                                    int items, int n_q, int n_kv, int head_dim, float scale, int window,
-                                    int* status, void* stream) {
-    return prefill_tc(false, out, q, k_pages, v_pages, n_pages, q_start, context_len, block_table, table_width,
-                      page_size, work, items, n_q, n_kv, head_dim, scale, window, status, stream);
-}
-
-// The same through the wide kernel (256 tokens per CTA, 128-key tiles): head_dim 128.
-extern "C" int kipp_attn_prefill_tc_wide(void* out, const void* q, const void* k_pages, const void* v_pages,
-                                         int n_pages, const int* q_start, const int* context_len,
-                                         const int* block_table, int table_width, int page_size, const int* work,
-                                         int items, int n_q, int n_kv, int head_dim, float scale, int window,
-                                         int* status, void* stream) {
-    if (head_dim != 128) return KIPP_ERR_ARG;
-    return prefill_tc(true, out, q, k_pages, v_pages, n_pages, q_start, context_len, block_table, table_width,
-                      page_size, work, items, n_q, n_kv, head_dim, scale, window, status, stream);
 }

@@ -44,29 +44,13 @@ PREFILL_TC = True           # prompt portions on tcgen05 where the sizes allow
 PREFILL_TC_MIN_TOKENS = 64  # shorter portions waste a 128-row tile: they stay on mma.sync
 
 
-PREFILL_TC_WIDE = None      # None: by the amount of work; True / False: forced (tests, timing)
-PREFILL_TC_WIDE_MIN_CTAS = 148   # the wide kernel runs one CTA of 256 tokens per SM: fewer leave SMs idle
-
-
-def prefill_tc_wide_wanted(meta, n_q: int, head_dim: int) -> bool:
-    """Whether the step's portions go through the wide kernel (256 tokens per CTA,
-    128-key tiles, head_dim 128): when its CTAs fill the device."""
-    if head_dim != 128:
-        return False
-    if PREFILL_TC_WIDE is not None:
-        return bool(PREFILL_TC_WIDE)
-    ctas = n_q * sum(-(-n // 256) for n in meta.q_lens if n > 1)
-    return ctas >= PREFILL_TC_WIDE_MIN_CTAS
-
-
 def prefill_tc(out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv, head_dim, scale,
                window, status) -> None:
-    """Portions of more than one token through a tcgen05 kernel (work list of 128-token tiles)."""
+    """Portions of more than one token through the tcgen05 kernel (128-token tiles)."""
     if not (k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape
             and tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)):
         raise KernelError("attn_prefill_tc: pages must be contiguous [pages, n_kv, page_size, head_dim]")
-    name = "kipp_attn_prefill_tc_wide" if prefill_tc_wide_wanted(meta, n_q, head_dim) else "kipp_attn_prefill_tc"
-    f = _fn("attention_tc", name,
+    f = _fn("attention_tc", "kipp_attn_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
              c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
     _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(meta.q_start),
