@@ -13,18 +13,24 @@
 //   warp 8     gathers the key and value tiles page by page with TMA (one box
 //              per lane, 128-byte swizzle) into a two-stage ring;
 //   warp 9     one thread issues the products.
-// Per tile of 64 keys: S = Q K^T (128 x 64 x D) into one of two score buffers in
-// tensor memory; the softmax threads scale, mask, take the running maximum
-// (exchanged between the two threads of a row through shared memory), form
-// p = 2^(s - m) and put it, as bfloat16, over the scores it came from; if some
-// row's maximum moved, the output accumulator in tensor memory is rescaled;
-// O += P V (128 x D x 64) takes P from tensor memory and V as an MN-major
-// shared-memory operand.  The products run ahead of the softmax: S of tile
-// i + 1 is computed while tile i is in the softmax, O += P V of tile i while
-// tile i + 1 is.  Everything is handed over through mbarriers; every wait is
-// bounded in time, and on a time-out status[1] is set and the CTA drains and
-// frees its tensor memory.  Two CTAs fit an SM (98 KB shared memory, 256
-// tensor-memory columns each).  All arithmetic outside the MMAs is float32.
+// Per tile of 64 keys: S = Q K^T (128 x 64 x D) into the score buffer in tensor
+// memory; the softmax threads take their scores into registers and release the
+// buffer at once, so S of the next tile runs while they scale, mask, take the
+// running maximum (exchanged between the two threads of a row through shared
+// memory) and form p = 2^(s - m), which goes as bfloat16 into one of two weight
+// buffers in tensor memory.  The running maximum moves only when a tile exceeds
+// it by more than 2^8 (numerator and denominator carry the same reference), so the
+// output accumulator in tensor memory is rescaled rarely.  O += P V (128 x D x 64)
+// takes P from tensor memory and V as an MN-major shared-memory operand; it runs
+// while the next tile is in the softmax.  Everything is handed over through
+// mbarriers; every wait is bounded in time, and on a time-out status[1] is set
+// and the CTA drains and frees its tensor memory.  Two CTAs fit an SM (98 KB
+// shared memory, 256 tensor-memory columns each: 64 scores, 2 x 32 weights, 128
+// output).  All arithmetic outside the MMAs is float32.
+//
+// The gather costs one TMA box per page and 64-column half: with 16-slot pages a
+// tile is 16 boxes of 2 KB, and the kernel is then a tenth slower than with pages
+// of 32 slots and more (4-8 boxes); with 8-slot pages a third slower.
 //
 // Keys beyond a row's limits are masked after the product, so whole pages are
 // fetched; rows of a tile without a page are fetched from beyond the end of the
