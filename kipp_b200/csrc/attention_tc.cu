@@ -99,6 +99,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// Box of a 4-dimensional map: columns x, slot y, kv head z, page w.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z,
+                                            int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
                  : "memory");
@@ -209,6 +217,8 @@ struct Params {
     const int* work;            // [items][2] = (entry, first token of the tile within the entry)
     int table_width, page_size, n_q, n_kv, window;
     int box_rows;               // rows of one TMA box = min(page_size, 64)
+    int pages_per_box;          // > 1: pages of fewer than 64 slots; a tile whose pages follow one another
+                                // in the pool comes as one box per 64-column half (the 4-dimensional maps)
     int rows_total;             // pages x kv heads x page_size: a row coordinate from here on reads zeros
     float scale_log2;
     uint32_t v_lbo, v_sbo;      // descriptor strides of the MN-major value tile
@@ -228,6 +238,7 @@ template <int D> struct Cfg {
 template <int D>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const __grid_constant__ CUtensorMap map_k4, const __grid_constant__ CUtensorMap map_v4,
                        const Params p) {
     using C = Cfg<D>;
     extern __shared__ __align__(1024) uint8_t smem[];     // swizzled tiles need 1024-byte alignment
@@ -296,23 +307,62 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const bool has_box = rb * p.box_rows < BN;
         const uint32_t dst_off = (uint32_t)(half * (BN * 128) + rb * p.box_rows * 128);
         bool ok = true;
-        for (int i = 0; i < n_tiles; ++i) {
-            const int kt = first_tile + i, b = i & 1, use = i >> 1;
-            int row_coord = p.rows_total;                  // beyond the pool: zeros
-            if (has_box) {
-                const int j = kt * BN + rb * p.box_rows;
-                const int slot = j / p.page_size;
-                const int page = (j <= hi && slot < p.table_width) ? __ldg(table + slot) : -1;
-                if (page >= 0) row_coord = (page * p.n_kv + g) * p.page_size + (j - slot * p.page_size);
+        // (This warp shares its scheduler with busy softmax warps and the stages come
+        // back to it just in time: every instruction between a stage's release and
+        // the issue of its load counts, so what can be is computed before the loop.)
+        if (p.pages_per_box > 1) {
+            // Pages of 8, 16 or 32 slots: a box is one page (box_rows = page_size), the
+            // boxes of a tile are the table entries kt * pages_per_box + rb.  When those
+            // pages follow one another in the pool (a request that grew without
+            // interruption), the tile comes as one box per half from the 4-dimensional
+            // map instead (a box costs the TMA unit about as much whatever its size).
+            const int last_slot = min(hi / p.page_size, p.table_width - 1);
+            const int page_rows = p.n_kv * p.page_size, head_row = g * p.page_size;
+            const uint32_t whole_off = (uint32_t)(half * (BN * 128));
+            for (int i = 0; i < n_tiles; ++i) {
+                const int kt = first_tile + i, b = i & 1, use = i >> 1;
+                const int slot = kt * p.pages_per_box + rb;
+                const int page = (has_box && slot <= last_slot) ? __ldg(table + slot) : -1;
+                const int first_page = __shfl_sync(0xffffffffu, page, 0);
+                const bool whole = __all_sync(0xffffffffu, !has_box || page == first_page + rb) && first_page >= 0;
+                const int row_coord = page >= 0 ? page * page_rows + head_row : p.rows_total;   // beyond the pool: zeros
+                if (i >= 2 && ok && !mbar_wait(&k_empty[b], (use - 1) & 1, abort_flag)) ok = false;
+                if (lane == 0) mbar_expect_tx(&k_full[b], C::KV_BYTES);
+                __syncwarp();
+                if (whole) {
+                    if (rb == 0 && ok) tma_load_4d(k_tiles + b * C::KV_BYTES + whole_off, &map_k4, &k_full[b], half * 64, 0, g, first_page);
+                } else if (has_box && ok) {
+                    tma_load_2d(k_tiles + b * C::KV_BYTES + dst_off, &map_k, &k_full[b], half * 64, row_coord);
+                }
+                if (i >= 2 && ok && !mbar_wait(&v_empty[b], (use - 1) & 1, abort_flag)) ok = false;
+                if (lane == 0) mbar_expect_tx(&v_full[b], C::KV_BYTES);
+                __syncwarp();
+                if (whole) {
+                    if (rb == 0 && ok) tma_load_4d(v_tiles + b * C::KV_BYTES + whole_off, &map_v4, &v_full[b], half * 64, 0, g, first_page);
+                } else if (has_box && ok) {
+                    tma_load_2d(v_tiles + b * C::KV_BYTES + dst_off, &map_v, &v_full[b], half * 64, row_coord);
+                }
             }
-            if (i >= 2 && ok && !mbar_wait(&k_empty[b], (use - 1) & 1, abort_flag)) ok = false;
-            if (lane == 0) mbar_expect_tx(&k_full[b], C::KV_BYTES);
-            __syncwarp();
-            if (has_box && ok) tma_load_2d(k_tiles + b * C::KV_BYTES + dst_off, &map_k, &k_full[b], half * 64, row_coord);
-            if (i >= 2 && ok && !mbar_wait(&v_empty[b], (use - 1) & 1, abort_flag)) ok = false;
-            if (lane == 0) mbar_expect_tx(&v_full[b], C::KV_BYTES);
-            __syncwarp();
-            if (has_box && ok) tma_load_2d(v_tiles + b * C::KV_BYTES + dst_off, &map_v, &v_full[b], half * 64, row_coord);
+        } else {
+            // Pages of 64 slots and multiples: a box is the 64-key half of a tile, inside one page.
+            for (int i = 0; i < n_tiles; ++i) {
+                const int kt = first_tile + i, b = i & 1, use = i >> 1;
+                int row_coord = p.rows_total;                  // beyond the pool: zeros
+                if (has_box) {
+                    const int j = kt * BN;
+                    const int slot = j / p.page_size;
+                    const int page = (j <= hi && slot < p.table_width) ? __ldg(table + slot) : -1;
+                    if (page >= 0) row_coord = (page * p.n_kv + g) * p.page_size + (j - slot * p.page_size);
+                }
+                if (i >= 2 && ok && !mbar_wait(&k_empty[b], (use - 1) & 1, abort_flag)) ok = false;
+                if (lane == 0) mbar_expect_tx(&k_full[b], C::KV_BYTES);
+                __syncwarp();
+                if (has_box && ok) tma_load_2d(k_tiles + b * C::KV_BYTES + dst_off, &map_k, &k_full[b], half * 64, row_coord);
+                if (i >= 2 && ok && !mbar_wait(&v_empty[b], (use - 1) & 1, abort_flag)) ok = false;
+                if (lane == 0) mbar_expect_tx(&v_full[b], C::KV_BYTES);
+                __syncwarp();
+                if (has_box && ok) tma_load_2d(v_tiles + b * C::KV_BYTES + dst_off, &map_v, &v_full[b], half * 64, row_coord);
+            }
         }
     } else if (warp == 9) {
         // ------------------------------------------------------------ MMA issuer
@@ -561,7 +611,34 @@ int pool_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int bo
     return 0;
 }
 
-template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int items, cudaStream_t s) {
+// The same pool as [n_pages][n_kv][page_size][D]; box = [pages_per_box pages, one kv head,
+// page_size slots, 64 columns] = 64 consecutive rows of a key tile when the pages
+// follow one another.
+int pool_map4(CUtensorMap* out, const void* ptr, int n_pages, int n_kv, int page_size, int cols, int pages_per_box) {
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, (long long)n_pages * n_kv, cols, page_size * 1024 + pages_per_box};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiled fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)page_size, (cuuint64_t)n_kv, (cuuint64_t)n_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)cols * 2, (cuuint64_t)page_size * cols * 2,
+                             (cuuint64_t)n_kv * page_size * cols * 2};
+    cuuint32_t box[4] = {64u, (cuuint32_t)page_size, 1u, (cuuint32_t)pages_per_box};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mk4, const CUtensorMap& mv4,
+                            const Params& p, int items, cudaStream_t s) {
     using C = Cfg<D>;
     static bool configured = false;
     if (!configured) {
@@ -570,7 +647,7 @@ template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, p);
+    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, mk4, mv4, p);
 }
 }  // namespace
 
@@ -618,6 +695,15 @@ extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_page
     if (rc) return rc;
     rc = pool_map(&mv, v_pages, rows, head_dim, p.box_rows);
     if (rc) return rc;
+    // pages of fewer than 64 slots: maps whose box is the whole 64-key half of a tile
+    CUtensorMap mk4 = mk, mv4 = mv;
+    p.pages_per_box = page_size < BN ? BN / page_size : 1;
+    if (p.pages_per_box > 1) {
+        rc = pool_map4(&mk4, k_pages, n_pages, n_kv, page_size, head_dim, p.pages_per_box);
+        if (rc) return rc;
+        rc = pool_map4(&mv4, v_pages, n_pages, n_kv, page_size, head_dim, p.pages_per_box);
+        if (rc) return rc;
+    }
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 64 ? launch<64>(mk, mv, p, items, s) : launch<128>(mk, mv, p, items, s);
+    return head_dim == 64 ? launch<64>(mk, mv, mk4, mv4, p, items, s) : launch<128>(mk, mv, mk4, mv4, p, items, s);
 }

@@ -237,16 +237,28 @@ def test_qk_norm_rope_write(case, dtype):
 
 
 # ------------------------------------------------------------------ attention
-def attention_case(seed, D, nq, nkv, page, layout, dtype, width=None):
+def attention_case(seed, D, nq, nkv, page, layout, dtype, width=None, order="permuted"):
     """layout: list of (cached tokens, new tokens).  Random pages in a permuted
-    pool; returns everything the kernels and the reference need."""
+    pool (order "consecutive": page ids in a row, as a request gets them from a
+    fresh pool; "runs": rows of 1 to 9 consecutive ids, in shuffled order);
+    returns everything the kernels and the reference need."""
     g = torch.Generator().manual_seed(seed)
     entries = [StepEntry(i, [0] * n, []) for i, (_, n) in enumerate(layout)]
     starts = [c for c, _ in layout]
     need = [-(-(c + n) // page) for c, n in layout]
     width = width or max(need)
     n_pages = sum(need) + 3
-    perm = torch.randperm(n_pages, generator=g).int().tolist()
+    if order == "consecutive":
+        perm = list(range(2, n_pages))
+    elif order == "runs":
+        runs, at = [], 0
+        while at < n_pages:
+            k = int(torch.randint(1, 10, (1,), generator=g))
+            runs.append(list(range(at, min(at + k, n_pages))))
+            at += k
+        perm = [x for i in torch.randperm(len(runs), generator=g).tolist() for x in runs[i]]
+    else:
+        perm = torch.randperm(n_pages, generator=g).int().tolist()
     table = np.full((len(layout), width), -1, dtype=np.int32)
     at = 0
     for i, k in enumerate(need):
@@ -337,6 +349,27 @@ def test_attention_tensor_core(shape, window):
         finally:
             attention_bf16.PREFILL_TC = True
         assert torch.allclose(out2.double().cpu(), ref, rtol=2e-2, atol=2e-2), (shape, li, window)
+
+
+@pytest.mark.parametrize("order", ["consecutive", "runs"])
+@pytest.mark.parametrize("page", [8, 16, 32])
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_pages_in_a_row(D, page, order):
+    """Pages that follow one another in the pool (what a request gets from a fresh
+    pool) are fetched as whole key tiles by the prompt kernel, pages in any other
+    order one by one: both in one launch, rows of consecutive pages that start and
+    end anywhere in a tile."""
+    nq, nkv = 4, 2
+    for window in (None, 150):
+        for li, layout in enumerate([[(0, 700)], [(300, 150), (0, 64), (77, 513)], [(64, 200), (1000, 129)]]):
+            meta, table, q, kp, vp = attention_case(40 + li, D, nq, nkv, page, layout, torch.bfloat16, order=order)
+            out = torch.full_like(q, 9.0)
+            st = status()
+            ops().attention(out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D),
+                            window, st, impl="mma")
+            ref = attention_ref(meta, table, q, kp, vp, layout, page, window, 1 / math.sqrt(D))
+            assert st.tolist() == [0, 0, 0, 0]
+            assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2), (D, page, order, li, window)
 
 
 @pytest.mark.parametrize("impl,dtype", [("simt", torch.float32), ("simt", torch.bfloat16),
