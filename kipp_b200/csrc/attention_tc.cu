@@ -28,9 +28,11 @@
 // shared memory, 256 tensor-memory columns each: 64 scores, 2 x 32 weights, 128
 // output).  All arithmetic outside the MMAs is float32.
 //
-// The gather costs one TMA box per page and 64-column half: with 16-slot pages a
-// tile is 16 boxes of 2 KB, and the kernel is then a tenth slower than with pages
-// of 32 slots and more (4-8 boxes); with 8-slot pages a third slower.
+// The gather costs one TMA box per page and 64-column half (with 16-slot pages 16
+// boxes of 2 KB a tile; the kernel is then 3 % slower than with pages of 64 slots,
+// with 8-slot pages 40 %), unless the pages of a tile follow one another in the pool,
+// as those of a request that grew without interruption do: then the tile comes as
+// one box per half, from a 4-dimensional map [page][kv head][slot][column].
 //
 // Keys beyond a row's limits are masked after the product, so whole pages are
 // fetched; rows of a tile without a page are fetched from beyond the end of the
