@@ -240,16 +240,23 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
            | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Ring of a narrow token tile (two CTAs per SM): as deep as two CTAs allow.  The weight
+// matrices of a decode step are 20-100 MB, and the rings of all CTAs together hold
+// about a quarter of the smallest: the deeper the ring, the more of the matrix is
+// asked for before the kernel's dependency wait (measured: 96 KB -> 110 KB is 0.9 % of
+// a decode step; 72, 56 and 40 KB, which would let the next kernel's CTAs move in
+// beside this one's, cost 3, 8 and 29 %).
+constexpr int NARROW_RING_BYTES = 110 * 1024;
 template <int TILE_T, int TILE_F> struct Cfg {
     static constexpr int HALVES = TILE_F / UMMA_M;               // accumulators (128 features each)
     static constexpr int W_BYTES = TILE_F * TILE_K * 2;
     static constexpr int X_BYTES = TILE_T * TILE_K * 2;
     static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-    // stages: as many as fit in ~96 KB for narrow token tiles (two CTAs per
-    // SM), ~192 KB for wide ones
+    // stages: as many as fit in NARROW_RING_BYTES for narrow token tiles (two CTAs
+    // per SM), ~192 KB for wide ones
     static constexpr int STAGES = (TILE_T >= 128 || TILE_F > 128)
                                       ? (192 * 1024) / STAGE_BYTES
-                                      : ((96 * 1024) / STAGE_BYTES > 8 ? 8 : (96 * 1024) / STAGE_BYTES);
+                                      : (NARROW_RING_BYTES / STAGE_BYTES > 8 ? 8 : NARROW_RING_BYTES / STAGE_BYTES);
     static constexpr int ACC_COLS = TILE_T * HALVES;
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;   // 32, 64, 128, 256 or 512
     // epilogue warp groups: two groups of four warps split the token columns
