@@ -362,7 +362,9 @@ attn_decode_kernel(const DecodeParams p) {
     constexpr int STAGES = DECODE_STAGES;
     const uint32_t k_base = smem_u32(smem), v_base = k_base + STAGES * TILE_BYTES;
     pdl_launch_dependents();
-    pdl_wait();
+    // (What is read before the dependency wait below comes with the step's lists, which a
+    // copy brought before any kernel of the step started, or lies in the cache since
+    // earlier steps.)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 2, t4 = lane & 3;
     // Grid (kv heads, tokens, splits): the splits are the slowest dimension, so the CTAs
@@ -385,6 +387,21 @@ attn_decode_kernel(const DecodeParams p) {
     float* my_o = p.part_o + (((size_t)n * p.n_q + g * group) * p.max_splits + split) * D;
     const size_t head_stride_ml = (size_t)p.max_splits * 2, head_stride_o = (size_t)p.max_splits * D;
 
+    // The first tiles of the split are fetched before the wait, while the kernel before
+    // this one ends, unless one of them holds the token's own position: its key and
+    // value are this step's (made below, or by the kernel before this one).
+    const int first_tile = lo / TILE_KEYS, last_tile = hi / TILE_KEYS, n_tiles = last_tile - first_tile + 1;
+    const bool early = lo <= hi && (first_tile + min(STAGES - 1, n_tiles)) * TILE_KEYS <= pos;
+    if (early) {
+#pragma unroll
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < n_tiles)
+                load_kv_tile<D>(k_base + s * TILE_BYTES, v_base + s * TILE_BYTES, p.k_pages, p.v_pages, table,
+                                p.table_width, p.page_size, p.n_kv, g, (first_tile + s) * TILE_KEYS, lo, hi);
+            cp_async_commit();
+        }
+    }
+    pdl_wait();
     if (lo > hi) {                                         // split wholly behind the window
         for (int i = threadIdx.x; i < group; i += THREADS) {
             my_ml[i * head_stride_ml] = -INFINITY;
@@ -396,10 +413,10 @@ attn_decode_kernel(const DecodeParams p) {
     uint32_t qf[D / 16][4];
     if (p.qkv != nullptr) {
         // Fused form: norm and rotation of the group's queries here, a warp per head, into
-        // shared memory (the tiles are not in use yet); the split that holds the token's
-        // own position also makes the new key and value and puts them into the cache.
+        // shared memory (behind the tiles); the split that holds the token's own position
+        // also makes the new key and value and puts them into the cache.
         constexpr int NE = D / 32;
-        bf16* q_s = reinterpret_cast<bf16*>(smem);                 // [16][D]
+        bf16* q_s = reinterpret_cast<bf16*>(smem + 2 * STAGES * TILE_BYTES);   // [16][D]
         const bf16* raw = p.qkv + (size_t)tok * p.ld_qkv;
         const float2* cs_row = p.cos_sin != nullptr ? p.cos_sin + (size_t)tok * (D / 2) : nullptr;
         for (int hh = warp; hh < group; hh += WARPS) {
@@ -439,7 +456,6 @@ attn_decode_kernel(const DecodeParams p) {
             qf[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + 2 * t4) : 0u;
             qf[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + 2 * t4) : 0u;
         }
-        __syncthreads();                                           // the tiles may now be loaded over q_s
     } else {
         const bf16* q0 = p.q + ((size_t)tok * p.n_q + g * group + min(g4, group - 1)) * D;
         const bf16* q1 = p.q + ((size_t)tok * p.n_q + g * group + min(g4 + 8, group - 1)) * D;
@@ -457,13 +473,14 @@ attn_decode_kernel(const DecodeParams p) {
     for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    const int first_tile = lo / TILE_KEYS, last_tile = hi / TILE_KEYS, n_tiles = last_tile - first_tile + 1;
+    if (!early) {
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_tiles)
-            load_kv_tile<D>(k_base + s * TILE_BYTES, v_base + s * TILE_BYTES, p.k_pages, p.v_pages, table,
-                            p.table_width, p.page_size, p.n_kv, g, (first_tile + s) * TILE_KEYS, lo, hi);
-        cp_async_commit();
+        for (int s = 0; s < STAGES - 1; ++s) {
+            if (s < n_tiles)
+                load_kv_tile<D>(k_base + s * TILE_BYTES, v_base + s * TILE_BYTES, p.k_pages, p.v_pages, table,
+                                p.table_width, p.page_size, p.n_kv, g, (first_tile + s) * TILE_KEYS, lo, hi);
+            cp_async_commit();
+        }
     }
     for (int i = 0; i < n_tiles; ++i) {
         const int buf = i % STAGES;
@@ -635,7 +652,7 @@ template <int D> int launch_prefill(const PrefillParams& p, int items, cudaStrea
 }
 
 template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s) {
-    constexpr int PIPE = 2 * DECODE_STAGES * TILE_KEYS * D * 2;
+    constexpr int PIPE = 2 * DECODE_STAGES * TILE_KEYS * D * 2 + 16 * D * 2;   // tiles, and the group's queries
     constexpr int MERGE = (2 * WARPS * 16 + WARPS * 16 * D) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
     static bool configured = false;
