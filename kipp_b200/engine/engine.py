@@ -102,8 +102,6 @@ class Engine:
         self._graphs: dict = {}
         self._shapes_seen: dict = {}
         self._last_decode_graph = None
-        self._burst_host = None
-        self._burst_events: list = []
         self.last_forward_launches = 0
         self.graph_replays = 0
         self.graph_kernel_launches = 0
@@ -261,14 +259,14 @@ class Engine:
         """Greedy decoding of ``steps`` tokens for every request without the host in
         the loop.  ``tokens[i]`` is the next token of ``requests[i]`` (its logits
         give the first new token).  Returns int32 ``[steps, len(requests)]`` on
-        the device: row k holds the tokens chosen at step k.  Each step's argmax
-        is fed to the next step on the device; the host only prepares positions
-        and launches, so nothing waits for a copy back.  Pages for all steps are
+        the device: row k holds the tokens chosen at step k.  The step is captured
+        in a CUDA graph together with its argmax, the hand-over of the chosen
+        tokens and the move of every request to its next position, so a burst is
+        a run of graph replays with no copy and no other launch in between.  Pages for all steps are
         taken first (``OutOfPages`` leaves every request as it was).  Callers
         that must look at every token (stop tokens, sampling with penalties)
         use :meth:`step`."""
         from ..kernels import sampling as _sampling
-        from .batch import decode_split_length
         n = len(requests)
         if n == 0 or steps <= 0:
             return torch.empty((0, n), dtype=torch.int32, device=self.runtime.device)
@@ -294,48 +292,27 @@ class Engine:
                 _sampling.argmax_rows(logits, out=ring[k])
                 cur = ring[k].tolist()
             return ring
-        # step 0 through the ordinary path (it captures the graph if need be)
+        # a graph of the step that feeds itself: argmax, token feedback and the move to
+        # the next position are captured behind the forward pass
+        from .graphs import DecodeGraph
         with torch.cuda.device(rt.device):
-            logits = self.step([StepEntry(r, [t], [0]) for r, t in zip(requests, tokens)])
-            _sampling.argmax_rows(logits, out=ring[0])
-            graph = self._last_decode_graph
-            if steps > 1 and (graph is None or graph.graph is None or graph.batch != n):
-                raise RuntimeError("decode_burst: the decode graph is missing")
-            if steps > 1:
-                o, static = graph.static.offsets, graph.static
-                # A ring of pinned rows, one per step in flight; a row is rewritten only
-                # after the copy that read it has run (an event per row).
-                depth = 16
-                host = self._burst_host
-                if host is None or host.shape[1] != static.n_ints:
-                    host = self._burst_host = torch.empty((depth, static.n_ints), dtype=torch.int32,
-                                                          pin_memory=True)
-                    self._burst_events = [None] * depth
-                template = static.host
-                token_section = static.device[o[1]:o[1] + n]
-                for k in range(1, steps):
-                    i = k % depth
-                    if self._burst_events[i] is not None:
-                        self._burst_events[i].synchronize()
-                    row = host[i]
-                    row.copy_(template)
-                    hv = row.numpy()
-                    at = [s + k for s in starts]
-                    hv[o[0]] = decode_split_length([a + 1 for a in at])
-                    hv[o[2]:o[2] + n] = at
-                    hv[o[5]:o[5] + n] = at
-                    static.device.copy_(row, non_blocking=True)
-                    if self._burst_events[i] is None:
-                        self._burst_events[i] = torch.cuda.Event()
-                    self._burst_events[i].record()
-                    token_section.copy_(ring[k - 1], non_blocking=True)
-                    graph.graph.replay()
-                    _sampling.argmax_rows(graph.logits, out=ring[k])
-                for r, s in zip(requests, starts):
-                    self.cache.advance(r, s + steps)
-                self.steps_run += steps - 1
-                self.graph_replays += steps - 1
-                self.graph_kernel_launches += (steps - 1) * graph.launches
+            entries = [StepEntry(r, [t], [0]) for r, t in zip(requests, tokens)]
+            slots = [self.cache.slot(r) for r in requests]
+            widths, tables = self._table_widths(requests, 64)
+            key = ("burst", n, tuple(widths))
+            graph = self._graphs.pop(key, None)
+            if graph is None:
+                if len(self._graphs) >= 24:
+                    self._graphs.pop(next(iter(self._graphs)))
+                graph = DecodeGraph(self, n, widths, feedback=True)
+            self._graphs[key] = graph
+            ring = graph.run_burst(entries, starts, slots, tables, steps)
+            for r, s in zip(requests, starts):
+                self.cache.advance(r, s + steps)
+            self.steps_run += steps
+            self.graph_replays += steps
+            self.graph_kernel_launches += steps * graph.launches
+            self.last_h2d_bytes = graph.static.n_ints * 4
         return ring
 
     def _shape_repeats(self, entries) -> bool:
@@ -351,10 +328,10 @@ class Engine:
         seen[sig] = n + 1
         return False
 
-    def _graph_step(self, entries, starts, slots, rids, bucket: int = 64, decode: bool = True) -> torch.Tensor:
-        from .graphs import DecodeGraph
-        # table width: what the longest entry needs, rounded up to `bucket` pages so that
-        # a captured graph serves many steps and little is copied for short contexts
+    def _table_widths(self, rids, bucket: int):
+        """Block-table width per cache group for a captured step, and the tables: what
+        the longest entry needs, rounded up to ``bucket`` pages so that a captured graph
+        serves many steps and little is copied for short contexts."""
         limit = self.spec.max_positions
         widths = []
         for gi, g in enumerate(self.cache.groups):
@@ -362,6 +339,11 @@ class Engine:
             need = max(len(self.cache.table(r, gi)) for r in rids)
             widths.append(max(1, min(max(cap, need), -(-(need + 1) // bucket) * bucket)))
         tables = [self.cache.block_table_rows(rids, gi, width=w) for gi, w in enumerate(widths)]
+        return widths, tables
+
+    def _graph_step(self, entries, starts, slots, rids, bucket: int = 64, decode: bool = True) -> torch.Tensor:
+        from .graphs import DecodeGraph
+        widths, tables = self._table_widths(rids, bucket)
         if decode:
             key = (len(entries), tuple(widths))
         else:

@@ -324,6 +324,28 @@ def test_decode_burst_gives_the_tokens_of_greedy_steps(dtype):
     a.cache.check()
 
 
+def test_decode_burst_longer_than_its_ring(monkeypatch):
+    """The tokens of a burst collect in a ring on the device that is read out when
+    it is full: with a ring of 8 rows, 21 steps give the tokens of 21 single steps."""
+    from kipp_b200.engine import Engine, StepEntry, graphs
+    from kipp_b200.kernels import argmax_rows
+    monkeypatch.setattr(graphs, "BURST_RING_ROWS", 8)
+    folder = model_folder("A")
+    opts = dict(dtype="bfloat16", page_size=16, cache_tokens=512, max_requests=4, max_batch_tokens=128)
+    a, b = Engine.from_folder(folder, **opts), Engine.from_folder(folder, **opts)
+    prompts = {r: random_tokens("A", n, seed=90 + n) for r, n in (("p", 30), ("q", 17))}
+    cur = []
+    for eng in (a, b):
+        cur = [int(argmax_rows(eng.step([StepEntry(r, p, [len(p) - 1])], check=True))[0]) for r, p in prompts.items()]
+    rids = list(prompts)
+    ring = a.decode_burst(rids, cur, 21).cpu()
+    for k in range(21):
+        cur = argmax_rows(b.step([StepEntry(r, [t], [0]) for r, t in zip(rids, cur)], check=True)).tolist()
+        assert ring[k].tolist() == cur, k
+    a.runtime.check_status()
+    a.cache.check()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_truncate_and_reset_continue_like_a_fresh_request(dtype):
     """A request cut back to 23 tokens and fed other tokens gives what a new
