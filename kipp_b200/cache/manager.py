@@ -17,52 +17,23 @@ unchanged (as pooled_map_blocks, src/kipp.c:3616-3635, and the batch rollback,
 src/kipp.c:4043-4072).
 
 This module is host bookkeeping only; device tensors are attached by the
-engine (``CacheGroup.k`` / ``.v``).
+engine (``CacheGroup.k`` / ``.v``).  The pools, the slots and the tables are kept
+by the C++ library csrc/host/cache_core.cpp; this class groups the runs, maps
+request ids to the library's integers and its error codes to exceptions.
 """
 from __future__ import annotations
 
-import dataclasses
+import ctypes
 from typing import Iterable, Optional
 
 import numpy as np
 
 from ..parts.base import PagedKVSpec
+from . import _native as N
 from .pages import OutOfPages, PagePool
-from .slots import StateSlots
+from .slots import OutOfSlots, StateSlots
 
 UNMAPPED = -1
-
-
-@dataclasses.dataclass
-class _RequestCache:
-    slot: int
-    length: int = 0
-    # per group: logical page index -> physical page (UNMAPPED if none)
-    tables: list = dataclasses.field(default_factory=list)
-    # per group: first logical page that may still be mapped (pages before it
-    # were given back by the window)
-    first_live: list = dataclasses.field(default_factory=list)
-    # per group: int32 mirror of ``tables`` (grown by doubling) so that block
-    # tables of a step are copied, not converted from lists
-    mirrors: list = dataclasses.field(default_factory=list)
-
-    def set_page(self, group: int, logical: int, page: int) -> None:
-        table = self.tables[group]
-        while len(table) <= logical:
-            table.append(UNMAPPED)
-        table[logical] = page
-        mirror = self.mirrors[group]
-        if logical >= mirror.shape[0]:
-            grown = np.full(max(2 * mirror.shape[0], logical + 1, 16), UNMAPPED, dtype=np.int32)
-            grown[:mirror.shape[0]] = mirror
-            self.mirrors[group] = mirror = grown
-        mirror[logical] = page
-
-    def trim(self, group: int) -> None:
-        """Drop trailing unmapped entries (after a roll-back)."""
-        table = self.tables[group]
-        while table and table[-1] == UNMAPPED:
-            table.pop()
 
 
 class CacheGroup:
@@ -72,7 +43,8 @@ class CacheGroup:
         self.spec = spec
         self.cache_ids = list(cache_ids)          # ids of the runs' caches, in storage order
         self.page_size = page_size
-        self.pool = PagePool(n_pages)
+        self.n_pages = n_pages
+        self.pool: Optional[PagePool] = None      # a view of the manager's pool of this group
         self.k = None                             # device [caches, pages, kv_heads, page_size, D]
         self.v = None
 
@@ -112,7 +84,6 @@ class CacheManager:
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
-        self.slots = StateSlots(max_requests)
         by_spec: dict[PagedKVSpec, list[int]] = {}
         for cid in sorted(specs_by_cache_id):
             by_spec.setdefault(specs_by_cache_id[cid], []).append(cid)
@@ -120,103 +91,108 @@ class CacheManager:
         self.group_of_cache: dict[int, tuple[int, int]] = {}     # cache id -> (group, index in group)
         for gi, (spec, cids) in enumerate(by_spec.items()):
             n = pages_per_group[spec] if isinstance(pages_per_group, dict) else pages_per_group
+            if n <= 0:
+                raise ValueError("a page pool needs at least one page")
             self.groups.append(CacheGroup(gi, spec, cids, page_size, n))
             for j, cid in enumerate(cids):
                 self.group_of_cache[cid] = (gi, j)
-        self._requests: dict[object, _RequestCache] = {}
+        if max_requests <= 0:
+            raise ValueError("max_requests must be positive")
+        # the pools, the slots and the tables live in the C++ library; requests are
+        # 64-bit integers there
+        self._lib = N.lib()
+        ng = len(self.groups)
+        pages = (ctypes.c_int * max(ng, 1))(*[g.n_pages for g in self.groups])
+        windows = (ctypes.c_int * max(ng, 1))(*[-1 if g.window is None else g.window for g in self.groups])
+        self._h = self._lib.kipp_cm_create(ng, pages, windows, page_size, max_requests)
+        if not self._h:
+            raise ValueError("the cache manager could not be created")
+        self._owners = N.OwnerIds()
+        for gi, g in enumerate(self.groups):
+            g.pool = PagePool(g.n_pages, _handle=self._lib.kipp_cm_pool(self._h, gi), _owners=self._owners,
+                              _keep=self)
+        self.slots = StateSlots(max_requests, _handle=self._lib.kipp_cm_slots(self._h), _owners=self._owners,
+                                _keep=self)
+        self._held = (ctypes.c_int * max(ng, 1))()
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self._lib.kipp_cm_destroy(h)
+            self._h = None
+
+    def _id(self, rid) -> int:
+        i = self._owners.id_of(rid)
+        if not i:
+            raise KeyError(rid)
+        return i
 
     # -- requests ---------------------------------------------------------------
     def __contains__(self, rid) -> bool:
-        return rid in self._requests
+        return rid in self._owners
 
     def live_requests(self) -> list:
-        return list(self._requests)
+        return self._owners.objects()
 
     def admit(self, rid) -> int:
         """Give ``rid`` a slot; it holds no pages yet.  Returns the slot."""
-        if rid in self._requests:
+        if rid in self._owners:
             raise ValueError(f"request {rid!r} is already live")
-        slot = self.slots.alloc(rid)
-        self._requests[rid] = _RequestCache(slot=slot, tables=[[] for _ in self.groups],
-                                            first_live=[0 for _ in self.groups],
-                                            mirrors=[np.full(16, UNMAPPED, dtype=np.int32)
-                                                     for _ in self.groups])
+        slot = self._lib.kipp_cm_admit(self._h, self._owners.id_of(rid, create=True))
+        if slot < 0:
+            self._owners.forget(rid)
+            if slot == N.ERR_OUT_OF_SLOTS:
+                raise OutOfSlots(f"all {self.slots.max_requests} request slots are in use")
+            raise RuntimeError(f"admit: error {slot}")
         return slot
 
     def slot(self, rid) -> int:
-        return self._requests[rid].slot
+        return self._lib.kipp_cm_slot(self._h, self._id(rid))
 
     def length(self, rid) -> int:
-        return self._requests[rid].length
+        return self._lib.kipp_cm_length(self._h, self._id(rid))
 
     def release(self, rid) -> None:
         """The request ended: give back all its pages and its slot."""
-        rc = self._requests.pop(rid)
-        for g, table in zip(self.groups, rc.tables):
-            for page in table:
-                if page != UNMAPPED:
-                    g.pool.free(page, rid)
-        self.slots.free(rc.slot, rid)
+        rc = self._lib.kipp_cm_release(self._h, self._id(rid))
+        self._owners.forget(rid)
+        if rc:
+            raise RuntimeError(f"release of {rid!r}: error {rc}")
 
     # -- growth -------------------------------------------------------------------
     def missing_pages(self, rid, new_length: int) -> list[int]:
         """Pages per group that ``reserve`` would have to take for ``rid`` to
         hold positions up to ``new_length``."""
-        rc = self._requests[rid]
-        out = []
-        for gi, g in enumerate(self.groups):
-            table = rc.tables[gi]
-            out.append(sum(1 for lp in g.pages_for(rc.length, new_length)
-                           if lp >= len(table) or table[lp] == UNMAPPED))
-        return out
+        self._lib.kipp_cm_missing_pages(self._h, self._id(rid), new_length, self._held)
+        return list(self._held[:len(self.groups)])
 
     def reserve(self, wants: Iterable[tuple[object, int]]) -> None:
         """Map pages so that each ``(rid, new_length)`` can be written.  Either
         every request of the call gets its pages or none does."""
-        taken: list[tuple[int, object, int, int]] = []       # (group, rid, logical, page)
-        try:
-            for rid, new_length in wants:
-                rc = self._requests[rid]
-                if new_length < rc.length:
-                    raise ValueError("a request cannot shrink")
-                for gi, g in enumerate(self.groups):
-                    table = rc.tables[gi]
-                    for lp in g.pages_for(rc.length, new_length):
-                        if lp >= len(table) or table[lp] == UNMAPPED:
-                            if lp < rc.first_live[gi]:
-                                raise RuntimeError("a page behind the window was asked for")
-                            page = g.pool.alloc(rid)
-                            rc.set_page(gi, lp, page)
-                            taken.append((gi, rid, lp, page))
-        except OutOfPages:
-            for gi, rid, lp, page in reversed(taken):
-                self.groups[gi].pool.free(page, rid)
-                self._requests[rid].set_page(gi, lp, UNMAPPED)
-            for rid, _ in wants:
-                rc = self._requests.get(rid)
-                if rc is None:
-                    continue
-                for gi in range(len(self.groups)):  # drop trailing holes the call made
-                    rc.trim(gi)
-            raise
+        wants = list(wants)
+        n = len(wants)
+        if n == 0:
+            return
+        rids = (ctypes.c_longlong * n)(*[self._id(r) for r, _ in wants])
+        lengths = (ctypes.c_int * n)(*[int(length) for _, length in wants])
+        rc = self._lib.kipp_cm_reserve(self._h, n, rids, lengths)
+        if rc == N.ERR_OUT_OF_PAGES:
+            raise OutOfPages("page pool exhausted")
+        if rc == N.ERR_ARGUMENT:
+            raise ValueError("a request cannot shrink")
+        if rc == N.ERR_BEHIND_WINDOW:
+            raise RuntimeError("a page behind the window was asked for")
+        if rc:
+            raise RuntimeError(f"reserve: error {rc}")
 
     def advance(self, rid, new_length: int) -> None:
         """The step wrote positions up to ``new_length``.  Window groups give
         back the pages no later token can see."""
-        rc = self._requests[rid]
-        if new_length < rc.length:
+        rc = self._lib.kipp_cm_advance(self._h, self._id(rid), new_length)
+        if rc == N.ERR_ARGUMENT:
             raise ValueError("a request cannot shrink")
-        rc.length = new_length
-        for gi, g in enumerate(self.groups):
-            if g.window is None:
-                continue
-            table = rc.tables[gi]
-            keep_from = g.first_needed_position(new_length) // g.page_size
-            for lp in range(rc.first_live[gi], min(keep_from, len(table))):
-                if table[lp] != UNMAPPED:
-                    g.pool.free(table[lp], rid)
-                    rc.set_page(gi, lp, UNMAPPED)
-            rc.first_live[gi] = max(rc.first_live[gi], min(keep_from, len(table)))
+        if rc:
+            raise RuntimeError(f"advance: error {rc}")
 
     def truncate(self, rid, new_length: int) -> None:
         """Forget the positions from ``new_length`` on: pages that hold none of the
@@ -225,70 +201,47 @@ class CacheManager:
         src/kipp.c:3755-3768; its reset is a truncate to 0).  A window group can
         only be cut back to where the pages it still holds cover what the next
         token may see; else the call is refused and nothing changes."""
-        rc = self._requests[rid]
-        if new_length < 0 or new_length > rc.length:
-            raise ValueError(f"truncate to {new_length} is outside 0..{rc.length}")
-        for gi, g in enumerate(self.groups):
-            if g.window is None or new_length == 0:
-                continue
-            first_page = g.first_needed_position(new_length) // g.page_size
-            if first_page < rc.first_live[gi]:
-                raise ValueError(f"request {rid!r} cannot be cut back to {new_length}: the window of cache "
-                                 f"group {gi} has already given back pages it would need")
-        for gi, g in enumerate(self.groups):
-            table = rc.tables[gi]
-            keep = -(-new_length // g.page_size)              # pages with positions below new_length
-            for lp in range(keep, len(table)):
-                if table[lp] != UNMAPPED:
-                    g.pool.free(table[lp], rid)
-                    rc.set_page(gi, lp, UNMAPPED)
-            del table[keep:]
-            if new_length == 0:
-                rc.first_live[gi] = 0
-            else:
-                rc.first_live[gi] = min(rc.first_live[gi], keep)
-        rc.length = new_length
+        group = ctypes.c_int(-1)
+        rc = self._lib.kipp_cm_truncate(self._h, self._id(rid), new_length, ctypes.byref(group))
+        if rc == N.ERR_ARGUMENT:
+            raise ValueError(f"truncate to {new_length} is outside 0..{self.length(rid)}")
+        if rc == N.ERR_WINDOW_REFUSES:
+            raise ValueError(f"request {rid!r} cannot be cut back to {new_length}: the window of cache "
+                             f"group {group.value} has already given back pages it would need")
+        if rc:
+            raise RuntimeError(f"truncate: error {rc}")
 
     # -- views ----------------------------------------------------------------------
     def table(self, rid, group: int) -> list[int]:
-        return self._requests[rid].tables[group]
+        i = self._id(rid)
+        n = self._lib.kipp_cm_table_len(self._h, i, group)
+        buf = (ctypes.c_int * max(n, 1))()
+        self._lib.kipp_cm_table(self._h, i, group, buf, n)
+        return list(buf[:n])
+
+    def table_len(self, rid, group: int) -> int:
+        return self._lib.kipp_cm_table_len(self._h, self._id(rid), group)
 
     def block_table_rows(self, rids: list, group: int, width: Optional[int] = None) -> np.ndarray:
         """int32 [len(rids), width] of physical pages, UNMAPPED where none."""
-        reqs = [self._requests[r] for r in rids]
-        lens = [len(rc.tables[group]) for rc in reqs]
+        n = len(rids)
+        ids = (ctypes.c_longlong * max(n, 1))(*[self._id(r) for r in rids])
         if width is None:
-            width = max(lens + [1])
-        out = np.full((len(rids), width), UNMAPPED, dtype=np.int32)
-        for i, (rc, n) in enumerate(zip(reqs, lens)):
-            if n:
-                out[i, :n] = rc.mirrors[group][:n]
+            width = max([self._lib.kipp_cm_table_len(self._h, i, group) for i in ids[:n]] + [1])
+        out = np.empty((n, width), dtype=np.int32)
+        if n and self._lib.kipp_cm_rows(self._h, group, n, ids, width, out.ctypes.data):
+            raise ValueError("block_table_rows: a table is longer than the width asked for")
         return out
 
     def pages_held(self, rid) -> list[int]:
-        return [sum(1 for p in t if p != UNMAPPED) for t in self._requests[rid].tables]
+        self._lib.kipp_cm_pages_held(self._h, self._id(rid), self._held)
+        return list(self._held[:len(self.groups)])
 
     def free_pages(self) -> list[int]:
         return [g.pool.free_pages for g in self.groups]
 
     def check(self) -> None:
-        """No page lost, held twice or free and held; tables and pools agree."""
-        for gi, g in enumerate(self.groups):
-            g.pool.check()
-            seen: dict[int, object] = {}
-            for rid, rc in self._requests.items():
-                for page in rc.tables[gi]:
-                    if page == UNMAPPED:
-                        continue
-                    if page in seen:
-                        raise AssertionError(f"page {page} of group {gi} is held twice")
-                    seen[page] = rid
-                    if g.pool.owner(page) != rid:
-                        raise AssertionError(f"page {page} of group {gi}: table and pool disagree")
-            for rid, rc in self._requests.items():
-                n = len(rc.tables[gi])
-                if rc.mirrors[gi][:n].tolist() != rc.tables[gi]:
-                    raise AssertionError(f"group {gi}: the int32 mirror of {rid!r}'s table is stale")
-            if len(seen) != g.pool.used_pages:
-                raise AssertionError(f"group {gi}: {g.pool.used_pages - len(seen)} pages are lost")
-        self.slots.check()
+        """No page lost, held twice or free and held; tables, pools and slots agree."""
+        if self._lib.kipp_cm_check(self._h):
+            raise AssertionError("the cache manager's tables, pools and slots disagree "
+                                 "(a page lost, held twice, or both free and held)")

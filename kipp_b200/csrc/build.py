@@ -1,5 +1,6 @@
 """Builds the CUDA sources of this folder into shared libraries for sm_100a
-and loads them with ctypes.
+and loads them with ctypes; the plain C++ sources under ``host/`` (bookkeeping
+that needs no GPU) are built with the C++ compiler in the same way.
 
 Each ``<name>.cu`` becomes ``_build/lib<name>.so`` the first time one of its
 kernels is needed, so a run compiles only what its model uses.  A library is
@@ -172,6 +173,82 @@ def compile_library(name: str, *, verbose: bool = True, force: bool = False) -> 
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
+# ---------------------------------------------------------------------- host libraries
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
+
+
+def _cxx() -> str:
+    for cand in (os.environ.get("KIPP_B200_CXX"), os.environ.get("CXX"), shutil.which("g++"),
+                 shutil.which("c++"), shutil.which("clang++")):
+        if cand and (os.path.isfile(cand) or shutil.which(cand)):
+            return cand
+    raise BuildError("no C++ compiler found (set CXX or KIPP_B200_CXX); the host libraries of kipp_b200 "
+                     "cannot be built and there is no fallback")
+
+
+def compile_host_library(name: str, *, verbose: bool = True) -> str:
+    """Compile ``host/<name>.cpp`` (plain C++, no CUDA) if its library is missing or stale."""
+    src = os.path.join(_HERE, "host", name + ".cpp")
+    if not os.path.isfile(src):
+        raise BuildError(f"no host source {src}")
+    out_dir = build_dir()
+    so = os.path.join(out_dir, f"lib{name}.so")
+    stamp = so + ".sha256"
+    h = hashlib.sha256()
+    with open(src, "rb") as fh:
+        h.update(fh.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    digest = h.hexdigest()
+
+    def fresh() -> bool:
+        try:
+            with open(stamp, "r") as f:
+                return os.path.isfile(so) and f.read().strip() == digest
+        except OSError:
+            return False
+
+    if fresh():
+        return so
+    with open(os.path.join(out_dir, f".{name}.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if fresh():
+                return so
+            tmp = f"{so}.{os.getpid()}.tmp"
+            cmd = [_cxx()] + HOST_FLAGS + ["-o", tmp, src]
+            t0 = time.time()
+            proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=out_dir)
+            if proc.returncode != 0:
+                try:
+                    os.unlink(tmp)
+                except OSError:
+                    pass
+                raise BuildError(f"the C++ compiler failed for host/{name}.cpp:\n{' '.join(cmd)}\n{proc.stdout}")
+            os.replace(tmp, so)
+            with open(stamp, "w") as f:
+                f.write(digest)
+            if verbose:
+                print(f"[kipp_b200] built lib{name}.so in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+            return so
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def host_source_names() -> list[str]:
+    d = os.path.join(_HERE, "host")
+    return sorted(f[:-4] for f in os.listdir(d) if f.endswith(".cpp")) if os.path.isdir(d) else []
+
+
+def load_host_library(name: str) -> ctypes.CDLL:
+    key = "host/" + name
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is None:
+            lib = ctypes.CDLL(compile_host_library(name))
+            _loaded[key] = lib
+        return lib
+
+
 def load_library(name: str) -> ctypes.CDLL:
     with _lock:
         lib = _loaded.get(name)
@@ -187,4 +264,5 @@ def build_all(verbose: bool = True, jobs: int | None = None) -> list[str]:
     names = source_names()
     jobs = jobs or min(len(names), os.cpu_count() or 1) or 1
     with ThreadPoolExecutor(max_workers=jobs) as pool:
-        return list(pool.map(lambda n: compile_library(n, verbose=verbose), names))
+        built = list(pool.map(lambda n: compile_library(n, verbose=verbose), names))
+    return built + [compile_host_library(n, verbose=verbose) for n in host_source_names()]

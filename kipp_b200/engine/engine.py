@@ -336,7 +336,7 @@ class Engine:
         widths = []
         for gi, g in enumerate(self.cache.groups):
             cap = g.pool.n_pages if limit is None else min(g.pool.n_pages, -(-limit // g.page_size))
-            need = max(len(self.cache.table(r, gi)) for r in rids)
+            need = max(self.cache.table_len(r, gi) for r in rids)
             widths.append(max(1, min(max(cap, need), -(-(need + 1) // bucket) * bucket)))
         tables = [self.cache.block_table_rows(rids, gi, width=w) for gi, w in enumerate(widths)]
         return widths, tables
