@@ -187,3 +187,29 @@ def test_truncate_gives_back_the_pages_past_the_new_length():
     assert w.free_pages() == [8, 8]
     w.reserve([("b", 6)]); w.advance("b", 6)
     w.check()
+
+
+def test_errors_leave_everything_as_it_was():
+    """Whatever refuses a reserve (a pool that is empty, a request that would shrink),
+    the pages the call had taken are back and the tables are as before; rows narrower
+    than a table are refused; unknown requests are KeyErrors."""
+    m = CacheManager({0: FULL}, page_size=4, pages_per_group=8, max_requests=2)
+    m.admit("a"); m.admit("b")
+    with pytest.raises(OutOfSlots):
+        m.admit("c")
+    assert "c" not in m and m.live_requests() == ["a", "b"]
+    m.reserve([("a", 9)]); m.advance("a", 9)
+    before = (m.table("a", 0), m.table("b", 0), m.free_pages())
+    with pytest.raises(ValueError):
+        m.reserve([("b", 7), ("a", 3)])                      # b would get pages, then a shrinks
+    assert (m.table("a", 0), m.table("b", 0), m.free_pages()) == before
+    with pytest.raises(ValueError):
+        m.block_table_rows(["a"], 0, width=2)                # a holds three pages
+    assert m.block_table_rows(["a", "b"], 0, width=4).tolist() == [[0, 1, 2, UNMAPPED], [UNMAPPED] * 4]
+    for call in (lambda: m.length("zz"), lambda: m.reserve([("zz", 1)]), lambda: m.release("zz")):
+        with pytest.raises(KeyError):
+            call()
+    assert m.groups[0].pool.owner(1) == "a" and m.groups[0].pool.owner(5) is None
+    m.release("a"); m.release("b")
+    m.check()
+    assert m.free_pages() == [8] and m.slots.free_slots == 2
