@@ -451,6 +451,38 @@ def test_attention_scores_that_climb(rate):
 
 
 # ------------------------------------------------------------------ sampling
+def test_burst_advance_moves_a_step_on():
+    """The kernel between two greedy steps of a burst: tokens handed over and put into
+    the ring row the counter names, positions and cached lengths + 1, and the keys per
+    decode-attention split chosen as the host chooses them for the new lengths."""
+    from kipp_b200.engine.batch import (DECODE_CTA_FIXED_TILES, DECODE_MAX_SPLITS, DECODE_MIN_SPLIT,
+                                        DECODE_RESIDENT_CTAS, decode_split_length)
+    from kipp_b200.kernels import sampling
+    g = torch.Generator().manual_seed(5)
+    for n, longest in ((1, 100), (1, 2047), (3, 5000), (8, 8190), (8, 127), (64, 2047), (64, 40_000), (130, 700)):
+        lens = torch.randint(1, longest + 1, (n,), generator=g).int()
+        lens[int(torch.randint(0, n, (1,), generator=g))] = longest
+        dev = lambda t: t.clone().to(DEV)
+        tokens, positions, context = dev(torch.zeros(n).int()), dev(lens), dev(lens)
+        split, counter = dev(torch.zeros(4).int()), dev(torch.tensor([2]).int())
+        nxt = torch.randint(0, 50_000, (n,), generator=g).int()
+        ring = torch.full((4, n), -7, dtype=torch.int32, device=DEV)
+        sampling.burst_advance(tokens, positions, context, split[:1], dev(nxt), ring, counter, 8,
+                               DECODE_RESIDENT_CTAS, DECODE_CTA_FIXED_TILES, DECODE_MIN_SPLIT, DECODE_MAX_SPLITS)
+        assert tokens.cpu().tolist() == nxt.tolist()
+        assert positions.cpu().tolist() == (lens + 1).tolist() == context.cpu().tolist()
+        assert int(counter) == 3 and ring[2].cpu().tolist() == nxt.tolist()
+        assert ring[[0, 1, 3]].eq(-7).all()
+        # the next step's tokens sit at positions lens + 1 and see lens + 2 keys
+        assert int(split[0]) == decode_split_length([int(x) + 2 for x in lens]), (n, longest)
+        assert split[1:].eq(0).all()
+        # a full ring: the tokens are still handed over, no row is written
+        counter.fill_(4)
+        sampling.burst_advance(tokens, positions, context, split[:1], dev(nxt), ring, counter, 8,
+                               DECODE_RESIDENT_CTAS, DECODE_CTA_FIXED_TILES, DECODE_MIN_SPLIT, DECODE_MAX_SPLITS)
+        assert int(counter) == 5 and ring[[0, 1, 3]].eq(-7).all()
+
+
 def test_argmax_first_maximum():
     logits = torch.randn(5, 1000, generator=torch.Generator().manual_seed(1)).to(DEV)
     logits[1, 7] = logits[1, 900] = 50.0
