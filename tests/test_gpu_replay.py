@@ -10,7 +10,8 @@ from tiny import nmse
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 97], "B": [1, 64, 100, 200], "C": [9, 70, 130, 41], "D": [3, 129, 260, 66]}
+LENGTHS = {"A": [5, 17, 33, 97], "B": [1, 64, 100, 200], "C": [9, 70, 130, 41], "D": [3, 129, 260, 66],
+           "E": [3, 200, 330, 70]}
 PORTIONS = [7, 2, 19, 2, 48, 3, 2, 31, 64, 2, 5]
 
 
@@ -74,10 +75,10 @@ def build_trace(name: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_every_way_of_cutting_matches_the_plain_model(name, dtype):
     seqs, tr = build_trace(name)
-    page = {"A": 16, "B": 8, "C": 16, "D": 32}[name]
+    page = {"A": 16, "B": 8, "C": 16, "D": 32, "E": 16}[name]
     got = tr.collect(replay(name, dtype, tr.steps, max_tokens=tr.peak_tokens, page_size=page))
     total_pages_needed = sum(-(-len(t) // page) for t in seqs.values()) * 5
     assert total_pages_needed > 2 * tr.peak_tokens // page           # pages had to be used again
@@ -92,9 +93,10 @@ def test_every_way_of_cutting_matches_the_plain_model(name, dtype):
         worst[mode] = max(worst.get(mode, 0.0), nmse(row, want))
     assert all(n > 0 for n in modes.values()), modes
     assert modes["whole"] == sum(LENGTHS[name]) and modes["cut"] == sum(LENGTHS[name])
-    # the ways of cutting agree with one another far inside the bound of the 32-bit path
+    # the 32-bit kernels sum in an order that does not depend on the cut, the batch
+    # or the pages: every way of cutting gives the same bits
     if dtype == "float32":
         for (rid, pos), row in got.items():
             mode, base = rid.split("-", 1)
             if mode != "whole":
-                assert nmse(row, got[("whole-" + base, pos)]) <= 1e-11, (rid, pos)
+                assert torch.equal(row, got[("whole-" + base, pos)]), (rid, pos)

@@ -47,8 +47,19 @@ TINY_D = dict(
     sliding_window=50, layer_types=["sliding_attention", "full_attention"], torch_dtype="float32")
 TINY_D_INIT = dict(seed=11, sigma=0.05, norm_jitter=0.1)
 
+# E has the head size of the shipped Qwen3 models (128): prompt portions of 64
+# tokens and more run on the tcgen05 attention kernel, shorter ones on mma.sync,
+# decoded tokens on the split-K kernel with the fused norm/rotation/cache write.
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=640, hidden_size=256,
+    intermediate_size=416, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+    head_dim=128, max_position_embeddings=2048, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, hidden_act="silu", attention_bias=False, initializer_range=0.03,
+    torch_dtype="float32")
+TINY_E_INIT = dict(seed=13, sigma=0.03, norm_jitter=0.1)
+
 CONFIGS = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT),
-           "D": (TINY_D, TINY_D_INIT)}
+           "D": (TINY_D, TINY_D_INIT), "E": (TINY_E, TINY_E_INIT)}
 
 
 def make_model_folder(folder: str, name: str, dtype=torch.float32) -> str:
