@@ -1,4 +1,5 @@
-"""ctypes bindings of the C++ bookkeeping (csrc/host/cache_core.cpp)."""
+"""ctypes bindings of the cache manager's C functions (csrc/host/cache_core.cpp,
+part of the host core's library)."""
 from __future__ import annotations
 
 import ctypes
@@ -43,7 +44,7 @@ def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         from ..csrc import build
-        loaded = build.load_host_library("cache_core")
+        loaded = build.load_host_library()
         for name, (res, args) in _SIGNATURES.items():
             fn = getattr(loaded, name)
             fn.restype, fn.argtypes = res, args

@@ -115,11 +115,34 @@ class CacheManager:
                                 _keep=self)
         self._held = (ctypes.c_int * max(ng, 1))()
 
+    @classmethod
+    def view_of(cls, handle, groups: list, page_size: int, max_requests: int, owners: "N.OwnerIds",
+                keep=None) -> "CacheManager":
+        """A face of a cache manager that someone else owns (an engine's): the
+        same queries and checks, nothing is created or destroyed.  ``groups`` is a
+        list of ``(PagedKVSpec, number of caches, pages)``."""
+        self = cls.__new__(cls)
+        self.page_size = page_size
+        self._lib = N.lib()
+        self._h = handle
+        self._owned = False
+        self._keep = keep
+        self._owners = owners
+        self.groups = []
+        self.group_of_cache = {}
+        for gi, (spec, n_caches, n_pages) in enumerate(groups):
+            g = CacheGroup(gi, spec, list(range(n_caches)), page_size, n_pages)
+            g.pool = PagePool(n_pages, _handle=self._lib.kipp_cm_pool(handle, gi), _owners=owners, _keep=self)
+            self.groups.append(g)
+        self.slots = StateSlots(max_requests, _handle=self._lib.kipp_cm_slots(handle), _owners=owners, _keep=self)
+        self._held = (ctypes.c_int * max(len(self.groups), 1))()
+        return self
+
     def __del__(self):
         h = getattr(self, "_h", None)
-        if h:
+        if h and getattr(self, "_owned", True):
             self._lib.kipp_cm_destroy(h)
-            self._h = None
+        self._h = None
 
     def _id(self, rid) -> int:
         i = self._owners.id_of(rid)
@@ -129,10 +152,11 @@ class CacheManager:
 
     # -- requests ---------------------------------------------------------------
     def __contains__(self, rid) -> bool:
-        return rid in self._owners
+        i = self._owners.id_of(rid)
+        return bool(i) and self._lib.kipp_cm_slot(self._h, i) >= 0
 
     def live_requests(self) -> list:
-        return self._owners.objects()
+        return [r for r in self._owners.objects() if r in self]
 
     def admit(self, rid) -> int:
         """Give ``rid`` a slot; it holds no pages yet.  Returns the slot."""

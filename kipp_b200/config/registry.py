@@ -41,6 +41,11 @@ def registered_architectures() -> list[str]:
     return sorted(_REGISTRY)
 
 
+def is_registered(name: str) -> bool:
+    _ensure_builtin()
+    return name in _REGISTRY
+
+
 def get_architecture(name: str) -> Architecture:
     _ensure_builtin()
     try:

@@ -55,6 +55,6 @@ extern "C" int kipp_attn_decode_mma_noalloc(void* out, const void* q, const void
     const int rc = scratch_for_current_device(&scratch);
     if (rc) return rc;
     return kipp_attn_decode_mma(out, q, k_pages, v_pages, q_start, context_len, block_table, table_width,
-                                page_size, rows, n, n_q, n_kv, head_dim, scale, window, max_splits, split_keys,
+                                page_size, rows, n, n_q, n_kv, head_dim, scale, window, max_splits, split_keys, 0,
                                 scratch, stream);
 }

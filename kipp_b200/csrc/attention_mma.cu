@@ -302,7 +302,9 @@ struct DecodeParams {
     float* part_o;              // [n][n_q][max_splits][D]
     float* part_ml;             // [n][n_q][max_splits][2]  (max in log2 units, sum)
     bf16* out;                  // [tokens][n_q][D]: written here when a token has one split
-    const int* split_keys;      // device: keys per split of this step (a multiple of 64)
+    const int* split_keys;      // device: keys per split (a multiple of 64): one value for the step
+                                // (split_stride 0) or one per decoded token (split_stride 1)
+    int split_stride;
     int table_width, page_size, n_q, n_kv, window, max_splits;
     float scale_log2;
     // Fused form (qkv != nullptr): queries, the new key and the new value come raw out of
@@ -378,7 +380,7 @@ attn_decode_kernel(const DecodeParams p) {
     const int pos = p.context_len[entry];                  // position of the decoded token
     const int kv_len = pos + 1;
     const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int split_keys = decode_split_keys(kv_len, p.max_splits, __ldg(p.split_keys));
+    const int split_keys = decode_split_keys(kv_len, p.max_splits, __ldg(p.split_keys + n * p.split_stride));
     const int n_splits = (kv_len + split_keys - 1) / split_keys;
     if (split >= n_splits) return;
     const int lo = max(first_key, split * split_keys), hi = min(pos, (split + 1) * split_keys - 1);
@@ -589,13 +591,13 @@ __global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __
                                          const float* __restrict__ part_ml, const int* __restrict__ rows,
                                          const int* __restrict__ q_start, const int* __restrict__ context_len,
                                          int n_q, int head_dim, int max_splits,
-                                         const int* __restrict__ split_keys_ptr) {
+                                         const int* __restrict__ split_keys_ptr, int split_stride) {
     pdl_launch_dependents();
     pdl_wait();
     const int n = blockIdx.y, h = blockIdx.x;
     const int entry = rows[n];
     const int kv_len = context_len[entry] + 1;
-    const int split_keys = decode_split_keys(kv_len, max_splits, __ldg(split_keys_ptr));
+    const int split_keys = decode_split_keys(kv_len, max_splits, __ldg(split_keys_ptr + n * split_stride));
     const int n_splits = (kv_len + split_keys - 1) / split_keys;
     if (n_splits == 1) return;                     // the split kernel wrote the result itself
     const float* ml = part_ml + ((size_t)n * n_q + h) * max_splits * 2;
@@ -703,7 +705,7 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
                                     const int* q_start, const int* context_len, const int* block_table,
                                     int table_width, int page_size, const int* rows, int n, int n_q, int n_kv,
                                     int head_dim, float scale, int window, int max_splits,
-                                    const int* split_keys, float* scratch, void* stream) {
+                                    const int* split_keys, int split_stride, float* scratch, void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
         max_splits > 64 || split_keys == nullptr || scratch == nullptr)
@@ -715,7 +717,7 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     p.out = (bf16*)out;
     p.part_ml = scratch + (size_t)n * n_q * max_splits * head_dim;
     p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
-    p.max_splits = max_splits; p.split_keys = split_keys;
+    p.max_splits = max_splits; p.split_keys = split_keys; p.split_stride = split_stride ? 1 : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.qkv = nullptr; p.ld_qkv = 0; p.q_norm_w = p.k_norm_w = nullptr; p.norm_dtype = 0; p.eps = 0.f;
     p.cos_sin = nullptr; p.k_write = p.v_write = nullptr; p.status = nullptr;
@@ -724,7 +726,68 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     if (rc) return rc;
     return kipp_launch(attn_decode_merge_kernel, dim3(n_q, n), dim3(head_dim >= 128 ? 128 : 64), 0, s, 1,
                        (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, rows, q_start, context_len, n_q,
-                       head_dim, max_splits, split_keys);
+                       head_dim, max_splits, split_keys, split_stride ? 1 : 0);
+}
+
+// The keys per split of each decoded token, chosen on the device from the cached lengths
+// (context_len[rows[i]] + 1 keys), by the rule the host uses when it packs a step
+// (csrc/host/attention_plan.hpp): with own_length, an eighth of the token's own context
+// (so a token's result does not depend on its neighbours); else, for the whole step, the
+// number of splits with the best (share of the resident CTA slots that the waves fill) x
+// (share of a CTA's time spent on keys rather than on its fixed cost).  One block; used
+// between the steps of a burst that runs without the host.
+namespace {
+struct SplitRule { int pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits, own_length; };
+__global__ void attn_decode_replan_kernel(int* split_keys, const int* context_len, const int* rows, int n,
+                                          SplitRule rule) {
+    __shared__ int shared_s;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0) shared_s = 0;
+    __syncthreads();
+    int longest = 0;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) longest = max(longest, context_len[rows[i]] + 1);
+    atomicMax(&shared_s, longest);
+    __syncthreads();
+    longest = shared_s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const long long pairs = (long long)n * rule.pairs_per_entry;
+        int best = 1;
+        double best_score = -1.0;
+        for (int splits = 1; splits <= rule.max_splits; ++splits) {
+            if (splits > 1 && longest / splits < rule.min_split) break;
+            const long long ctas = pairs * splits;
+            const long long waves = (ctas + rule.resident_ctas - 1) / rule.resident_ctas;
+            const int keys = (longest + splits - 1) / splits;
+            const int tiles = (keys + TILE_KEYS - 1) / TILE_KEYS;
+            const double score = (double)ctas / (double)(waves * rule.resident_ctas) * (double)tiles /
+                                 (double)(tiles + rule.fixed_tiles);
+            if (score > best_score + 1e-9) { best = splits; best_score = score; }
+        }
+        const int keys = (longest + best - 1) / best;
+        shared_s = max(rule.min_split, (keys + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        if (rule.own_length) {
+            const int own = (context_len[rows[i]] + 1 + 7) / 8;
+            split_keys[i] = max(rule.min_split, (own + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS);
+        } else {
+            split_keys[i] = shared_s;
+        }
+    }
+}
+}  // namespace
+
+extern "C" int kipp_attn_decode_replan(int* split_keys, const int* context_len, const int* rows, int n,
+                                       int pairs_per_entry, int resident_ctas, int fixed_tiles, int min_split,
+                                       int max_splits, int own_length, void* stream) {
+    if (n <= 0) return 0;
+    if (pairs_per_entry <= 0 || resident_ctas <= 0 || min_split <= 0 || max_splits <= 0) return KIPP_ERR_ARG;
+    SplitRule rule{pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits, own_length ? 1 : 0};
+    return kipp_launch(attn_decode_replan_kernel, dim3(1), dim3(128), 0, (cudaStream_t)stream, 1, split_keys,
+                       context_len, rows, n, rule);
 }
 
 // The same for a step of decoded tokens only, taking the raw output of the q/k/v
@@ -737,7 +800,8 @@ extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long 
                                           const int* q_start, const int* context_len, const int* block_table,
                                           int table_width, int page_size, const int* rows, int n, int n_q,
                                           int n_kv, int head_dim, float scale, int window, int max_splits,
-                                          const int* split_keys, float* scratch, int* status, void* stream) {
+                                          const int* split_keys, int split_stride, float* scratch, int* status,
+                                          void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
         max_splits > 64 || split_keys == nullptr || scratch == nullptr || status == nullptr || qkv == nullptr ||
@@ -752,7 +816,7 @@ extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long 
     p.out = (bf16*)out;
     p.part_ml = scratch + (size_t)n * n_q * max_splits * head_dim;
     p.table_width = table_width; p.page_size = page_size; p.n_q = n_q; p.n_kv = n_kv; p.window = window;
-    p.max_splits = max_splits; p.split_keys = split_keys;
+    p.max_splits = max_splits; p.split_keys = split_keys; p.split_stride = split_stride ? 1 : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.qkv = (const bf16*)qkv; p.ld_qkv = (int)ld_qkv;
     p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.norm_dtype = norm_dtype; p.eps = eps;
@@ -765,5 +829,5 @@ extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long 
     if (rc) return rc;
     return kipp_launch(attn_decode_merge_kernel, dim3(n_q, n), dim3(head_dim >= 128 ? 128 : 64), 0, s, 1,
                        (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, rows, q_start, context_len, n_q,
-                       head_dim, max_splits, split_keys);
+                       head_dim, max_splits, split_keys, split_stride ? 1 : 0);
 }

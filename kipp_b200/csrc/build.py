@@ -1,6 +1,8 @@
 """Builds the CUDA sources of this folder into shared libraries for sm_100a
-and loads them with ctypes; the plain C++ sources under ``host/`` (bookkeeping
-that needs no GPU) are built with the C++ compiler in the same way.
+and loads them with ctypes; the C++ sources under ``host/`` (the host core:
+configuration, checkpoints, parts, cache manager, step function, scheduler and
+the C interface, ``libkipp_engine.so``) are built with the C++ compiler in the
+same way and linked against the CUDA runtime.
 
 Each ``<name>.cu`` becomes ``_build/lib<name>.so`` the first time one of its
 kernels is needed, so a run compiles only what its model uses.  A library is
@@ -173,8 +175,10 @@ def compile_library(name: str, *, verbose: bool = True, force: bool = False) -> 
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
-# ---------------------------------------------------------------------- host libraries
+# ---------------------------------------------------------------------- the host core
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
+ENGINE_LIBRARY = "kipp_engine"
+_HOST_SOURCES = ("kipp_engine.cpp", "cache_core.cpp")
 
 
 def _cxx() -> str:
@@ -182,22 +186,41 @@ def _cxx() -> str:
                  shutil.which("c++"), shutil.which("clang++")):
         if cand and (os.path.isfile(cand) or shutil.which(cand)):
             return cand
-    raise BuildError("no C++ compiler found (set CXX or KIPP_B200_CXX); the host libraries of kipp_b200 "
+    raise BuildError("no C++ compiler found (set CXX or KIPP_B200_CXX); the host core of kipp_b200 "
                      "cannot be built and there is no fallback")
 
 
-def compile_host_library(name: str, *, verbose: bool = True) -> str:
-    """Compile ``host/<name>.cpp`` (plain C++, no CUDA) if its library is missing or stale."""
-    src = os.path.join(_HERE, "host", name + ".cpp")
-    if not os.path.isfile(src):
-        raise BuildError(f"no host source {src}")
+def _cuda_home() -> str:
+    for cand in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda",
+                 os.path.dirname(os.path.dirname(_nvcc()))):
+        if cand and os.path.isfile(os.path.join(cand, "include", "cuda_runtime_api.h")):
+            return cand
+    raise BuildError("the CUDA toolkit's headers were not found (set CUDA_HOME)")
+
+
+def host_source_names() -> list[str]:
+    return [ENGINE_LIBRARY]
+
+
+def compile_host_library(name: str = ENGINE_LIBRARY, *, verbose: bool = True) -> str:
+    """Compile the host core (``host/*.cpp`` with its headers) into
+    ``lib<name>.so`` if that is missing or stale."""
+    if name != ENGINE_LIBRARY:
+        raise BuildError(f"no host library {name!r}")
+    host = os.path.join(_HERE, "host")
     out_dir = build_dir()
     so = os.path.join(out_dir, f"lib{name}.so")
     stamp = so + ".sha256"
+    cuda = _cuda_home()
+    lib_dir = os.path.join(cuda, "lib64")
+    link = ["-I", os.path.join(cuda, "include"), "-L", lib_dir, "-lcudart", "-ldl", f"-Wl,-rpath,{lib_dir}"]
     h = hashlib.sha256()
-    with open(src, "rb") as fh:
-        h.update(fh.read())
-    h.update(" ".join(HOST_FLAGS).encode())
+    for f in sorted(os.listdir(host)):
+        if f.endswith((".cpp", ".hpp", ".h")):
+            with open(os.path.join(host, f), "rb") as fh:
+                h.update(f.encode())
+                h.update(fh.read())
+    h.update(" ".join(HOST_FLAGS + link).encode())
     digest = h.hexdigest()
 
     def fresh() -> bool:
@@ -215,15 +238,29 @@ def compile_host_library(name: str, *, verbose: bool = True) -> str:
             if fresh():
                 return so
             tmp = f"{so}.{os.getpid()}.tmp"
-            cmd = [_cxx()] + HOST_FLAGS + ["-o", tmp, src]
+            cmd = [_cxx()] + HOST_FLAGS + ["-o", tmp] + [os.path.join(host, f) for f in _HOST_SOURCES] + link
+            if verbose:
+                print(f"[kipp_b200] compiling the host core (lib{name}.so) ...", file=sys.stderr, flush=True)
             t0 = time.time()
-            proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=out_dir)
+            proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=out_dir)
+            out_chunks: list[str] = []
+            reader = threading.Thread(target=lambda: out_chunks.append(proc.stdout.read()), daemon=True)
+            reader.start()
+            while True:
+                try:
+                    proc.wait(timeout=10)
+                    break
+                except subprocess.TimeoutExpired:
+                    if verbose:
+                        print(f"[kipp_b200] still compiling the host core ({time.time() - t0:.0f} s)",
+                              file=sys.stderr, flush=True)
+            reader.join()
             if proc.returncode != 0:
                 try:
                     os.unlink(tmp)
                 except OSError:
                     pass
-                raise BuildError(f"the C++ compiler failed for host/{name}.cpp:\n{' '.join(cmd)}\n{proc.stdout}")
+                raise BuildError(f"the C++ compiler failed for the host core:\n{' '.join(cmd)}\n{''.join(out_chunks)}")
             os.replace(tmp, so)
             with open(stamp, "w") as f:
                 f.write(digest)
@@ -234,17 +271,40 @@ def compile_host_library(name: str, *, verbose: bool = True) -> str:
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
-def host_source_names() -> list[str]:
-    d = os.path.join(_HERE, "host")
-    return sorted(f[:-4] for f in os.listdir(d) if f.endswith(".cpp")) if os.path.isdir(d) else []
+_resolver_keepalive = None
+_resolved_paths: dict[str, bytes] = {}
 
 
-def load_host_library(name: str) -> ctypes.CDLL:
+def load_host_library(name: str = ENGINE_LIBRARY) -> ctypes.CDLL:
+    """The host core, built at first use.  It finds the kernel libraries through
+    a resolver that compiles each of them when a model first needs it."""
+    global _resolver_keepalive
     key = "host/" + name
     with _lock:
         lib = _loaded.get(key)
+        if lib is not None:
+            return lib
+    path = compile_host_library(name)
+    with _lock:
+        lib = _loaded.get(key)
         if lib is None:
-            lib = ctypes.CDLL(compile_host_library(name))
+            lib = ctypes.CDLL(path)
+
+            @ctypes.CFUNCTYPE(ctypes.c_char_p, ctypes.c_char_p)
+            def resolve(kernel_library):
+                try:
+                    text = kernel_library.decode()
+                    if text not in _resolved_paths:
+                        _resolved_paths[text] = compile_library(text).encode()
+                    return _resolved_paths[text]
+                except Exception as e:          # the core reports the missing library
+                    print(f"[kipp_b200] {e}", file=sys.stderr, flush=True)
+                    return None
+
+            lib.kipp_set_library_resolver.argtypes = [ctypes.c_void_p]
+            lib.kipp_set_library_resolver.restype = None
+            lib.kipp_set_library_resolver(ctypes.cast(resolve, ctypes.c_void_p))
+            _resolver_keepalive = resolve
             _loaded[key] = lib
         return lib
 

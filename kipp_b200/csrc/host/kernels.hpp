@@ -1,0 +1,282 @@
+// The kernels as the host core calls them: typed wrappers over the `extern "C"` launchers of
+// the kernel libraries, and the choice between kernels where several can do an operation
+// (tensor-core or CUDA-core product; tcgen05, mma.sync or CUDA-core attention).  The Python
+// package's kernel functions call the same launchers.
+//
+// No sizes of a model and no property of the device stand here as constants: tile sizes and
+// split rules belong to the attention kernels and are kept beside them (AttentionPlanner).
+#pragma once
+#include <algorithm>
+#include <cmath>
+
+#include "runtime.hpp"
+
+namespace kipp {
+
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+
+// The work lists of the paged attention kernels for one step (device pointers into the
+// step's metadata) and what the host needs to choose a kernel.
+struct AttentionWork {
+    const int* decode_rows = nullptr;      // [n_decode] entries that bring one token
+    int n_decode = 0;
+    const int* split_keys = nullptr;       // [n_decode] keys per split of each decoded token
+    const int* prefill_work = nullptr;     // [(entry, first token)] per 64-token tile, entries of > 1 token
+    int n_prefill_items = 0;
+    const int* all_work = nullptr;         // the same over every entry
+    int n_all_items = 0;
+    const int* prefill_work128 = nullptr;  // per 128-token tile, entries of > 1 token
+    int n_prefill_items128 = 0;
+    int longest_portion = 0;               // most tokens an entry of > 1 token brings
+    int entries = 0, tokens = 0;
+};
+
+struct PagedCacheView {
+    void* k_pages = nullptr;               // [pages, kv_heads, page_size, head_dim] of one run's cache
+    void* v_pages = nullptr;
+    int n_pages = 0;
+    const int* block_table = nullptr;      // int32 [entries, table_width] of this step
+    int table_width = 0;
+    int page_size = 0;
+};
+
+class Ops {
+public:
+    cudaStream_t stream = nullptr;
+    int* status = nullptr;                 // int32[4] on the device: what kernels refused or gave up
+    Workspace* workspace = nullptr;
+    long long launches = 0;                // kernels of this package launched through this object
+    bool prefill_tensor_core = true;       // prompt portions on tcgen05 where the sizes allow
+
+    static constexpr int DECODE_MAX_SPLITS = 32;
+    static constexpr int PREFILL_TC_MIN_TOKENS = 64;   // shorter portions waste a 128-row tile
+
+    void embed_gather(float* out, const void* table, int table_dtype, const int* ids, int tokens, int hidden,
+                      int vocab) {
+        using Fn = int (*)(float*, const void*, int, const int*, int, int, int, int*, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_embed_gather");
+        run(f(out, table, table_dtype, ids, tokens, hidden, vocab, status, stream), "embed_gather");
+    }
+
+    // out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight, float32 arithmetic.
+    void rmsnorm(void* out, int out_dtype, const float* x, const void* weight, int weight_dtype, const int* rows,
+                 int n_rows, int size, float eps) {
+        using Fn = int (*)(void*, int, const float*, const void*, int, const int*, int, int, float, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_rmsnorm");
+        run(f(out, out_dtype, x, weight, weight_dtype, rows, n_rows, size, eps, stream), "rmsnorm");
+    }
+
+    static bool gemm_tc_ok(int dtype, const void* a, long long lda, const void* w, long long ldw) {
+        return dtype == BF16 && lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    }
+
+    // out = a @ w^T with float32 accumulation; a [M, K] (lda), w [N, K] (ldw), both of `dtype`.
+    // EPI_STORE: out[M, N]; EPI_ADD: float32 out[M, N] += product; EPI_SWIGLU: out[M, N/2] =
+    // silu(p[:, 0::2]) * p[:, 1::2].  float32 runs on the CUDA cores, bfloat16 on the tensor-core
+    // kernel where it takes the operands.
+    void gemm(void* out, int out_dtype, long long ldc, const void* a, long long lda, const void* w, long long ldw,
+              int dtype, int M, int N, int K, Epilogue epilogue) {
+        if (M <= 0 || N <= 0) return;
+        if (gemm_tc_ok(dtype, a, lda, w, ldw)) {
+            using Fn = int (*)(void*, int, const void*, const void*, int, int, int, long long, long long, long long, int,
+                               int, int, int, int*, void*);
+            static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc");
+            run(f(out, out_dtype, a, w, M, N, K, lda, ldw, ldc, (int)epilogue, 0, 0, 0, status, stream), "gemm_tc");
+        } else {
+            using Fn = int (*)(void*, int, const void*, const void*, int, int, int, int, int, int, int, int, void*);
+            static Fn f = kernel_symbol<Fn>("gemm_simt", "kipp_gemm_simt");
+            run(f(out, out_dtype, a, w, dtype, M, N, K, (int)lda, (int)ldw, (int)ldc, (int)epilogue, stream),
+                "gemm_simt");
+        }
+    }
+
+    // float32 [tokens, half, 2]: (cos, sin) of position * inv_freq, made once per step.
+    void rope_table(float* out, const int* positions, const float* inv_freq, int tokens, int half) {
+        using Fn = int (*)(void*, const int*, const float*, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_rope_table");
+        run(f(out, positions, inv_freq, tokens, half, stream), "rope_table");
+    }
+
+    // Per-head RMSNorm of q and k, rotation, q to q_out [T, n_q, D], k and v into the pages.
+    // write_cache: bit 0 write keys and values, bit 1 round them to bfloat16 first (32-bit cache).
+    void qk_norm_rope_write(const void* qkv, int ld_qkv, void* q_out, const PagedCacheView& cache, int dtype,
+                            const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps, const float* cos_sin,
+                            int rotary_dim, const int* positions, const int* entry_of_token, int tokens, int n_q,
+                            int n_kv, int head_dim, int write_cache) {
+        using Fn = int (*)(const void*, int, void*, void*, void*, int, const void*, const void*, int, float, const void*,
+                           int, const int*, const int*, const int*, int, int, int, int, int, int, int, int*, void*);
+        static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_qk_norm_rope_write");
+        run(f(qkv, ld_qkv, q_out, cache.k_pages, cache.v_pages, dtype, q_norm_w, k_norm_w, norm_dtype, eps, cos_sin,
+              cos_sin ? rotary_dim : 0, positions, entry_of_token, cache.block_table, cache.table_width,
+              cache.page_size, tokens, n_q, n_kv, head_dim, write_cache, status, stream),
+            "qk_norm_rope_write");
+    }
+
+    static bool attention_mma_supported(int head_dim, int n_q, int n_kv) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_mma_supported");
+        return f(head_dim, n_q, n_kv) != 0;
+    }
+    static bool attention_decode_supported(int head_dim, int n_q, int n_kv) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_decode_supported");
+        return f(head_dim, n_q, n_kv) != 0;
+    }
+    static bool attention_tc_supported(int head_dim, int n_q, int n_kv, int page_size) {
+        using Fn = int (*)(int, int, int);
+        using Fp = int (*)(int);
+        static Fn f = kernel_symbol<Fn>("attention_tc", "kipp_attn_prefill_tc_supported");
+        static Fp g = kernel_symbol<Fp>("attention_tc", "kipp_attn_prefill_tc_page_ok");
+        return f(head_dim, n_q, n_kv) != 0 && g(page_size) != 0;
+    }
+
+    float* decode_scratch(int n, int n_q, int head_dim) {
+        size_t floats = (size_t)n * n_q * DECODE_MAX_SPLITS * (head_dim + 2);
+        if (floats < (1u << 20)) floats = 1u << 20;
+        return workspace->get<float>("attention_decode_scratch", floats);
+    }
+
+    // Causal grouped-query attention of the step's tokens over the paged cache.
+    void attention(void* out, const void* q, const PagedCacheView& cache, int dtype, const AttentionWork& work,
+                   const int* positions, const int* entry_of_token, const int* q_start, const int* context_len,
+                   int n_q, int n_kv, int head_dim, float scale, int window) {
+        if (dtype == BF16 && attention_mma_supported(head_dim, n_q, n_kv)) {
+            attention_tensor_core(out, q, cache, work, q_start, context_len, n_q, n_kv, head_dim, scale, window);
+            return;
+        }
+        using Fn = int (*)(void*, const void*, const void*, const void*, int, const int*, const int*, const int*, int,
+                           int, int, int, int, int, float, int, int*, void*);
+        static Fn f = kernel_symbol<Fn>("attention_simt", "kipp_paged_attention_simt");
+        run(f(out, q, cache.k_pages, cache.v_pages, dtype, positions, entry_of_token, cache.block_table,
+              cache.table_width, cache.page_size, work.tokens, n_q, n_kv, head_dim, scale, window, status, stream),
+            "attention_simt");
+    }
+
+    // Whether a step can take attention_decode_fused: decoded tokens only, bfloat16, a head size
+    // and group the split-K kernel takes, the whole head rotated or none of it.
+    static bool attention_decode_fused_ok(const AttentionWork& work, int dtype, int n_q, int n_kv, int head_dim,
+                                          int rotary_dim) {
+        return dtype == BF16 && work.n_decode > 0 && work.n_decode == work.entries && work.entries == work.tokens &&
+               (rotary_dim == 0 || rotary_dim == head_dim) && attention_mma_supported(head_dim, n_q, n_kv) &&
+               attention_decode_supported(head_dim, n_q, n_kv);
+    }
+
+    // qk_norm_rope_write and attention of a step of decoded tokens in one pair of launches: the
+    // attention kernel normalises and rotates the raw queries and the new key itself and writes
+    // the new key and value into the pages.
+    void attention_decode_fused(void* out, const void* qkv, long long ld_qkv, const PagedCacheView& cache,
+                                const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
+                                const float* cos_sin, bool write_cache, const AttentionWork& work, const int* q_start,
+                                const int* context_len, int n_q, int n_kv, int head_dim, float scale, int window) {
+        using Fn = int (*)(void*, const void*, long long, void*, void*, const void*, const void*, int, float, const void*,
+                           int, const int*, const int*, const int*, int, int, const int*, int, int, int, int, float, int,
+                           int, const int*, int, float*, int*, void*);
+        static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_decode_mma_fused");
+        float* scratch = decode_scratch(work.n_decode, n_q, head_dim);
+        run(f(out, qkv, ld_qkv, cache.k_pages, cache.v_pages, q_norm_w, k_norm_w, norm_dtype, eps, cos_sin,
+              write_cache ? 1 : 0, q_start, context_len, cache.block_table, cache.table_width, cache.page_size,
+              work.decode_rows, work.n_decode, n_q, n_kv, head_dim, scale, window, DECODE_MAX_SPLITS, work.split_keys, 1,
+              scratch, status, stream),
+            "attn_decode_mma_fused", 2);
+        ++fused_decode_launches;
+    }
+
+    void argmax_rows(const float* logits, long long ld, int rows, int n, int* out) {
+        using Fn = int (*)(const float*, long long, int, int, int*, void*);
+        static Fn f = kernel_symbol<Fn>("sampling", "kipp_argmax_rows");
+        run(f(logits, ld, rows, n, out, stream), "argmax_rows");
+    }
+    void sample_rows(const float* logits, long long ld, int rows, int n, const float* temperature, const int* top_k,
+                     const float* top_p, const float* min_p, const double* uniform, int* out) {
+        using Fn = int (*)(const float*, long long, int, int, const float*, const int*, const float*, const float*,
+                           const double*, int*, void*);
+        static Fn f = kernel_symbol<Fn>("sampling", "kipp_sample_rows");
+        run(f(logits, ld, rows, n, temperature, top_k, top_p, min_p, uniform, out, stream), "sample_rows");
+    }
+    void apply_penalties(float* logits, long long ld, int rows, int n, const int* recent, int recent_width,
+                         const int* recent_count, const float* repetition, const float* presence,
+                         const float* frequency, const int* bias_tokens, const float* bias_values, int bias_width,
+                         const int* bias_count) {
+        using Fn = int (*)(float*, long long, int, int, const int*, int, const int*, const float*, const float*,
+                           const float*, const int*, const float*, int, const int*, void*);
+        static Fn f = kernel_symbol<Fn>("sampling", "kipp_apply_penalties");
+        run(f(logits, ld, rows, n, recent, recent_width, recent_count, repetition, presence, frequency, bias_tokens,
+              bias_values, bias_width, bias_count, stream),
+            "apply_penalties");
+    }
+    // Between two greedy decode steps on the device: `next` become the step's tokens and row
+    // *counter of `ring`, positions and cached lengths move on by one.
+    void burst_advance(int* tokens, int* positions, int* context_len, const int* next, int* ring, int* counter, int n,
+                       int ring_rows) {
+        using Fn = int (*)(int*, int*, int*, const int*, int*, int*, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("sampling", "kipp_burst_advance");
+        run(f(tokens, positions, context_len, next, ring, counter, n, ring_rows, stream), "burst_advance");
+    }
+    // The keys per split of every decoded token, chosen on the device for the lengths a
+    // burst_advance left, by AttentionPlanner's rule.
+    void decode_replan(int* split_keys, const int* context_len, const int* rows, int n, int pairs_per_entry,
+                       int resident_ctas, int fixed_tiles, int min_split, int max_splits, int own_length) {
+        using Fn = int (*)(int*, const int*, const int*, int, int, int, int, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_decode_replan");
+        run(f(split_keys, context_len, rows, n, pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits,
+              own_length, stream),
+            "attn_decode_replan");
+    }
+    void convert_rows(void* dst, int dst_dtype, long long dst_pitch, const void* src, int src_dtype,
+                      long long src_pitch, long long rows, long long cols) {
+        using Fn = int (*)(void*, int, long long, const void*, int, long long, long long, long long, void*);
+        static Fn f = kernel_symbol<Fn>("convert", "kipp_convert_rows");
+        run(f(dst, dst_dtype, dst_pitch, src, src_dtype, src_pitch, rows, cols, stream), "convert_rows");
+    }
+
+private:
+    void run(int code, const char* what, int kernels = 1) {
+        kernel_check(code, what);
+        launches += kernels;
+    }
+
+    void attention_tensor_core(void* out, const void* q, const PagedCacheView& cache, const AttentionWork& work,
+                               const int* q_start, const int* context_len, int n_q, int n_kv, int head_dim,
+                               float scale, int window) {
+        const bool use_decode = work.n_decode > 0 && attention_decode_supported(head_dim, n_q, n_kv);
+        const int* tiles = use_decode ? work.prefill_work : work.all_work;
+        const int items = use_decode ? work.n_prefill_items : work.n_all_items;
+        const bool aligned = (((uintptr_t)out | (uintptr_t)q | (uintptr_t)cache.k_pages | (uintptr_t)cache.v_pages) &
+                              15) == 0;
+        if (prefill_tensor_core && work.n_prefill_items128 > 0 && work.longest_portion >= PREFILL_TC_MIN_TOKENS &&
+            (use_decode || work.n_decode == 0) && aligned &&
+            attention_tc_supported(head_dim, n_q, n_kv, cache.page_size)) {
+            using Fn = int (*)(void*, const void*, const void*, const void*, int, const int*, const int*, const int*, int,
+                               int, const int*, int, int, int, int, float, int, int*, void*);
+            static Fn f = kernel_symbol<Fn>("attention_tc", "kipp_attn_prefill_tc");
+            run(f(out, q, cache.k_pages, cache.v_pages, cache.n_pages, q_start, context_len, cache.block_table,
+                  cache.table_width, cache.page_size, work.prefill_work128, work.n_prefill_items128, n_q, n_kv,
+                  head_dim, scale, window, status, stream),
+                "attn_prefill_tc");
+            ++tc_prefill_launches;
+        } else if (items > 0) {
+            using Fn = int (*)(void*, const void*, const void*, const void*, const int*, const int*, const int*, int, int,
+                               const int*, int, int, int, int, float, int, void*);
+            static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_prefill_mma");
+            run(f(out, q, cache.k_pages, cache.v_pages, q_start, context_len, cache.block_table, cache.table_width,
+                  cache.page_size, tiles, items, n_q, n_kv, head_dim, scale, window, stream),
+                "attn_prefill_mma");
+        }
+        if (use_decode) {
+            using Fn = int (*)(void*, const void*, const void*, const void*, const int*, const int*, const int*, int, int,
+                               const int*, int, int, int, int, float, int, int, const int*, int, float*, void*);
+            static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_decode_mma");
+            float* scratch = decode_scratch(work.n_decode, n_q, head_dim);
+            run(f(out, q, cache.k_pages, cache.v_pages, q_start, context_len, cache.block_table, cache.table_width,
+                  cache.page_size, work.decode_rows, work.n_decode, n_q, n_kv, head_dim, scale, window,
+                  DECODE_MAX_SPLITS, work.split_keys, 1, scratch, stream),
+                "attn_decode_mma", 2);
+        }
+    }
+
+public:
+    long long tc_prefill_launches = 0;      // launches of the tcgen05 prompt attention (tests look at it)
+    long long fused_decode_launches = 0;
+};
+
+}  // namespace kipp

@@ -40,6 +40,12 @@ __device__ __forceinline__ void store2(float* p, float a, float b) {
 __device__ __forceinline__ void store2(bf16* p, float a, float b) {
     *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
+// The reference's storage contract on a 32-bit cache: keys and values are rounded to
+// bfloat16 when they are stored (src/kipp.c:2806-2811, 2614-2615).  Bit 1 of the
+// launchers' write_cache argument asks for it.
+__device__ __forceinline__ float stored(float v, bool round_bf16) {
+    return round_bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+}
 
 // V = elements a lane handles side by side (2 when head_dim is a multiple of 4:
 // 4- or 8-byte loads and stores; else 1).
@@ -61,7 +67,8 @@ __global__ void qk_norm_rope_write_kernel(
     const int t = warp_global / heads_total;
     const int h = warp_global % heads_total;
     const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
-    if (!is_q && !write_cache) return;
+    if (!is_q && !(write_cache & 1)) return;
+    const bool rnd = !is_q && (write_cache & 2);
     const T* src = qkv + (size_t)t * ld_qkv + (size_t)h * head_dim;
     const int pos = positions[t];
 
@@ -86,10 +93,10 @@ __global__ void qk_norm_rope_write_kernel(
             for (int i = 2 * lane; i < head_dim; i += 64) {
                 float a, b;
                 load2(src + i, a, b);
-                store2(dst + i, a, b);
+                store2(dst + i, stored(a, rnd), stored(b, rnd));
             }
         } else {
-            for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+            for (int i = lane; i < head_dim; i += 32) dst[i] = from_f32<T>(stored(to_f32(src[i]), rnd));
         }
         return;
     }
@@ -155,11 +162,11 @@ __global__ void qk_norm_rope_write_kernel(
             const int i = V * (lane + 32 * j);
             if (i < half) {
                 if constexpr (V == 2) {
-                    store2(dst + i, lo[j][0], lo[j][1]);
-                    store2(dst + i + half, hi[j][0], hi[j][1]);
+                    store2(dst + i, stored(lo[j][0], rnd), stored(lo[j][1], rnd));
+                    store2(dst + i + half, stored(hi[j][0], rnd), stored(hi[j][1], rnd));
                 } else {
-                    dst[i] = from_f32<T>(lo[j][0]);
-                    dst[i + half] = from_f32<T>(hi[j][0]);
+                    dst[i] = from_f32<T>(stored(lo[j][0], rnd));
+                    dst[i + half] = from_f32<T>(stored(hi[j][0], rnd));
                 }
             }
         }
@@ -190,7 +197,7 @@ __global__ void qk_norm_rope_write_kernel(
             const float c = cs.x, s = cs.y;
             v = i < rh ? row[i] * c - row[i + rh] * s : row[i] * c + row[i - rh] * s;
         }
-        dst[i] = from_f32<T>(v);
+        dst[i] = from_f32<T>(stored(v, rnd));
     }
 }
 

@@ -353,92 +353,31 @@ __global__ void apply_penalties_kernel(float* __restrict__ logits, long long ld,
 // Between two greedy decode steps that run without the host (captured in one CUDA
 // graph with the step itself): the tokens just chosen become the next step's
 // tokens and go into row `*counter` of the ring; every request moves on by one
-// position; the keys per split of the decode attention are chosen anew, by the
-// same rule as on the host (engine/batch.py, decode_split_length): the number of
-// splits with the best (share of the resident CTA slots the waves fill) x (share
-// of a CTA's time spent on keys).  One block.
+// position.  What a mixer's kernels derive from the lengths (the keys per split of
+// the decode attention) is made anew by that mixer's own kernel after this one.
+// One block.
 namespace {
-struct BurstRule { int pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits; };
-__global__ void burst_advance_kernel(int* tokens, int* positions, int* context_len, int* split_keys,
-                                     const int* next, int* ring, int* counter, int n, int ring_rows,
-                                     BurstRule rule) {
-    __shared__ int longest_s;
+__global__ void burst_advance_kernel(int* tokens, int* positions, int* context_len, const int* next, int* ring,
+                                     int* counter, int n, int ring_rows) {
     pdl_launch_dependents();
     pdl_wait();                                      // the tokens are chosen, every kernel of the step is through
-    if (threadIdx.x == 0) longest_s = 0;
-    __syncthreads();
     const int c = *counter;
-    int longest = 0;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int t = next[i];
         tokens[i] = t;
         if (c < ring_rows) ring[(size_t)c * n + i] = t;
         positions[i] += 1;
-        const int len = context_len[i] + 1;          // cached tokens before the next step's token
-        context_len[i] = len;
-        longest = max(longest, len + 1);             // keys the next step's token sees
+        context_len[i] += 1;                         // cached tokens before the next step's token
     }
-    atomicMax(&longest_s, longest);
     __syncthreads();
-    if (threadIdx.x == 0) {
-        *counter = c + 1;
-        longest = longest_s;
-        const long long pairs = (long long)n * rule.pairs_per_entry;
-        int best = 1;
-        double best_score = -1.0;
-        for (int splits = 1; splits <= rule.max_splits; ++splits) {
-            if (splits > 1 && longest / splits < rule.min_split) break;
-            const long long ctas = pairs * splits;
-            const long long waves = (ctas + rule.resident_ctas - 1) / rule.resident_ctas;
-            const int keys = (longest + splits - 1) / splits;
-            const int tiles = (keys + 63) / 64;
-            const double score = (double)ctas / (double)(waves * rule.resident_ctas) * (double)tiles /
-                                 (double)(tiles + rule.fixed_tiles);
-            if (score > best_score + 1e-9) { best = splits; best_score = score; }
-        }
-        const int keys = (longest + best - 1) / best;
-        split_keys[0] = max(rule.min_split, (keys + 63) / 64 * 64);
-    }
+    if (threadIdx.x == 0) *counter = c + 1;
 }
 }  // namespace
 
-extern "C" int kipp_argmax_rows(const float* logits, long long ld, int rows, int n, int* out,
-                                void* stream) {
-    if (rows <= 0) return 0;
-    if (n <= 0) return KIPP_ERR_ARG;
-    return kipp_launch(argmax_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n, out);
-}
-
-extern "C" int kipp_sample_rows(const float* logits, long long ld, int rows, int n,
-                                const float* temperature, const int* top_k, const float* top_p,
-                                const float* min_p, const double* uniform, int* out, void* stream) {
-    if (rows <= 0) return 0;
-    if (n <= 0) return KIPP_ERR_ARG;
-    return kipp_launch(sample_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n,
-                       temperature, top_k, top_p, min_p, uniform, out);
-}
-
-extern "C" int kipp_apply_penalties(float* logits, long long ld, int rows, int n, const int* recent,
-                                    int recent_width, const int* recent_count,
-                                    const float* repetition, const float* presence,
-                                    const float* frequency, const int* bias_tokens,
-                                    const float* bias_values, int bias_width, const int* bias_count,
-                                    void* stream) {
-    if (rows <= 0) return 0;
-    if (n <= 0) return KIPP_ERR_ARG;
-    return kipp_launch(apply_penalties_kernel, dim3(rows), dim3(64), 0, (cudaStream_t)stream, 1, logits, ld, n,
-                       recent, recent_width, recent_count, repetition, presence, frequency, bias_tokens,
-                       bias_values, bias_width, bias_count);
-}
-
-// See burst_advance_kernel.  `next` holds the n tokens just chosen.
-extern "C" int kipp_burst_advance(int* tokens, int* positions, int* context_len, int* split_keys, const int* next,
-                                  int* ring, int* counter, int n, int ring_rows, int pairs_per_entry,
-                                  int resident_ctas, int fixed_tiles, int min_split, int max_splits, void* stream) {
+extern "C" int kipp_burst_advance(int* tokens, int* positions, int* context_len, const int* next, int* ring,
+                                  int* counter, int n, int ring_rows, void* stream) {
     if (n <= 0) return 0;
-    if (ring_rows <= 0 || pairs_per_entry <= 0 || resident_ctas <= 0 || min_split <= 0 || max_splits <= 0)
-        return KIPP_ERR_ARG;
-    BurstRule rule{pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits};
+    if (ring_rows <= 0) return KIPP_ERR_ARG;
     return kipp_launch(burst_advance_kernel, dim3(1), dim3(128), 0, (cudaStream_t)stream, 1, tokens, positions,
-                       context_len, split_keys, next, ring, counter, n, ring_rows, rule);
+                       context_len, next, ring, counter, n, ring_rows);
 }

@@ -1,12 +1,10 @@
-from .batch import StepEntry, StepMeta
-from .engine import CacheView, Engine, StepContext
-from .runtime import Runtime, Workspace, parse_dtype
+from .batch import StepEntry
+from .engine import Engine, ExternalContext, device_tensor
+from .runtime import parse_dtype
+from .scheduler import Request, RequestState, Scheduler, StepPlan
 
-__all__ = ["StepEntry", "StepMeta", "CacheView", "Engine", "StepContext", "Runtime", "Workspace",
-           "parse_dtype"]
-from .scheduler import Request, RequestState, Scheduler, StepPlan  # noqa: E402
-
-__all__ += ["Request", "RequestState", "Scheduler", "StepPlan", "LLM", "GenerationResult"]
+__all__ = ["StepEntry", "Engine", "ExternalContext", "device_tensor", "parse_dtype", "Request", "RequestState",
+           "Scheduler", "StepPlan", "LLM", "GenerationResult"]
 
 
 def __getattr__(name):

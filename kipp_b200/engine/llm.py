@@ -4,19 +4,20 @@ The reference has no Python entry to its engine (Python is tooling only,
 docs/ARCHITECTURE.md:25-26); this one follows its C API's vocabulary
 (src/kipp.h: open a model, evaluate, sample) and its CLI's option names
 (src/kipp_cli.c:571-610): ``decode`` = tokens to generate, ``temperature`` 0 =
-greedy, ``top_p``, ``top_k``, ``min_p``, ``seed``.
+greedy, ``top_p``, ``top_k``, ``min_p``, ``seed``.  Generation itself (plan a
+step, run it, sample, record) is the host core's loop (``kipp_engine_run``,
+csrc/host/scheduler.hpp); the command line and the benchmark go through the
+same loop.
 """
 from __future__ import annotations
 
+import ctypes
 import dataclasses
 import time
 from typing import Optional, Sequence
 
-import torch
-
 from ..config.base import ModelConfig
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler
 from .engine import Engine
 from .scheduler import Request, Scheduler
 
@@ -37,8 +38,8 @@ class LLM:
                          (random weights from ``seed``)
     ``dtype``            "bfloat16" (serving kernels) or "float32" (true 32-bit)
     ``kv_block_size``    tokens per cache page
-    ``kv_blocks``        pages in each cache group (default: enough for ``ctx`` tokens
-                         of ``max_requests`` requests, capped by ``kv_tokens``)
+    ``kv_blocks``        pages in each cache group (default: what the free device
+                         memory holds, at most ``ctx`` tokens of ``max_requests`` requests)
     ``ctx``              most tokens one request may hold (default: the model's
                          max_position_embeddings)
     ``max_batch_tokens`` token budget of one step
@@ -50,25 +51,21 @@ class LLM:
                  kv_blocks: Optional[int] = None, kv_tokens: Optional[int] = None,
                  ctx: Optional[int] = None, max_requests: int = 64, max_batch_tokens: int = 8192,
                  chunk: Optional[int] = None, policy: str = "reserve", seed: int = 0,
-                 stop_token_ids: Sequence[int] = ()):
+                 stop_token_ids: Sequence[int] = (), **engine_options):
         if kv_blocks is not None:
             cache_tokens = kv_blocks * kv_block_size
         elif kv_tokens is not None:
             cache_tokens = kv_tokens
         else:
-            cache_tokens = None
+            cache_tokens = None                       # sized from the free device memory
         opts = dict(dtype=dtype, device=device, page_size=kv_block_size, max_requests=max_requests,
-                    max_batch_tokens=max_batch_tokens)
+                    max_batch_tokens=max_batch_tokens, cache_tokens=cache_tokens, **engine_options)
         if isinstance(model, ModelConfig):
-            limit = ctx or model.max_position_embeddings
-            opts["cache_tokens"] = cache_tokens or min(limit * max_requests, 1 << 20)
             self.engine = Engine.from_config(model, seed, **opts)
         else:
-            from ..config.registry import load_config
-            limit = ctx or getattr(load_config(model), "max_position_embeddings", 8192)
-            opts["cache_tokens"] = cache_tokens or min(limit * max_requests, 1 << 20)
             self.engine = Engine.from_folder(model, **opts)
-        self.ctx = limit
+        limit = self.engine.info()["max_positions"] or 8192
+        self.ctx = min(ctx, limit) if ctx else limit
         self.chunk = chunk
         self.policy = policy
         self.max_batch_tokens = max_batch_tokens
@@ -76,14 +73,14 @@ class LLM:
         eos = getattr(self.engine.spec.config, "eos_token_id", None)
         if eos is not None and not self.stop_token_ids:
             self.stop_token_ids = (int(eos),)
-        self.sampler = Sampler(self.engine.runtime.device)
         self.metrics: dict = {}
+        self.step_log: list = []
 
     def new_scheduler(self) -> Scheduler:
+        """The engine's own scheduler, set up anew with this object's options."""
         e = self.engine
         return Scheduler(e.cache, max_batch_tokens=self.max_batch_tokens, chunk_size=self.chunk,
-                         max_positions=min(self.ctx, e.spec.max_positions or self.ctx),
-                         policy=self.policy, admit=e.add_request, release=e.finish)
+                         max_positions=self.ctx, policy=self.policy, engine=e)
 
     def generate(self, prompts: Sequence[Sequence[int]], decode: int = 16, *,
                  temperature: float = 0.0, top_p: float = 1.0, top_k: int = 0, min_p: float = 0.0,
@@ -108,41 +105,27 @@ class LLM:
                                  r.preemptions) for r in requests]
 
     def run(self, sched: Scheduler, record_steps: bool = False) -> None:
-        """Drive ``sched`` until no request is left: plan, step, sample, record.
-        With ``record_steps`` every step's wall time (token ids on the host
-        before, sampled ids on the host after) goes to ``self.step_log``."""
+        """Drive ``sched`` (the engine's scheduler) until no request is left.  With
+        ``record_steps`` the loop is run one step at a time and every step's wall
+        time (token ids on the host before, sampled ids on the host after) goes to
+        ``self.step_log``."""
         engine = self.engine
-        steps = tokens = sampled_total = 0
+        lib, h = engine._lib, engine._h
+        steps = ctypes.c_int()
         self.step_log = []
         t0 = time.perf_counter()
-        while sched.has_work():
-            t_step = time.perf_counter()
-            plan = sched.schedule()
-            if plan is None:
-                raise RuntimeError("requests are waiting but none can be admitted")
-            logits = engine.step(plan.entries)
-            sampled = []
-            if plan.sampled:
-                rs = [plan.requests[i] for i in plan.sampled]
-                states = [r.rng_state for r in rs]
-                out = self.sampler.sample(logits, [r.sampling for r in rs], states,
-                                          [r.recent for r in rs])
-                sampled = out.to("cpu").tolist()        # device -> host: the step's result
-                for r, s in zip(rs, states):
-                    r.rng_state = s
-            sched.complete(plan, sampled)
-            if record_steps:
-                if not sampled:
-                    torch.cuda.synchronize(engine.runtime.device)
-                self.step_log.append({
-                    "seconds": time.perf_counter() - t_step, "tokens": plan.tokens,
-                    "sampled": len(sampled),
-                    "decode_only": all(len(e.tokens) == 1 for e in plan.entries),
-                    "h2d_bytes": engine.last_h2d_bytes, "d2h_bytes": 4 * len(sampled)})
-            steps += 1
-            tokens += plan.tokens
-            sampled_total += len(sampled)
-        engine.runtime.check_status()
-        self.metrics = {"steps": steps, "tokens_fed": tokens, "tokens_sampled": sampled_total,
-                        "seconds": time.perf_counter() - t0, **sched.stats}
-
+        total = 0
+        if not record_steps:
+            engine._check(lib.kipp_engine_run(h, 0, ctypes.byref(steps)))
+            total = steps.value
+        else:
+            while sched.has_work():
+                t_step = time.perf_counter()
+                engine._check(lib.kipp_engine_run(h, 1, ctypes.byref(steps)))
+                engine.synchronize()
+                self.step_log.append({"seconds": time.perf_counter() - t_step,
+                                      "h2d_bytes": engine.last_h2d_bytes})
+                total += steps.value
+        sched.sync()
+        engine.synchronize()
+        self.metrics = {"steps": total, "seconds": time.perf_counter() - t0, **sched.stats}

@@ -1,5 +1,7 @@
 """The scheduler above ``step``: admits requests, cuts prompts into portions
-under a token budget, decodes, finishes and frees.
+under a token budget, decodes, finishes and frees.  The decisions are the host
+core's (csrc/host/scheduler.hpp); this module is their face: requests as Python
+objects, plans as lists of ``StepEntry``.
 
 It is the reference's server loop without sockets (src/kipp_server.c): FIFO
 admission with head-of-line blocking (:2514-2531), a prompt portion for each
@@ -27,13 +29,15 @@ the device, so its decisions are tested without a GPU.
 """
 from __future__ import annotations
 
+import ctypes
 import dataclasses
 import enum
 from collections import deque
 from typing import Optional
 
+from .. import native as N
 from ..cache import CacheManager
-from ..sampling.params import MASK64, RECENT_WINDOW, SamplingParams
+from ..sampling.params import MASK64, RECENT_WINDOW, SamplingParams, to_native
 from .batch import StepEntry
 
 
@@ -43,6 +47,9 @@ class RequestState(enum.Enum):
     FINISHED = "finished"
 
 
+_REASONS = {0: None, 1: "stop", 2: "length", 3: "abort"}
+
+
 @dataclasses.dataclass
 class Request:
     id: object
@@ -50,7 +57,7 @@ class Request:
     max_new_tokens: int
     sampling: SamplingParams = dataclasses.field(default_factory=SamplingParams)
     stop_token_ids: tuple = ()
-    # -- scheduler-owned ---------------------------------------------------------
+    # -- mirrored from the scheduler -----------------------------------------------
     state: RequestState = RequestState.WAITING
     output: list = dataclasses.field(default_factory=list)
     finish_reason: Optional[str] = None
@@ -58,21 +65,10 @@ class Request:
     rng_state: int = 1
     arrival: int = 0
     preemptions: int = 0
-    last_logits = None                 # optional: logits of the last sampled position
 
     @property
     def all_tokens(self) -> list:
         return self.prompt + self.output
-
-    def tokens_between(self, a: int, b: int) -> list:
-        """Tokens [a, b) of prompt + output, without building the whole list
-        (a decoding request asks for one token every step)."""
-        n = len(self.prompt)
-        if b <= n:
-            return self.prompt[a:b]
-        if a >= n:
-            return self.output[a - n:b - n]
-        return self.prompt[a:] + self.output[:b - n]
 
     @property
     def pending(self) -> int:
@@ -105,216 +101,185 @@ class StepPlan:
 class Scheduler:
     def __init__(self, cache: CacheManager, *, max_batch_tokens: int, chunk_size: Optional[int] = None,
                  max_running: Optional[int] = None, max_positions: Optional[int] = None,
-                 policy: str = "reserve", admit=None, release=None):
-        """``admit(rid)`` / ``release(rid)`` take and give back a request's slot
-        and pages; they default to the cache manager's own (an engine passes
-        its ``add_request`` / ``finish`` so that per-request state is zeroed)."""
+                 policy: str = "reserve", engine=None):
+        """Over a cache manager (the scheduler takes and gives back slots and pages
+        itself), or, with ``engine``, over that engine's own scheduler, which
+        ``Engine``/``LLM`` drive through ``kipp_engine_run``."""
         if policy not in ("reserve", "preempt"):
             raise ValueError("policy must be 'reserve' or 'preempt'")
         if max_batch_tokens <= 0:
             raise ValueError("max_batch_tokens must be positive")
         self.cache = cache
-        self._admit = admit or cache.admit
-        self._release = release or cache.release
         self.max_batch_tokens = max_batch_tokens
         self.chunk_size = chunk_size or max_batch_tokens
-        self.max_running = min(max_running or cache.slots.max_requests, cache.slots.max_requests)
         self.max_positions = max_positions
         self.policy = policy
-        self.waiting: deque[Request] = deque()
-        self.running: list[Request] = []
-        self.finished: list[Request] = []
+        self._lib = N.lib()
+        self._engine = engine
+        opt = N.SchedulerOptions(max_batch_tokens, int(chunk_size or 0), int(max_running or 0),
+                                 int(max_positions or 0), 1 if policy == "preempt" else 0)
+        if engine is not None:
+            N.check(self._lib.kipp_engine_scheduler_configure(engine._h, ctypes.byref(opt)), engine=engine._h)
+            self._h = self._lib.kipp_engine_scheduler(engine._h)
+            self._owned = False
+        else:
+            ng = len(cache.groups)
+            pages = (ctypes.c_int * max(ng, 1))(*[g.n_pages for g in cache.groups])
+            windows = (ctypes.c_int * max(ng, 1))(*[int(g.window or 0) for g in cache.groups])
+            h = ctypes.c_void_p()
+            N.check(self._lib.kipp_scheduler_create(cache._h, ng, pages, windows, cache.page_size,
+                                                    cache.slots.max_requests, ctypes.byref(opt), ctypes.byref(h)))
+            self._h = h
+            self._owned = True
+        self._owners = cache._owners
+        self._requests: dict = {}          # request id -> Request
+        self._ints: dict = {}              # the library's number of a request -> its id
+        self._numbers: dict = {}           # and back (a finished request's number is forgotten by the cache)
         self._arrivals = 0
-        self.stats = {"preemptions": 0, "steps": 0, "admitted": 0}
+        self.finished: list[Request] = []
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and getattr(self, "_h", None):
+            self._lib.kipp_scheduler_destroy(self._h)
+            self._h = None
+
+    def _check(self, rc: int) -> None:
+        N.check(rc, scheduler=self._h)
 
     # -- intake ----------------------------------------------------------------------
     def add(self, request: Request) -> None:
-        if not request.prompt:
-            raise ValueError("a request needs at least one prompt token")
-        if request.max_new_tokens < 0:
-            raise ValueError("max_new_tokens must not be negative")
         request.sampling.validate()
-        if self.max_positions is not None and request.total_budget > self.max_positions:
-            # the reference rejects prompt + max_tokens > context (src/kipp_server.c:1676-1684)
-            raise ValueError(f"request {request.id!r}: prompt + max_new_tokens "
-                             f"({request.total_budget}) exceeds the context of {self.max_positions}")
-        for g in self.cache.groups:
-            if g.peak_pages(request.total_budget, self._step_cap()) > g.pool.n_pages:
-                raise ValueError(f"request {request.id!r} can never fit: it needs more pages than "
-                                 f"group {g.index} has ({g.pool.n_pages})")
+        params, keep = to_native([request.sampling])
+        prompt = (ctypes.c_int32 * max(len(request.prompt), 1))(*[int(t) for t in request.prompt])
+        stops = (ctypes.c_int32 * max(len(request.stop_token_ids), 1))(*[int(t) for t in request.stop_token_ids])
         seed = request.sampling.seed & MASK64
+        known = request.id in self._owners
+        g = N.GenerationRequest()
+        g.id = self._owners.id_of(request.id, create=True)
+        g.prompt, g.n_prompt = prompt, len(request.prompt)
+        g.max_new_tokens = request.max_new_tokens
+        g.sampling = params[0]
+        g.seed = seed
+        g.stop_tokens, g.n_stop_tokens = stops, len(request.stop_token_ids)
+        try:
+            self._check(self._lib.kipp_scheduler_submit(self._h, ctypes.byref(g)))
+        except Exception:
+            if not known:
+                self._owners.forget(request.id)
+            raise
+        del keep
         request.rng_state = seed if seed else 1
         request.arrival = self._arrivals
         self._arrivals += 1
         request.state = RequestState.WAITING
-        self.waiting.append(request)
+        self._requests[request.id] = request
+        self._ints[int(g.id)] = request.id
+        self._numbers[request.id] = int(g.id)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.kipp_scheduler_has_work(self._h))
 
-    # -- page arithmetic ---------------------------------------------------------------
-    def _step_cap(self) -> int:
-        return min(self.chunk_size, self.max_batch_tokens)
+    def _ids(self, which: int) -> list:
+        n = ctypes.c_int()
+        cap = max(len(self._requests), 1)
+        buf = (ctypes.c_int64 * cap)()
+        self._check(self._lib.kipp_scheduler_list(self._h, which, buf, cap, ctypes.byref(n)))
+        return [self._ints[int(buf[i])] for i in range(min(n.value, cap))]
 
-    def _outstanding(self, group) -> int:
-        """Pages the running requests may still take in ``group``."""
-        total = 0
-        for r in self.running:
-            held = self.cache.pages_held(r.id)[group.index]
-            total += max(0, group.peak_pages(r.total_budget, self._step_cap()) - held)
-        return total
+    @property
+    def waiting(self) -> deque:
+        return deque(self._requests[i] for i in self._ids(0))
 
-    def _can_admit(self, request: Request) -> bool:
-        if len(self.running) >= self.max_running or self.cache.slots.free_slots == 0:
-            return False
-        for g in self.cache.groups:
-            if self.policy == "reserve":
-                need = g.peak_pages(request.total_budget, self._step_cap())
-                if g.pool.free_pages < need + self._outstanding(g):
-                    return False
-            else:
-                first = min(request.pending, self._step_cap())
-                if g.pool.free_pages < -(-first // g.page_size):
-                    return False
-        return True
+    @property
+    def running(self) -> list:
+        return [self._requests[i] for i in self._ids(1)]
 
-    def _admit_waiting(self) -> None:
-        while self.waiting and self._can_admit(self.waiting[0]):   # head-of-line blocking
-            r = self.waiting.popleft()
-            self._admit(r.id)
-            r.state = RequestState.RUNNING
-            r.fed = 0
-            self.running.append(r)
-            self.stats["admitted"] += 1
+    @property
+    def stats(self) -> dict:
+        out = (ctypes.c_longlong * 3)()
+        self._lib.kipp_scheduler_stats(self._h, out)
+        return {"preemptions": int(out[0]), "steps": int(out[1]), "admitted": int(out[2])}
+
+    def _refresh(self, request: Request) -> None:
+        i = self._numbers[request.id]
+        st = N.GenerationState()
+        self._check(self._lib.kipp_scheduler_poll(self._h, i, ctypes.byref(st)))
+        if st.n_tokens != len(request.output):
+            buf = (ctypes.c_int32 * max(st.n_tokens, 1))()
+            n = ctypes.c_int()
+            self._check(self._lib.kipp_scheduler_output(self._h, i, buf, st.n_tokens, ctypes.byref(n)))
+            request.output = [int(buf[k]) for k in range(st.n_tokens)]
+        request.preemptions = st.preemptions
+        request.finish_reason = _REASONS.get(st.reason)
+        request.rng_state = int(self._lib.kipp_scheduler_rng_state(self._h, i))
+        if st.finished:
+            request.state = RequestState.FINISHED
+
+    def sync(self) -> list:
+        """Bring the Python requests up to date with the scheduler; returns the
+        requests that have finished since the last call."""
+        waiting, running = set(self._ids(0)), set(self._ids(1))
+        done = []
+        for rid in self._ids(2):
+            r = self._requests[rid]
+            if r.state is not RequestState.FINISHED:
+                self._refresh(r)
+                r.state = RequestState.FINISHED
+                self.finished.append(r)
+                done.append(r)
+                if not self._live_in_cache(rid):
+                    self._owners.forget(rid)
+        for rid, r in self._requests.items():
+            if rid in running:
+                r.state = RequestState.RUNNING
+                self._refresh(r)
+            elif rid in waiting:
+                if r.state is RequestState.RUNNING:          # put back by a preemption
+                    r.fed = 0
+                r.state = RequestState.WAITING
+                self._refresh(r)
+        return done
+
+    def _live_in_cache(self, rid) -> bool:
+        i = self._owners.id_of(rid)
+        return bool(i) and self.cache._lib.kipp_cm_slot(self.cache._h, i) >= 0
 
     # -- planning ------------------------------------------------------------------------
-    def _plan(self) -> StepPlan:
-        budget = self.max_batch_tokens
-        entries, requests, sampled = [], [], []
-        # decoding requests first: one token each
-        for r in self.running:
-            if r.pending == 1 and r.fed >= len(r.prompt) and budget > 0:
-                entries.append(StepEntry(r.id, r.tokens_between(r.fed, r.fed + 1), [0]))
-                requests.append(r)
-                sampled.append(len(entries) - 1)
-                budget -= 1
-        # then prompt portions (and recomputation after a preemption) in arrival order
-        for r in self.running:
-            if budget <= 0:
-                break
-            if r.pending == 1 and r.fed >= len(r.prompt):
-                continue
-            n = min(r.pending, self.chunk_size, budget)
-            if n <= 0:
-                continue
-            toks = r.tokens_between(r.fed, r.fed + n)
-            last = r.fed + n == len(r.prompt) + len(r.output)
-            want = [n - 1] if last and len(r.output) < r.max_new_tokens else []
-            entries.append(StepEntry(r.id, toks, want))
-            requests.append(r)
-            if want:
-                sampled.append(len(entries) - 1)
-            budget -= n
-        return StepPlan(entries, requests, sampled)
-
-    def _fits(self, plan: StepPlan) -> bool:
-        need = [0] * len(self.cache.groups)
-        for e, r in zip(plan.entries, plan.requests):
-            for gi, m in enumerate(self.cache.missing_pages(r.id, r.fed + len(e.tokens))):
-                need[gi] += m
-        return all(n <= g.pool.free_pages for n, g in zip(need, self.cache.groups))
-
-    def _preempt_youngest(self) -> bool:
-        if len(self.running) <= 1:
-            return False
-        victim = max(self.running, key=lambda r: r.arrival)
-        self.running.remove(victim)
-        self._release(victim.id)
-        victim.state = RequestState.WAITING
-        victim.fed = 0
-        victim.preemptions += 1
-        self.stats["preemptions"] += 1
-        self.waiting.appendleft(victim)
-        return True
-
     def schedule(self) -> Optional[StepPlan]:
         """The next step's batch, or None when nothing can run."""
-        # finished-at-zero requests (max_new_tokens == 0) still prefill nothing
-        self._admit_waiting()
-        while True:
-            if not self.running:
-                return None
-            plan = self._plan()
-            if not plan.entries:
-                return None
-            if self._fits(plan):
-                self.stats["steps"] += 1
-                return plan
-            if self.policy == "reserve":
-                raise RuntimeError("reservation failed to keep a step within the pool")
-            if not self._preempt_youngest():
-                # one request alone does not fit: shrink its portion to what does
-                r = plan.requests[0]
-                g_free = min(g.pool.free_pages * g.page_size for g in self.cache.groups)
-                room = g_free + (-r.fed) % self.cache.page_size
-                if room <= 0:
-                    raise RuntimeError(f"request {r.id!r} cannot grow: the pool is exhausted")
-                e = plan.entries[0]
-                n = min(len(e.tokens), room)
-                last = r.fed + n == len(r.prompt) + len(r.output)
-                plan = StepPlan([StepEntry(r.id, e.tokens[:n], [n - 1] if last and e.want else [])],
-                                [r], [0] if last and e.want else [])
-                if not self._fits(plan):
-                    raise RuntimeError(f"request {r.id!r} cannot grow: the pool is exhausted")
-                self.stats["steps"] += 1
-                return plan
+        cap = max(len(self._requests), 1)
+        buf = (N.PlanEntry * cap)()
+        n = ctypes.c_int()
+        self._check(self._lib.kipp_scheduler_schedule(self._h, buf, cap, ctypes.byref(n)))
+        self.sync()
+        if n.value == 0:
+            return None
+        entries, requests, sampled = [], [], []
+        for k in range(n.value):
+            pe = buf[k]
+            r = self._requests[self._ints[int(pe.id)]]
+            toks = (ctypes.c_int32 * pe.n_tokens)()
+            self._check(self._lib.kipp_scheduler_tokens(self._h, pe.id, pe.first, pe.n_tokens, toks))
+            r.fed = pe.first
+            entries.append(StepEntry(r.id, [int(t) for t in toks], [pe.n_tokens - 1] if pe.want_last else []))
+            requests.append(r)
+            if pe.want_last:
+                sampled.append(k)
+        return StepPlan(entries, requests, sampled)
 
     # -- after the step -------------------------------------------------------------------
     def complete(self, plan: StepPlan, tokens: list) -> list:
         """Record a finished step.  ``tokens[i]`` is the token sampled for
         ``plan.sampled[i]``.  The cache manager's lengths must already have
-        advanced (``Engine.step`` does that).  Returns the requests that finished."""
+        advanced (the step does that).  Returns the requests that finished."""
         if len(tokens) != len(plan.sampled):
             raise ValueError("one sampled token per sampled entry")
+        buf = (ctypes.c_int32 * max(len(tokens), 1))(*[int(t) for t in tokens])
+        self._check(self._lib.kipp_scheduler_complete(self._h, buf, len(tokens)))
         for e, r in zip(plan.entries, plan.requests):
             r.fed += len(e.tokens)
-        done = []
-        for idx, tok in zip(plan.sampled, tokens):
-            r = plan.requests[idx]
-            tok = int(tok)
-            if tok in r.stop_token_ids:
-                r.finish_reason = "stop"              # the stop token is not kept
-            else:
-                r.output.append(tok)
-                if len(r.output) >= r.max_new_tokens:
-                    r.finish_reason = "length"
-                elif self.max_positions is not None and len(r.prompt) + len(r.output) >= self.max_positions:
-                    r.finish_reason = "length"
-            if r.finish_reason is not None:
-                done.append(r)
-        for r in list(self.running):
-            if r.finish_reason is None and r.max_new_tokens == 0 and r.pending == 0:
-                r.finish_reason = "length"
-                done.append(r)
-        for r in done:
-            self._finish(r)
-        return done
-
-    def _finish(self, r: Request) -> None:
-        r.state = RequestState.FINISHED
-        self.running.remove(r)
-        self._release(r.id)                            # pages and slot go back at once
-        self.finished.append(r)
+        return self.sync()
 
     def abort(self, request_id) -> None:
-        for r in list(self.running):
-            if r.id == request_id:
-                r.finish_reason = "abort"
-                self._finish(r)
-                return
-        for r in list(self.waiting):
-            if r.id == request_id:
-                self.waiting.remove(r)
-                r.state, r.finish_reason = RequestState.FINISHED, "abort"
-                self.finished.append(r)
-                return
+        self._check(self._lib.kipp_scheduler_abort(self._h, self._numbers[request_id]))
+        self.sync()

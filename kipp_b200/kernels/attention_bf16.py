@@ -8,7 +8,7 @@ import torch
 
 from .ops import KernelError, _check, _fn, _ptr, _stream, c_float, c_int, c_void_p
 
-MAX_SPLITS = 32           # key splits of one decoded token (engine.batch.DECODE_MAX_SPLITS)
+MAX_SPLITS = 32           # key splits of one decoded token
 
 _scratch: dict = {}
 _generation = 0
@@ -105,12 +105,35 @@ def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv,
         scratch = decode_scratch(q.device, meta.n_decode, n_q, head_dim)
         f = _fn("attention_mma", "kipp_attn_decode_mma",
                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
+                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p])
         _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(meta.q_start),
                  _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
                  _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale),
-                 int(window or 0), MAX_SPLITS, _ptr(meta.decode_split_keys), _ptr(scratch), _stream()),
+                 int(window or 0), MAX_SPLITS, _ptr(meta.decode_split_keys), _split_stride(meta),
+                 _ptr(scratch), _stream()),
                "attn_decode_mma")
+
+
+def _split_stride(meta) -> int:
+    """1 when ``meta.decode_split_keys`` holds one split length per decoded token,
+    0 when it holds one for the whole step."""
+    return 1 if meta.decode_split_keys.numel() >= max(meta.n_decode, 2) else 0
+
+
+def decode_replan(split_keys: torch.Tensor, context_len: torch.Tensor, rows: torch.Tensor, pairs_per_entry: int,
+                  resident_ctas: int, fixed_tiles: int, min_split: int, max_splits: int, own_length: bool) -> None:
+    """The keys per split of every decoded token, chosen on the device from the
+    cached lengths (between the steps of a burst that runs without the host)."""
+    n = rows.numel()
+    for t in (split_keys, context_len, rows):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("decode_replan takes contiguous int32 tensors")
+    if split_keys.numel() < n:
+        raise KernelError("decode_replan: one split length per decoded token")
+    f = _fn("attention_mma", "kipp_attn_decode_replan",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(split_keys), _ptr(context_len), _ptr(rows), n, pairs_per_entry, resident_ctas, fixed_tiles,
+             min_split, max_splits, 1 if own_length else 0, _stream()), "attn_decode_replan")
 
 
 def decode_fused_ok(meta, q_dtype, n_q: int, n_kv: int, head_dim: int, rotary_dim: int) -> bool:
@@ -137,10 +160,10 @@ def decode_fused(out, qkv, k_pages, v_pages, q_norm_w, k_norm_w, eps, cos_sin, w
     f = _fn("attention_mma", "kipp_attn_decode_mma_fused",
             [c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
-             c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+             c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(out), _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(q_norm_w), _ptr(k_norm_w),
              norm_dtype, float(eps), _ptr(cos_sin), 1 if write_cache else 0, _ptr(meta.q_start),
              _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
              _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale), int(window or 0),
-             MAX_SPLITS, _ptr(meta.decode_split_keys), _ptr(scratch), _ptr(status), _stream()),
+             MAX_SPLITS, _ptr(meta.decode_split_keys), _split_stride(meta), _ptr(scratch), _ptr(status), _stream()),
            "attn_decode_mma_fused")

@@ -12,8 +12,7 @@ c_int, c_float, c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 EPILOGUES = {"store": 0, "add": 1, "swiglu": 2}
 
 
-class KernelError(RuntimeError):
-    pass
+from ..native import KernelError  # noqa: E402  (the library's and these wrappers' refusals are one type)
 
 
 def dtype_code(dtype: torch.dtype) -> int:

@@ -27,24 +27,20 @@ def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
 
 
 def burst_advance(tokens: torch.Tensor, positions: torch.Tensor, context_len: torch.Tensor,
-                  split_keys: torch.Tensor, next_tokens: torch.Tensor, ring: torch.Tensor,
-                  counter: torch.Tensor, pairs_per_entry: int, resident_ctas: int, fixed_tiles: int,
-                  min_split: int, max_splits: int) -> None:
+                  next_tokens: torch.Tensor, ring: torch.Tensor, counter: torch.Tensor) -> None:
     """Between two greedy decode steps on the device: ``next_tokens`` become the
     step's tokens and row ``counter`` of ``ring``, positions and cached lengths move
-    on by one, the keys per decode-attention split are chosen for the new lengths."""
+    on by one."""
     n = next_tokens.numel()
-    for t in (tokens, positions, context_len, split_keys, next_tokens, ring, counter):
+    for t in (tokens, positions, context_len, next_tokens, ring, counter):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("burst_advance takes contiguous int32 tensors")
     if min(tokens.numel(), positions.numel(), context_len.numel()) < n or ring.shape[1] != n:
         raise KernelError("burst_advance: sections shorter than the batch")
     f = _fn("sampling", "kipp_burst_advance",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(tokens), _ptr(positions), _ptr(context_len), _ptr(split_keys), _ptr(next_tokens), _ptr(ring),
-             _ptr(counter), n, ring.shape[0], pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits,
-             _stream()), "burst_advance")
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(tokens), _ptr(positions), _ptr(context_len), _ptr(next_tokens), _ptr(ring), _ptr(counter), n,
+             ring.shape[0], _stream()), "burst_advance")
 
 
 def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,

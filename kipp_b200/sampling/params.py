@@ -50,3 +50,32 @@ def next_uniform(state: int) -> tuple[int, float]:
     """(new state, uniform in [0, 1) with 53 bits) (src/kipp.c:3331-3333)."""
     state, r = xorshift64_star(state)
     return state, (r >> 11) / 9007199254740992.0
+
+
+def to_native(params, recent=None):
+    """The library's array of sampling options for rows with these ``SamplingParams``
+    (and the tokens each row's penalties look back over); returns (array, what
+    must stay alive while it is used)."""
+    import ctypes
+
+    from .. import native as N
+    rows = len(params)
+    arr = (N.SampleParams * max(rows, 1))()
+    keep = []
+    for i, p in enumerate(params):
+        p.validate()
+        a = arr[i]
+        a.temperature, a.top_p, a.top_k, a.min_p = p.temperature, p.top_p, p.top_k, p.min_p
+        a.frequency_penalty, a.presence_penalty = p.frequency_penalty, p.presence_penalty
+        a.repetition_penalty = p.repetition_penalty
+        r = list(recent[i])[-RECENT_WINDOW:] if recent is not None and p.has_penalties else []
+        if r:
+            buf = (ctypes.c_int32 * len(r))(*[int(t) for t in r])
+            keep.append(buf)
+            a.recent_tokens, a.recent_count = buf, len(r)
+        if p.logit_bias:
+            toks = (ctypes.c_int32 * len(p.logit_bias))(*[int(t) for t in p.logit_bias])
+            vals = (ctypes.c_float * len(p.logit_bias))(*[float(v) for v in p.logit_bias.values()])
+            keep += [toks, vals]
+            a.logit_bias_tokens, a.logit_bias_values, a.logit_bias_count = toks, vals, len(p.logit_bias)
+    return arr, keep

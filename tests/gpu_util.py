@@ -125,6 +125,53 @@ def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = 
 
 
 # ---------------------------------------------------------------------------
+class StepMetaForTests:
+    """The flattened description of a step as the kernels read it, for the tests of
+    single kernels (the engine's own packing is the library's, csrc/host/engine.hpp)."""
+
+
+def split_length(decoded: int, longest: int, kv_heads: int = 8, sm_count: int = 148, own: bool = False) -> int:
+    """Keys per decode-attention split as the library's planner chooses them."""
+    from kipp_b200 import native as N
+    return N.lib().kipp_attention_split_length(decoded, longest, kv_heads, sm_count, 1 if own else 0)
+
+
+def pack_meta(entries: list, starts: list, slots: list, tables: list, device) -> StepMetaForTests:
+    """``entries``: (request, tokens, want) or objects with ``.tokens`` / ``.want``;
+    ``starts[i]`` tokens entry i has cached; ``tables[g]`` int32 [entries, width_g]."""
+    toks = [list(e.tokens) if hasattr(e, "tokens") else list(e[1]) for e in entries]
+    wants = [list(e.want) if hasattr(e, "want") else list(e[2]) for e in entries]
+    q_lens = [len(t) for t in toks]
+    T = sum(q_lens)
+    q_start = np.zeros(len(entries) + 1, dtype=np.int32)
+    np.cumsum(q_lens, out=q_start[1:])
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(np.asarray(a, dtype=np.int32))).to(device)   # noqa: E731
+    m = StepMetaForTests()
+    m.tokens, m.entries = T, len(entries)
+    m.q_lens, m.kv_lens = q_lens, [s + q for s, q in zip(starts, q_lens)]
+    m.token_ids = dev([t for ts in toks for t in ts])
+    m.positions = dev([s + i for s, q in zip(starts, q_lens) for i in range(q)])
+    m.entry_of_token = dev([i for i, q in enumerate(q_lens) for _ in range(q)])
+    m.q_start, m.context_len, m.slots = dev(q_start), dev(starts), dev(slots)
+    rows = [int(q_start[i]) + w for i, ws in enumerate(wants) for w in ws]
+    m.logit_rows, m.n_logit_rows = (dev(rows) if rows else None), len(rows)
+    m.block_tables = [dev(t) for t in tables]
+    decode_rows = [i for i, q in enumerate(q_lens) if q == 1]
+    m.decode_rows, m.n_decode = (dev(decode_rows) if decode_rows else None), len(decode_rows)
+    tile = 64
+    work = [(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(0, q, tile)]
+    every = [(i, t) for i, q in enumerate(q_lens) for t in range(0, q, tile)]
+    work128 = [(i, t) for i, q in enumerate(q_lens) if q > 1 for t in range(0, q, 2 * tile)]
+    m.prefill_work, m.n_prefill_items = (dev(work).view(-1, 2) if work else None), len(work)
+    m.all_work, m.n_all_items = dev(every).view(-1, 2), len(every)
+    m.prefill_work128, m.n_prefill_items128 = (dev(work128).view(-1, 2) if work128 else None), len(work128)
+    longest = max([starts[i] + 1 for i in decode_rows], default=0)
+    m.decode_split_keys = dev([split_length(len(decode_rows), longest)] * max(len(decode_rows), 4))
+    m.extra = {}
+    return m
+
+
+# ---------------------------------------------------------------------------
 class PartHarness:
     """Runs single parts the way the engine does: a runtime, a cache manager
     and the step context a part sees, without a model around them."""

@@ -7,7 +7,8 @@ import pytest
 import torch
 
 import plain_qwen3 as P
-from kipp_b200.engine.batch import StepEntry, pack_step
+from gpu_util import pack_meta as pack_step, split_length
+from kipp_b200.engine.batch import StepEntry
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -452,34 +453,38 @@ def test_attention_scores_that_climb(rate):
 
 # ------------------------------------------------------------------ sampling
 def test_burst_advance_moves_a_step_on():
-    """The kernel between two greedy steps of a burst: tokens handed over and put into
-    the ring row the counter names, positions and cached lengths + 1, and the keys per
-    decode-attention split chosen as the host chooses them for the new lengths."""
-    from kipp_b200.engine.batch import (DECODE_CTA_FIXED_TILES, DECODE_MAX_SPLITS, DECODE_MIN_SPLIT,
-                                        DECODE_RESIDENT_CTAS, decode_split_length)
-    from kipp_b200.kernels import sampling
+    """The kernels between two greedy steps of a burst: tokens handed over and put into
+    the ring row the counter names, positions and cached lengths + 1; then the keys per
+    decode-attention split of every token, chosen as the host chooses them for the new
+    lengths (for the whole step, or from each token's own context)."""
+    from kipp_b200.kernels import attention_bf16, sampling
     g = torch.Generator().manual_seed(5)
     for n, longest in ((1, 100), (1, 2047), (3, 5000), (8, 8190), (8, 127), (64, 2047), (64, 40_000), (130, 700)):
         lens = torch.randint(1, longest + 1, (n,), generator=g).int()
         lens[int(torch.randint(0, n, (1,), generator=g))] = longest
         dev = lambda t: t.clone().to(DEV)
         tokens, positions, context = dev(torch.zeros(n).int()), dev(lens), dev(lens)
-        split, counter = dev(torch.zeros(4).int()), dev(torch.tensor([2]).int())
+        counter = dev(torch.tensor([2]).int())
         nxt = torch.randint(0, 50_000, (n,), generator=g).int()
         ring = torch.full((4, n), -7, dtype=torch.int32, device=DEV)
-        sampling.burst_advance(tokens, positions, context, split[:1], dev(nxt), ring, counter, 8,
-                               DECODE_RESIDENT_CTAS, DECODE_CTA_FIXED_TILES, DECODE_MIN_SPLIT, DECODE_MAX_SPLITS)
+        sampling.burst_advance(tokens, positions, context, dev(nxt), ring, counter)
         assert tokens.cpu().tolist() == nxt.tolist()
         assert positions.cpu().tolist() == (lens + 1).tolist() == context.cpu().tolist()
         assert int(counter) == 3 and ring[2].cpu().tolist() == nxt.tolist()
         assert ring[[0, 1, 3]].eq(-7).all()
         # the next step's tokens sit at positions lens + 1 and see lens + 2 keys
-        assert int(split[0]) == decode_split_length([int(x) + 2 for x in lens]), (n, longest)
-        assert split[1:].eq(0).all()
+        rows = dev(torch.arange(n).int())
+        split = dev(torch.zeros(n + 3).int())
+        for kv_heads, sms in ((8, 148), (2, 148), (1, 132)):
+            attention_bf16.decode_replan(split, context, rows, kv_heads, 3 * sms, 5, 128, 32, own_length=False)
+            want = split_length(n, longest + 2, kv_heads, sms)
+            assert split[:n].cpu().tolist() == [want] * n, (n, longest, kv_heads)
+            assert split[n:].eq(0).all()
+        attention_bf16.decode_replan(split, context, rows, 8, 444, 5, 128, 32, own_length=True)
+        assert split[:n].cpu().tolist() == [split_length(1, int(x) + 2, own=True) for x in lens]
         # a full ring: the tokens are still handed over, no row is written
         counter.fill_(4)
-        sampling.burst_advance(tokens, positions, context, split[:1], dev(nxt), ring, counter, 8,
-                               DECODE_RESIDENT_CTAS, DECODE_CTA_FIXED_TILES, DECODE_MIN_SPLIT, DECODE_MAX_SPLITS)
+        sampling.burst_advance(tokens, positions, context, dev(nxt), ring, counter)
         assert int(counter) == 5 and ring[[0, 1, 3]].eq(-7).all()
 
 
@@ -524,18 +529,20 @@ def test_penalties_and_bias_match_the_reference_sampler():
     import os
     with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "operators.json")) as f:
         gold = json.load(f)["penalties"]
-    from kipp_b200.sampling import SamplingParams
-    from kipp_b200.sampling.sampler import Sampler
+    from kipp_b200.kernels import sampling as ks
     logits = torch.tensor([gold["logits"], gold["logits"]], dtype=torch.float32, device=DEV)
-    sp = SamplingParams(repetition_penalty=gold["repetition"], presence_penalty=gold["presence"],
-                        frequency_penalty=gold["frequency"],
-                        logit_bias={int(k): v for k, v in gold["bias"].items()})
-    plain = SamplingParams()
-    states = [1, 1]
-    out = Sampler(DEV).sample(logits, [sp, plain], states, [gold["recent"], []]).cpu().tolist()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)          # noqa: E731
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)        # noqa: E731
+    recent = gold["recent"]
+    bias = {int(k): v for k, v in gold["bias"].items()}
+    # row 0 has the penalties and the bias, row 1 none
+    ks.apply_penalties(logits, i32([recent, [-1] * len(recent)]), i32([len(recent), 0]),
+                       f32([gold["repetition"], 1.0]), f32([gold["presence"], 0.0]), f32([gold["frequency"], 0.0]),
+                       i32([list(bias), [0] * len(bias)]), f32([list(bias.values()), [0.0] * len(bias)]),
+                       i32([len(bias), 0]))
+    out = ks.argmax_rows(logits).cpu().tolist()
     assert out[0] == gold["token"]                       # what kipp_sample_ex chose with the same settings
     assert out[1] == int(np.argmax(np.asarray(gold["logits"], dtype=np.float32))) and out[0] != out[1]
-    assert states == [1, 1]                              # greedy leaves the generators alone
 
 
 @pytest.mark.parametrize("case", [dict(D=128, nq=8, nkv=2, page=16, rot=True, norm=True, w16=True, window=None),
