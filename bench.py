@@ -114,12 +114,22 @@ class ClockSampler:
                 "reasons": sorted({r for x in chosen for r in x[3]}), "samples": len(chosen), "window": window}
 
 
-def reference_arm() -> int:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "the reference is a C project without setup.py or pyproject.toml: pip cannot "
-                       "install it, and its CUDA path needs a GGUF checkpoint of a registered repository"}))
-    return 0
+def reference_arm(args) -> int:
+    """The reference's own CUDA path on the same workload: see baseline/reference_arm.py."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_arm as ref
+    except Exception as e:                                   # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"baseline/reference_arm.py cannot be imported: {e}"}))
+        return 0
+    return ref.main(args, QWEN3_4B, WEIGHT_SEED, POINT_PROMPT, PREFILL_TOKENS)
+
+
+def median_mad(values: list) -> tuple[float, float]:
+    """Median and median absolute deviation (the reference's policy for its own
+    benchmark figures, tools/bench.py:260-268)."""
+    m = statistics.median(values)
+    return m, statistics.median(abs(v - m) for v in values)
 
 
 def main() -> int:
@@ -133,9 +143,13 @@ def main() -> int:
                     help="run fewer layers than the configuration has (named in the record)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and the prefill")
     ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--repeats", type=int, default=5, help="timed runs of --steps steps each; the median counts")
+    ap.add_argument("--preset", default="qwen3-4b", help="another preset's sizes (the record names them)")
+    ap.add_argument("--own-length-splits", action="store_true",
+                    help="decode attention splits from each token's own context only")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -143,28 +157,28 @@ def main() -> int:
         args.warmup = 3
 
     import torch
-    from kipp_b200 import kernels
     from kipp_b200.config import config_from_dict
     from kipp_b200.engine import StepEntry
     from kipp_b200.engine.llm import LLM
-    from kipp_b200.kernels import ops as kops
 
     pk, pk_src = peaks()
-    cfg = dict(QWEN3_4B)
+    cfg = dict(QWEN3_4B if args.preset == "qwen3-4b" else load_preset(args.preset)[0])
+    seed = WEIGHT_SEED if args.preset == "qwen3-4b" else int(load_preset(args.preset)[1]["seed"])
     layers_full = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     config = config_from_dict(cfg)
-    K, W, B = args.steps, args.warmup, args.batch
-    span = K + W + 2
-    batches = [B] if args.skip_points else sorted({1, B, 64})
+    K, W, B, R = args.steps, args.warmup, args.batch, max(args.repeats, 1)
+    span = R * K + W + 2
+    batches = [B] if args.skip_points else sorted({1, 8, B, 64})
     cache_tokens = max([B * (args.context + PAGE)] +
                        [b * (POINT_PROMPT + span + PAGE) for b in batches if b != B])
     llm = LLM(config, dtype="bfloat16", kv_block_size=PAGE, kv_tokens=cache_tokens, ctx=args.context,
               max_requests=max(batches), max_batch_tokens=max(PREFILL_TOKENS, max(batches)),
-              chunk=PREFILL_TOKENS, seed=WEIGHT_SEED)
+              chunk=PREFILL_TOKENS, seed=seed, own_length_splits=args.own_length_splits)
     eng = llm.engine
     dev = eng.runtime.device
+    stream = eng.stream                      # the engine's stream: the timing events are recorded there
     g = torch.Generator().manual_seed(1234)
 
     def prompt(n):
@@ -178,24 +192,25 @@ def main() -> int:
     if not args.skip_points:
         toks = prompt(PREFILL_TOKENS)
         times = []
-        for i in range(3 + 3):
+        for i in range(3 + R):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize(dev)
-            a.record()
+            a.record(stream)
             eng.step([StepEntry(("prefill", i), toks, [PREFILL_TOKENS - 1])])
-            b.record()
+            b.record(stream)
             torch.cuda.synchronize(dev)
             eng.finish(("prefill", i))
             if i >= 3:
                 times.append(a.elapsed_time(b))
-        ms = statistics.median(times)
+        ms, ms_mad = median_mad(times)
         c = config
         gemm_params = c.num_hidden_layers * (c.hidden_size * (c.q_dim + 2 * c.kv_dim) +
                                              c.q_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
         T = PREFILL_TOKENS
         flops = 2.0 * T * gemm_params + 2.0 * c.hidden_size * c.vocab_size \
             + c.num_hidden_layers * 2.0 * T * (T + 1) * c.head_dim * c.num_attention_heads
-        prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+        prefill = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3), "ms_mad": round(ms_mad, 3),
+                   "runs": len(times),
                    "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                    "flops": flops, "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src}
 
@@ -209,13 +224,14 @@ def main() -> int:
                 eng.step([StepEntry(rid, toks[a:a + PREFILL_TOKENS], [])])
         return rids
 
-    def decode_run(rids: list, steps: int, warmup: int, sample_clocks: bool):
-        """Greedy decode of all ``rids`` for warmup + steps steps; device-timed.  The
-        argmax of a step is fed to the next one on the device (Engine.decode_burst):
-        the host prepares positions and launches but waits for no token.  (The
-        end-to-end figure below has the host in every step.)"""
+    def decode_run(rids: list, steps: int, warmup: int, repeats: int, sample_clocks: bool):
+        """Greedy decode of all ``rids``: ``warmup`` steps, then ``repeats`` timed runs of
+        ``steps`` steps each, device-timed on the engine's stream.  The argmax of a step is
+        fed to the next one on the device (Engine.decode_burst, which the generation loop
+        uses for greedy requests): the host launches and waits for no token.  (The
+        end-to-end figure below has the host in every step.)  Returns the median
+        milliseconds per step, its median absolute deviation, clocks, kernel launches."""
         next_tokens = prompt(len(rids))
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         sampler = ClockSampler() if sample_clocks else None
         ring = eng.decode_burst(rids, next_tokens, warmup)
         next_tokens = ring[-1].tolist()
@@ -223,22 +239,27 @@ def main() -> int:
         launches0 = eng.kernel_launches()
         if sampler:
             sampler.mark_start()
-        a.record()
-        ring = eng.decode_burst(rids, next_tokens, steps)
-        b.record()
-        torch.cuda.synchronize(dev)
+        per_step = []
+        for _ in range(repeats):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            a.record(stream)
+            ring = eng.decode_burst(rids, next_tokens, steps)
+            b.record(stream)
+            torch.cuda.synchronize(dev)
+            assert ring.shape[0] == steps and int(ring.min()) >= 0
+            next_tokens = ring[-1].tolist()
+            per_step.append(a.elapsed_time(b) / steps)
         if sampler:
             sampler.mark_end()
         clocks = sampler.stop() if sampler else None
-        assert ring.shape[0] == steps and int(ring.min()) >= 0
-        ms = a.elapsed_time(b) / steps
-        # every step's argmax kernel is ours too, launched outside the graph
-        return ms, clocks, eng.kernel_launches() - launches0 + steps
+        ms, mad = median_mad(per_step)
+        return ms, mad, clocks, (eng.kernel_launches() - launches0) // repeats
 
     headline_ctx = args.context - span
     rids = fill(B, headline_ctx, "head")
-    ms_step, clocks, launches = decode_run(rids, K, W, True)
-    ctx_mid = headline_ctx + W + K / 2.0
+    ms_step, ms_mad, clocks, launches = decode_run(rids, K, W, R, True)
+    ctx_mid = headline_ctx + W + R * K / 2.0
     step_bytes = weight_bytes + B * ctx_mid * kv_bytes_token
     achieved = step_bytes / (ms_step / 1e3) / 1e9
     for r in rids:
@@ -247,14 +268,16 @@ def main() -> int:
 
     points = {}
     if not args.skip_points:
-        for b in (1, 64):
-            if b == B and args.context == POINT_PROMPT + span:
-                points[f"decode_b{b}"] = round(B / (ms_step / 1e3), 1)
-                continue
+        for b in sorted({1, 8, 64}):
             rr = fill(b, POINT_PROMPT, f"p{b}")
-            ms_b, _, _ = decode_run(rr, min(K, 32), 3, False)
+            steps_b = min(K, 32)
+            ms_b, mad_b, _, _ = decode_run(rr, steps_b, 3, R, False)
+            ctx_b = POINT_PROMPT + 3 + R * steps_b / 2.0
+            gbs = (weight_bytes + b * ctx_b * kv_bytes_token) / (ms_b / 1e3) / 1e9
             points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
             points[f"decode_b{b}_ms"] = round(ms_b, 4)
+            points[f"decode_b{b}_ms_mad"] = round(mad_b, 4)
+            points[f"decode_b{b}_hbm_frac"] = round(gbs / pk["hbm_gbs"], 4)
             for r in rr:
                 eng.finish(r)
 
@@ -263,7 +286,8 @@ def main() -> int:
     sched = llm.new_scheduler()
     # requests finish their prompts one after the other; each keeps decoding until
     # all of them have decoded together for K steps
-    prefill_steps = B * (-(-(args.context - span) // PREFILL_TOKENS))
+    e2e_span = K + W + 2
+    prefill_steps = B * (-(-(args.context - e2e_span) // PREFILL_TOKENS))
     e2e_new = K + 4 + prefill_steps
     e2e_ctx = args.context - e2e_new - 1
     for i in range(B):
@@ -277,13 +301,15 @@ def main() -> int:
            "d2h_bytes_per_step": int(statistics.median(s["d2h_bytes"] for s in dec)) if dec else 0,
            "steps": len(dec)}
 
+    model_name = "Qwen3-4B-shaped" if args.preset == "qwen3-4b" else args.preset + "-shaped"
     record = {
-        "metric": "decode tokens/s, Qwen3-4B-shaped bf16, batch 8 (prefill and batch 1/64 beside it)",
+        "metric": f"decode tokens/s, {model_name} bf16, batch {B} (prefill and batch 1/8/64 after 2,048-token prompts beside it)",
         "value": round(B / (ms_step / 1e3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": K,
-        "warmup": W, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+        "warmup": W, "ms_per_step": round(ms_step, 4), "ms_per_step_mad": round(ms_mad, 4), "repeats": R,
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic: random weights N(0,0.02) seed 2, seeded random token ids",
-        "config": {"model": "Qwen3-4B-shaped", "layers": config.num_hidden_layers,
+        "data": f"synthetic: random weights N(0,0.02) seed {seed}, seeded random token ids",
+        "config": {"model": model_name, "layers": config.num_hidden_layers,
                    "layers_full": layers_full, "hidden": config.hidden_size,
                    "heads": config.num_attention_heads, "kv_heads": config.num_key_value_heads,
                    "head_dim": config.head_dim, "intermediate": config.intermediate_size,
@@ -292,7 +318,8 @@ def main() -> int:
                    "points_prompt": POINT_PROMPT, "kv_block": PAGE, "parallelism": "none (1 GPU)",
                    "l2": "inputs larger than L2 (weights + cache read once per step)",
                    "weight_gb": round(weight_bytes / 1e9, 3),
-                   "value_loop": "argmax fed back on the device, tokens read at the end; e2e has the host in every step"},
+                   "value_loop": "median of the repeats; argmax fed back on the device, tokens read at the end (the loop "
+                                 "generation takes for greedy requests); e2e has the host in every step"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],

@@ -1,10 +1,13 @@
-"""Command line in the reference's manner (src/kipp_cli.c): one prompt is
-evaluated, then tokens are sampled and fed back one at a time.
+"""Command line in the reference's manner (src/kipp_cli.c): prompts are
+evaluated, then tokens are sampled and fed back one at a time, all of it by the
+library's scheduler (the loop every front end shares), so several prompts run
+beside one another.
 
 Options the reference has keep their names and meanings (usage text
 src/kipp_cli.c:571-610): --model, --decode, --temperature, --top-p, --top-k,
 --min-p, --seed, --top, --ctx.  The prompt is token ids (there is no
-tokenizer here): --prompt-ids, --prompt-file or --random-prompt.  --backend
+tokenizer here): --prompt-ids (repeat it for several prompts), --prompt-file or
+--random-prompt.  --backend
 and --kv-quant have one value each here (cuda, the compute dtype's cache), so
 --dtype stands in their place.  Output: ``generated\\t<ids>`` on stdout, the
 final top-N logits as ``rank\\tid\\tlogit``, and on stderr the line
@@ -27,7 +30,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--weights-seed", type=int, default=None,
                     help="seed of the random weights (default: the preset's, else 0)")
     prompt = ap.add_mutually_exclusive_group(required=True)
-    prompt.add_argument("--prompt-ids", help="comma-separated token ids")
+    prompt.add_argument("--prompt-ids", action="append",
+                        help="comma-separated token ids; give it again for another prompt (they run together)")
     prompt.add_argument("--prompt-file", help="file of little-endian uint32 token ids")
     prompt.add_argument("--random-prompt", type=int, metavar="LEN", help="LEN seeded random token ids")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
@@ -49,19 +53,22 @@ def build_parser() -> argparse.ArgumentParser:
                     help="tokens one step may hold (default: --chunk); sizes the activation buffers")
     ap.add_argument("--stop-token", type=int, action="append", default=None,
                     help="token id that ends decoding (default: the config's eos_token_id)")
+    ap.add_argument("--policy", default="reserve", choices=["reserve", "preempt"],
+                    help="when pages run out: admit only what can never run out (reserve, default), or admit "
+                         "early and put the youngest request back (preempt)")
     ap.add_argument("--device", default="cuda:0")
     return ap
 
 
-def _prompt_tokens(args, vocab: int) -> list:
+def _prompts(args, vocab: int) -> list:
     if args.prompt_ids is not None:
-        return [int(t) for t in args.prompt_ids.replace(" ", "").split(",") if t]
+        return [[int(t) for t in ids.replace(" ", "").split(",") if t] for ids in args.prompt_ids]
     if args.prompt_file is not None:
         import numpy as np
-        return np.fromfile(args.prompt_file, dtype="<u4").astype("int64").tolist()
+        return [np.fromfile(args.prompt_file, dtype="<u4").astype("int64").tolist()]
     import torch
     g = torch.Generator().manual_seed(args.seed)
-    return torch.randint(0, vocab, (args.random_prompt,), generator=g).tolist()
+    return [torch.randint(0, vocab, (args.random_prompt,), generator=g).tolist()]
 
 
 def main(argv=None) -> int:
@@ -75,11 +82,11 @@ def main(argv=None) -> int:
     if args.temperature > 0 and args.seed == 0:
         print("kipp: --seed must be nonzero", file=sys.stderr)
         return 2
-    import torch
+    import numpy as np
     from .config.registry import config_from_dict, load_config
-    from .engine import Engine, StepEntry
+    from .engine.llm import LLM
+    from .engine.scheduler import Request
     from .sampling.params import SamplingParams
-    from .sampling.sampler import Sampler
 
     init = {}
     if args.model is not None:
@@ -100,34 +107,32 @@ def main(argv=None) -> int:
                 return 2
         if args.weights_seed is None:
             args.weights_seed = int(init.get("seed", 0))
-    tokens = _prompt_tokens(args, config.vocab_size)
-    if not tokens:
+    prompts = _prompts(args, config.vocab_size)
+    if not prompts or any(not p for p in prompts):
         print("kipp: the prompt is empty", file=sys.stderr)
         return 2
-    capacity = args.ctx or (len(tokens) + args.decode)
-    if len(tokens) + args.decode > capacity:
-        print(f"kipp: prompt ({len(tokens)}) + decode ({args.decode}) exceeds --ctx {capacity}",
-              file=sys.stderr)
+    # one more token than asked for is sampled (and dropped) when the final logits are wanted:
+    # they are the logits the token after the last generated one is sampled from
+    extra = 1 if args.top > 0 and len(prompts) == 1 and args.decode > 0 else 0
+    longest = max(len(p) for p in prompts)
+    capacity = args.ctx or (longest + args.decode + extra)
+    if longest + args.decode > capacity:
+        print(f"kipp: prompt ({longest}) + decode ({args.decode}) exceeds --ctx {capacity}", file=sys.stderr)
         return 2
+    if longest + args.decode + extra > capacity:
+        extra = 0
     if args.max_batch_tokens is not None and args.max_batch_tokens < 1:
         print("kipp: --max-batch-tokens must be positive", file=sys.stderr)
         return 2
     if args.max_batch_tokens is not None:
         args.chunk = min(args.chunk, args.max_batch_tokens)
-    cache_tokens = capacity + args.kv_block_size
+    page = args.kv_block_size
+    cache_tokens = sum(-(-(len(p) + args.decode + extra) // page) * page for p in prompts)
     if args.kv_blocks is not None:
-        cache_tokens = args.kv_blocks * args.kv_block_size
-        if cache_tokens < capacity:
-            print(f"kipp: --kv-blocks {args.kv_blocks} x {args.kv_block_size} tokens cannot hold {capacity}",
-                  file=sys.stderr)
+        cache_tokens = args.kv_blocks * page
+        if cache_tokens < -(-capacity // page) * page and args.policy == "reserve":
+            print(f"kipp: --kv-blocks {args.kv_blocks} x {page} tokens cannot hold {capacity}", file=sys.stderr)
             return 2
-    opts = dict(dtype=args.dtype, device=args.device, page_size=args.kv_block_size,
-                cache_tokens=cache_tokens, max_requests=1,
-                max_batch_tokens=max(args.max_batch_tokens or args.chunk, 1))
-    engine = (Engine.from_folder(args.model, **opts) if args.model is not None
-              else Engine.from_config(config, args.weights_seed, sigma=init.get("sigma"),
-                                      norm_jitter=init.get("norm_jitter", 0.1), **opts))
-    sampler = Sampler(engine.runtime.device)
     params = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                             min_p=args.min_p, seed=args.seed or 1)
     try:
@@ -135,46 +140,40 @@ def main(argv=None) -> int:
     except ValueError as e:
         print(f"kipp: {e}", file=sys.stderr)
         return 2
-    stops = set(args.stop_token) if args.stop_token else (
-        {config.eos_token_id} if getattr(config, "eos_token_id", None) is not None else set())
-    print(f"kipp: evaluating {len(tokens)} token{'' if len(tokens) == 1 else 's'} of "
-          f"{config.architecture} on cuda ({args.dtype})", file=sys.stderr)
-
-    def sync():
-        torch.cuda.synchronize(engine.runtime.device)
-
-    sync()
-    t0 = time.perf_counter()
-    logits = None
-    for a in range(0, len(tokens), args.chunk):
-        part = tokens[a:a + args.chunk]
-        last = a + len(part) == len(tokens)
-        logits = engine.step([StepEntry("cli", part, [len(part) - 1] if last else [])])
-    sync()
-    prefill_seconds = time.perf_counter() - t0
-
-    generated, rng = [], [params.seed]
-    t0 = time.perf_counter()
-    if args.decode:
-        sys.stdout.write("generated\t")
-        for _ in range(args.decode):
-            token = int(sampler.sample(logits, [params], rng, [generated[-64:]]).item())
-            if token in stops:
-                break
-            sys.stdout.write(("" if not generated else " ") + str(token))
-            sys.stdout.flush()
-            generated.append(token)
-            logits = engine.step([StepEntry("cli", [token], [0])])
-        sync()
-        sys.stdout.write("\n")
-    decode_seconds = time.perf_counter() - t0 if args.decode else 0.0
-    if args.top > 0:
-        values, ids = torch.topk(logits[0], min(args.top, logits.shape[1]))
-        for rank, (v, i) in enumerate(zip(values.tolist(), ids.tolist()), 1):
-            print(f"{rank}\t{i}\t{v:.9g}")
-    engine.runtime.check_status()
-    print(f"KIPP_METRIC backend=cuda prefill_tokens={len(tokens)} prefill_seconds={prefill_seconds:.9f} "
-          f"decode_tokens={len(generated)} decode_seconds={decode_seconds:.9f}", file=sys.stderr)
+    llm = LLM(args.model if args.model is not None else config, dtype=args.dtype, device=args.device,
+              kv_block_size=page, kv_tokens=cache_tokens, ctx=capacity, max_requests=max(len(prompts), 1),
+              max_batch_tokens=max(args.max_batch_tokens or args.chunk, 1), chunk=args.chunk, policy=args.policy,
+              seed=args.weights_seed or 0, stop_token_ids=tuple(args.stop_token or ()),
+              **({"sigma": init.get("sigma"), "norm_jitter": init.get("norm_jitter", 0.1)}
+                 if args.model is None else {}))
+    total = sum(len(p) for p in prompts)
+    print(f"kipp: evaluating {total} token{'' if total == 1 else 's'} of {config.architecture} on cuda "
+          f"({args.dtype})", file=sys.stderr)
+    sched = llm.new_scheduler()
+    requests = []
+    for i, prompt in enumerate(prompts):
+        sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, min_p=args.min_p,
+                            seed=(params.seed + i) or 1)
+        requests.append(Request(id=i, prompt=prompt, max_new_tokens=args.decode + extra, sampling=sp,
+                                stop_token_ids=llm.stop_token_ids))
+        sched.add(requests[-1])
+    llm.run(sched, record_steps=True)
+    prefill_seconds = sum(s["seconds"] for s in llm.step_log if s["prefill"])
+    decode_seconds = sum(s["seconds"] for s in llm.step_log if not s["prefill"])
+    generated = 0
+    for r in requests:
+        out = r.output[:args.decode]
+        generated += len(out)
+        if args.decode:
+            print("generated\t" + " ".join(str(t) for t in out))
+    if args.top > 0 and len(prompts) == 1:
+        logits = llm.engine.last_logits()
+        if logits is not None and logits.shape[0] == 1:
+            order = np.argsort(-logits[0], kind="stable")[:min(args.top, logits.shape[1])]
+            for rank, i in enumerate(order.tolist(), 1):
+                print(f"{rank}\t{i}\t{float(logits[0, i]):.9g}")
+    print(f"KIPP_METRIC backend=cuda prefill_tokens={total} prefill_seconds={prefill_seconds:.9f} "
+          f"decode_tokens={generated} decode_seconds={decode_seconds:.9f}", file=sys.stderr)
     return 0
 
 

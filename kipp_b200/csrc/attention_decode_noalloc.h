@@ -33,6 +33,11 @@
  *     the split kernel of the same call.  But two calls whose kernels overlap
  *     on the GPU (different streams, or graphs replayed side by side) write
  *     the same memory and race: keep calls on one stream, or order them.
+ *   - The looked-up address is kept in a plain per-device table without a lock.
+ *     Two host threads that make their first call on a device at the same moment
+ *     both look the address up and store the same value, which is harmless; the
+ *     library adds no other synchronisation between host threads.
+ *   - split_keys points at ONE value on the device: the keys per split of the step.
  *   - Inputs, outputs and every other rule are those of kipp_attn_decode_mma.
  */
 #ifndef KIPP_ATTENTION_DECODE_NOALLOC_H

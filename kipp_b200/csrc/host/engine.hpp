@@ -142,7 +142,9 @@ struct StepEntryView {
 
 class Engine {
 public:
-    static constexpr int BURST_RING_ROWS = 1024;   // steps a feedback graph runs before its ring of tokens is read out
+    // steps a feedback graph runs before its ring of tokens is read out (KIPP_B200_BURST_RING_ROWS
+    // in the environment of the process makes it shorter: tests do)
+    int burst_ring_rows = 1024;
     static constexpr int MAX_GRAPHS = 24;
 
     Engine(std::unique_ptr<ModelPlan> plan, TensorSource& source, const kipp_engine_options& options);
@@ -173,6 +175,12 @@ public:
     size_t weight_bytes() const;
     size_t cache_bytes_per_token() const;
     void check_status();
+    void debug_set_status(int word, int value) {
+        if (word < 0 || word > 3) fail(KIPP_E_ARGUMENT, "there are four status words");
+        cuda_check(cudaMemcpyAsync(status_.as<int>() + word, &value, sizeof(int), cudaMemcpyHostToDevice, stream_),
+                   "status write");
+        cuda_check(cudaStreamSynchronize(stream_), "synchronize");
+    }
 
     // -- what parts and the scheduler reach ---------------------------------------------------------
     PagedCacheView cache_view(const StepMeta& meta, const LayerRun& run, int mixer_slot) const;
@@ -427,6 +435,7 @@ inline Engine::Engine(std::unique_ptr<ModelPlan> plan, TensorSource& source, con
     ops_.status = status_.as<int>();
     ops_.workspace = &workspace_;
 
+    if (const char* rows = getenv("KIPP_B200_BURST_RING_ROWS"); rows && atoi(rows) > 0) burst_ring_rows = atoi(rows);
     if (opt_.max_logit_rows <= 0) {
         // a default that keeps the logits buffer near half a GiB
         const long long by_bytes = (512ll << 20) / ((long long)plan_->vocab_size * 4);
@@ -837,7 +846,7 @@ inline Engine::StepGraph& Engine::graph_for(const std::string& key, bool feedbac
     g->feedback = feedback;
     if (feedback) {
         g->next_tokens.reset((size_t)batch * sizeof(int), "burst tokens");
-        g->ring.reset((size_t)BURST_RING_ROWS * batch * sizeof(int), "burst ring");
+        g->ring.reset((size_t)burst_ring_rows * batch * sizeof(int), "burst ring");
         g->counter.reset(sizeof(int), "burst counter");
     }
     graphs_.push_back(std::move(g));
@@ -851,7 +860,7 @@ inline void Engine::feedback_tail(StepGraph& g) {
     ops_.argmax_rows(g.logits, plan_->vocab_size, n, plan_->vocab_size, g.next_tokens.as<int>());
     ops_.burst_advance(const_cast<int*>(g.meta.token_ids), const_cast<int*>(g.meta.positions),
                        const_cast<int*>(g.meta.context_len), g.next_tokens.as<int>(), g.ring.as<int>(),
-                       g.counter.as<int>(), n, BURST_RING_ROWS);
+                       g.counter.as<int>(), n, burst_ring_rows);
     for (auto& p : planners_) p->advance_on_device(ops_, g.meta.work.at(p->key()).data(), g.meta.context_len, n);
 }
 
@@ -985,8 +994,9 @@ inline void Engine::debug_part(const StepEntryView* entries, int n, int run_inde
     std::vector<int> rows;
     validate(entries, n, shape, rows);
     cuda_check(cudaSetDevice(opt_.device), "cudaSetDevice");
-    if (run_index < 0 || run_index >= (int)plan_->order.size()) fail(KIPP_E_ARGUMENT, "no such run");
-    const LayerRun& run = plan_->order[(size_t)run_index];
+    const bool layer_part = which != "embedding" && which != "final_norm" && which != "head";
+    if (layer_part && (run_index < 0 || run_index >= (int)plan_->order.size())) fail(KIPP_E_ARGUMENT, "no such run");
+    const LayerRun run = layer_part ? plan_->order[(size_t)run_index] : LayerRun{};
     std::vector<int64_t> rids((size_t)n);
     std::vector<int> new_lengths((size_t)n);
     shape.starts.resize((size_t)n);
@@ -1014,7 +1024,7 @@ inline void Engine::debug_part(const StepEntryView* entries, int n, int run_inde
     ctx.stream = stream_;
     ctx.kv_round_bf16 = opt_.kv_round_bf16 != 0;
     const int T = shape.tokens;
-    Block* block = plan_->layers[(size_t)run.layer].second.get();
+    Block* block = layer_part ? plan_->layers[(size_t)run.layer].second.get() : nullptr;
     PreNormBlock* pre = dynamic_cast<PreNormBlock*>(block);
     auto need_pre = [&] {
         if (!pre) fail(KIPP_E_UNSUPPORTED, "this layer's block does not name its parts");
@@ -1141,7 +1151,7 @@ inline void Engine::decode_burst(const int64_t* requests, const int32_t* tokens,
     int done = 0;
     bool first = true;
     while (done < steps) {
-        const int chunk = std::min(steps - done, BURST_RING_ROWS);
+        const int chunk = std::min(steps - done, burst_ring_rows);
         cuda_check(cudaMemsetAsync(g.counter.get(), 0, sizeof(int), stream_), "burst counter");
         int replays = chunk;
         if (first) {

@@ -225,6 +225,11 @@ int kipp_engine_step(kipp_engine* engine, const kipp_step_entry* entries, int n_
                      const float** logits, int* n_rows);
 /* Copies the last step's logits to host memory [n_rows, vocab] and checks the kernels' status words. */
 int kipp_engine_read_logits(kipp_engine* engine, float* host_out, size_t capacity_floats);
+/* Writes a value into one of the engine's four status words, as a kernel that refused an access or
+   gave up a bounded wait does (tests of the error path). */
+int kipp_engine_debug_set_status(kipp_engine* engine, int word, int value);
+/* Rows of logits the last step left (0 when it wanted none). */
+int kipp_engine_last_rows(kipp_engine* engine);
 /* Waits for the engine's stream and checks the kernels' status words. */
 int kipp_engine_synchronize(kipp_engine* engine);
 
@@ -319,8 +324,8 @@ int kipp_scheduler_forget(kipp_scheduler* scheduler, int64_t id);
 /* Ids of the requests that are waiting (0), running (1) or finished (2), in the scheduler's order. */
 int kipp_scheduler_list(kipp_scheduler* scheduler, int which, int64_t* ids, int capacity, int* n);
 uint64_t kipp_scheduler_rng_state(kipp_scheduler* scheduler, int64_t id);
-/* preemptions, steps planned, requests admitted */
-void kipp_scheduler_stats(const kipp_scheduler* scheduler, long long out[3]);
+/* preemptions, steps planned, requests admitted, tokens fed, tokens sampled */
+void kipp_scheduler_stats(const kipp_scheduler* scheduler, long long out[5]);
 
 /* The engine's own scheduler (made with default options at first use, or by configure). */
 int kipp_engine_scheduler_configure(kipp_engine* engine, const kipp_scheduler_options* options);

@@ -278,6 +278,12 @@ int kipp_engine_step(kipp_engine* e, const kipp_step_entry* entries, int n_entri
 int kipp_engine_read_logits(kipp_engine* e, float* host_out, size_t capacity_floats) {
     return guarded(e->error, [&] { e->engine->read_logits(host_out, capacity_floats); });
 }
+// Writes a value into one of the engine's status words, as a kernel that refused an access or gave
+// up a wait does (tests of the error path; no kernel is made to fail for it).
+int kipp_engine_debug_set_status(kipp_engine* e, int word, int value) {
+    return guarded(e->error, [&] { e->engine->debug_set_status(word, value); });
+}
+int kipp_engine_last_rows(kipp_engine* e) { return e->engine->last_rows(); }
 int kipp_engine_synchronize(kipp_engine* e) {
     return guarded(e->error, [&] { e->engine->synchronize(); });
 }
@@ -402,10 +408,12 @@ uint64_t kipp_scheduler_rng_state(kipp_scheduler* s, int64_t id) {
     guarded(s->error, [&] { out = s->scheduler->find(id)->rng_state; });
     return out;
 }
-void kipp_scheduler_stats(const kipp_scheduler* s, long long out[3]) {
+void kipp_scheduler_stats(const kipp_scheduler* s, long long out[5]) {
     out[0] = s->scheduler->stat_preemptions;
     out[1] = s->scheduler->stat_steps;
     out[2] = s->scheduler->stat_admitted;
+    out[3] = s->scheduler->stat_tokens_fed;
+    out[4] = s->scheduler->stat_tokens_sampled;
 }
 
 int kipp_engine_scheduler_configure(kipp_engine* e, const kipp_scheduler_options* options) {

@@ -97,7 +97,7 @@ public:
         preempt_ = o.preempt != 0;
     }
 
-    long long stat_preemptions = 0, stat_steps = 0, stat_admitted = 0;
+    long long stat_preemptions = 0, stat_steps = 0, stat_admitted = 0, stat_tokens_fed = 0, stat_tokens_sampled = 0;
 
     bool has_work() const { return !waiting_.empty() || !running_.empty(); }
     const std::deque<GenRequest*>& waiting() const { return waiting_; }
@@ -179,6 +179,8 @@ public:
     void complete(const StepPlan& plan, const int32_t* tokens, int n_tokens) {
         if (n_tokens != plan.sampled()) fail(KIPP_E_ARGUMENT, "one sampled token per sampled entry");
         for (auto& e : plan.entries) e.request->fed += e.n_tokens;
+        stat_tokens_fed += plan.tokens();
+        stat_tokens_sampled += n_tokens;
         std::vector<GenRequest*> done;
         int k = 0;
         for (auto& e : plan.entries) {
@@ -367,10 +369,31 @@ inline SchedulerHost engine_scheduler_host(Engine& e) {
     return h;
 }
 
+// Whether the planned step can be the first of a burst (Engine::decode_burst: greedy steps whose
+// tokens are fed back on the device): every running request is in the plan with one decoded
+// token, is greedy without penalties, bias or stop tokens (nothing the host would have to look at
+// between steps).  Returns the number of steps until the first request ends (0: no burst).
+inline int burst_length(const Scheduler& sched, const StepPlan& plan, long long max_positions) {
+    if (plan.entries.size() != sched.running().size()) return 0;
+    int steps = 1 << 30;
+    for (auto& e : plan.entries) {
+        const GenRequest& r = *e.request;
+        const kipp_sample_params& p = r.sampling;
+        if (e.n_tokens != 1 || !e.want_last || !r.decoding()) return 0;
+        if (p.temperature > 0.f || p.frequency_penalty != 0.f || p.presence_penalty != 0.f ||
+            (p.repetition_penalty != 0.f && p.repetition_penalty != 1.f) || !r.bias_tokens.empty() || !r.stop.empty())
+            return 0;
+        steps = std::min(steps, r.max_new_tokens - (int)r.output.size());
+        if (max_positions > 0) steps = std::min<long long>(steps, max_positions - r.known());
+    }
+    return steps;
+}
+
 // Drives the scheduler until no request is left (or max_steps steps ran): plan, step, sample,
 // record.  Token ids go to the device with each step's metadata and the sampled ids come back to
-// the host after each step.  Returns the steps run.
-inline int run_scheduler(Engine& engine, Scheduler& sched, int max_steps) {
+// the host after each step; where nothing has to be looked at between steps (burst_length) a run
+// of decode steps goes as one burst and its tokens come back together.  Returns the steps run.
+inline int run_scheduler(Engine& engine, Scheduler& sched, int max_steps, bool bursts = true) {
     int steps = 0;
     std::vector<StepEntryView> views;
     std::vector<std::vector<int32_t>> tokens;
@@ -382,6 +405,41 @@ inline int run_scheduler(Engine& engine, Scheduler& sched, int max_steps) {
         StepPlan plan = sched.schedule();
         if (plan.entries.empty()) fail(KIPP_E_STATE, "requests are waiting but none can be admitted");
         const size_t n = plan.entries.size();
+        int burst = bursts ? burst_length(sched, plan, engine.max_positions()) : 0;
+        if (max_steps > 0) burst = std::min(burst, max_steps - steps);
+        if (burst >= 2) {
+            std::vector<int64_t> rids(n);
+            std::vector<int32_t> first(n), ring((size_t)burst * n);
+            for (size_t i = 0; i < n; ++i) {
+                rids[i] = plan.entries[i].request->id;
+                first[i] = plan.entries[i].request->token_at(plan.entries[i].first);
+            }
+            bool ran = true;
+            try {
+                engine.decode_burst(rids.data(), first.data(), (int)n, burst, ring.data());
+            } catch (const Error& e) {
+                if (e.code != KIPP_E_OUT_OF_PAGES) throw;
+                ran = false;                 // the pages of all steps cannot be had at once: step by step
+            }
+            if (ran) {
+                for (int k = 0; k < burst; ++k) {
+                    if (k > 0) {
+                        plan = sched.schedule();
+                        if (plan.entries.size() != n) fail(KIPP_E_STATE, "the batch changed inside a burst");
+                    }
+                    // the ring's columns follow the order of the burst's requests
+                    sampled.resize(n);
+                    for (size_t i = 0; i < n; ++i) {
+                        size_t col = 0;
+                        while (rids[col] != plan.entries[i].request->id) ++col;
+                        sampled[i] = ring[(size_t)k * n + col];
+                    }
+                    sched.complete(plan, sampled.data(), (int)n);
+                }
+                steps += burst;
+                continue;
+            }
+        }
         views.resize(n);
         tokens.resize(n);
         want.resize(n);

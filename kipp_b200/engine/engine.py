@@ -334,6 +334,12 @@ class Engine:
                 return 1
         return forward
 
+    @property
+    def stream(self) -> torch.cuda.Stream:
+        """The CUDA stream the engine's kernels run on (events that time its work are
+        recorded there)."""
+        return self._stream
+
     # -- requests ------------------------------------------------------------------
     def _id(self, rid, create: bool = False) -> int:
         i = self._owners.id_of(rid, create=create)
@@ -425,6 +431,20 @@ class Engine:
         if not logits.value or rows.value == 0:
             return None
         return device_tensor(logits.value, (rows.value, self.vocab_size), torch.float32, self.device, owner=self)
+
+    def last_logits(self):
+        """The logits of the last step as a float32 array ``[rows, vocab]`` on the host
+        (None when it wanted none)."""
+        import numpy as np
+        rows = self._lib.kipp_engine_last_rows(self._h)
+        if rows <= 0:
+            return None
+        out = np.empty((rows, self.vocab_size), dtype=np.float32)
+        self._check(self._lib.kipp_engine_read_logits(self._h, out.ctypes.data, out.size))
+        return out
+
+    def _debug_set_status(self, word: int, value: int) -> None:
+        self._check(self._lib.kipp_engine_debug_set_status(self._h, word, value))
 
     def synchronize(self) -> None:
         """Wait for the engine's stream and raise if a kernel refused an access or

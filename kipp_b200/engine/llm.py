@@ -51,7 +51,8 @@ class LLM:
                  kv_blocks: Optional[int] = None, kv_tokens: Optional[int] = None,
                  ctx: Optional[int] = None, max_requests: int = 64, max_batch_tokens: int = 8192,
                  chunk: Optional[int] = None, policy: str = "reserve", seed: int = 0,
-                 stop_token_ids: Sequence[int] = (), **engine_options):
+                 stop_token_ids: Sequence[int] = (), sigma: Optional[float] = None, norm_jitter: float = 0.1,
+                 **engine_options):
         if kv_blocks is not None:
             cache_tokens = kv_blocks * kv_block_size
         elif kv_tokens is not None:
@@ -61,7 +62,7 @@ class LLM:
         opts = dict(dtype=dtype, device=device, page_size=kv_block_size, max_requests=max_requests,
                     max_batch_tokens=max_batch_tokens, cache_tokens=cache_tokens, **engine_options)
         if isinstance(model, ModelConfig):
-            self.engine = Engine.from_config(model, seed, **opts)
+            self.engine = Engine.from_config(model, seed, sigma=sigma, norm_jitter=norm_jitter, **opts)
         else:
             self.engine = Engine.from_folder(model, **opts)
         limit = self.engine.info()["max_positions"] or 8192
@@ -119,12 +120,20 @@ class LLM:
             engine._check(lib.kipp_engine_run(h, 0, ctypes.byref(steps)))
             total = steps.value
         else:
+            before = sched.stats
             while sched.has_work():
                 t_step = time.perf_counter()
                 engine._check(lib.kipp_engine_run(h, 1, ctypes.byref(steps)))
                 engine.synchronize()
-                self.step_log.append({"seconds": time.perf_counter() - t_step,
-                                      "h2d_bytes": engine.last_h2d_bytes})
+                seconds = time.perf_counter() - t_step
+                after = sched.stats
+                fed = after["tokens_fed"] - before["tokens_fed"]
+                sampled = after["tokens_sampled"] - before["tokens_sampled"]
+                # a step that feeds more tokens than it samples carries a prompt portion
+                self.step_log.append({"seconds": seconds, "tokens": fed, "sampled": sampled,
+                                      "prefill": fed > sampled or fed == 0, "decode_only": fed == sampled and fed > 0,
+                                      "h2d_bytes": engine.last_h2d_bytes, "d2h_bytes": 4 * sampled})
+                before = after
                 total += steps.value
         sched.sync()
         engine.synchronize()

@@ -196,9 +196,10 @@ class Scheduler:
 
     @property
     def stats(self) -> dict:
-        out = (ctypes.c_longlong * 3)()
+        out = (ctypes.c_longlong * 5)()
         self._lib.kipp_scheduler_stats(self._h, out)
-        return {"preemptions": int(out[0]), "steps": int(out[1]), "admitted": int(out[2])}
+        return {"preemptions": int(out[0]), "steps": int(out[1]), "admitted": int(out[2]),
+                "tokens_fed": int(out[3]), "tokens_sampled": int(out[4])}
 
     def _refresh(self, request: Request) -> None:
         i = self._numbers[request.id]

@@ -123,6 +123,8 @@ _SIGNATURES = {
     "kipp_engine_step": (_i, [_vp, POINTER(StepEntryC), _i, POINTER(_vp), _ip]),
     "kipp_engine_read_logits": (_i, [_vp, _vp, c_size_t]),
     "kipp_engine_synchronize": (_i, [_vp]),
+    "kipp_engine_last_rows": (_i, [_vp]),
+    "kipp_engine_debug_set_status": (_i, [_vp, _i, _i]),
     "kipp_engine_decode_burst": (_i, [_vp, POINTER(c_int64), POINTER(c_int32), _i, _i, _vp]),
     "kipp_sample_default_params": (None, [POINTER(SampleParams)]),
     "kipp_engine_sample": (_i, [_vp, POINTER(SampleParams), POINTER(c_uint64), _i, POINTER(c_int32)]),

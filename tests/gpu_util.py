@@ -172,60 +172,33 @@ def pack_meta(entries: list, starts: list, slots: list, tables: list, device) ->
 
 
 # ---------------------------------------------------------------------------
-class PartHarness:
-    """Runs single parts the way the engine does: a runtime, a cache manager
-    and the step context a part sees, without a model around them."""
-
-    def __init__(self, dtype: str, cache_specs: dict, page_size: int = 8, n_pages: int = 64,
-                 state_specs: dict | None = None, max_requests: int = 4):
-        from kipp_b200.cache import CacheManager
-        from kipp_b200.engine.runtime import Runtime
-        self.runtime = Runtime("cuda:0", dtype)
-        self.cache = CacheManager(cache_specs, page_size, n_pages, max_requests)
-        rt = self.runtime
-        for g in self.cache.groups:
-            shape = (len(g.cache_ids), n_pages, g.spec.kv_heads, page_size, g.spec.head_dim)
-            g.k = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
-            g.v = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
-        self.states = {cid: torch.zeros((max_requests,) + tuple(s.shape), dtype=s.dtype, device=rt.device)
-                       for cid, s in (state_specs or {}).items()}
-
-    def context(self, layout: list):
-        """layout: [(request id, number of new tokens)].  Reserves pages; call
-        ``commit`` after the parts ran."""
-        from kipp_b200.engine.batch import StepEntry, pack_step
-        from kipp_b200.engine.engine import CacheView
-        for rid, _ in layout:
-            if rid not in self.cache:
-                self.cache.admit(rid)
-        starts = [self.cache.length(rid) for rid, _ in layout]
-        self.cache.reserve([(rid, s + n) for (rid, n), s in zip(layout, starts)])
-        rids = [rid for rid, _ in layout]
-        tables = [self.cache.block_table_rows(rids, gi) for gi in range(len(self.cache.groups))]
-        entries = [StepEntry(rid, [0] * n, []) for rid, n in layout]
-        meta = pack_step(entries, starts, [self.cache.slot(r) for r in rids], tables, self.runtime.device)
-        harness, rt = self, self.runtime
-        self._pending = [(rid, s + n) for (rid, n), s in zip(layout, starts)]
-
-        class Ctx:
-            pass
-        ctx = Ctx()
-        ctx.meta, ctx.device, ctx.dtype, ctx.ops = meta, rt.device, rt.dtype, rt.ops
-        ctx.workspace, ctx.status = rt.workspace, rt.status
-        ctx.step_cache = {}
-
-        def cache_view(run):
-            gi, j = harness.cache.group_of_cache[run.cache]
-            g = harness.cache.groups[gi]
-            return CacheView(g.k[j], g.v[j], meta.block_tables[gi], g.page_size)
-        ctx.cache_view = cache_view
-        ctx.state_view = lambda run: harness.states[run.cache]
-        return ctx
-
-    def commit(self) -> None:
-        for rid, n in self._pending:
-            self.cache.advance(rid, n)
-        self.runtime.check_status()
+def part_engine(dtype: str, hidden: int, *, block=None, final_norm=None, head=None, embedding=None, vocab: int = 32,
+                page_size: int = 8, n_pages: int = 64, max_requests: int = 4, seed: int = 0, sigma: float = 0.1,
+                norm_jitter: float = 0.2, **options):
+    """An engine around the parts under test (the rest of the model is filler):
+    returns (engine, the tensors it was bound with as float32/bfloat16-rounded CPU
+    tensors).  ``Engine.run_part`` then runs one part alone the way a step does."""
+    from kipp_b200.engine import Engine
+    from kipp_b200.models.spec import LayerRun, ModelSpec
+    from kipp_b200.parts import (AttentionMixer, NoPositionEncoding, OutputHead, PreNormBlock, RMSNorm,
+                                 SwiGLUFeedForward, TokenEmbedding)
+    from kipp_b200.weights import random_tensors
+    if block is None:
+        block = PreNormBlock(RMSNorm(hidden, 1e-5), AttentionMixer(hidden, 1, 1, 16, NoPositionEncoding()),
+                             RMSNorm(hidden, 1e-5), SwiGLUFeedForward(hidden, 16))
+    emb = embedding or TokenEmbedding(vocab, hidden)
+    spec = ModelSpec(config=None, hidden_size=hidden, vocab_size=vocab, embedding=emb,
+                     layers=[("model.layers.0.", block)], order=[LayerRun(0, 0)],
+                     final_norm=("model.norm.", final_norm or RMSNorm(hidden, 1e-5)),
+                     head=("lm_head.", head or OutputHead(vocab, hidden, tied_to="model.embed_tokens.weight")),
+                     embedding_prefix="model.embed_tokens.", max_positions=4096)
+    t = dict(random_tensors(spec.tensor_specs(), seed, sigma=sigma, norm_jitter=norm_jitter))
+    if dtype == "bfloat16":
+        # matrices are rounded to bfloat16 for the tensor cores; 1-D scales stay float32
+        t = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in t.items()}
+    eng = Engine(spec, t, dtype=dtype, page_size=page_size, cache_tokens=n_pages * page_size,
+                 max_requests=max_requests, max_batch_tokens=512, **options)
+    return eng, t
 
 
 def part_tol(dtype: str) -> dict:

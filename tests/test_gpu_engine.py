@@ -37,8 +37,8 @@ def test_long_decoding(name, dtype):
     assert_close(got, want[29:], dtype, f"{name} long decode")
     worst = max(nmse(got[i], want[29 + i]) for i in range(0, 301, 25))
     assert worst <= BOUND[dtype]
-    if dtype == "bfloat16":
-        assert eng.graph_replays == 300              # the decode steps ran as captured graphs
+    # the decode steps ran as captured graphs (a graph's first step runs directly and is then captured)
+    assert eng.graph_replays >= 290
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -201,42 +201,20 @@ def test_command_line(tmp_path):
     full = plain_logits("A", "float32", ids + generated)
     assert int(lines[1].split("\t")[1]) == int(full[-1].argmax())
     assert "KIPP_METRIC backend=cuda prefill_tokens=12" in proc.stderr and "decode_tokens=6" in proc.stderr
+    # two prompts of different lengths run beside one another through the same scheduler
+    other = random_tokens("A", 31, seed=6)
+    both = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kipp"), "--model", model_folder("A"),
+                           "--prompt-ids", ",".join(map(str, ids)), "--prompt-ids", ",".join(map(str, other)),
+                           "--decode", "5", "--dtype", "float32", "--chunk", "16", "--top", "0"],
+                          capture_output=True, text=True, timeout=300)
+    assert both.returncode == 0, both.stderr[-2000:]
+    got = [[int(t) for t in line.split("\t")[1].split()] for line in both.stdout.strip().splitlines()]
+    assert got == [greedy_plain("A", "float32", ids, 5)[0], greedy_plain("A", "float32", other, 5)[0]]
+    assert "prefill_tokens=43" in both.stderr and "decode_tokens=10" in both.stderr
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kipp"), "--model", model_folder("A"),
                           "--prompt-ids", "1,2", "--decode", "2", "--temperature", "0.5", "--top-p", "0"],
                          capture_output=True, text=True, timeout=300)
     assert bad.returncode == 2 and "top_p" in bad.stderr
-
-
-def test_decode_metadata_fast_path_equals_the_general_packing():
-    """pack_decode rewrites only what changes between decode steps of one shape;
-    the buffer must equal what pack_step builds from scratch."""
-    import numpy as np
-    from kipp_b200.engine.batch import StaticStep, StepEntry, pack_decode, pack_step, step_ints
-    dev = torch.device("cuda:0")
-    n, widths = 5, [8, 3]
-    ints = step_ints(n, n, n, n, 0, n, [n * w for w in widths])
-    rng = np.random.default_rng(0)
-
-    def random_step():
-        tokens = rng.integers(0, 1000, n).tolist()
-        starts = rng.integers(0, 3000, n).tolist()
-        slots = rng.permutation(16)[:n].tolist()
-        tables = [rng.integers(-1, 500, (n, w)).astype(np.int32) for w in widths]
-        return tokens, starts, slots, tables
-
-    fast, plain = StaticStep(ints, dev), StaticStep(ints, dev)
-    tokens, starts, slots, tables = random_step()
-    pack_step([StepEntry(i, [t], [0]) for i, t in enumerate(tokens)], starts, slots, tables, dev, static=fast)
-    for _ in range(4):
-        tokens, starts, slots, tables = random_step()
-        meta = pack_decode(fast, tokens, starts, slots, tables)
-        ref = pack_step([StepEntry(i, [t], [0]) for i, t in enumerate(tokens)], starts, slots, tables, dev,
-                        static=plain)
-        torch.cuda.synchronize()
-        assert torch.equal(fast.host, plain.host) and torch.equal(fast.device, plain.device)
-        assert meta.kv_lens == ref.kv_lens and meta.q_lens == ref.q_lens
-    with pytest.raises(ValueError):
-        pack_decode(fast, tokens[:-1], starts[:-1], slots[:-1], [t[:-1] for t in tables])
 
 
 def test_refuses_a_model_that_cannot_fit_before_uploading_anything():
@@ -244,11 +222,12 @@ def test_refuses_a_model_that_cannot_fit_before_uploading_anything():
     from kipp_b200.config import config_from_dict, load_preset
     from kipp_b200.engine import Engine
     cfg_dict, init = load_preset("qwen3-32b")
-    before = torch.cuda.memory_allocated()
+    torch.cuda.synchronize()
+    before = torch.cuda.mem_get_info()[0]
     with pytest.raises(MemoryError, match="device bytes"):
         Engine.from_config(config_from_dict(cfg_dict), init["seed"], dtype="bfloat16", page_size=16,
                            cache_tokens=4_000_000, max_requests=4)
-    assert torch.cuda.memory_allocated() == before
+    assert abs(torch.cuda.mem_get_info()[0] - before) < (64 << 20)      # nothing was uploaded
 
 
 def test_repeating_prompt_shapes_replay_a_graph_with_the_eager_results():
@@ -327,9 +306,9 @@ def test_decode_burst_gives_the_tokens_of_greedy_steps(dtype):
 def test_decode_burst_longer_than_its_ring(monkeypatch):
     """The tokens of a burst collect in a ring on the device that is read out when
     it is full: with a ring of 8 rows, 21 steps give the tokens of 21 single steps."""
-    from kipp_b200.engine import Engine, StepEntry, graphs
+    from kipp_b200.engine import Engine, StepEntry
     from kipp_b200.kernels import argmax_rows
-    monkeypatch.setattr(graphs, "BURST_RING_ROWS", 8)
+    monkeypatch.setenv("KIPP_B200_BURST_RING_ROWS", "8")
     folder = model_folder("A")
     opts = dict(dtype="bfloat16", page_size=16, cache_tokens=512, max_requests=4, max_batch_tokens=128)
     a, b = Engine.from_folder(folder, **opts), Engine.from_folder(folder, **opts)
@@ -370,3 +349,88 @@ def test_truncate_and_reset_continue_like_a_fresh_request(dtype):
     again = eng.step([StepEntry("s", first[:23] + other, [23, 52])], check=True)
     assert nmse(again, want) < 1e-12                        # the same kernels on the same tokens
     eng.cache.check()
+
+
+def test_equal_prompt_portions_without_a_wait_in_between():
+    """Six and more equal portions of one prompt, nothing wanted and nothing waited
+    for between them: from the third on they replay one captured graph, and the host
+    runs ahead of the device.  Each step's metadata must be the one it was packed
+    with (the host buffer of a graph is rewritten only after its copy was read)."""
+    from kipp_b200.engine import Engine, StepEntry
+    folder = model_folder("E")
+    opts = dict(dtype="bfloat16", page_size=16, cache_tokens=2048, max_requests=2, max_batch_tokens=256)
+    toks = random_tokens("E", 8 * 128 + 3, seed=77)
+    outs = []
+    for graphs in (True, False):
+        eng = Engine.from_folder(folder, cuda_graphs=graphs, **opts)
+        for k in range(8):
+            eng.step([StepEntry("p", toks[128 * k:128 * (k + 1)], [])])       # no sync, no check
+        outs.append(eng.step([StepEntry("p", toks[1024:], [0, 2])], check=True).cpu().clone())
+        if graphs:
+            assert eng.graph_replays >= 5
+    assert torch.equal(outs[0], outs[1])
+    assert_close(outs[0], plain_logits("E", "bfloat16", toks)[[1024, 1026]], "bfloat16", "after eight portions")
+
+
+def test_the_serving_kernels_ran_at_the_benchmark_head_size():
+    """Configuration E (128-wide heads): a portion of 64 tokens and more takes the
+    tcgen05 attention, decoded tokens the split-K kernel with the fused norm, rotation
+    and cache write, and decode steps replay a graph."""
+    from kipp_b200.engine import Engine, StepEntry
+    eng = Engine.from_folder(model_folder("E"), dtype="bfloat16", page_size=16, cache_tokens=1024, max_requests=4,
+                             max_batch_tokens=512)
+    toks = random_tokens("E", 210, seed=5)
+    eng.step([StepEntry("a", toks[:200], []), StepEntry("b", toks[:3], [])], check=True)
+    for t in toks[200:]:
+        eng.step([StepEntry("a", [t], [0]), StepEntry("b", [t], [0])])
+    eng.synchronize()
+    c = eng.info()["counters"]
+    assert c["tc_prefill_launches"] >= 2 and c["fused_decode_launches"] >= 2 and c["graph_replays"] >= 8
+
+
+def test_logit_rows_are_limited():
+    from kipp_b200.engine import Engine, StepEntry
+    eng = Engine.from_folder(model_folder("A"), dtype="float32", page_size=16, cache_tokens=256, max_requests=2,
+                             max_batch_tokens=128, max_logit_rows=4)
+    assert eng.info()["max_logit_rows"] == 4
+    with pytest.raises(ValueError, match="max_logit_rows"):
+        eng.step([StepEntry("a", [1, 2, 3, 4, 5, 6], [0, 1, 2, 3, 4])])
+    assert not eng.is_live("a")
+    assert eng.step([StepEntry("a", [1, 2, 3, 4, 5, 6], [0, 1, 2, 5])]).shape == (4, 256)
+
+
+def test_a_decoded_token_does_not_depend_on_its_neighbours_with_own_length_splits():
+    """With own_length_splits the keys per split of a decoded token come from its
+    own context alone: decoded alone or beside seven others of other lengths, its
+    bfloat16 logits are the same bits."""
+    from kipp_b200.engine import Engine, StepEntry
+    folder = model_folder("E")
+    opts = dict(dtype="bfloat16", page_size=16, cache_tokens=8192, max_requests=8, max_batch_tokens=2048,
+                own_length_splits=True)
+    lengths = [700, 30, 1500, 129, 64, 1023, 300, 5]
+    seqs = [random_tokens("E", n + 4, seed=200 + n) for n in lengths]
+    alone = Engine.from_folder(folder, **opts)
+    alone.step([StepEntry("x", seqs[0][:-4], [])])
+    rows_alone = [alone.step([StepEntry("x", [t], [0])], check=True).clone() for t in seqs[0][-4:]]
+    beside = Engine.from_folder(folder, **opts)
+    beside.step([StepEntry(i, s[:-4], []) for i, s in enumerate(seqs)])
+    for k in range(4):
+        out = beside.step([StepEntry(i, [s[len(s) - 4 + k]], [0]) for i, s in enumerate(seqs)], check=True)
+        assert torch.equal(out[0], rows_alone[k][0]), k
+    assert_close(rows_alone[-1][0].cpu(), plain_logits("E", "bfloat16", seqs[0])[-1], "bfloat16")
+
+
+def test_status_words_are_all_read():
+    """A kernel that refused an access or gave up a bounded wait leaves a word in the
+    engine's status buffer; every word is read and turned into an error."""
+    import json
+    from kipp_b200.engine import Engine, StepEntry
+    from kipp_b200.native import KernelError
+    eng = Engine.from_folder(model_folder("A"), dtype="bfloat16", page_size=16, cache_tokens=256, max_requests=2,
+                             max_batch_tokens=128)
+    eng.step([StepEntry("a", [1, 2, 3], [2])], check=True)
+    for word, needle in ((0, "refused"), (1, "bounded wait"), (2, "bounded wait")):
+        eng._debug_set_status(word, 2 if word == 0 else 1)
+        with pytest.raises(KernelError, match=needle):
+            eng.synchronize()
+        eng.synchronize()                                  # the words were cleared

@@ -1,43 +1,47 @@
 """Each part alone against the plain functions, at sizes that are not the
-engine's test configurations."""
-import math
-
+engine's test configurations.  A part is run the way a step runs it
+(``Engine.run_part``: the same reservation and metadata, then only that part's
+forward pass) inside a model whose other parts are filler."""
 import pytest
 import torch
 
 import plain_qwen3 as P
-from gpu_util import PartHarness, part_tol
-from kipp_b200.models.spec import LayerRun
+from gpu_util import part_engine, part_tol
 from kipp_b200.parts import (AttentionMixer, NoPositionEncoding, OutputHead, PagedKVSpec, PreNormBlock,
                              RMSNorm, RotaryEncoding, SwiGLUFeedForward, TokenEmbedding)
-from kipp_b200.weights import random_tensors
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-
-
-def weights_for(part, prefix, dtype, seed=0, sigma=0.1):
-    t = dict(random_tensors(part.tensor_specs(prefix), seed, sigma=sigma, norm_jitter=0.2))
-    if dtype == "bfloat16":
-        t = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in t.items()}
-    return t
+DEV = "cuda:0"
 
 
 def rounding(dtype):
     return P.bf16_round if dtype == "bfloat16" else P.no_round
 
 
+def torch_dtype(dtype):
+    return torch.bfloat16 if dtype == "bfloat16" else torch.float32
+
+
+def filler(hidden):
+    return (AttentionMixer(hidden, 1, 1, 16, NoPositionEncoding()), RMSNorm(hidden, 1e-5),
+            SwiGLUFeedForward(hidden, 16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_rmsnorm_part(dtype):
-    h = PartHarness(dtype, {})
-    norm = RMSNorm(200, 3e-5)
-    w = weights_for(norm, "n.", dtype)
-    norm.bind(w, "n.", h.runtime)
-    ctx = h.context([("a", 6)])
-    x = torch.randn(6, 200, device="cuda:0") * 2
-    out = norm.forward(ctx, x)
-    assert out.dtype == h.runtime.dtype
-    assert torch.allclose(out.double().cpu(), P.plain_rmsnorm(x.cpu(), w["n.weight"], 3e-5), **part_tol(dtype))
+    mixer, norm2, ffn = filler(200)
+    eng, w = part_engine(dtype, 200, block=PreNormBlock(RMSNorm(200, 3e-5), mixer, norm2, ffn))
+    x = torch.randn(6, 200, device=DEV) * 2
+    out = torch.empty(6, 200, dtype=torch_dtype(dtype), device=DEV)
+    eng.run_part([("a", [0] * 6, [])], 0, "input_norm", residual=x, output=out)
+    want = P.plain_rmsnorm(x.cpu(), w["model.layers.0.input_layernorm.weight"], 3e-5)
+    assert torch.allclose(out.double().cpu(), want, **part_tol(dtype))
+    # the final norm gathers the wanted rows
+    out2 = torch.empty(2, 200, dtype=torch_dtype(dtype), device=DEV)
+    eng.run_part([("b", [0] * 6, [1, 4])], 0, "final_norm", residual=x, output=out2)
+    want2 = P.plain_rmsnorm(x.cpu()[[1, 4]], w["model.norm.weight"], 1e-5)
+    assert torch.allclose(out2.double().cpu(), want2, **part_tol(dtype))
 
 
 def test_rotary_frequencies_and_none():
@@ -50,49 +54,43 @@ def test_rotary_frequencies_and_none():
     with pytest.raises(ValueError):
         RotaryEncoding(64, 1e4, rotary_dim=70)
     none = NoPositionEncoding()
-    assert none.rotary_dim == 0 and none.inv_freq("cuda:0") is None
+    assert none.rotary_dim == 0 and none.frequencies() is None
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_embedding_and_heads(dtype):
-    h = PartHarness(dtype, {})
-    emb = TokenEmbedding(333, 40)
-    w = weights_for(emb, "model.embed_tokens.", dtype, sigma=1.0)
-    emb.bind(w, "model.embed_tokens.", h.runtime)
-    ctx = h.context([("a", 5)])
-    ids = torch.tensor([0, 332, 7, 7, 100], dtype=torch.int32, device="cuda:0")
-    ctx.meta.token_ids = ids
-    x = emb.forward(ctx)
-    assert x.dtype == torch.float32
-    assert torch.equal(x.cpu(), w["model.embed_tokens.weight"][ids.cpu().long()])
-    hidden = torch.randn(3, 40, device="cuda:0").to(h.runtime.dtype)
-    tied = OutputHead(333, 40, tied_to=emb)
-    assert [s.optional for s in tied.tensor_specs("lm_head.")] == [True]
-    tied.bind({}, "lm_head.", h.runtime)
-    logits = tied.forward(ctx, hidden, 3)
+    eng, w = part_engine(dtype, 40, vocab=333, sigma=1.0)
+    ids = [0, 332, 7, 7, 100]
+    x = torch.zeros(5, 40, device=DEV)
+    eng.run_part([("a", ids, [])], 0, "embedding", residual=x)
+    assert torch.equal(x.cpu(), w["model.embed_tokens.weight"][ids])
+    hidden = torch.randn(3, 40, device=DEV).to(torch_dtype(dtype))
+    assert [s.optional for s in OutputHead(333, 40, tied_to="model.embed_tokens.weight").tensor_specs("lm_head.")] \
+        == [True]
+    logits = torch.empty(3, 333, device=DEV)
+    eng.run_part([("b", [1, 2, 3], [0, 1, 2])], 0, "head", input=hidden, output=logits)
     ref = P.plain_linear(hidden.float().cpu(), w["model.embed_tokens.weight"])
-    assert logits.dtype == torch.float32 and torch.allclose(logits.double().cpu(), ref, **part_tol(dtype))
-    own = OutputHead(77, 40)
-    wo = weights_for(own, "lm_head.", dtype, seed=3)
-    own.bind(wo, "lm_head.", h.runtime)
-    logits = own.forward(ctx, hidden, 3)
-    assert torch.allclose(logits.double().cpu(), P.plain_linear(hidden.float().cpu(), wo["lm_head.weight"]),
+    assert torch.allclose(logits.double().cpu(), ref, **part_tol(dtype))
+    # a head of its own
+    eng2, w2 = part_engine(dtype, 40, vocab=77, head=OutputHead(77, 40), seed=3)
+    logits = torch.empty(3, 77, device=DEV)
+    eng2.run_part([("b", [1, 2, 3], [0, 1, 2])], 0, "head", input=hidden, output=logits)
+    assert torch.allclose(logits.double().cpu(), P.plain_linear(hidden.float().cpu(), w2["lm_head.weight"]),
                           **part_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_feed_forward_part_adds_to_the_residual(dtype):
-    h = PartHarness(dtype, {})
-    ffn = SwiGLUFeedForward(72, 200)
-    w = weights_for(ffn, "mlp.", dtype, sigma=0.2)
-    ffn.bind(w, "mlp.", h.runtime)
-    ctx = h.context([("a", 9)])
-    hid = torch.randn(9, 72, device="cuda:0").to(h.runtime.dtype)
-    res = torch.randn(9, 72, device="cuda:0")
-    want = res.double().cpu() + P.plain_feed_forward(hid.float().cpu(), w["mlp.gate_proj.weight"],
-                                                     w["mlp.up_proj.weight"], w["mlp.down_proj.weight"],
+    mixer, norm2, _ = filler(72)
+    eng, w = part_engine(dtype, 72, sigma=0.2,
+                         block=PreNormBlock(RMSNorm(72, 1e-5), mixer, norm2, SwiGLUFeedForward(72, 200)))
+    hid = torch.randn(9, 72, device=DEV).to(torch_dtype(dtype))
+    res = torch.randn(9, 72, device=DEV)
+    pre = "model.layers.0.mlp."
+    want = res.double().cpu() + P.plain_feed_forward(hid.float().cpu(), w[pre + "gate_proj.weight"],
+                                                     w[pre + "up_proj.weight"], w[pre + "down_proj.weight"],
                                                      rounding(dtype))
-    ffn.forward(ctx, hid, res)
+    eng.run_part([("a", [0] * 9, [])], 0, "feed_forward", input=hid, residual=res)
     assert torch.allclose(res.double().cpu(), want, **part_tol(dtype))
 
 
@@ -122,23 +120,20 @@ def test_attention_mixer_alone_in_two_steps(case, dtype):
     pos = RotaryEncoding(c["D"], 7e4, rotary_dim=c["rot"]) if c["rot"] else NoPositionEncoding()
     mixer = AttentionMixer(c["hidden"], c["n_q"], c["n_kv"], c["D"], pos, qk_norm_eps=c["eps"],
                            window=c["window"])
-    spec = mixer.cache_spec()
-    assert spec == PagedKVSpec(c["n_kv"], c["D"], c["window"])
-    h = PartHarness(dtype, {5: spec}, page_size=8, n_pages=32)
-    w = weights_for(mixer, "attn.", dtype, sigma=0.15)
-    mixer.bind(w, "attn.", h.runtime)
-    run = LayerRun(layer=0, cache=5)
+    assert mixer.cache_spec() == PagedKVSpec(c["n_kv"], c["D"], c["window"])
+    _, norm2, ffn = filler(c["hidden"])
+    eng, w = part_engine(dtype, c["hidden"], sigma=0.15, page_size=8, n_pages=32,
+                         block=PreNormBlock(RMSNorm(c["hidden"], 1e-5), mixer, norm2, ffn))
     total = 45
-    hid = torch.randn(total, c["hidden"]).to(h.runtime.dtype)
-    want = plain_mixer(hid.float(), w, "attn.", c["n_q"], c["n_kv"], c["D"], list(range(total)), 7e4,
-                       c["eps"], c["window"], c["rot"], rounding(dtype))
+    hid = torch.randn(total, c["hidden"]).to(torch_dtype(dtype))
+    want = plain_mixer(hid.float(), w, "model.layers.0.self_attn.", c["n_q"], c["n_kv"], c["D"], list(range(total)),
+                       7e4, c["eps"], c["window"], c["rot"], rounding(dtype))
     got = []
     for a, b in ((0, 30), (30, 32), (32, 33), (33, 45)):          # a portion, two tokens, one, a portion
-        ctx = h.context([("r", b - a)])
-        res = torch.zeros(b - a, c["hidden"], device="cuda:0")
-        mixer.forward(ctx, run, hid[a:b].to("cuda:0"), res)
-        h.commit()
+        res = torch.zeros(b - a, c["hidden"], device=DEV)
+        eng.run_part([("r", [0] * (b - a), [])], 0, "mixer", input=hid[a:b].to(DEV).contiguous(), residual=res)
         got.append(res.cpu())
+    assert eng.length("r") == total
     assert torch.allclose(torch.cat(got).double(), want, **part_tol(dtype))
 
 
@@ -148,14 +143,10 @@ def test_block_alone(dtype):
                intermediate_size=144, rms_norm_eps=1e-5, rope_theta=3e4)
     mixer = AttentionMixer(80, 5, 5, 16, RotaryEncoding(16, 3e4), qk_norm_eps=1e-5)
     block = PreNormBlock(RMSNorm(80, 1e-5), mixer, RMSNorm(80, 1e-5), SwiGLUFeedForward(80, 144))
-    h = PartHarness(dtype, {0: mixer.cache_spec()}, page_size=4, n_pages=32)
-    w = weights_for(block, "model.layers.0.", dtype, sigma=0.12)
-    assert len(w) == 11
-    block.bind(w, "model.layers.0.", h.runtime)
+    assert len(block.tensor_specs("model.layers.0.")) == 11
+    eng, w = part_engine(dtype, 80, sigma=0.12, page_size=4, n_pages=32, block=block)
     x = torch.randn(23, 80)
     want = P.plain_block(x.double(), cfg, w, "model.layers.0.", 0, rounding(dtype))
-    ctx = h.context([("r", 23)])
-    xd = x.to("cuda:0")
-    block.forward(ctx, LayerRun(0, 0), xd)
-    h.commit()
+    xd = x.to(DEV)
+    eng.run_part([("r", [0] * 23, [])], 0, "block", residual=xd)
     assert torch.allclose(xd.double().cpu(), want, **part_tol(dtype))

@@ -86,8 +86,9 @@ def _register():
         return ModelSpec(config=c, hidden_size=c.hidden_size, vocab_size=c.vocab_size, embedding=emb,
                          layers=layers, order=order,
                          final_norm=("model.norm.", RMSNorm(c.hidden_size, c.rms_norm_eps)),
-                         head=("lm_head.", OutputHead(c.vocab_size, c.hidden_size, tied_to=emb)),
-                         max_positions=256)
+                         head=("lm_head.", OutputHead(c.vocab_size, c.hidden_size,
+                                                      tied_to="model.embed_tokens.weight")),
+                         embedding_prefix="model.embed_tokens.", max_positions=256)
 
     unregister_architecture("ToyStateLM")
     register_architecture("ToyStateLM", ToyConfig, build)
@@ -197,6 +198,35 @@ def test_toy_architecture_with_state_repeated_layer_and_shared_cache(tmp_path, s
         unregister_architecture("ToyStateLM")
 
 
+def test_state_mixer_in_bfloat16_with_graphs_asked_for(tmp_path):
+    """A part defined in Python is not captured in CUDA graphs (it does not say it
+    may be): with graphs switched on the engine runs such a model's decode steps as
+    plain launches, and the state of a request advances once per step."""
+    ToyConfig = _register()
+    from kipp_b200.config import unregister_architecture
+    from kipp_b200.engine import Engine, StepEntry
+    from kipp_b200.weights import write_random_model
+    from tiny import read_weights
+    try:
+        cfg = ToyConfig(architecture="ToyStateLM")
+        folder = write_random_model(str(tmp_path / "toy16"), cfg, seed=5, sigma=0.2)
+        w = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in read_weights(folder).items()}
+        eng = Engine.from_folder(folder, dtype="bfloat16", page_size=4, cache_tokens=96, max_requests=3,
+                                 cuda_graphs=True)
+        assert not eng.cuda_graphs and eng.info()["cuda_graphs"] is False
+        g = torch.Generator().manual_seed(1)
+        seq = torch.randint(0, cfg.vocab_size, (30,), generator=g).tolist()
+        want = plain_toy(cfg, w, seq, False)
+        rows = [eng.step([StepEntry("a", seq[:12], [11])], check=True).cpu().clone()]
+        for t in seq[12:]:                                    # decode steps: each advances the state once
+            rows.append(eng.step([StepEntry("a", [t], [0])], check=True).cpu().clone())
+        got = torch.cat(rows)
+        assert nmse(got, want[11:]) < 2e-3                    # bfloat16 activations against a float64 model
+        assert eng.graph_replays == 0
+    finally:
+        unregister_architecture("ToyStateLM")
+
+
 # ---------------------------------------------------------------------------------------
 # A feed-forward with routing, a rotation of another kind and a position encoding that is
 # not a rotation at all: toy parts again, defined here, beside the framework's attention.
@@ -204,8 +234,8 @@ def _register_routed():
     from kipp_b200.config import register_architecture, unregister_architecture
     from kipp_b200.config.base import ModelConfig
     from kipp_b200.models.spec import LayerRun, ModelSpec
-    from kipp_b200.parts import (AttentionMixer, FeedForward, NoPositionEncoding, OutputHead, PositionEncoding,
-                                 PreNormBlock, RMSNorm, SwiGLUFeedForward, TokenEmbedding)
+    from kipp_b200.parts import (AttentionMixer, EmbeddingStage, FeedForward, NoPositionEncoding, OutputHead,
+                                 PositionEncoding, PreNormBlock, RMSNorm, SwiGLUFeedForward, TokenEmbedding)
     from kipp_b200.weights import TensorSpec
 
     @dataclasses.dataclass(frozen=True)
@@ -261,7 +291,6 @@ def _register_routed():
 
         def __init__(self, rotary_dim, theta, scale):
             self.rotary_dim, self.theta, self.scale = rotary_dim, theta, scale
-            self._dev = {}
 
         def frequencies(self):
             i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
@@ -270,34 +299,26 @@ def _register_routed():
         def table_key(self):
             return ("toy-scaled", self.theta, self.rotary_dim, self.scale)
 
-        def inv_freq(self, device):
-            if str(device) not in self._dev:
-                self._dev[str(device)] = self.frequencies().to(device)
-            return self._dev[str(device)]
+    class LearnedPositions(EmbeddingStage):
+        """x_t += P[position_t]: positions enter at the bottom, after the token
+        embedding and not in the mixer."""
 
-    class LearnedPositionEmbedding(TokenEmbedding):
-        """x_t = E[id_t] + P[position_t]: positions enter at the bottom, not in the mixer."""
-
-        def __init__(self, vocab, hidden, max_positions):
-            super().__init__(vocab, hidden)
-            self.max_positions = max_positions
+        def __init__(self, hidden, max_positions):
+            self.hidden_size, self.max_positions = hidden, max_positions
 
         def tensor_specs(self, prefix):
-            return super().tensor_specs(prefix) + [
-                TensorSpec("model.embed_positions.weight", (self.max_positions, self.hidden_size))]
+            return [TensorSpec(prefix + "weight", (self.max_positions, self.hidden_size))]
 
         def bind(self, tensors, prefix, runtime):
-            super().bind(tensors, prefix, runtime)
-            self.positions = tensors["model.embed_positions.weight"].to(runtime.device).float()
+            self.positions = tensors[prefix + "weight"].to(runtime.device).float()
 
-        def forward(self, ctx):
-            x = super().forward(ctx)
+        def forward(self, ctx, x):
             T = ctx.meta.tokens
             x[:T] += self.positions[ctx.meta.positions[:T].long()]
-            return x
 
     def build(c):
-        emb = LearnedPositionEmbedding(c.vocab_size, c.hidden_size, c.max_positions)
+        emb = [("model.embed_tokens.", TokenEmbedding(c.vocab_size, c.hidden_size)),
+               ("model.embed_positions.", LearnedPositions(c.hidden_size, c.max_positions))]
         norm = lambda: RMSNorm(c.hidden_size, c.rms_norm_eps)
         rotary = ScaledPartialRotary(c.rotary_dim, c.rope_theta, c.rope_scale)
         layers = [
@@ -311,7 +332,8 @@ def _register_routed():
         return ModelSpec(config=c, hidden_size=c.hidden_size, vocab_size=c.vocab_size, embedding=emb,
                          layers=layers, order=[LayerRun(0, cache=0), LayerRun(1, cache=1)],
                          final_norm=("model.norm.", norm()),
-                         head=("lm_head.", OutputHead(c.vocab_size, c.hidden_size, tied_to=emb)),
+                         head=("lm_head.", OutputHead(c.vocab_size, c.hidden_size,
+                                                      tied_to="model.embed_tokens.weight")),
                          max_positions=c.max_positions)
 
     unregister_architecture("ToyRoutedLM")

@@ -7,7 +7,7 @@ process whose memory is fixed and given out at start-up).  For them the scratch
 is a fixed array inside the library.  This test calls that entry point through
 its exported C symbol, twice in a row on different inputs, and checks each
 result against the ordinary entry point, which takes its scratch from the
-caller.  The file sorts last so that a run that stops at the first failure has
+caller, and against a plain float64 attention.  The file sorts last so that a run that stops at the first failure has
 run everything else before.
 """
 import ctypes
@@ -25,7 +25,8 @@ MAX_SPLITS = 32
 def make_case(seed, n_q, n_kv, D, page, contexts):
     """Single decoded tokens with ``contexts`` cached tokens each, pages taken
     from a shuffled pool."""
-    from kipp_b200.engine.batch import StepEntry, pack_step
+    from gpu_util import pack_meta as pack_step
+    from kipp_b200.engine.batch import StepEntry
     g = torch.Generator().manual_seed(seed)
     entries = [StepEntry(i, [0], []) for i in range(len(contexts))]
     need = [-(-(c + 1) // page) for c in contexts]
@@ -41,7 +42,13 @@ def make_case(seed, n_q, n_kv, D, page, contexts):
     q = torch.randn(len(contexts), n_q, D, generator=g).to(torch.bfloat16).to(DEV)
     kp = torch.randn(n_pages, n_kv, page, D, generator=g).to(torch.bfloat16).to(DEV)
     vp = torch.randn(n_pages, n_kv, page, D, generator=g).to(torch.bfloat16).to(DEV)
-    return meta, q, kp, vp
+    return meta, q, kp, vp, table
+
+
+def plain_attention_of(meta, table, q, kp, vp, contexts, page, window, D):
+    """Softmax attention of every decoded token over its own keys, in float64."""
+    from test_gpu_kernels import attention_ref
+    return attention_ref(meta, table, q, kp, vp, [(c, 1) for c in contexts], page, window, 1 / math.sqrt(D))
 
 
 def reference_entry(meta, q, kp, vp, n_q, n_kv, D, page, window):
@@ -82,7 +89,7 @@ def test_two_calls_in_a_row_match_the_entry_point_that_is_given_scratch():
     before = torch.cuda.memory_allocated(DEV)
     results = []
     for seed, contexts, window in ((1, [700, 15, 16, 255, 1023], None), (2, [40, 900, 333], 100)):
-        meta, q, kp, vp = make_case(seed, n_q, n_kv, D, page, contexts)
+        meta, q, kp, vp, table = make_case(seed, n_q, n_kv, D, page, contexts)
         want = reference_entry(meta, q, kp, vp, n_q, n_kv, D, page, window)
         held = torch.cuda.memory_allocated(DEV)
         rc, got = call_noalloc(fn, meta, q, kp, vp, n_q, n_kv, D, page, window)
@@ -92,6 +99,9 @@ def test_two_calls_in_a_row_match_the_entry_point_that_is_given_scratch():
         assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert torch.equal(got, want)
         assert float(got.float().abs().sum()) > 0
+        # and it is the attention of these queries over these pages, whatever the other entry point says
+        plain = plain_attention_of(meta, table, q, kp, vp, contexts, page, window, D)
+        assert torch.allclose(got.double().cpu(), plain, rtol=2e-2, atol=2e-2)
         # torch allocated only this test's own output tensor around the call
         assert torch.cuda.memory_allocated(DEV) - held <= got.numel() * 2 + 512
         results.append(got)
@@ -99,6 +109,6 @@ def test_two_calls_in_a_row_match_the_entry_point_that_is_given_scratch():
     # sizes beyond the built-in scratch are refused before anything runs
     assert need(8, n_q, D, MAX_SPLITS) == 8 * n_q * MAX_SPLITS * (D + 2) * 4
     assert need(4096, 64, 128, MAX_SPLITS) > (16 << 20)
-    meta, q, kp, vp = make_case(3, 64, 2, 128, page, [10] * 40)
+    meta, q, kp, vp, _ = make_case(3, 64, 2, 128, page, [10] * 40)
     rc, out = call_noalloc(fn, meta, q, kp, vp, 64, 2, 128, page, None)
     assert rc == -4 and float(out.float().abs().sum()) == 0.0
