@@ -272,7 +272,7 @@ def compile_host_library(name: str = ENGINE_LIBRARY, *, verbose: bool = True) ->
 
 
 _resolver_keepalive = None
-_resolved_paths: dict[str, bytes] = {}
+_resolved_paths: dict = {}
 
 
 def load_host_library(name: str = ENGINE_LIBRARY) -> ctypes.CDLL:
@@ -290,13 +290,14 @@ def load_host_library(name: str = ENGINE_LIBRARY) -> ctypes.CDLL:
         if lib is None:
             lib = ctypes.CDLL(path)
 
-            @ctypes.CFUNCTYPE(ctypes.c_char_p, ctypes.c_char_p)
+            @ctypes.CFUNCTYPE(ctypes.c_void_p, ctypes.c_char_p)
             def resolve(kernel_library):
+                # returns the address of a path that stays alive in _resolved_paths
                 try:
                     text = kernel_library.decode()
                     if text not in _resolved_paths:
-                        _resolved_paths[text] = compile_library(text).encode()
-                    return _resolved_paths[text]
+                        _resolved_paths[text] = ctypes.create_string_buffer(compile_library(text).encode())
+                    return ctypes.addressof(_resolved_paths[text])
                 except Exception as e:          # the core reports the missing library
                     print(f"[kipp_b200] {e}", file=sys.stderr, flush=True)
                     return None

@@ -374,6 +374,36 @@ __global__ void burst_advance_kernel(int* tokens, int* positions, int* context_l
 }
 }  // namespace
 
+extern "C" int kipp_argmax_rows(const float* logits, long long ld, int rows, int n, int* out,
+                                void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0) return KIPP_ERR_ARG;
+    return kipp_launch(argmax_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n, out);
+}
+
+extern "C" int kipp_sample_rows(const float* logits, long long ld, int rows, int n,
+                                const float* temperature, const int* top_k, const float* top_p,
+                                const float* min_p, const double* uniform, int* out, void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0) return KIPP_ERR_ARG;
+    return kipp_launch(sample_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n,
+                       temperature, top_k, top_p, min_p, uniform, out);
+}
+
+extern "C" int kipp_apply_penalties(float* logits, long long ld, int rows, int n, const int* recent,
+                                    int recent_width, const int* recent_count,
+                                    const float* repetition, const float* presence,
+                                    const float* frequency, const int* bias_tokens,
+                                    const float* bias_values, int bias_width, const int* bias_count,
+                                    void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0) return KIPP_ERR_ARG;
+    return kipp_launch(apply_penalties_kernel, dim3(rows), dim3(64), 0, (cudaStream_t)stream, 1, logits, ld, n,
+                       recent, recent_width, recent_count, repetition, presence, frequency, bias_tokens,
+                       bias_values, bias_width, bias_count);
+}
+
+// See burst_advance_kernel.  `next` holds the n tokens just chosen.
 extern "C" int kipp_burst_advance(int* tokens, int* positions, int* context_len, const int* next, int* ring,
                                   int* counter, int n, int ring_rows, void* stream) {
     if (n <= 0) return 0;
