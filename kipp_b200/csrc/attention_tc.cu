@@ -43,6 +43,7 @@
 // Sizes: head_dim 64 or 128; page size 8, 16, 32 or a multiple of 64.  Cache
 // layout of a layer: [page][kv_head][slot][D].
 #include "common.cuh"
+#include "mbarrier.cuh"
 #include <cuda.h>
 #include <math.h>
 #include <mutex>
@@ -54,7 +55,6 @@ constexpr int BN = 64;             // keys per tile
 constexpr float RESCALE_SLACK = 8.f;   // log2 of the largest weight a stale running maximum may give
 constexpr int SOFTMAX_THREADS = 256;  // two threads per query row: each half of a tile's keys
 constexpr int THREADS = 320;          // + the TMA warp and the MMA warp
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // ~1 s: a wait that long has failed
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -68,25 +68,10 @@ __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) { return kipp_mbar_try_wait(bar, parity); }
+// bounded in time (mbarrier.cuh): false when the wait ran out or another thread of the CTA gave up
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    // Bounded by time, not by polls (a poll may itself block for a while): about
-    // a second of SM clocks, or at once when another thread of the CTA gave up.
-    const long long t0 = clock64();
-    for (unsigned i = 0;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
-        }
-    }
-    *abort_flag = 1;
-    return false;
+    return kipp_mbar_wait_limited(bar, parity, abort_flag, KIPP_WAIT_LIMIT_CYCLES);
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");

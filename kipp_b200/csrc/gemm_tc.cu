@@ -42,6 +42,7 @@
 //
 // No multicast: every CTA fetches its own tiles.
 #include "common.cuh"
+#include "mbarrier.cuh"
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -56,7 +57,6 @@ constexpr int UMMA_M = 128;          // features per accumulator = MMA M (a CTA 
 constexpr int TILE_K = 64;           // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 320;         // TMA warp, MMA warp, 8 epilogue warps
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;   // ~1 s: a wait that long has failed
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -72,30 +72,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) { return kipp_mbar_try_wait(bar, parity); }
+// bounded in time (mbarrier.cuh): false when the wait ran out or another thread of the CTA gave up
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    // Bounded by time, not by polls (a poll may itself block for a while): about
-    // a second of SM clocks, or at once when another thread of the CTA gave up.
-    const long long t0 = clock64();
-    for (unsigned i = 0;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
-        }
-    }
-    *abort_flag = 1;
-    return false;
+    return kipp_mbar_wait_limited(bar, parity, abort_flag, KIPP_WAIT_LIMIT_CYCLES);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(

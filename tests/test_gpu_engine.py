@@ -434,3 +434,56 @@ def test_status_words_are_all_read():
         with pytest.raises(KernelError, match=needle):
             eng.synchronize()
         eng.synchronize()                                  # the words were cleared
+
+
+def test_engine_in_32_bit_against_the_reference_oracle_with_rounded_keys_and_values():
+    """The engine's own float32 logits (not only the plain model's) against the
+    reference's CPU oracle at the smallest shape its registry takes, on the same
+    random weights: with kv_round_bf16 the 32-bit cache keeps keys and values
+    rounded to bfloat16, the reference's storage contract (src/kipp.c:2806-2811).
+    The prompt goes in as a portion and then token by token."""
+    import importlib.util
+    import json
+    import os
+    from kipp_b200.config import config_from_dict
+    from kipp_b200.engine import Engine, StepEntry
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(golden, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    with open(os.path.join(golden, "model_06b.json")) as f:
+        gold = json.load(f)
+    m = gold["shape"]
+    cfg = config_from_dict(dict(
+        architectures=["Qwen3ForCausalLM"], num_hidden_layers=m["L"], hidden_size=m["H"],
+        num_attention_heads=m["NH"], num_key_value_heads=m["KV"], head_dim=m["HD"], intermediate_size=m["F"],
+        vocab_size=m["V"], rope_theta=m["theta"], rms_norm_eps=m["eps"], tie_word_embeddings=True,
+        max_position_embeddings=256))
+    names = {name: (i, shape) for i, (name, shape) in enumerate(mg.model_tensors())}
+
+    class Weights:                                     # one tensor at a time: the model is 2.4 GB in float32
+        def get(self, name, default=None):
+            if name not in names:
+                return default
+            i, shape = names[name]
+            return mg.model_tensor(i, shape)
+
+    from kipp_b200.models.spec import ModelSpec
+    eng = Engine(ModelSpec.from_library(cfg), Weights(), dtype="float32", page_size=16, cache_tokens=64,
+                 max_requests=1, max_batch_tokens=64, kv_round_bf16=True)
+    toks = gold["tokens"]
+    head = len(toks) // 2
+    rows = [eng.step([StepEntry("g", toks[:head], list(range(head)))], check=True).cpu().clone()]
+    for t in toks[head:]:
+        rows.append(eng.step([StepEntry("g", [t], [0])], check=True).cpu().clone())
+    logits = torch.cat(rows).double()
+    idx = torch.tensor(gold["indices"])
+    for pos, row in enumerate(gold["positions"]):
+        assert int(logits[pos].argmax()) == row["argmax"], pos
+        got, want = logits[pos][idx], torch.tensor(row["sample"], dtype=torch.float64)
+        assert float(((got - want) ** 2).sum() / (want ** 2).sum()) < 5e-5, pos     # the reference's own bound
+    # without the rounding the cache holds more bits than the reference's: the logits move
+    plain = Engine(ModelSpec.from_library(cfg), Weights(), dtype="float32", page_size=16, cache_tokens=64,
+                   max_requests=1, max_batch_tokens=64)
+    other = plain.step([StepEntry("g", toks, [len(toks) - 1])], check=True).cpu().double()
+    assert 0 < nmse(other[0], logits[-1]) < 1e-3

@@ -599,3 +599,23 @@ def test_decode_attention_fused_with_norm_rotation_and_cache_write(case):
                                  page, nq, nkv, D, 1 / math.sqrt(D), window, st)
     assert torch.equal(k3, k1) and torch.equal(v3, v1)
     assert torch.allclose(got3.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_a_bounded_wait_runs_out_and_reports():
+    """The give-up branch of the mbarrier wait every tensor-core kernel uses
+    (csrc/mbarrier.cuh), run by a probe kernel on a barrier nothing arrives at, with
+    a limit of some ten microseconds: the kernel returns by itself, the status word
+    the engine reads is set, and the wait lasted as long as its limit."""
+    import ctypes
+    from kipp_b200.csrc.build import load_library
+    lib = load_library("wait_probe")
+    lib.kipp_wait_probe.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p]
+    lib.kipp_wait_probe.restype = ctypes.c_int
+    st = status()
+    waited = torch.zeros(1, dtype=torch.int64, device=DEV)
+    limit = 20_000
+    rc = lib.kipp_wait_probe(st.data_ptr(), waited.data_ptr(), limit, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert st.tolist() == [0, 1, 0, 0]
+    assert limit <= int(waited) < 200 * limit
