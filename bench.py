@@ -122,7 +122,8 @@ def reference_arm(args) -> int:
     except Exception as e:                                   # noqa: BLE001
         print(json.dumps({"impl": "reference", "unavailable": f"baseline/reference_arm.py cannot be imported: {e}"}))
         return 0
-    return ref.main(args, QWEN3_4B, WEIGHT_SEED, POINT_PROMPT, PREFILL_TOKENS)
+    config = QWEN3_4B if args.preset == "qwen3-4b" else load_preset(args.preset)[0]
+    return ref.main(args, dict(config), WEIGHT_SEED, POINT_PROMPT, PREFILL_TOKENS)
 
 
 def median_mad(values: list) -> tuple[float, float]:
