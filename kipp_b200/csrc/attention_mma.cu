@@ -443,7 +443,7 @@ attn_decode_kernel(const DecodeParams p) {
                 if (warp == 0) warp_norm_rope<D>(x, p.k_norm_w, p.norm_dtype, p.eps, cs_row, lane);
                 bf16* dst = (warp == 0 ? p.k_write : p.v_write) + at;
 #pragma unroll
-                for (int j = 0; j < NE; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(x[j]);
+                for (int j = 0; j < NE; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(cache_value(x[j]));
             }
             __threadfence();                                       // before this CTA gathers that page
         }

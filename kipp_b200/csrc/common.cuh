@@ -22,6 +22,22 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 // Round to nearest even, as the reference narrows (src/kipp.c:2181-2186).
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// What goes into the cache must be a finite number in the cache's type: kernels that read whole
+// tiles multiply masked keys and values by zero, and a page is handed from one request to the
+// next as it is, so one request's overflow must not leave an infinity or a NaN behind for the
+// next one.  A value that is not finite (or would round to an infinity in bfloat16) is stored as 0.
+__device__ __forceinline__ float cache_value(float v) { return fabsf(v) < 3.38e38f ? v : 0.f; }
+// the same for eight bfloat16 values in a 16-byte vector: lanes with all exponent bits set become 0
+__device__ __forceinline__ uint4 cache_values_bf16x8(uint4 v) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if ((w[i] & 0x7f800000u) == 0x7f800000u) w[i] &= 0x0000ffffu;
+        if ((w[i] & 0x00007f80u) == 0x00007f80u) w[i] &= 0xffff0000u;
+    }
+    return v;
+}
+
 // Loads an element of a weight vector stored either as float32 or bfloat16.
 __device__ __forceinline__ float load_w(const void* p, int dtype, size_t i) {
     return dtype == KIPP_DT_F32 ? reinterpret_cast<const float*>(p)[i]

@@ -46,6 +46,10 @@ __device__ __forceinline__ void store2(bf16* p, float a, float b) {
 __device__ __forceinline__ float stored(float v, bool round_bf16) {
     return round_bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : v;
 }
+// what a key or value element becomes in the cache: rounded if asked for, never an infinity or NaN
+__device__ __forceinline__ float stored(float v, bool round_bf16, bool into_cache) {
+    return into_cache ? cache_value(stored(v, round_bf16)) : v;
+}
 
 // V = elements a lane handles side by side (2 when head_dim is a multiple of 4:
 // 4- or 8-byte loads and stores; else 1).
@@ -68,7 +72,7 @@ __global__ void qk_norm_rope_write_kernel(
     const int h = warp_global % heads_total;
     const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
     if (!is_q && !(write_cache & 1)) return;
-    const bool rnd = !is_q && (write_cache & 2);
+    const bool rnd = !is_q && (write_cache & 2), kv = !is_q;
     const T* src = qkv + (size_t)t * ld_qkv + (size_t)h * head_dim;
     const int pos = positions[t];
 
@@ -93,10 +97,10 @@ __global__ void qk_norm_rope_write_kernel(
             for (int i = 2 * lane; i < head_dim; i += 64) {
                 float a, b;
                 load2(src + i, a, b);
-                store2(dst + i, stored(a, rnd), stored(b, rnd));
+                store2(dst + i, stored(a, rnd, true), stored(b, rnd, true));
             }
         } else {
-            for (int i = lane; i < head_dim; i += 32) dst[i] = from_f32<T>(stored(to_f32(src[i]), rnd));
+            for (int i = lane; i < head_dim; i += 32) dst[i] = from_f32<T>(stored(to_f32(src[i]), rnd, true));
         }
         return;
     }
@@ -162,11 +166,11 @@ __global__ void qk_norm_rope_write_kernel(
             const int i = V * (lane + 32 * j);
             if (i < half) {
                 if constexpr (V == 2) {
-                    store2(dst + i, stored(lo[j][0], rnd), stored(lo[j][1], rnd));
-                    store2(dst + i + half, stored(hi[j][0], rnd), stored(hi[j][1], rnd));
+                    store2(dst + i, stored(lo[j][0], rnd, kv), stored(lo[j][1], rnd, kv));
+                    store2(dst + i + half, stored(hi[j][0], rnd, kv), stored(hi[j][1], rnd, kv));
                 } else {
-                    dst[i] = from_f32<T>(stored(lo[j][0], rnd));
-                    dst[i + half] = from_f32<T>(stored(hi[j][0], rnd));
+                    dst[i] = from_f32<T>(stored(lo[j][0], rnd, kv));
+                    dst[i + half] = from_f32<T>(stored(hi[j][0], rnd, kv));
                 }
             }
         }
@@ -197,7 +201,7 @@ __global__ void qk_norm_rope_write_kernel(
             const float c = cs.x, s = cs.y;
             v = i < rh ? row[i] * c - row[i + rh] * s : row[i] * c + row[i - rh] * s;
         }
-        dst[i] = from_f32<T>(stored(v, rnd));
+        dst[i] = from_f32<T>(stored(v, rnd, kv));
     }
 }
 
@@ -263,7 +267,7 @@ qk_norm_rope_write_bf16_kernel(
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (active) raw = *reinterpret_cast<const uint4*>(qkv + (size_t)t * ld_qkv + (size_t)h * HEAD_DIM + sub * 8);
     if (valid && !is_q && !is_k) {                // values: copy
-        if (dst) *reinterpret_cast<uint4*>(dst) = raw;
+        if (dst) *reinterpret_cast<uint4*>(dst) = cache_values_bf16x8(raw);
         dst = nullptr;
     }
     // queries and keys.  No lane leaves early: a warp holds several heads, and
@@ -318,7 +322,7 @@ qk_norm_rope_write_bf16_kernel(
         __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
         for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-        *reinterpret_cast<uint4*>(dst) = out;
+        *reinterpret_cast<uint4*>(dst) = is_q ? out : cache_values_bf16x8(out);
     }
 }
 

@@ -237,6 +237,38 @@ def test_qk_norm_rope_write(case, dtype):
     assert float(kp2.float().abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D", [48, 128])
+def test_no_infinity_or_nan_reaches_the_cache(D, dtype):
+    """A page goes from one request to the next as it is, and kernels that read whole
+    tiles multiply masked keys and values by zero: so a key or value that is not
+    finite (an overflow in one request) is stored as 0, in both kernels that write
+    the cache."""
+    nq, nkv, page, T = 4, 2, 8, 5
+    g = torch.Generator().manual_seed(D)
+    entries = [StepEntry("a", [0] * T, [])]
+    meta = pack_step(entries, [0], [0], [np.arange(2, dtype=np.int32).reshape(1, 2)], torch.device(DEV))
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, generator=g).to(dtype)
+    k0, v0 = nq * D, (nq + nkv) * D
+    qkv[1, k0 + 3] = float("inf")              # a key element; with the norm the whole head turns NaN
+    qkv[2, v0 + 5] = float("nan")
+    qkv[3, v0 + D + 1] = float("-inf")
+    qkv = qkv.to(DEV)
+    kw = torch.ones(D, device=DEV)
+    kp = torch.zeros(2, nkv, page, D, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.zeros(T, nq, D, dtype=dtype, device=DEV)
+    st = status()
+    ops().qk_norm_rope_write(qkv, q_out, kp, vp, kw, kw, 1e-6, None, 0, meta.positions, meta.entry_of_token,
+                             meta.block_tables[0], page, T, nq, nkv, D, True, st)
+    torch.cuda.synchronize()
+    assert torch.isfinite(kp.float()).all() and torch.isfinite(vp.float()).all()
+    assert float(kp[0, 0, 1].float().abs().sum()) == 0.0           # the poisoned key head became zeros
+    assert float(vp[0, 0, 2, 5]) == 0.0 and float(vp[0, 1, 3, 1]) == 0.0
+    assert float(vp[0, 0, 2, 4]) == float(qkv[2, v0 + 4])          # its finite neighbours are kept
+    assert float(kp[0, 1, 1].float().abs().sum()) > 0              # and the other key head of that token
+
+
 # ------------------------------------------------------------------ attention
 def attention_case(seed, D, nq, nkv, page, layout, dtype, width=None, order="permuted"):
     """layout: list of (cached tokens, new tokens).  Random pages in a permuted
