@@ -143,7 +143,7 @@ inline std::vector<float> rotary_frequencies(int rotary_dim, double theta) {
 class AttentionPlanner : public WorkPlanner {
 public:
     static constexpr int TILE = 64;
-    static constexpr int MIN_SPLIT = 128;
+    static constexpr int MIN_SPLIT = 64;
     static constexpr int CTA_FIXED_TILES = 5;   // what a decode CTA costs beside its key tiles, in 64-key tiles
     static constexpr int CTAS_PER_SM = 3;
 

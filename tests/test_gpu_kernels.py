@@ -508,11 +508,11 @@ def test_burst_advance_moves_a_step_on():
         rows = dev(torch.arange(n).int())
         split = dev(torch.zeros(n + 3).int())
         for kv_heads, sms in ((8, 148), (2, 148), (1, 132)):
-            attention_bf16.decode_replan(split, context, rows, kv_heads, 3 * sms, 5, 128, 32, own_length=False)
+            attention_bf16.decode_replan(split, context, rows, kv_heads, 3 * sms, 5, 64, 32, own_length=False)
             want = split_length(n, longest + 2, kv_heads, sms)
             assert split[:n].cpu().tolist() == [want] * n, (n, longest, kv_heads)
             assert split[n:].eq(0).all()
-        attention_bf16.decode_replan(split, context, rows, 8, 444, 5, 128, 32, own_length=True)
+        attention_bf16.decode_replan(split, context, rows, 8, 444, 5, 64, 32, own_length=True)
         assert split[:n].cpu().tolist() == [split_length(1, int(x) + 2, own=True) for x in lens]
         # a full ring: the tokens are still handed over, no row is written
         counter.fill_(4)
