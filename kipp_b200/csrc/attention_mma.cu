@@ -731,13 +731,13 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
 
 // The keys per split of each decoded token, chosen on the device from the cached lengths
 // (context_len[rows[i]] + 1 keys), by the rule the host uses when it packs a step
-// (csrc/host/attention_plan.hpp): with own_length, an eighth of the token's own context
-// (so a token's result does not depend on its neighbours); else, for the whole step, the
-// number of splits with the best (share of the resident CTA slots that the waves fill) x
-// (share of a CTA's time spent on keys rather than on its fixed cost).  One block; used
-// between the steps of a burst that runs without the host.
+// (AttentionPlanner in csrc/host/parts.hpp): with own_length, an eighth of the token's own
+// context (so a token's result does not depend on its neighbours); else, for the whole step,
+// the number of 64-key tiles per split with the best (share of the resident CTA slots that the
+// waves fill) x (share of a CTA's time spent on keys rather than on its fixed cost), on a tie
+// the fewer splits.  One block; used between the steps of a burst that runs without the host.
 namespace {
-struct SplitRule { int pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits, own_length; };
+struct SplitRule { int pairs_per_entry, resident_ctas, fixed_tiles, max_splits, own_length; };
 __global__ void attn_decode_replan_kernel(int* split_keys, const int* context_len, const int* rows, int n,
                                           SplitRule rule) {
     __shared__ int shared_s;
@@ -753,26 +753,25 @@ __global__ void attn_decode_replan_kernel(int* split_keys, const int* context_le
     __syncthreads();
     if (threadIdx.x == 0) {
         const long long pairs = (long long)n * rule.pairs_per_entry;
-        int best = 1;
+        const int total = (longest + TILE_KEYS - 1) / TILE_KEYS;
+        int best = total;
         double best_score = -1.0;
-        for (int splits = 1; splits <= rule.max_splits; ++splits) {
-            if (splits > 1 && longest / splits < rule.min_split) break;
+        for (int k = total; k >= 1; --k) {
+            const int splits = (total + k - 1) / k;
+            if (splits > rule.max_splits) break;
             const long long ctas = pairs * splits;
             const long long waves = (ctas + rule.resident_ctas - 1) / rule.resident_ctas;
-            const int keys = (longest + splits - 1) / splits;
-            const int tiles = (keys + TILE_KEYS - 1) / TILE_KEYS;
-            const double score = (double)ctas / (double)(waves * rule.resident_ctas) * (double)tiles /
-                                 (double)(tiles + rule.fixed_tiles);
-            if (score > best_score + 1e-9) { best = splits; best_score = score; }
+            const double score = (double)ctas / (double)(waves * rule.resident_ctas) * (double)k /
+                                 (double)(k + rule.fixed_tiles);
+            if (score > best_score + 1e-9) { best = k; best_score = score; }
         }
-        const int keys = (longest + best - 1) / best;
-        shared_s = max(rule.min_split, (keys + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS);
+        shared_s = best * TILE_KEYS;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         if (rule.own_length) {
             const int own = (context_len[rows[i]] + 1 + 7) / 8;
-            split_keys[i] = max(rule.min_split, (own + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS);
+            split_keys[i] = max(TILE_KEYS, (own + TILE_KEYS - 1) / TILE_KEYS * TILE_KEYS);
         } else {
             split_keys[i] = shared_s;
         }
@@ -781,11 +780,11 @@ __global__ void attn_decode_replan_kernel(int* split_keys, const int* context_le
 }  // namespace
 
 extern "C" int kipp_attn_decode_replan(int* split_keys, const int* context_len, const int* rows, int n,
-                                       int pairs_per_entry, int resident_ctas, int fixed_tiles, int min_split,
-                                       int max_splits, int own_length, void* stream) {
+                                       int pairs_per_entry, int resident_ctas, int fixed_tiles, int max_splits,
+                                       int own_length, void* stream) {
     if (n <= 0) return 0;
-    if (pairs_per_entry <= 0 || resident_ctas <= 0 || min_split <= 0 || max_splits <= 0) return KIPP_ERR_ARG;
-    SplitRule rule{pairs_per_entry, resident_ctas, fixed_tiles, min_split, max_splits, own_length ? 1 : 0};
+    if (pairs_per_entry <= 0 || resident_ctas <= 0 || max_splits <= 0) return KIPP_ERR_ARG;
+    SplitRule rule{pairs_per_entry, resident_ctas, fixed_tiles, max_splits, own_length ? 1 : 0};
     return kipp_launch(attn_decode_replan_kernel, dim3(1), dim3(128), 0, (cudaStream_t)stream, 1, split_keys,
                        context_len, rows, n, rule);
 }

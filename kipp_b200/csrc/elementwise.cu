@@ -45,7 +45,7 @@ extern "C" int kipp_embed_gather(float* out, const void* table, int table_dtype,
 template <typename TO>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x,
                                const void* __restrict__ w, int w_dtype, const int* __restrict__ rows,
-                               int size, float eps) {
+                               int size, float eps, float* __restrict__ ssq_out) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -57,7 +57,9 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
-    const float scale = 1.0f / sqrtf(ss / (float)size + eps);
+    // deferred form: x * w alone goes out, the sum of squares beside it (see kipp_rmsnorm_deferred)
+    const float scale = ssq_out ? 1.0f : 1.0f / sqrtf(ss / (float)size + eps);
+    if (ssq_out && threadIdx.x == 0) ssq_out[r] = ss;
     TO* dst = out + (size_t)r * size;
     for (int i = threadIdx.x; i < size; i += blockDim.x)
         dst[i] = from_f32<TO>(src[i] * scale * load_w(w, w_dtype, i));
@@ -68,7 +70,7 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
 template <typename TO>
 __global__ void __launch_bounds__(256)
 rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const void* __restrict__ w, int w_dtype,
-                   const int* __restrict__ rows, int size, float eps) {
+                   const int* __restrict__ rows, int size, float eps, float* __restrict__ ssq_out) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -86,7 +88,8 @@ rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const void
         }
     }
     ss = block_sum(ss, scratch);
-    const float scale = 1.0f / sqrtf(ss / (float)size + eps);
+    const float scale = ssq_out ? 1.0f : 1.0f / sqrtf(ss / (float)size + eps);
+    if (ssq_out && threadIdx.x == 0) ssq_out[r] = ss;
     TO* dst = out + (size_t)r * size;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -108,8 +111,8 @@ rmsnorm_vec_kernel(TO* __restrict__ out, const float* __restrict__ x, const void
     }
 }
 
-extern "C" int kipp_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype,
-                            const int* rows, int n_rows, int size, float eps, void* stream) {
+static int rmsnorm_launch(void* out, int out_dtype, const float* x, const void* w, int w_dtype, const int* rows,
+                          int n_rows, int size, float eps, float* ssq_out, void* stream) {
     if (n_rows <= 0) return 0;
     if (size <= 0) return KIPP_ERR_ARG;
     if (w_dtype != KIPP_DT_F32 && w_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
@@ -117,18 +120,35 @@ extern "C" int kipp_rmsnorm(void* out, int out_dtype, const float* x, const void
     if (size % 4 == 0 && size <= 4096 && size >= 256 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         if (out_dtype == KIPP_DT_F32)
             return kipp_launch(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(256), 0, s, 1, (float*)out, x, w,
-                               w_dtype, rows, size, eps);
+                               w_dtype, rows, size, eps, ssq_out);
         if (out_dtype == KIPP_DT_BF16)
             return kipp_launch(rmsnorm_vec_kernel<bf16>, dim3(n_rows), dim3(256), 0, s, 1, (bf16*)out, x, w,
-                               w_dtype, rows, size, eps);
+                               w_dtype, rows, size, eps, ssq_out);
         return KIPP_ERR_DTYPE;
     }
     int threads = size >= 2048 ? 512 : (size >= 512 ? 256 : 64);
     if (out_dtype == KIPP_DT_F32)
         return kipp_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, 1, (float*)out, x, w, w_dtype,
-                           rows, size, eps);
+                           rows, size, eps, ssq_out);
     if (out_dtype == KIPP_DT_BF16)
         return kipp_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, s, 1, (bf16*)out, x, w, w_dtype,
-                           rows, size, eps);
+                           rows, size, eps, ssq_out);
     return KIPP_ERR_DTYPE;
+}
+
+extern "C" int kipp_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype,
+                            const int* rows, int n_rows, int size, float eps, void* stream) {
+    return rmsnorm_launch(out, out_dtype, x, w, w_dtype, rows, n_rows, size, eps, nullptr, stream);
+}
+
+// The norm with its per-row factor left to whoever reads the result: out[r, i] = x[row r, i] * w[i]
+// (rounded to out's type) and ssq_out[r] = sum of x[row r, :]^2, so that
+// rmsnorm(x)[r] = out[r] / sqrt(ssq_out[r] / size + eps).  A matrix product that follows applies
+// the factor to its own result rows in float32 (kipp_gemm_tc_fold); a residual add that leaves
+// x * w itself (the same kernel library) rounds the same values the same way, so both routes to
+// the product's input agree to the bit.
+extern "C" int kipp_rmsnorm_deferred(void* out, int out_dtype, float* ssq_out, const float* x, const void* w,
+                                     int w_dtype, const int* rows, int n_rows, int size, void* stream) {
+    if (ssq_out == nullptr) return KIPP_ERR_ARG;
+    return rmsnorm_launch(out, out_dtype, x, w, w_dtype, rows, n_rows, size, 0.f, ssq_out, stream);
 }

@@ -241,7 +241,8 @@ template <int TILE_T, int TILE_F> struct Cfg {
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;   // 32, 64, 128, 256 or 512
     // epilogue warp groups: two groups of four warps split the token columns
     static constexpr int COL_GROUPS = TILE_T >= 32 ? 2 : 1;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ +
+                                   TILE_T * 4 /*per-token factors*/;
 };
 
 struct Params {
@@ -253,10 +254,36 @@ struct Params {
     int k_blocks_per_split; // TILE_K blocks each split handles
     int splits;
     int* status;
+    // Folding an RMSNorm into the products around it (few-token kernel only; all optional):
+    // a residual add can leave, beside the new residual r, what the NEXT norm needs:
+    // xn[t, f] = bf16(r * norm_w[f]) and the sum of r^2 over each 32 features of a token
+    // (ssq_out[t, f / 32]); a store or SwiGLU product whose input lacks the norm's factor
+    // rsqrt(mean(r^2) + eps) per token gets it from those sums (ssq_in) and scales its rows.
+    const void* norm_w; int norm_w_dtype;
+    bf16* xn; long long ldn;
+    float* ssq_out; int ssq_slots;
+    const float* ssq_in; int ssq_in_slots;
+    float inv_n, eps;
 };
 
-// Epilogue of 16 tokens (t_first .. + 15) of this thread's feature f.
-__device__ __forceinline__ void epilogue_chunk(const Params& p, const float* v, int t_first, int f, int lane) {
+// What the next norm needs of a new residual value r of token t, feature f (see Params): called
+// by whole warps whose lanes hold 32 neighbouring features of one token.
+__device__ __forceinline__ void emit_for_next_norm(const Params& p, float r, bool valid, int t, int f, int lane,
+                                                   float w) {
+    if (valid) p.xn[(size_t)t * p.ldn + f] = __float2bfloat16_rn(r * w);
+    const float s = warp_sum(valid ? r * r : 0.f);
+    const int slot = (f - lane) >> 5;
+    if (lane == 0 && t < p.tokens && slot < p.ssq_slots) p.ssq_out[(size_t)t * p.ssq_slots + slot] = s;
+}
+
+// Epilogue of 16 tokens (t_first .. + 15) of this thread's feature f; `rstd` (or nullptr) holds
+// the factor of each of these tokens that the product's input lacks.
+__device__ __forceinline__ void epilogue_chunk(const Params& p, float* v, int t_first, int f, int lane,
+                                               const float* rstd) {
+    if (rstd != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] *= rstd[j];
+    }
     if (p.epilogue == EPI_ADD) {
         // all loads of the residual first, then the stores: the loads overlap
         float* cbase = reinterpret_cast<float*>(p.C) + f;
@@ -270,6 +297,35 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, const float* v, 
         for (int j = 0; j < 16; ++j) {
             const int t = t_first + j;
             if (t < p.tokens && f < p.features) cbase[(size_t)t * p.ldc] = old[j] + v[j];
+        }
+        if (p.xn != nullptr) {
+            const bool f_ok = f < p.features;
+            const float w = f_ok ? load_w(p.norm_w, p.norm_w_dtype, f) : 0.f;
+            float sq[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int t = t_first + j;
+                const float r = old[j] + v[j];
+                const bool valid = t < p.tokens && f_ok;
+                if (valid) p.xn[(size_t)t * p.ldn + f] = __float2bfloat16_rn(r * w);
+                sq[j] = valid ? r * r : 0.f;
+            }
+            // Sums over the warp's 32 features of all 16 tokens at once: each exchange halves
+            // the tokens a lane carries (16 shuffles instead of 5 per token); lane bits 4..1
+            // then spell the token whose sum the lane holds.
+#define KIPP_FOLD_STEP(n, bit)                                                    \
+            _Pragma("unroll") for (int j = 0; j < n; ++j) {                       \
+                const bool up = (lane & bit) != 0;                                \
+                const float send = up ? sq[j] : sq[j + n];                        \
+                const float keep = up ? sq[j + n] : sq[j];                        \
+                sq[j] = keep + __shfl_xor_sync(0xffffffffu, send, bit);           \
+            }
+            KIPP_FOLD_STEP(8, 16) KIPP_FOLD_STEP(4, 8) KIPP_FOLD_STEP(2, 4) KIPP_FOLD_STEP(1, 2)
+#undef KIPP_FOLD_STEP
+            sq[0] += __shfl_xor_sync(0xffffffffu, sq[0], 1);
+            const int t = t_first + (lane >> 1);        // bits 4..1 of the lane: 8, 4, 2, 1
+            const int slot = (f - lane) >> 5;
+            if ((lane & 1) == 0 && t < p.tokens && slot < p.ssq_slots) p.ssq_out[(size_t)t * p.ssq_slots + slot] = sq[0];
         }
     } else if (p.epilogue == EPI_SWIGLU) {
         // gate rows are even, up rows odd: the even lane takes its neighbour's
@@ -312,6 +368,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* acc_ready = empty + C::STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* rstd_s = (float*)(tiles + (size_t)C::STAGES * C::STAGE_BYTES + 256);   // [TILE_T], see Params::ssq_in
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -396,6 +453,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;                    // tensor-memory lane quarter of this warp
         const int cg = (warp - 2) >> 2;            // which share of the token columns
         pdl_wait();                                // the epilogue reads and writes what earlier kernels made
+        if (p.ssq_in != nullptr) {
+            // the factor each token's row still lacks, while the products run: thread i of the
+            // 256 epilogue threads sums token t0 + i's partial sums in slot order
+            for (int j = threadIdx.x - 64; j < TILE_T; j += 256) {
+                float sum = 0.f;
+                if (t0 + j < p.tokens) {
+                    const float* row = p.ssq_in + (size_t)(t0 + j) * p.ssq_in_slots;
+#pragma unroll 8
+                    for (int i = 0; i < p.ssq_in_slots; ++i) sum += row[i];
+                }
+                rstd_s[j] = 1.0f / sqrtf(sum * p.inv_n + p.eps);
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+        const float* rstd_tile = p.ssq_in != nullptr ? rstd_s : nullptr;
         bool ok = n_kb > 0 ? mbar_wait(acc_ready, 0, abort_flag) : true;
         tcgen05_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
@@ -413,7 +485,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                             for (int j = 0; j < 16; ++j) v[j] = 0.f;
                         }
-                        epilogue_chunk(p, v, t0 + c, f, lane);
+                        epilogue_chunk(p, v, t0 + c, f, lane, rstd_tile ? rstd_tile + c : nullptr);
                     }
                 }
             } else {
@@ -462,6 +534,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float v = 0.f;
 #pragma unroll
                 for (int s = 0; s < 8; ++s) v += part[s];              // absent splits add zero
+                if (p.ssq_in != nullptr) v *= rstd_s[j];
                 const int t = t0 + j;
                 // one value per thread: the epilogue of a 16-token chunk with one live token
                 if (p.epilogue == EPI_SWIGLU) {
@@ -471,6 +544,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         if (p.out_dtype == KIPP_DT_F32) reinterpret_cast<float*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = r;
                         else reinterpret_cast<bf16*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = __float2bfloat16_rn(r);
                     }
+                } else if (p.epilogue == EPI_ADD && p.xn != nullptr) {
+                    const bool valid = t < p.tokens && f < p.features;
+                    float r = 0.f;
+                    if (valid) {
+                        float* c = reinterpret_cast<float*>(p.C) + (size_t)t * p.ldc + f;
+                        r = *c + v;
+                        *c = r;
+                    }
+                    emit_for_next_norm(p, r, valid, t, f, lane, valid ? load_w(p.norm_w, p.norm_w_dtype, f) : 0.f);
                 } else if (t < p.tokens && f < p.features) {
                     if (p.out_dtype == KIPP_DT_F32) {
                         float* c = reinterpret_cast<float*>(p.C) + (size_t)t * p.ldc + f;
@@ -606,10 +688,22 @@ __device__ __forceinline__ void tokm_epilogue_tile(const Params& p, const CUtens
             }
         }
     } else {
+        // the factor this thread's token still lacks (see Params::ssq_in), summed in slot order
+        float rstd = 1.0f;
+        if (p.ssq_in != nullptr && t < p.tokens) {
+            const float* row = p.ssq_in + (size_t)t * p.ssq_in_slots;
+            float sum = 0.f;
+            for (int i = 0; i < p.ssq_in_slots; ++i) sum += row[i];
+            rstd = 1.0f / sqrtf(sum * p.inv_n + p.eps);
+        }
 #pragma unroll 1
         for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
             float v[16];
             tmem_ld16(taddr + c, v);
+            if (p.ssq_in != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] *= rstd;
+            }
             if (ok) epilogue_row16(p, v, t, f0 + c);
         }
     }
@@ -1136,10 +1230,47 @@ extern "C" int kipp_gemm_tc_plan(int tokens, int features, int K, int want_split
 
 // C (+)= X W^T.  X [tokens, K] bf16 (ldx), W [features, K] bf16 (ldw), C float32
 // or bf16 (ldc).  Pointers 16-byte aligned, ldx and ldw multiples of 8.
+// What folds an RMSNorm into the products around it (the few-token kernel only; see Params).
+struct kipp_gemm_norm_fold {
+    const void* norm_w;       // EPI_ADD: weight of the norm that follows the add, or NULL
+    int norm_w_dtype;
+    void* xn;                 //   bf16 [tokens, ldn]: new residual x that weight, without the per-token factor
+    long long ldn;
+    float* ssq_out;           //   float32 [tokens, features / 32]: sums of squares of the new residual
+    const float* ssq_in;      // store / SwiGLU: such sums for this product's input rows, or NULL
+    int ssq_in_slots;
+    float inv_n, eps;         //   the factor is 1 / sqrt(sum * inv_n + eps)
+};
+
+// Whether a residual add of this many tokens can leave what the next norm needs (norm_w; prompt-
+// sized batches run the other kernels, whose add goes out as reducing stores that never see the
+// new value).  Row factors (ssq_in) are taken at every size.
+extern "C" int kipp_gemm_tc_fold_ok(int tokens) { return tokens > 0 && tokens < 512; }
+
+extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const void* W, int tokens, int features,
+                                 int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
+                                 int want_tile, int want_tile_f, const kipp_gemm_norm_fold* fold, int* status,
+                                 void* stream);
+
 extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W, int tokens, int features,
                             int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
                             int want_tile, int want_tile_f, int* status, void* stream) {
+    return kipp_gemm_tc_fold(C, out_dtype, X, W, tokens, features, K, ldx, ldw, ldc, epilogue, splits, want_tile,
+                             want_tile_f, nullptr, status, stream);
+}
+
+extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const void* W, int tokens, int features,
+                                 int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
+                                 int want_tile, int want_tile_f, const kipp_gemm_norm_fold* fold, int* status,
+                                 void* stream) {
     if (tokens <= 0 || features <= 0) return 0;
+    if (fold != nullptr) {
+        if (fold->norm_w != nullptr &&
+            (!kipp_gemm_tc_fold_ok(tokens) || want_tile_f < 0 || epilogue != EPI_ADD || fold->xn == nullptr || fold->ssq_out == nullptr || (features % 32) ||
+             (fold->norm_w_dtype != KIPP_DT_F32 && fold->norm_w_dtype != KIPP_DT_BF16)))
+            return KIPP_ERR_ARG;
+        if (fold->ssq_in != nullptr && (epilogue == EPI_ADD || fold->ssq_in_slots <= 0)) return KIPP_ERR_ARG;
+    }
     if (K <= 0) return KIPP_ERR_ARG;
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -3;
     if (epilogue == EPI_ADD && out_dtype != KIPP_DT_F32) return KIPP_ERR_DTYPE;
@@ -1170,10 +1301,14 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
         } else {
             mc = mw;                                    // unused
         }
-        Params p;
+        Params p = {};
         p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
         p.tokens = tokens; p.features = features; p.K = K; p.ldc = ldc;
         p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
+        if (fold != nullptr && fold->ssq_in != nullptr) {
+            p.ssq_in = fold->ssq_in; p.ssq_in_slots = fold->ssq_in_slots;
+            p.inv_n = fold->inv_n; p.eps = fold->eps;
+        }
         const int rows = pair ? 2 * UMMA_M : UMMA_M;
         const long long total = (long long)((tokens + rows - 1) / rows) * ((features + tile_n - 1) / tile_n);
         if (total > 0x7fffffffLL) return KIPP_ERR_ARG;
@@ -1192,12 +1327,23 @@ extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W
     if (rc) return rc;
     rc = make_map(&mx, X, tokens, K, ldx, tile_t);
     if (rc) return rc;
-    Params p;
+    Params p = {};
     p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
     p.tokens = tokens; p.features = features; p.K = K; p.ldc = ldc;
     const int kb = (K + TILE_K - 1) / TILE_K;
     p.k_blocks_per_split = (kb + splits - 1) / splits;
     p.splits = splits; p.status = status;
+    if (fold != nullptr) {
+        if (fold->norm_w != nullptr) {
+            p.norm_w = fold->norm_w; p.norm_w_dtype = fold->norm_w_dtype;
+            p.xn = (bf16*)fold->xn; p.ldn = fold->ldn;
+            p.ssq_out = fold->ssq_out; p.ssq_slots = features / 32;
+        }
+        if (fold->ssq_in != nullptr) {
+            p.ssq_in = fold->ssq_in; p.ssq_in_slots = fold->ssq_in_slots;
+            p.inv_n = fold->inv_n; p.eps = fold->eps;
+        }
+    }
     dim3 grid((tokens + tile_t - 1) / tile_t, (features + tile_f - 1) / tile_f, splits);
     if (grid.y > 65535) return KIPP_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;

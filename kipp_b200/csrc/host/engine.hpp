@@ -304,7 +304,9 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
     const StepMeta& m = *ctx.meta;
     const int qkv_cols = q_dim_ + 2 * kv_dim_;
     void* qkv = ctx.workspace->buffer("qkv", (size_t)T * qkv_cols * es);
-    ops.gemm(qkv, ctx.dtype, qkv_cols, h, hidden_, w_qkv_, hidden_, dtype_, T, qkv_cols, hidden_, EPI_STORE);
+    NormFold fold_in, fold_out;
+    ops.gemm(qkv, ctx.dtype, qkv_cols, h, hidden_, w_qkv_, hidden_, dtype_, T, qkv_cols, hidden_, EPI_STORE,
+             fold_input(ctx, fold_in));
     const PagedCacheView cache = ctx.cache_view(run, mixer_slot);       // pages of this run's cache id
     const float* cos_sin = nullptr;
     const int rot = position_->rotary_dim();
@@ -338,7 +340,9 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
         ops.attention(attn, q, cache, ctx.dtype, work, m.positions, m.entry_of_token, m.q_start, m.context_len,
                       heads_, kv_heads_, head_dim_, scale_, window_);
     }
-    ops.gemm(residual, F32, hidden_, attn, q_dim_, w_o_, q_dim_, dtype_, T, hidden_, q_dim_, EPI_ADD);
+    const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
+    ops.gemm(residual, F32, hidden_, attn, q_dim_, w_o_, q_dim_, dtype_, T, hidden_, q_dim_, EPI_ADD, emit);
+    fold_emitted(ctx, emit, hidden_);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -801,7 +805,15 @@ inline const float* Engine::forward(StepMeta& meta) {
     const int T = meta.shape.tokens;
     float* x = workspace_.get<float>("residual", (size_t)T * plan_->hidden_size);
     for (auto& e : plan_->embedding) e.second->forward(ctx, x);
-    for (auto& run : plan_->order) plan_->layers[(size_t)run.layer].second->forward(ctx, run, x);
+    for (size_t i = 0; i < plan_->order.size(); ++i) {
+        const LayerRun& run = plan_->order[i];
+        // the block that runs next starts with this norm: the last residual add of this one may
+        // leave its deferred form
+        ctx.following_norm = i + 1 < plan_->order.size()
+                                 ? plan_->layers[(size_t)plan_->order[i + 1].layer].second->deferred_first_norm()
+                                 : nullptr;
+        plan_->layers[(size_t)run.layer].second->forward(ctx, run, x);
+    }
     const float* logits = nullptr;
     const int rows = meta.shape.logit_rows;
     if (rows > 0) {
@@ -1357,6 +1369,7 @@ inline std::string Engine::info_json() {
     counters.set("last_h2d_bytes", last_h2d_bytes);
     counters.set("tc_prefill_launches", ops_.tc_prefill_launches);
     counters.set("fused_decode_launches", ops_.fused_decode_launches);
+    counters.set("folded_norms", ops_.folded_norms);
     j.set("counters", std::move(counters));
     info_ = j.dump();
     return info_;

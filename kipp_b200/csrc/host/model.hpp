@@ -100,7 +100,25 @@ struct StepMeta {
     std::map<std::string, std::vector<int>> work_sizes;   // planner key -> ints per section
 };
 
+// What a norm that is a plain RMSNorm tells the parts around it, so that they can fold it
+// into their products (see NormFold): y = x * rsqrt(mean(x^2) + eps) * weight.
+struct RmsNormSpec {
+    const void* weight = nullptr;
+    int weight_dtype = F32;
+    float eps = 0.f;
+    int size = 0;
+};
+
+// An input whose rows lack the factor rsqrt(sum(ssq[t, :slots]) * inv_n + eps).
+struct RowScale {
+    const float* ssq = nullptr;
+    int slots = 0;
+    float inv_n = 0.f, eps = 0.f;
+    bool valid() const { return ssq != nullptr; }
+};
+
 class Engine;
+class Norm;
 
 // What a part sees during one step.
 struct StepContext {
@@ -112,6 +130,19 @@ struct StepContext {
     cudaStream_t stream = nullptr;
     bool kv_round_bf16 = false;            // 32-bit cache: keys and values are rounded to bfloat16 when stored
     std::map<std::string, void*> step_cache;   // what parts share within ONE forward pass (rotary tables)
+
+    // Norms in deferred form (set by a block around the calls of its parts; a part that says
+    // folds_rms() honours them, any other part never sees them set).  Deferred: the part's input
+    // h is bf16(x * norm weight) and the per-row factor rsqrt(mean(x^2) + eps) is applied by the
+    // part's first product to its result rows, in float32.  Whether a part takes its input so is
+    // a matter of the model, never of the step: the same rounding at every way of cutting.
+    RowScale input_scale;                  // the part's input h lacks this per-row factor
+    const RmsNormSpec* emit_for = nullptr; // the part's residual add may also leave this norm's deferred form in `normed`
+    bool emitted = false;                  //   ... and says so here, with the sums in emitted_scale
+    RowScale emitted_scale;
+    const Norm* pending_norm = nullptr;    // `normed` holds the deferred form of this norm of the NEXT block
+    RowScale pending_scale;
+    const Norm* following_norm = nullptr;  // Block::deferred_first_norm of the block that runs next (set by the engine)
 
     size_t element() const { return dtype_size(dtype); }
     int tokens() const { return meta->shape.tokens; }
@@ -154,6 +185,8 @@ public:
     // out[r, :] (compute dtype) = norm(x[rows ? rows[r] : r, :]); x float32 [T, size]
     virtual void forward(StepContext& ctx, const float* x, void* out, const int* rows, int n_rows) = 0;
     virtual int size() const = 0;
+    // a plain RMSNorm says what it is, so that the products around it can fold it
+    virtual std::optional<RmsNormSpec> rms_spec() const { return std::nullopt; }
 };
 
 class PositionEncoding : public Part {
@@ -173,11 +206,15 @@ public:
     virtual std::shared_ptr<WorkPlanner> planner(const DeviceInfo& device, bool own_length_splits) { return nullptr; }
     // ADDS its output to the float32 residual [T, hidden]; h [T, hidden] in the compute dtype
     virtual void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) = 0;
+    // true: the part applies ctx.input_scale to its first product, at every size of step, and may
+    // honour ctx.emit_for in its residual add
+    virtual bool folds_rms() const { return false; }
 };
 
 class FeedForward : public Part {
 public:
     virtual void forward(StepContext& ctx, const void* h, float* residual) = 0;
+    virtual bool folds_rms() const { return false; }      // as Mixer::folds_rms
 };
 
 // A stage at the bottom of the model: the first one writes the residual stream x [T, hidden]
@@ -198,6 +235,9 @@ class Block : public Part {
 public:
     virtual std::vector<Mixer*> mixers() = 0;
     virtual void forward(StepContext& ctx, const LayerRun& run, float* x) = 0;
+    // the norm the block applies to the residual stream first, if the part after it takes its
+    // input in deferred form (see StepContext::input_scale)
+    virtual const Norm* deferred_first_norm() const { return nullptr; }
 };
 
 // ---------------------------------------------------------------------------------------------

@@ -88,6 +88,7 @@ public:
     }
     size_t weight_bytes() const override { return (size_t)size_ * dtype_size(wdtype_); }
     int size() const override { return size_; }
+    std::optional<RmsNormSpec> rms_spec() const override { return RmsNormSpec{weight_, wdtype_, eps_, size_}; }
     void forward(StepContext& ctx, const float* x, void* out, const int* rows, int n_rows) override {
         ctx.ops->rmsnorm(out, ctx.dtype, x, weight_, wdtype_, rows, n_rows, size_, eps_);
     }
@@ -143,7 +144,6 @@ inline std::vector<float> rotary_frequencies(int rotary_dim, double theta) {
 class AttentionPlanner : public WorkPlanner {
 public:
     static constexpr int TILE = 64;
-    static constexpr int MIN_SPLIT = 64;
     static constexpr int CTA_FIXED_TILES = 5;   // what a decode CTA costs beside its key tiles, in 64-key tiles
     static constexpr int CTAS_PER_SM = 3;
 
@@ -167,35 +167,36 @@ public:
         n[0] = decode; n[1] = decode; n[2] = 2 * items; n[3] = 2 * all; n[4] = 2 * items128;
     }
 
-    // Keys per split for the decoded tokens of a step.  The number of splits is the one with the
-    // best (share of the resident CTA slots that the waves fill) x (share of a CTA's time spent
-    // on keys rather than on its set-up, its merge of four warps and its partial results): many
-    // short splits fill the GPU when there are few (token, kv head) pairs, few long ones are
-    // better once the pairs alone fill it.
+    // Keys per split for the decoded tokens of a step, in whole 64-key tiles.  Among the numbers of
+    // tiles per split k (splits = total tiles / k, rounded up, at most DECODE_MAX_SPLITS) the one
+    // with the best (share of the resident CTA slots that the waves fill) x (share of a CTA's time
+    // spent on keys rather than on its set-up, its merge of four warps and its partial results):
+    // many short splits fill the GPU when there are few (token, kv head) pairs (a single token's
+    // attention is bound by latency, so one tile per split), few long ones are better once the
+    // pairs alone fill it.  On a tie the fewer splits.  The device makes the same choice between
+    // the steps of a burst (kipp_attn_decode_replan): same integers, same double arithmetic.
     int step_split_length(int decoded, int longest) const {
-        if (decoded <= 0) return MIN_SPLIT;
+        if (decoded <= 0 || longest <= 0) return TILE;
         const long long pairs = (long long)decoded * kv_heads_;
-        int best = 1;
+        const int total = (longest + TILE - 1) / TILE;
+        int best = total;
         double best_score = -1.0;
-        for (int splits = 1; splits <= Ops::DECODE_MAX_SPLITS; ++splits) {
-            if (splits > 1 && longest / splits < MIN_SPLIT) break;
+        for (int k = total; k >= 1; --k) {
+            const int splits = (total + k - 1) / k;
+            if (splits > Ops::DECODE_MAX_SPLITS) break;
             const long long ctas = pairs * splits;
             const long long waves = (ctas + resident_ - 1) / resident_;
-            const int keys = (longest + splits - 1) / splits;
-            const int tiles = (keys + TILE - 1) / TILE;
-            const double score = (double)ctas / (double)(waves * resident_) * (double)tiles /
-                                 (double)(tiles + CTA_FIXED_TILES);
-            if (score > best_score + 1e-9) { best = splits; best_score = score; }
+            const double score = (double)ctas / (double)(waves * resident_) * (double)k / (double)(k + CTA_FIXED_TILES);
+            if (score > best_score + 1e-9) { best = k; best_score = score; }
         }
-        const int keys = (longest + best - 1) / best;
-        return std::max(MIN_SPLIT, (keys + TILE - 1) / TILE * TILE);
+        return best * TILE;
     }
     // From the token's own context only (an eighth of it): the grouping of its partial sums then
     // does not depend on what else is in the batch (the reference's lesson,
     // metal/kipp_kernels.metal:82-100).
     static int own_split_length(int kv_len) {
         const int own = (kv_len + 7) / 8;
-        return std::max(MIN_SPLIT, (own + TILE - 1) / TILE * TILE);
+        return std::max(TILE, (own + TILE - 1) / TILE * TILE);
     }
 
     void fill(const StepShape& s, int* const* sec) const override {
@@ -220,7 +221,7 @@ public:
     }
 
     void advance_on_device(Ops& ops, int* const* sec, const int* context_len, int entries) const override {
-        ops.decode_replan(sec[1], context_len, sec[0], entries, kv_heads_, resident_, CTA_FIXED_TILES, MIN_SPLIT,
+        ops.decode_replan(sec[1], context_len, sec[0], entries, kv_heads_, resident_, CTA_FIXED_TILES,
                           Ops::DECODE_MAX_SPLITS, own_length_ ? 1 : 0);
     }
 
@@ -246,6 +247,43 @@ private:
     int kv_heads_, resident_;
     bool own_length_;
 };
+
+// ---------------------------------------------------------------------------------------------
+// Norms in deferred form (see NormFold, StepContext::input_scale): what a part's first product and
+// its residual add pass to the kernels, and what a block runs where no residual add left the form.
+inline const NormFold* fold_input(const StepContext& ctx, NormFold& f) {
+    if (!ctx.input_scale.valid()) return nullptr;
+    f = NormFold{};
+    f.ssq_in = ctx.input_scale.ssq;
+    f.ssq_in_slots = ctx.input_scale.slots;
+    f.inv_n = ctx.input_scale.inv_n;
+    f.eps = ctx.input_scale.eps;
+    return &f;
+}
+inline float* fold_sums(StepContext& ctx, int hidden) {
+    return ctx.workspace->get<float>("norm_ssq", (size_t)ctx.tokens() * (size_t)std::max(1, hidden / 32));
+}
+inline const NormFold* fold_emit(StepContext& ctx, NormFold& f, int hidden) {
+    const int T = ctx.tokens();
+    if (ctx.emit_for == nullptr || ctx.emit_for->size != hidden || hidden % 32 || !Ops::gemm_emit_ok(T)) return nullptr;
+    f = NormFold{};
+    f.norm_w = ctx.emit_for->weight;
+    f.norm_w_dtype = ctx.emit_for->weight_dtype;
+    f.xn = ctx.workspace->buffer("normed", (size_t)T * hidden * ctx.element());
+    f.ldn = hidden;
+    f.ssq_out = fold_sums(ctx, hidden);
+    return &f;
+}
+inline RowScale deferred_norm(StepContext& ctx, const RmsNormSpec& norm, const float* x, void* h) {
+    float* ssq = fold_sums(ctx, norm.size);
+    ctx.ops->rmsnorm_deferred(h, ctx.dtype, ssq, x, norm.weight, norm.weight_dtype, nullptr, ctx.tokens(), norm.size);
+    return RowScale{ssq, 1, 1.0f / (float)norm.size, norm.eps};
+}
+inline void fold_emitted(StepContext& ctx, const NormFold* f, int hidden) {
+    if (f == nullptr) return;
+    ctx.emitted = true;
+    ctx.emitted_scale = RowScale{f->ssq_out, hidden / 32, 1.0f / (float)hidden, ctx.emit_for->eps};
+}
 
 // ---------------------------------------------------------------------------------------------
 // Causal grouped-query attention over the paged cache, with optional per-head q/k RMSNorm and a
@@ -322,6 +360,7 @@ public:
         if (qk_norm_) n += 2 * (size_t)head_dim_ * dtype_size(norm_dtype_);
         return n;
     }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_qkv_, hidden_, w_qkv_, hidden_); }
     void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) override;
 
 private:
@@ -367,12 +406,16 @@ public:
         b.load(p + "down_proj.weight", w_down_, dtype_, inter_, hidden_, inter_);
     }
     size_t weight_bytes() const override { return (size_t)3 * inter_ * hidden_ * dtype_size(dtype_); }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_gate_up_, hidden_, w_gate_up_, hidden_); }
     void forward(StepContext& ctx, const void* h, float* residual) override {
         const int T = ctx.tokens();
+        NormFold in, out;
         void* act = ctx.workspace->buffer("ffn_act", (size_t)T * inter_ * ctx.element());
         ctx.ops->gemm(act, ctx.dtype, inter_, h, hidden_, w_gate_up_, hidden_, dtype_, T, 2 * inter_, hidden_,
-                      EPI_SWIGLU);
-        ctx.ops->gemm(residual, F32, hidden_, act, inter_, w_down_, inter_, dtype_, T, hidden_, inter_, EPI_ADD);
+                      EPI_SWIGLU, fold_input(ctx, in));
+        const NormFold* emit = fold_emit(ctx, out, hidden_);
+        ctx.ops->gemm(residual, F32, hidden_, act, inter_, w_down_, inter_, dtype_, T, hidden_, inter_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
     }
 
 private:
@@ -409,13 +452,45 @@ public:
         return n1_->graph_safe() && mixer_->graph_safe() && n2_->graph_safe() && ffn_->graph_safe();
     }
     std::vector<Mixer*> mixers() override { return {mixer_.get()}; }
+    const Norm* deferred_first_norm() const override {
+        return mixer_->folds_rms() && n1_->rms_spec() ? n1_.get() : nullptr;
+    }
+    // A plain RMSNorm before a part that folds it runs in deferred form, at every size of step:
+    // the part's input is bf16(x * weight), the row factor goes into its first product.  In steps
+    // of few tokens the residual add BEFORE the norm leaves that form itself (two launches fewer
+    // per layer, where a launch costs more than the norm's arithmetic); otherwise one kernel makes
+    // it.  Both give the same bits, so the logits do not depend on which ran.
     void forward(StepContext& ctx, const LayerRun& run, float* x) override {
         const int T = ctx.tokens();
         void* h = ctx.workspace->buffer("normed", (size_t)T * n1_->size() * ctx.element());
-        n1_->forward(ctx, x, h, nullptr, T);
+        const std::optional<RmsNormSpec> spec1 = n1_->rms_spec(), spec2 = n2_->rms_spec();
+        const bool defer1 = spec1 && mixer_->folds_rms(), defer2 = spec2 && ffn_->folds_rms();
+        // -- norm 1 and the mixer
+        ctx.input_scale = RowScale{};
+        if (defer1 && ctx.pending_norm == n1_.get()) ctx.input_scale = ctx.pending_scale;   // h is made already
+        else if (defer1) ctx.input_scale = deferred_norm(ctx, *spec1, x, h);
+        else n1_->forward(ctx, x, h, nullptr, T);
+        ctx.pending_norm = nullptr;
+        ctx.emit_for = defer2 ? &*spec2 : nullptr;
+        ctx.emitted = false;
         mixer_->forward(ctx, run, 0, h, x);
-        n2_->forward(ctx, x, h, nullptr, T);
+        // -- norm 2 and the feed-forward
+        ctx.input_scale = RowScale{};
+        if (defer2 && ctx.emitted) ctx.input_scale = ctx.emitted_scale;
+        else if (defer2) ctx.input_scale = deferred_norm(ctx, *spec2, x, h);
+        else n2_->forward(ctx, x, h, nullptr, T);
+        const Norm* next = ctx.following_norm;
+        const std::optional<RmsNormSpec> spec_next = next ? next->rms_spec() : std::nullopt;
+        ctx.emit_for = spec_next && ffn_->folds_rms() && next->size() == n1_->size() ? &*spec_next : nullptr;
+        ctx.emitted = false;
         ffn_->forward(ctx, h, x);
+        if (ctx.emitted) {
+            ctx.pending_norm = next;
+            ctx.pending_scale = ctx.emitted_scale;
+        }
+        ctx.input_scale = RowScale{};
+        ctx.emit_for = nullptr;
+        ctx.emitted = false;
     }
     Norm* input_norm() { return n1_.get(); }
     Norm* post_norm() { return n2_.get(); }

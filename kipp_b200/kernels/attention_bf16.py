@@ -121,7 +121,7 @@ def _split_stride(meta) -> int:
 
 
 def decode_replan(split_keys: torch.Tensor, context_len: torch.Tensor, rows: torch.Tensor, pairs_per_entry: int,
-                  resident_ctas: int, fixed_tiles: int, min_split: int, max_splits: int, own_length: bool) -> None:
+                  resident_ctas: int, fixed_tiles: int, max_splits: int, own_length: bool) -> None:
     """The keys per split of every decoded token, chosen on the device from the
     cached lengths (between the steps of a burst that runs without the host)."""
     n = rows.numel()
@@ -131,9 +131,9 @@ def decode_replan(split_keys: torch.Tensor, context_len: torch.Tensor, rows: tor
     if split_keys.numel() < n:
         raise KernelError("decode_replan: one split length per decoded token")
     f = _fn("attention_mma", "kipp_attn_decode_replan",
-            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(split_keys), _ptr(context_len), _ptr(rows), n, pairs_per_entry, resident_ctas, fixed_tiles,
-             min_split, max_splits, 1 if own_length else 0, _stream()), "attn_decode_replan")
+             max_splits, 1 if own_length else 0, _stream()), "attn_decode_replan")
 
 
 def decode_fused_ok(meta, q_dtype, n_q: int, n_kv: int, head_dim: int, rotary_dim: int) -> bool:

@@ -31,7 +31,27 @@ def choose(M, N, K, a, w, out, epilogue) -> str:
     return "tc" if tc_ok(a, w) else "simt"
 
 
-def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 0, tile_f: int = 0) -> None:
+class NormFold(ctypes.Structure):
+    """kipp_gemm_norm_fold of the kernel library: what folds an RMSNorm into the
+    products around it (few-token kernel only)."""
+    _fields_ = [("norm_w", c_void_p), ("norm_w_dtype", c_int), ("xn", c_void_p), ("ldn", c_ll),
+                ("ssq_out", c_void_p), ("ssq_in", c_void_p), ("ssq_in_slots", c_int),
+                ("inv_n", ctypes.c_float), ("eps", ctypes.c_float)]
+
+
+def fold_emit(norm_w: torch.Tensor, xn: torch.Tensor, ssq: torch.Tensor) -> NormFold:
+    """For a residual add: also write xn = bf16(new residual * norm_w) and
+    ssq[t, f // 32] = sums of squares of the new residual."""
+    return NormFold(_ptr(norm_w), dtype_code(norm_w.dtype), _ptr(xn), xn.stride(0), _ptr(ssq), None, 0, 0.0, 0.0)
+
+
+def fold_scale(ssq: torch.Tensor, n: int, eps: float) -> NormFold:
+    """For a store or SwiGLU product: scale row t by 1 / sqrt(sum(ssq[t]) / n + eps)."""
+    return NormFold(None, 0, None, 0, None, _ptr(ssq), ssq.shape[1], 1.0 / n, eps)
+
+
+def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 0, tile_f: int = 0,
+        fold: NormFold | None = None) -> None:
     if impl != "tc":
         raise KernelError(f"unknown gemm implementation {impl!r}")
     if not tc_ok(a, w):
@@ -39,11 +59,12 @@ def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 
     N, K = w.shape
     if status is None:
         status = _status(a.device)
-    f = _fn("gemm_tc", "kipp_gemm_tc",
+    f = _fn("gemm_tc", "kipp_gemm_tc_fold",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int,
-             c_int, c_int, c_void_p, c_void_p])
+             c_int, c_int, ctypes.POINTER(NormFold), c_void_p, c_void_p])
     _check(f(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
-             out.stride(0), EPILOGUES[epilogue], splits, tile, tile_f, _ptr(status), _stream()), "gemm_tc")
+             out.stride(0), EPILOGUES[epilogue], splits, tile, tile_f,
+             ctypes.byref(fold) if fold is not None else None, _ptr(status), _stream()), "gemm_tc")
 
 
 _status_words: dict = {}

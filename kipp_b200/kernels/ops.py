@@ -114,6 +114,27 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float
              _ptr(rows), n_rows, size, float(eps), _stream()), "rmsnorm")
 
 
+def rmsnorm_deferred(out: torch.Tensor, ssq: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+                     rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
+    """The norm with its row factor left to the reader: out[r] = x[rows[r] or r] * weight
+    (rounded to out's type), ssq[r] = sum(x[row]^2); rmsnorm(x)[r] = out[r] * rsqrt(ssq[r] / size + eps)."""
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("rmsnorm_deferred: x must be contiguous float32")
+    size = x.shape[-1]
+    if weight.numel() != size or out.shape[-1] != size:
+        raise KernelError("rmsnorm_deferred: size mismatch")
+    if n_rows is None:
+        n_rows = rows.numel() if rows is not None else x.shape[0]
+    if rows is not None:
+        _int32(rows, "rows")
+    if out.shape[0] < n_rows or ssq.dtype != torch.float32 or ssq.numel() < n_rows:
+        raise KernelError("rmsnorm_deferred: out or ssq has too few rows")
+    f = _fn("elementwise", "kipp_rmsnorm_deferred",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), dtype_code(out.dtype), _ptr(ssq), _ptr(x), _ptr(weight), dtype_code(weight.dtype),
+             _ptr(rows), n_rows, size, _stream()), "rmsnorm_deferred")
+
+
 def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: str = "store",
          m: Optional[int] = None, impl: Optional[str] = None) -> None:
     """out = a @ w.T with float32 accumulation; ``a`` [M, K], ``w`` [N, K].

@@ -49,9 +49,9 @@ def plain_logits(name: str, dtype: str, tokens: list) -> torch.Tensor:
     key = (name, dtype, tuple(tokens))
     if key not in _plain_cache:
         cfg, w = plain_weights(name, dtype)
-        rounding = P.bf16_round if dtype == "bfloat16" else P.no_round
+        path = P.BF16_PATH if dtype == "bfloat16" else P.F32_PATH
         with torch.no_grad():
-            _plain_cache[key] = P.plain_forward(cfg, w, list(tokens), rounding=rounding)
+            _plain_cache[key] = P.plain_forward(cfg, w, list(tokens), **path)
     return _plain_cache[key]
 
 

@@ -35,11 +35,14 @@ def plain_embedding(table: torch.Tensor, tokens) -> torch.Tensor:
     return table[torch.as_tensor(tokens, dtype=torch.long)].to(F64)
 
 
-def plain_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+def plain_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, stored=None) -> torch.Tensor:
     """y_i = x_i / sqrt(mean(x^2) + eps) * w_i over the last dim
-    (rms_norm, src/kipp.c:2221-2231)."""
+    (rms_norm, src/kipp.c:2221-2231).  ``stored`` emulates a 16-bit path that
+    keeps x_i * w_i in 16 bits and applies the row's factor afterwards in 32-bit."""
     x = x.to(F64)
     scale = 1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / x.shape[-1] + eps)
+    if stored is not None:
+        return stored(x * weight.to(F64)) * scale
     return x * scale * weight.to(F64)
 
 
@@ -122,10 +125,12 @@ def layer_window(config: dict, layer: int):
 
 
 def plain_block(x, config: dict, w: dict, prefix: str, layer: int, rounding=no_round,
-                positions=None, kv_rounding=None) -> torch.Tensor:
+                positions=None, kv_rounding=None, norm_stored=None) -> torch.Tensor:
     """One layer in the reference's order (cpu_forward, src/kipp.c:2587-2652):
     norm -> q,k,v -> per-head norm of q and k -> rotation of q and k ->
-    attention -> output projection -> add -> norm -> SwiGLU -> add."""
+    attention -> output projection -> add -> norm -> SwiGLU -> add.
+    ``norm_stored``: the two norms of the layer keep x * w in 16 bits and apply the
+    row's factor afterwards (see plain_rmsnorm) instead of rounding the norm's result."""
     T = x.shape[0]
     n_q, n_kv = config["num_attention_heads"], config["num_key_value_heads"]
     D = config.get("head_dim") or config["hidden_size"] // n_q
@@ -134,7 +139,11 @@ def plain_block(x, config: dict, w: dict, prefix: str, layer: int, rounding=no_r
         positions = list(range(T))
     if kv_rounding is None:
         kv_rounding = rounding
-    n = rounding(plain_rmsnorm(x, w[prefix + "input_layernorm.weight"], eps))
+    def block_norm(x, weight):
+        if norm_stored is not None:
+            return plain_rmsnorm(x, weight, eps, stored=norm_stored)
+        return rounding(plain_rmsnorm(x, weight, eps))
+    n = block_norm(x, w[prefix + "input_layernorm.weight"])
     q = rounding(plain_linear(n, w[prefix + "self_attn.q_proj.weight"])).reshape(T, n_q, D)
     k = rounding(plain_linear(n, w[prefix + "self_attn.k_proj.weight"])).reshape(T, n_kv, D)
     v = rounding(plain_linear(n, w[prefix + "self_attn.v_proj.weight"])).reshape(T, n_kv, D)
@@ -147,18 +156,25 @@ def plain_block(x, config: dict, w: dict, prefix: str, layer: int, rounding=no_r
     v = kv_rounding(v)
     a = rounding(plain_attention(q, k, v, layer_window(config, layer))).reshape(T, n_q * D)
     x = x + plain_linear(a, w[prefix + "self_attn.o_proj.weight"])
-    n = rounding(plain_rmsnorm(x, w[prefix + "post_attention_layernorm.weight"], eps))
+    n = block_norm(x, w[prefix + "post_attention_layernorm.weight"])
     x = x + plain_feed_forward(n, w[prefix + "mlp.gate_proj.weight"], w[prefix + "mlp.up_proj.weight"],
                                w[prefix + "mlp.down_proj.weight"], rounding)
     return x
 
 
-def plain_forward(config: dict, w: dict, tokens, rounding=no_round, kv_rounding=None) -> torch.Tensor:
+# How the engine's bfloat16 path stores activations: 16-bit between kernels, and the norms inside
+# a layer as x * w with the row's factor applied by the product that follows.
+BF16_PATH = dict(rounding=bf16_round, norm_stored=bf16_round)
+F32_PATH = dict(rounding=no_round)
+
+
+def plain_forward(config: dict, w: dict, tokens, rounding=no_round, kv_rounding=None, norm_stored=None) -> torch.Tensor:
     """Logits [T, vocab] (float64) of every position of one whole sequence
     (cpu_forward, src/kipp.c:2564-2664, which returns the last row only)."""
     x = plain_embedding(w["model.embed_tokens.weight"], tokens)
     for layer in range(config["num_hidden_layers"]):
-        x = plain_block(x, config, w, f"model.layers.{layer}.", layer, rounding, kv_rounding=kv_rounding)
+        x = plain_block(x, config, w, f"model.layers.{layer}.", layer, rounding, kv_rounding=kv_rounding,
+                        norm_stored=norm_stored)
     n = rounding(plain_rmsnorm(x, w["model.norm.weight"], config["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if config.get("tie_word_embeddings") else w["lm_head.weight"]
     return plain_linear(n, head)

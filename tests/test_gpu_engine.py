@@ -101,10 +101,10 @@ def test_out_of_pages_leaves_every_request_unchanged():
 
 def greedy_plain(name, dtype, prompt, steps):
     cfg, w = plain_weights(name, dtype)
-    rounding = P.bf16_round if dtype == "bfloat16" else P.no_round
+    path = P.BF16_PATH if dtype == "bfloat16" else P.F32_PATH
     seq, gaps = list(prompt), []
     for _ in range(steps):
-        logits = P.plain_forward(cfg, w, seq, rounding=rounding)[-1]
+        logits = P.plain_forward(cfg, w, seq, **path)[-1]
         top = torch.topk(logits, 2).values
         gaps.append(float(top[0] - top[1]))
         seq.append(int(logits.argmax()))
@@ -375,7 +375,8 @@ def test_equal_prompt_portions_without_a_wait_in_between():
 def test_the_serving_kernels_ran_at_the_benchmark_head_size():
     """Configuration E (128-wide heads): a portion of 64 tokens and more takes the
     tcgen05 attention, decoded tokens the split-K kernel with the fused norm, rotation
-    and cache write, and decode steps replay a graph."""
+    and cache write, the norms of a decode step but its first and last run inside the
+    products around them, and decode steps replay a graph."""
     from kipp_b200.engine import Engine, StepEntry
     eng = Engine.from_folder(model_folder("E"), dtype="bfloat16", page_size=16, cache_tokens=1024, max_requests=4,
                              max_batch_tokens=512)
@@ -386,6 +387,7 @@ def test_the_serving_kernels_ran_at_the_benchmark_head_size():
     eng.synchronize()
     c = eng.info()["counters"]
     assert c["tc_prefill_launches"] >= 2 and c["fused_decode_launches"] >= 2 and c["graph_replays"] >= 8
+    assert c["folded_norms"] >= 4 and c["folded_norms"] % 4 == 0       # 2 layers: 4 of a step's 5 norms
 
 
 def test_logit_rows_are_limited():

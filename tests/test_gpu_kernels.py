@@ -58,6 +58,28 @@ def test_rmsnorm(size, out_dtype):
     assert torch.allclose(out.double().cpu(), ref[[6, 0, 3]], **tol(out_dtype))
 
 
+@pytest.mark.parametrize("size", [24, 200, 320, 1000, 2560, 5120])
+def test_rmsnorm_deferred(size):
+    """x * weight alone and the sums of squares beside it; the two give the norm."""
+    g = torch.Generator().manual_seed(size + 1)
+    x = (torch.randn(9, size, generator=g) * 3).to(DEV)
+    for w_dtype in DTYPES:
+        w = (1 + 0.2 * torch.randn(size, generator=g)).to(w_dtype).to(DEV)
+        for out_dtype in DTYPES:
+            out = torch.empty(9, size, dtype=out_dtype, device=DEV)
+            ssq = torch.full((9,), -1.0, device=DEV)
+            ops().rmsnorm_deferred(out, ssq, x, w)
+            assert torch.equal(out.cpu(), (x.cpu() * w.float().cpu()).to(out_dtype))       # one rounding
+            assert torch.allclose(ssq.double().cpu(), (x.double().cpu() ** 2).sum(-1), rtol=1e-6)
+            both = out.double().cpu() / torch.sqrt(ssq.double().cpu()[:, None] / size + 1e-5)
+            assert torch.allclose(both, P.plain_rmsnorm(x.cpu(), w.float().cpu(), 1e-5), **tol(out_dtype))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, size, dtype=torch.bfloat16, device=DEV)
+    ssq = torch.zeros(3, device=DEV)
+    ops().rmsnorm_deferred(out, ssq, x, w, rows)
+    assert torch.equal(out.cpu(), (x.cpu()[[6, 0, 3]] * w.float().cpu()).to(torch.bfloat16))
+
+
 # ------------------------------------------------------------------ matrix products
 def gemm_ref(a, w, epilogue, base):
     p = a.double().cpu() @ w.double().cpu().t()
@@ -152,6 +174,55 @@ def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
             else:
                 scale = float(ref.abs().max())
                 assert float((got - ref).abs().max()) <= (1e-5 if odt == torch.float32 else 1e-2) * scale
+    assert gemm_bf16.status_word(torch.device(DEV)).tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 128, 64), (8, 256, 128), (17, 224, 192), (64, 992, 136), (100, 384, 2568),
+                                   (300, 640, 520), (5, 2560, 1216)])
+def test_gemm_folds_the_norm_around_it(shape, wdtype):
+    """The few-token kernel with an RMSNorm folded in: the residual add also leaves
+    bf16(new residual x norm weight) and the sums of squares of the new residual per
+    32 features; a store or SwiGLU product scales row t by 1 / sqrt(sum / n + eps).
+    Integer data exactly; every K split, the cluster's reduction included."""
+    from kipp_b200.kernels import gemm_bf16
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M * 5 + N)
+    for splits in (0, 1, 3, 8):
+        a = torch.randint(-3, 4, (M, K), generator=g).to(torch.bfloat16).to(DEV)
+        w = torch.randint(-2, 3, (N, K), generator=g).to(torch.bfloat16).to(DEV)
+        base = torch.randint(-8, 9, (M, N), generator=g).float().to(DEV)
+        nw = (torch.randint(1, 5, (N,), generator=g).float() * 0.25).to(wdtype).to(DEV)
+        out = base.clone()
+        xn = torch.full((M, N + 8), 7.0, dtype=torch.bfloat16, device=DEV)
+        ssq = torch.full((M, N // 32), -1.0, device=DEV)
+        gemm_bf16.run("tc", out, a, w, "add", M, splits=splits, fold=gemm_bf16.fold_emit(nw, xn, ssq))
+        ref = gemm_ref(a, w, "add", base).float()
+        assert torch.equal(out.cpu(), ref), (shape, splits)
+        assert torch.equal(xn[:, :N].float().cpu(), (ref * nw.float().cpu()).to(torch.bfloat16).float())
+        assert torch.all(xn[:, N:] == 7.0)
+        assert torch.equal(ssq.cpu(), (ref * ref).view(M, N // 32, 32).sum(-1))
+        # the consumer: rows scaled by the factor that the sums give
+        eps = 1e-3
+        rstd = 1.0 / torch.sqrt(ssq.double().cpu().sum(-1, keepdim=True) / N + eps)
+        for epilogue in ("store", "swiglu"):
+            n_out = N // 2 if epilogue == "swiglu" else N
+            got = torch.zeros(M, n_out, device=DEV)
+            gemm_bf16.run("tc", got, a, w, epilogue, M, splits=splits, fold=gemm_bf16.fold_scale(ssq, N, eps))
+            p = (a.double().cpu() @ w.double().cpu().t()) * rstd
+            want = P.plain_silu(p[:, 0::2]) * p[:, 1::2] if epilogue == "swiglu" else p
+            assert float((got.double().cpu() - want).abs().max()) <= 2e-6 * max(1.0, float(want.abs().max()))
+        # ... and so do the kernels of prompt-sized batches (forced here), which cannot emit
+        for tile_f in (-128, -1160):
+            for epilogue in ("store", "swiglu"):
+                n_out = N // 2 if epilogue == "swiglu" else N
+                got = torch.zeros(M, n_out, device=DEV)
+                gemm_bf16.run("tc", got, a, w, epilogue, M, tile_f=tile_f, fold=gemm_bf16.fold_scale(ssq, N, eps))
+                p = (a.double().cpu() @ w.double().cpu().t()) * rstd
+                want = P.plain_silu(p[:, 0::2]) * p[:, 1::2] if epilogue == "swiglu" else p
+                assert float((got.double().cpu() - want).abs().max()) <= 2e-6 * max(1.0, float(want.abs().max()))
+            with pytest.raises(Exception):
+                gemm_bf16.run("tc", out, a, w, "add", M, tile_f=tile_f, fold=gemm_bf16.fold_emit(nw, xn, ssq))
     assert gemm_bf16.status_word(torch.device(DEV)).tolist() == [0, 0, 0, 0]
 
 
@@ -508,11 +579,11 @@ def test_burst_advance_moves_a_step_on():
         rows = dev(torch.arange(n).int())
         split = dev(torch.zeros(n + 3).int())
         for kv_heads, sms in ((8, 148), (2, 148), (1, 132)):
-            attention_bf16.decode_replan(split, context, rows, kv_heads, 3 * sms, 5, 64, 32, own_length=False)
+            attention_bf16.decode_replan(split, context, rows, kv_heads, 3 * sms, 5, 32, own_length=False)
             want = split_length(n, longest + 2, kv_heads, sms)
             assert split[:n].cpu().tolist() == [want] * n, (n, longest, kv_heads)
             assert split[n:].eq(0).all()
-        attention_bf16.decode_replan(split, context, rows, 8, 444, 5, 64, 32, own_length=True)
+        attention_bf16.decode_replan(split, context, rows, 8, 444, 5, 32, own_length=True)
         assert split[:n].cpu().tolist() == [split_length(1, int(x) + 2, own=True) for x in lens]
         # a full ring: the tokens are still handed over, no row is written
         counter.fill_(4)

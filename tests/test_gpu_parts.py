@@ -146,7 +146,7 @@ def test_block_alone(dtype):
     assert len(block.tensor_specs("model.layers.0.")) == 11
     eng, w = part_engine(dtype, 80, sigma=0.12, page_size=4, n_pages=32, block=block)
     x = torch.randn(23, 80)
-    want = P.plain_block(x.double(), cfg, w, "model.layers.0.", 0, rounding(dtype))
+    want = P.plain_block(x.double(), cfg, w, "model.layers.0.", 0, **(P.BF16_PATH if dtype == "bfloat16" else P.F32_PATH))
     xd = x.to(DEV)
     eng.run_part([("r", [0] * 23, [])], 0, "block", residual=xd)
     assert torch.allclose(xd.double().cpu(), want, **part_tol(dtype))

@@ -61,7 +61,7 @@ def test_random_configuration_against_the_plain_model(tmp_path, seed):
         rows += [(at + i, out[k]) for k, i in enumerate(want)]
         at += n
     wb = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in w.items()}
-    ref = P.plain_forward(c, wb, toks[:at], rounding=P.bf16_round, kv_rounding=P.bf16_round).double()
+    ref = P.plain_forward(c, wb, toks[:at], kv_rounding=P.bf16_round, **P.BF16_PATH).double()
     worst = max((nmse(r, ref[pos]), pos) for pos, r in rows)
     assert worst[0] < 1e-4, (cfg, page, cuts, worst)
     eng.finish("r")

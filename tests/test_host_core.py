@@ -47,8 +47,9 @@ def test_split_rule_of_the_decode_attention():
     lib = N.lib()
     # few (token, kv head) pairs: many short splits; many pairs: few long ones
     few, many = lib.kipp_attention_split_length(1, 2048, 8, 148, 0), lib.kipp_attention_split_length(64, 2048, 8, 148, 0)
-    assert 64 <= few <= 256 and many >= 512 and few % 64 == 0 and many % 64 == 0
+    assert few == 64 and many >= 512 and many % 64 == 0        # one token: one tile per split (latency)
     assert lib.kipp_attention_split_length(1, 100, 8, 148, 0) == 64
+    assert lib.kipp_attention_split_length(8, 2048, 8, 148, 0) == 384      # 6 splits: 384 CTAs, one wave
     # from the token's own context: an eighth of it, in whole 64-key tiles, at least one tile
     assert lib.kipp_attention_split_length(1, 8192, 8, 148, 1) == 1024
     assert lib.kipp_attention_split_length(1, 700, 8, 148, 1) == 128
