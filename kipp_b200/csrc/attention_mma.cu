@@ -733,9 +733,9 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
 // (context_len[rows[i]] + 1 keys), by the rule the host uses when it packs a step
 // (AttentionPlanner in csrc/host/parts.hpp): with own_length, an eighth of the token's own
 // context (so a token's result does not depend on its neighbours); else, for the whole step,
-// the number of 64-key tiles per split with the best (share of the resident CTA slots that the
-// waves fill) x (share of a CTA's time spent on keys rather than on its fixed cost), on a tie
-// the fewer splits.  One block; used between the steps of a burst that runs without the host.
+// the number of 64-key tiles per split k with the least (waves of resident CTAs) x (k + a CTA's
+// fixed cost in tiles), on a tie the fewer splits.  One block; used between the steps of a
+// burst that runs without the host.
 namespace {
 struct SplitRule { int pairs_per_entry, resident_ctas, fixed_tiles, max_splits, own_length; };
 __global__ void attn_decode_replan_kernel(int* split_keys, const int* context_len, const int* rows, int n,
@@ -755,15 +755,13 @@ __global__ void attn_decode_replan_kernel(int* split_keys, const int* context_le
         const long long pairs = (long long)n * rule.pairs_per_entry;
         const int total = (longest + TILE_KEYS - 1) / TILE_KEYS;
         int best = total;
-        double best_score = -1.0;
+        long long best_cost = -1;
         for (int k = total; k >= 1; --k) {
             const int splits = (total + k - 1) / k;
             if (splits > rule.max_splits) break;
-            const long long ctas = pairs * splits;
-            const long long waves = (ctas + rule.resident_ctas - 1) / rule.resident_ctas;
-            const double score = (double)ctas / (double)(waves * rule.resident_ctas) * (double)k /
-                                 (double)(k + rule.fixed_tiles);
-            if (score > best_score + 1e-9) { best = k; best_score = score; }
+            const long long waves = (pairs * splits + rule.resident_ctas - 1) / rule.resident_ctas;
+            const long long cost = waves * (k + rule.fixed_tiles);
+            if (best_cost < 0 || cost < best_cost) { best = k; best_cost = cost; }
         }
         shared_s = best * TILE_KEYS;
     }

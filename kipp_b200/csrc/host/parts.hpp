@@ -167,27 +167,27 @@ public:
         n[0] = decode; n[1] = decode; n[2] = 2 * items; n[3] = 2 * all; n[4] = 2 * items128;
     }
 
-    // Keys per split for the decoded tokens of a step, in whole 64-key tiles.  Among the numbers of
-    // tiles per split k (splits = total tiles / k, rounded up, at most DECODE_MAX_SPLITS) the one
-    // with the best (share of the resident CTA slots that the waves fill) x (share of a CTA's time
-    // spent on keys rather than on its set-up, its merge of four warps and its partial results):
-    // many short splits fill the GPU when there are few (token, kv head) pairs (a single token's
-    // attention is bound by latency, so one tile per split), few long ones are better once the
-    // pairs alone fill it.  On a tie the fewer splits.  The device makes the same choice between
-    // the steps of a burst (kipp_attn_decode_replan): same integers, same double arithmetic.
+    // Keys per split for the decoded tokens of a step, in whole 64-key tiles.  A CTA takes one
+    // split of one (token, kv head) pair and costs its k tiles plus a fixed part (its set-up, the
+    // merge of its four warps, its partial results); the CTAs run in waves of as many as the GPU
+    // holds at once.  Among the numbers of tiles per split k (splits = total tiles / k, rounded
+    // up, at most DECODE_MAX_SPLITS) the one with the least waves x (k + fixed part) is taken: many
+    // short splits when there are few pairs (a single token's attention is bound by latency, so
+    // down to one tile per split), few long ones once the pairs alone fill the GPU.  On a tie the
+    // fewer splits.  The device makes the same choice between the steps of a burst
+    // (kipp_attn_decode_replan): integers only, so both agree.
     int step_split_length(int decoded, int longest) const {
         if (decoded <= 0 || longest <= 0) return TILE;
         const long long pairs = (long long)decoded * kv_heads_;
         const int total = (longest + TILE - 1) / TILE;
         int best = total;
-        double best_score = -1.0;
+        long long best_cost = -1;
         for (int k = total; k >= 1; --k) {
             const int splits = (total + k - 1) / k;
             if (splits > Ops::DECODE_MAX_SPLITS) break;
-            const long long ctas = pairs * splits;
-            const long long waves = (ctas + resident_ - 1) / resident_;
-            const double score = (double)ctas / (double)(waves * resident_) * (double)k / (double)(k + CTA_FIXED_TILES);
-            if (score > best_score + 1e-9) { best = k; best_score = score; }
+            const long long waves = (pairs * splits + resident_ - 1) / resident_;
+            const long long cost = waves * (k + CTA_FIXED_TILES);
+            if (best_cost < 0 || cost < best_cost) { best = k; best_cost = cost; }
         }
         return best * TILE;
     }
