@@ -224,10 +224,15 @@ public:
         ++fused_decode_launches;
     }
 
+    // The first maximum of each row; long rows are shared among blocks (two launches then).
     void argmax_rows(const float* logits, long long ld, int rows, int n, int* out) {
-        using Fn = int (*)(const float*, long long, int, int, int*, void*);
-        static Fn f = kernel_symbol<Fn>("sampling", "kipp_argmax_rows");
-        run(f(logits, ld, rows, n, out, stream), "argmax_rows");
+        using Fn = int (*)(const float*, long long, int, int, int*, void*, long long, void*);
+        using Fb = long long (*)(int, int);
+        static Fn f = kernel_symbol<Fn>("sampling", "kipp_argmax_rows_split");
+        static Fb bytes = kernel_symbol<Fb>("sampling", "kipp_argmax_scratch_bytes");
+        const long long need = bytes(rows, n);
+        void* scratch = need > 0 ? workspace->buffer("argmax_parts", (size_t)need) : nullptr;
+        run(f(logits, ld, rows, n, out, scratch, need, stream), "argmax_rows", need > 0 ? 2 : 1);
     }
     void sample_rows(const float* logits, long long ld, int rows, int n, const float* temperature, const int* top_k,
                      const float* top_p, const float* min_p, const double* uniform, int* out) {

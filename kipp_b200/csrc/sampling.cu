@@ -167,7 +167,8 @@ __device__ void select(const RowCtx& c, Shared& sh, int mode, unsigned long long
     }
 }
 
-__device__ void block_argmax(const float* v, int n, Shared& sh, float& best_v, int& best_i) {
+// best_i = 0x7fffffff when the row holds no number (NaN only)
+__device__ void block_argmax_raw(const float* v, int n, Shared& sh, float& best_v, int& best_i) {
     float bv = -INFINITY; int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float x = v[i];
@@ -194,11 +195,16 @@ __device__ void block_argmax(const float* v, int n, Shared& sh, float& best_v, i
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) { sh.f_val = bv; sh.i_val = (bi == 0x7fffffff) ? 0 : bi; }
+        if (lane == 0) { sh.f_val = bv; sh.i_val = bi; }
     }
     __syncthreads();
     best_v = sh.f_val; best_i = sh.i_val;
     __syncthreads();
+}
+
+__device__ void block_argmax(const float* v, int n, Shared& sh, float& best_v, int& best_i) {
+    block_argmax_raw(v, n, sh, best_v, best_i);
+    if (best_i == 0x7fffffff) best_i = 0;
 }
 
 __global__ void __launch_bounds__(THREADS)
@@ -209,6 +215,45 @@ argmax_rows_kernel(const float* __restrict__ logits, long long ld, int n, int* _
     float bv; int bi;
     block_argmax(logits + (size_t)blockIdx.x * ld, n, sh, bv, bi);
     if (threadIdx.x == 0) out[blockIdx.x] = bi;
+}
+
+// A long row by many blocks: block (c, r) leaves the first maximum of its share of row r, the
+// second kernel takes the first maximum of the shares (in share order, so the lowest index wins
+// a tie as in the one-block kernel).  One block per row would scan a 150,000-entry row alone
+// for 70 us; the shares take a few.
+struct ArgmaxPart { float v; int i; };
+
+__global__ void __launch_bounds__(THREADS)
+argmax_parts_kernel(const float* __restrict__ logits, long long ld, int n, int per, ArgmaxPart* __restrict__ parts) {
+    __shared__ Shared sh;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int first = blockIdx.x * per;
+    const int count = min(per, n - first);
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    if (count > 0) block_argmax_raw(logits + (size_t)blockIdx.y * ld + first, count, sh, bv, bi);
+    if (threadIdx.x == 0)
+        parts[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = ArgmaxPart{bv, bi == 0x7fffffff ? bi : first + bi};
+}
+
+__global__ void argmax_merge_kernel(const ArgmaxPart* __restrict__ parts, int n_parts, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    // one warp per row; lane l takes shares l, l + 32, ... in order, then the lanes in order
+    const ArgmaxPart* row = parts + (size_t)blockIdx.x * n_parts;
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < n_parts; c += 32) {
+        const ArgmaxPart p = row[c];
+        if (p.v > bv || (p.v == bv && p.i < bi)) { bv = p.v; bi = p.i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    // a row without any number (NaN only) leaves every share without an index: index 0 then
+    if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
 }
 
 __global__ void __launch_bounds__(THREADS)
@@ -379,6 +424,36 @@ extern "C" int kipp_argmax_rows(const float* logits, long long ld, int rows, int
     if (rows <= 0) return 0;
     if (n <= 0) return KIPP_ERR_ARG;
     return kipp_launch(argmax_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n, out);
+}
+
+// How a row of n entries is shared among blocks: shares of at least ARGMAX_SHARE entries, at most 64.
+namespace {
+constexpr int ARGMAX_SHARE = 4096;
+inline int argmax_shares(int n) { return n >= 2 * ARGMAX_SHARE ? (n / ARGMAX_SHARE > 64 ? 64 : n / ARGMAX_SHARE) : 1; }
+}  // namespace
+
+// Bytes of scratch kipp_argmax_rows_split wants for rows of n entries (0: the one-block kernel does it).
+extern "C" long long kipp_argmax_scratch_bytes(int rows, int n) {
+    const int shares = argmax_shares(n);
+    return shares > 1 ? (long long)rows * shares * (long long)sizeof(ArgmaxPart) : 0;
+}
+
+// kipp_argmax_rows with long rows shared among blocks; `scratch` of kipp_argmax_scratch_bytes,
+// 8-byte aligned, is the caller's and holds nothing between calls.
+extern "C" int kipp_argmax_rows_split(const float* logits, long long ld, int rows, int n, int* out, void* scratch,
+                                      long long scratch_bytes, void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0) return KIPP_ERR_ARG;
+    const int shares = argmax_shares(n);
+    if (shares <= 1) return kipp_argmax_rows(logits, ld, rows, n, out, stream);
+    if (scratch == nullptr || ((uintptr_t)scratch & 7) || scratch_bytes < kipp_argmax_scratch_bytes(rows, n) || rows > 65535)
+        return KIPP_ERR_ARG;
+    const int per = (n + shares - 1) / shares;
+    int rc = kipp_launch(argmax_parts_kernel, dim3(shares, rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld,
+                         n, per, (ArgmaxPart*)scratch);
+    if (rc) return rc;
+    return kipp_launch(argmax_merge_kernel, dim3(rows), dim3(32), 0, (cudaStream_t)stream, 1,
+                       (const ArgmaxPart*)scratch, shares, out);
 }
 
 extern "C" int kipp_sample_rows(const float* logits, long long ld, int rows, int n,

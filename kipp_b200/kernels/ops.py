@@ -62,13 +62,13 @@ def _check(code: int, what: str) -> None:
 _fn_cache: dict[tuple[str, str], object] = {}
 
 
-def _fn(lib: str, name: str, argtypes: list) -> object:
+def _fn(lib: str, name: str, argtypes: list, restype=c_int) -> object:
     key = (lib, name)
     f = _fn_cache.get(key)
     if f is None:
         f = getattr(load_library(lib), name)
         f.argtypes = argtypes
-        f.restype = c_int
+        f.restype = restype
         _fn_cache[key] = f
     return f
 

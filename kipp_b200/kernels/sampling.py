@@ -21,8 +21,10 @@ def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
     rows, n = _rows(logits)
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    f = _fn("sampling", "kipp_argmax_rows", [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(logits), logits.stride(0), rows, n, _ptr(out), _stream()), "argmax_rows")
+    need = _fn("sampling", "kipp_argmax_scratch_bytes", [c_int, c_int], restype=c_ll)(rows, n)
+    scratch = torch.empty(max(1, need // 8), dtype=torch.int64, device=logits.device)   # long rows: shares of blocks
+    f = _fn("sampling", "kipp_argmax_rows_split", [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_ll, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), rows, n, _ptr(out), _ptr(scratch), need, _stream()), "argmax_rows")
     return out
 
 

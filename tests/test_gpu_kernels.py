@@ -591,12 +591,18 @@ def test_burst_advance_moves_a_step_on():
         assert int(counter) == 5 and ring[[0, 1, 3]].eq(-7).all()
 
 
-def test_argmax_first_maximum():
-    logits = torch.randn(5, 1000, generator=torch.Generator().manual_seed(1)).to(DEV)
-    logits[1, 7] = logits[1, 900] = 50.0
+@pytest.mark.parametrize("n", [1000, 8191, 8192, 151936, 300001])
+def test_argmax_first_maximum(n):
+    """Short rows by one block, long rows shared among blocks: the first maximum either way,
+    also where the maxima sit in different shares, and index 0 for a row without a number."""
+    logits = torch.randn(7, n + 3, generator=torch.Generator().manual_seed(1))[:, :n].to(DEV)     # a pitch beside n
+    logits[1, 7] = logits[1, n - 100] = 50.0
     logits[2, :] = 0.25
+    logits[5, :] = float("nan")
+    logits[6, :] = float("-inf")
+    logits[6, : n // 2] = float("nan")
     out = ops().argmax_rows(logits).cpu().tolist()
-    assert out == [int(logits[0].argmax()), 7, 0, int(logits[3].argmax()), int(logits[4].argmax())]
+    assert out == [int(logits[0].argmax()), 7, 0, int(logits[3].argmax()), int(logits[4].argmax()), 0, n // 2]
 
 
 @pytest.mark.parametrize("vocab", [1000, 151936])
