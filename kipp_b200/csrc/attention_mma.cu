@@ -345,6 +345,62 @@ __device__ __forceinline__ void warp_norm_rope(float (&x)[D / 32], const void* n
     }
 }
 
+// out[:] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m) of one head, splits in order, by one
+// warp.  `ml` [n_splits][2], `po` [n_splits][D]; `weight` is 64 floats of shared memory of this warp.
+__device__ __forceinline__ void warp_merge_head(bf16* __restrict__ dst, const float* ml, const float* po,
+                                                int n_splits, int head_dim, float* weight, int lane) {
+    float m[2], l[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int s = lane + 32 * i;
+        m[i] = s < n_splits ? __ldcg(ml + 2 * s) : -INFINITY;
+        l[i] = s < n_splits ? __ldcg(ml + 2 * s + 1) : 0.f;
+    }
+    const float mx = warp_max(fmaxf(m[0], m[1]));
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float w = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - mx);
+        weight[lane + 32 * i] = w;
+        total += l[i] * w;
+    }
+    // sum in split order would need a serial loop; lanes hold splits s and s + 32,
+    // a fixed tree over lanes keeps the order the same for every token
+    total = warp_sum(total);
+    const float inv_sum = total > 0.f ? 1.f / total : 0.f;
+    __syncwarp();
+    // a lane takes four neighbouring values (head sizes are multiples of 16); the loads of eight
+    // splits are issued together, then added in split order
+    for (int d = 4 * lane; d < head_dim; d += 128) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                // a split with no key in reach (wholly behind a window) has weight 0 and wrote no
+                // partial output: what lies in the scratch there is not read (0 x garbage may be NaN)
+                const bool live = s0 + i < n_splits && weight[s0 + i] != 0.f;
+                v[i] = live ? __ldcg(reinterpret_cast<const float4*>(po + (size_t)(s0 + i) * head_dim + d))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float w = s0 + i < n_splits ? weight[s0 + i] : 0.f;
+                if (w != 0.f) {
+                    acc[0] += v[i].x * w; acc[1] += v[i].y * w; acc[2] += v[i].z * w; acc[3] += v[i].w * w;
+                }
+            }
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0] * inv_sum, acc[1] * inv_sum);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(acc[2] * inv_sum, acc[3] * inv_sum);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst + d) = packed;
+    }
+    __syncwarp();
+}
+
 // Keys per split for a context of kv_len keys: the step's split length, or
 // longer when max_splits of them would not cover the context.
 __host__ __device__ __forceinline__ int decode_split_keys(int kv_len, int max_splits, int split_keys_min) {
@@ -586,60 +642,30 @@ attn_decode_kernel(const DecodeParams p) {
     }
 }
 
-// out[token, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m), splits in order.
-__global__ void attn_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, const int* __restrict__ rows,
-                                         const int* __restrict__ q_start, const int* __restrict__ context_len,
-                                         int n_q, int head_dim, int max_splits,
-                                         const int* __restrict__ split_keys_ptr, int split_stride) {
+// The merge of a token's splits: a warp per head, WARPS heads per block.  (Merging inside the
+// split kernel, by the CTA that finishes a token's last split, was measured and is no faster:
+// one CTA then does behind a fence what this launch spreads over many while the next kernel
+// already prefetches its weights.)
+__global__ void __launch_bounds__(THREADS)
+attn_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                         const float* __restrict__ part_ml, const int* __restrict__ rows,
+                         const int* __restrict__ q_start, const int* __restrict__ context_len,
+                         int n_q, int head_dim, int max_splits,
+                         const int* __restrict__ split_keys_ptr, int split_stride) {
+    __shared__ float weight[WARPS * 64];           // max_splits <= 64 checked by the launcher
     pdl_launch_dependents();
     pdl_wait();
-    const int n = blockIdx.y, h = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.y, h = blockIdx.x * WARPS + warp;
+    if (h >= n_q) return;
     const int entry = rows[n];
     const int kv_len = context_len[entry] + 1;
     const int split_keys = decode_split_keys(kv_len, max_splits, __ldg(split_keys_ptr + n * split_stride));
     const int n_splits = (kv_len + split_keys - 1) / split_keys;
     if (n_splits == 1) return;                     // the split kernel wrote the result itself
-    const float* ml = part_ml + ((size_t)n * n_q + h) * max_splits * 2;
-    const float* po = part_o + ((size_t)n * n_q + h) * max_splits * head_dim;
-    // weights of the splits first (all loads at once), then the weighted sum
-    __shared__ float weight[64];                   // max_splits <= 64 checked by the launcher
-    __shared__ float inv_sum;
-    if (threadIdx.x < 32) {
-        float m[2], l[2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int s = threadIdx.x + 32 * i;
-            m[i] = s < n_splits ? ml[2 * s] : -INFINITY;
-            l[i] = s < n_splits ? ml[2 * s + 1] : 0.f;
-        }
-        const float mx = warp_max(fmaxf(m[0], m[1]));
-        float total = 0.f;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int s = threadIdx.x + 32 * i;
-            const float w = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - mx);
-            if (s < 64) weight[s] = w;
-            total += l[i] * w;
-        }
-        // sum in split order would need a serial loop; lanes hold splits s and s + 32,
-        // a fixed tree over lanes keeps the order the same for every token
-        total = warp_sum(total);
-        if (threadIdx.x == 0) inv_sum = total > 0.f ? 1.f / total : 0.f;
-    }
-    __syncthreads();
-    bf16* dst = out + ((size_t)q_start[entry] * n_q + h) * head_dim;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
-        float acc = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < n_splits; ++s) {
-            // a split with no key in reach (wholly behind a window) has weight 0 and wrote no
-            // partial output: what lies in the scratch there is not read (0 x garbage may be NaN)
-            const float w = weight[s];
-            if (w != 0.f) acc += po[(size_t)s * head_dim + d] * w;
-        }
-        dst[d] = __float2bfloat16_rn(acc * inv_sum);
-    }
+    const size_t head = (size_t)n * n_q + h;
+    warp_merge_head(out + ((size_t)q_start[entry] * n_q + h) * head_dim, part_ml + head * max_splits * 2,
+                    part_o + head * max_splits * head_dim, n_splits, head_dim, weight + warp * 64, lane);
 }
 
 template <int D> int launch_prefill(const PrefillParams& p, int items, cudaStream_t s) {
@@ -651,6 +677,12 @@ template <int D> int launch_prefill(const PrefillParams& p, int items, cudaStrea
         configured = true;
     }
     return kipp_launch(attn_prefill_kernel<D>, dim3(items, p.n_q), dim3(THREADS), SMEM, s, 1, p);
+}
+
+inline int launch_merge(const DecodeParams& p, void* out, int n, int head_dim, cudaStream_t s) {
+    return kipp_launch(attn_decode_merge_kernel, dim3((p.n_q + WARPS - 1) / WARPS, n), dim3(THREADS), 0, s, 1,
+                       (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, p.rows, p.q_start, p.context_len,
+                       p.n_q, head_dim, p.max_splits, p.split_keys, p.split_stride);
 }
 
 template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s) {
@@ -700,7 +732,7 @@ extern "C" long long kipp_attn_decode_scratch_bytes(int n, int n_q, int head_dim
 }
 
 // Single decoded tokens: `rows` lists the n entries; scratch as sized above
-// (part_o first, then part_ml).
+// (part_o first, then part_ml), 16-byte aligned.
 extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
                                     const int* q_start, const int* context_len, const int* block_table,
                                     int table_width, int page_size, const int* rows, int n, int n_q, int n_kv,
@@ -708,7 +740,8 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
                                     const int* split_keys, int split_stride, float* scratch, void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
-        max_splits > 64 || split_keys == nullptr || scratch == nullptr)
+        max_splits > 64 || split_keys == nullptr || scratch == nullptr || ((uintptr_t)scratch & 15) ||
+        ((uintptr_t)out & 7))
         return KIPP_ERR_ARG;
     DecodeParams p;
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
@@ -724,9 +757,7 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     cudaStream_t s = (cudaStream_t)stream;
     int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
     if (rc) return rc;
-    return kipp_launch(attn_decode_merge_kernel, dim3(n_q, n), dim3(head_dim >= 128 ? 128 : 64), 0, s, 1,
-                       (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, rows, q_start, context_len, n_q,
-                       head_dim, max_splits, split_keys, split_stride ? 1 : 0);
+    return launch_merge(p, out, n, head_dim, s);
 }
 
 // The keys per split of each decoded token, chosen on the device from the cached lengths
@@ -801,7 +832,8 @@ extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long 
                                           void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
-        max_splits > 64 || split_keys == nullptr || scratch == nullptr || status == nullptr || qkv == nullptr ||
+        max_splits > 64 || split_keys == nullptr || scratch == nullptr || ((uintptr_t)scratch & 15) ||
+        ((uintptr_t)out & 7) || status == nullptr || qkv == nullptr ||
         ld_qkv < (long long)(n_q + 2 * n_kv) * head_dim || ld_qkv > 0x7fffffffLL ||
         (q_norm_w == nullptr) != (k_norm_w == nullptr))
         return KIPP_ERR_ARG;
@@ -824,7 +856,5 @@ extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long 
     cudaStream_t s = (cudaStream_t)stream;
     int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
     if (rc) return rc;
-    return kipp_launch(attn_decode_merge_kernel, dim3(n_q, n), dim3(head_dim >= 128 ? 128 : 64), 0, s, 1,
-                       (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, rows, q_start, context_len, n_q,
-                       head_dim, max_splits, split_keys, split_stride ? 1 : 0);
+    return launch_merge(p, out, n, head_dim, s);
 }

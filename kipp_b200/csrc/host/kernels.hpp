@@ -178,7 +178,6 @@ public:
         if (floats < (1u << 20)) floats = 1u << 20;
         return workspace->get<float>("attention_decode_scratch", floats);
     }
-
     // Causal grouped-query attention of the step's tokens over the paged cache.
     void attention(void* out, const void* q, const PagedCacheView& cache, int dtype, const AttentionWork& work,
                    const int* positions, const int* entry_of_token, const int* q_start, const int* context_len,
