@@ -863,7 +863,18 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // back.  (A first version let a thread of the second CTA relay "my stage is full"
 // to the first: one relay per K block took about a microsecond, three times the
 // MMAs of the block.)
+//
+// Tiles wider than the 256 features one MMA takes (288, 320) are made of two MMAs of half the
+// width per K step, side by side in ONE accumulator (288 or 320 of the 512 tensor-memory
+// columns, so no second accumulator: the next tile's MMAs wait for this tile's epilogue).
+// They are for shapes whose narrower tiles leave a second, nearly empty round: 2,048 tokens x
+// 2,560 features are 8 x 9 tiles of 288 = 72 pairs = one round on 74 pairs of SMs.  A CTA's
+// share of the weight tile then lies in two blocks of SUB_N / 2 rows, one per MMA.
 template <int TILE_N, bool REDUCE> struct CfgPair {
+    static constexpr int SUBS = TILE_N > 256 ? 2 : 1;            // MMAs per K step
+    static constexpr int SUB_N = TILE_N / SUBS;                  // features of one MMA
+    static constexpr int SUB_ROWS = SUB_N / 2;                   // its weight rows in one CTA
+    static constexpr int SUB_BYTES = SUB_ROWS * TILE_K * 2;
     static constexpr int HALF_N = TILE_N / 2;                    // weight rows per CTA
     static constexpr int X_BYTES = UMMA_M * TILE_K * 2;
     static constexpr int W_BYTES = HALF_N * TILE_K * 2;
@@ -871,8 +882,11 @@ template <int TILE_N, bool REDUCE> struct CfgPair {
     static constexpr int STAGING = REDUCE ? 8 * RED_BYTES : 0;
     static constexpr int BUDGET = 227 * 1024 - 1024 - 512 - STAGING;
     static constexpr int STAGES = BUDGET / STAGE_BYTES > 8 ? 8 : BUDGET / STAGE_BYTES;
-    static constexpr int TMEM_COLS = TILE_N <= 128 ? 128 : 256;
+    static constexpr int TMEM_COLS = TILE_N <= 128 ? 128 : (TILE_N <= 256 ? 256 : 512);
+    static constexpr int ACCS = TILE_N <= 256 ? 2 : 1;           // accumulators in tensor memory
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING + 1024 + 512;
+    static_assert(SUB_N % 16 == 0 && SUB_ROWS % 8 == 0 && SUB_N <= 256, "one MMA of the pair");
+    static_assert(STAGE_BYTES % 1024 == 0 && SUB_BYTES % 1024 == 0, "swizzled tiles start on 1,024 bytes");
 };
 
 template <int TILE_N, bool REDUCE>
@@ -880,13 +894,13 @@ __global__ void __launch_bounds__(THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_c, const Params p) {
     using C = CfgPair<TILE_N, REDUCE>;
-    static_assert(TILE_N % RED_BOX == 0 && TILE_N >= 2 * RED_BOX && TILE_N <= 256, "feature tile");
+    static_assert(TILE_N % RED_BOX == 0 && TILE_N >= 2 * RED_BOX && TILE_N <= 320, "feature tile");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* staging = tiles + (size_t)C::STAGES * C::STAGE_BYTES;        // 1024-byte aligned
     uint64_t* full = (uint64_t*)(staging + C::STAGING);
     uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_full = empty + C::STAGES;        // [2]
+    uint64_t* acc_full = empty + C::STAGES;        // [2] (one in use with a single accumulator)
     uint64_t* acc_empty = acc_full + 2;            // [2], used in the first CTA only
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -908,7 +922,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc_pair(tmem_slot, 2 * C::TMEM_COLS);
+    if (warp == 1) tmem_alloc_pair(tmem_slot, C::ACCS * C::TMEM_COLS);
     tcgen05_fence_before();
     __syncthreads();
     cluster_sync_all();                             // the other CTA's barriers exist before anyone arrives on them
@@ -920,12 +934,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0 && pair < total_tiles) {
             const int ahead = min(n_kb, C::STAGES);
             {
-                const int f0 = (pair / m_tiles) * TILE_N + (int)rank * C::HALF_N;
+                const int f0 = (pair / m_tiles) * TILE_N + (int)rank * C::SUB_ROWS;
                 const int t0 = (pair % m_tiles) * (2 * UMMA_M) + (int)rank * UMMA_M;
                 for (int i = 0; i < ahead; ++i) {
                     if (rank == 0) mbar_expect_tx(&full[i], 2 * C::STAGE_BYTES);
-                    tma_load_2d_pair(tiles + (size_t)i * C::STAGE_BYTES + C::X_BYTES, &map_w, mbar_in_cta(&full[i], 0),
-                                     i * TILE_K, f0);
+#pragma unroll
+                    for (int j = 0; j < C::SUBS; ++j)
+                        tma_load_2d_pair(tiles + (size_t)i * C::STAGE_BYTES + C::X_BYTES + j * C::SUB_BYTES, &map_w,
+                                         mbar_in_cta(&full[i], 0), i * TILE_K, f0 + j * C::SUB_N);
                 }
                 pdl_wait();
                 for (int i = 0; i < ahead; ++i)
@@ -935,7 +951,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             int it = ahead;
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-                const int f0 = (tile / m_tiles) * TILE_N + (int)rank * C::HALF_N;
+                const int f0 = (tile / m_tiles) * TILE_N + (int)rank * C::SUB_ROWS;
                 const int t0 = (tile % m_tiles) * (2 * UMMA_M) + (int)rank * UMMA_M;
                 for (int i = (tile == pair ? ahead : 0); i < n_kb; ++i, ++it) {
                     const int s = it % C::STAGES;
@@ -947,19 +963,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const uint32_t bar = mbar_in_cta(&full[s], 0);
                     if (rank == 0) mbar_expect_tx(&full[s], 2 * C::STAGE_BYTES);
                     tma_load_2d_pair(xt, &map_x, bar, i * TILE_K, t0);
-                    tma_load_2d_pair(xt + C::X_BYTES, &map_w, bar, i * TILE_K, f0);
+#pragma unroll
+                    for (int j = 0; j < C::SUBS; ++j)
+                        tma_load_2d_pair(xt + C::X_BYTES + j * C::SUB_BYTES, &map_w, bar, i * TILE_K, f0 + j * C::SUB_N);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             // ------------------------------------------------------------ MMA issuer (first CTA)
-            constexpr uint32_t idesc = umma_idesc(2 * UMMA_M, TILE_N);
+            constexpr uint32_t idesc = umma_idesc(2 * UMMA_M, C::SUB_N);
             int it = 0, tile_iter = 0;
             bool ok = true;
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++tile_iter) {
-                const int b = tile_iter & 1, use = tile_iter >> 1;
-                if (tile_iter >= 2 && !mbar_wait(&acc_empty[b], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+                const int b = tile_iter % C::ACCS, use = tile_iter / C::ACCS;
+                if (tile_iter >= C::ACCS && !mbar_wait(&acc_empty[b], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t acc = tmem_base + b * C::TMEM_COLS;
                 for (int i = 0; i < n_kb; ++i, ++it) {
@@ -970,8 +988,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     const uint32_t xa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
                     const uint64_t xd = umma_smem_desc(xa), wd = umma_smem_desc(xa + C::X_BYTES);
 #pragma unroll
-                    for (int k = 0; k < TILE_K / UMMA_K; ++k)
-                        umma_bf16_pair(acc, xd + 2 * k, wd + 2 * k, idesc, (i | k) ? 1u : 0u);
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+#pragma unroll
+                        for (int j = 0; j < C::SUBS; ++j)
+                            umma_bf16_pair(acc + j * C::SUB_N, xd + 2 * k, wd + j * (C::SUB_BYTES >> 4) + 2 * k, idesc,
+                                           (i | k) ? 1u : 0u);
+                    }
                     umma_commit_pair(&empty[s]);
                 }
                 if (ok) umma_commit_pair(&acc_full[b]);
@@ -987,7 +1009,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         int tile_iter = 0;
         bool ok = true;
         for (int tile = pair; tile < total_tiles; tile += n_pairs, ++tile_iter) {
-            const int b = tile_iter & 1, use = tile_iter >> 1;
+            const int b = tile_iter % C::ACCS, use = tile_iter / C::ACCS;
             const int t_warp = (tile % m_tiles) * (2 * UMMA_M) + (int)rank * UMMA_M + q * 32;
             const int f0 = (tile / m_tiles) * TILE_N;
             if (ok && !mbar_wait(&acc_full[b], use & 1, abort_flag)) ok = false;
@@ -1008,7 +1030,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicExch(&p.status[1], 1);
     cluster_sync_all();                             // no MMA of the pair is in flight, no arrival under way
-    if (warp == 1) tmem_dealloc_pair(tmem_base, 2 * C::TMEM_COLS);
+    if (warp == 1) tmem_dealloc_pair(tmem_base, C::ACCS * C::TMEM_COLS);
 }
 
 // ------------------------------------------------------------------------ host side
@@ -1149,6 +1171,8 @@ int launch_pair_n(int tile_n, const CUtensorMap& mw, const CUtensorMap& mx, cons
     case 192: return launch_pair<192, REDUCE>(mw, mx, mc, p, total, s);
     case 224: return launch_pair<224, REDUCE>(mw, mx, mc, p, total, s);
     case 256: return launch_pair<256, REDUCE>(mw, mx, mc, p, total, s);
+    case 288: return launch_pair<288, REDUCE>(mw, mx, mc, p, total, s);
+    case 320: return launch_pair<320, REDUCE>(mw, mx, mc, p, total, s);
     }
     return KIPP_ERR_ARG;
 }
@@ -1159,17 +1183,22 @@ int launch_pair_n(int tile_n, const CUtensorMap& mw, const CUtensorMap& mx, cons
 // tiles = two rounds of which the second is nearly empty; 160 wide gives 256
 // tiles = two well-filled rounds of shorter tiles.
 // `pair`: tiles of 256 tokens, taken in rounds by the pairs of SMs.
-int pick_tile_n(int tokens, int features, bool pair = false) {
+// Tiles wider than 256 (pairs only) have one accumulator, so their epilogue is not hidden
+// behind the next tile's MMAs: they are taken only where they make the whole product one round.
+int pick_tile_n(int tokens, int features, bool pair = false, long long* cost_out = nullptr) {
     const int units = pair ? sm_count() / 2 : sm_count();
     const int rows = pair ? 2 * UMMA_M : UMMA_M;
     const int m_tiles = (tokens + rows - 1) / rows;
     int best = 256;
     long long best_cost = -1;
-    for (int n = 256; n >= 128; n -= 32) {
+    for (int n = pair ? 320 : 256; n >= 128; n -= 32) {
         const long long tiles = (long long)m_tiles * ((features + n - 1) / n);
-        const long long cost = ((tiles + units - 1) / units) * (n + TOKM_TILE_FIXED);
+        const long long rounds = (tiles + units - 1) / units;
+        if (n > 256 && rounds > 1) continue;
+        const long long cost = rounds * (n + TOKM_TILE_FIXED);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = n; }
     }
+    if (cost_out) *cost_out = best_cost;
     return best;
 }
 
@@ -1285,13 +1314,22 @@ extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const vo
         // By default: the pair kernel from 1,024 tokens on, except for the residual
         // add (measured 8-12 % faster for store and SwiGLU at 1,024 and 2,048 tokens,
         // no faster for the add, whose 2,560-feature shapes are bound by the rounds).
-        const bool pair = want_tile_f < 0 ? want_tile_f <= -1000 : (tokens >= 1024 && epilogue != EPI_ADD);
+        // The residual add (2,560-feature shapes here) is bound by the rounds, so there the pair
+        // is taken only where its tiles make fewer of them: 2,048 x 2,560 as 8 x 9 tiles of 288
+        // features is one round of 72 pairs (measured 34.9 against 42.5 us at K = 4,096 and 77.0
+        // against 94.8 us at K = 9,728).
+        long long cost_pair = 0, cost_one = 0;
+        const int n_pair = pick_tile_n(tokens, features, true, &cost_pair);
+        const int n_one = pick_tile_n(tokens, features, false, &cost_one);
+        const bool pair = want_tile_f < 0 ? want_tile_f <= -1000
+                                          : (tokens >= 1024 && (epilogue != EPI_ADD || cost_pair < cost_one));
         const int tile_n = want_tile_f <= -1000 ? -want_tile_f - 1000
                            : want_tile_f < 0    ? -want_tile_f
-                                                : pick_tile_n(tokens, features, pair);
-        if (tile_n < 128 || tile_n > 256 || tile_n % 32) return KIPP_ERR_ARG;
+                                                : (pair ? n_pair : n_one);
+        if (tile_n < 128 || tile_n > (pair ? 320 : 256) || tile_n % 32) return KIPP_ERR_ARG;
         CUtensorMap mw, mx, mc;
-        int rc = make_map(&mw, W, features, K, ldw, pair ? tile_n / 2 : tile_n);
+        // a CTA of a pair loads its half of the weight rows of each MMA (two MMAs above 256 features)
+        int rc = make_map(&mw, W, features, K, ldw, pair ? (tile_n > 256 ? tile_n / 4 : tile_n / 2) : tile_n);
         if (rc) return rc;
         rc = make_map(&mx, X, tokens, K, ldx, UMMA_M);
         if (rc) return rc;

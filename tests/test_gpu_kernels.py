@@ -148,7 +148,7 @@ def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
     M, N, K = shape
     g = torch.Generator().manual_seed(M + 3 * N)
     for integer in (True, False):
-        for tile_f in (0, -128, -160, -192, -224, -256, -1128, -1160, -1192, -1224, -1256):
+        for tile_f in (0, -128, -160, -192, -224, -256, -1128, -1160, -1192, -1224, -1256, -1288, -1320):
             if tile_f == 0 and M < 512:
                 continue
             if integer:
