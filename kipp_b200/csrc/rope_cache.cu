@@ -224,11 +224,9 @@ int launch_rope(const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v
 // whole head (or none): HEAD_DIM / 8 neighbouring lanes share a (token, head),
 // each holds 8 consecutive elements (one 16-byte load and store), the partner of
 // a rotated pair sits HEAD_DIM / 16 lanes away and is fetched with one shuffle
-// per element.  One block per token; a thread keeps its place inside the head and
-// walks over the heads (256 / lanes-per-head at a time), so the (cos, sin) values
-// and norm weights of its 8 elements are loaded once for all of them: with a block
-// per 16 heads the table was read 64 bytes per 16 bytes of data, 84 MB of L2 traffic
-// beside 50 MB of payload for a 2,048-token portion of 40 rotated heads.
+// per element.  Grid (blocks of heads, tokens): no division per thread but the
+// page lookup.  About a seventh of the instructions of the kernel above, which
+// for a 2,048-token portion was bound by instruction issue, not by memory.
 template <int HEAD_DIM>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_write_bf16_kernel(
@@ -240,106 +238,91 @@ qk_norm_rope_write_bf16_kernel(
     int page_size, int n_q, int n_kv, int write_cache, int* __restrict__ status) {
     constexpr int LPH = HEAD_DIM / 8;            // lanes per head
     constexpr int HALF = HEAD_DIM / 2;
-    constexpr int HEADS_PER_PASS = 256 / LPH;
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
+    const int t = blockIdx.y;
+    const int h = blockIdx.x * (256 / LPH) + (threadIdx.x / LPH);
     const int sub = threadIdx.x % LPH;
-    const int heads = n_q + 2 * n_kv;
+    const bool valid = h < n_q + 2 * n_kv;
+    const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
+    const bool active = valid && (is_q || write_cache);
 
-    // where this token's key and value go (the same page for every kv head)
-    bf16* k_dst = nullptr;
-    bf16* v_dst = nullptr;
-    if (write_cache & 1) {
-        const int pos = positions[t];
-        const int slot = pos / page_size;
-        const int page = slot < table_width ? block_table[(size_t)entry_of_token[t] * table_width + slot] : -1;
-        if (page < 0) {                           // unmapped page: refuse, never write
-            if (threadIdx.x == 0) atomicExch(status, 2);
+    bf16* dst = nullptr;
+    if (active) {
+        if (is_q) {
+            dst = q_out + ((size_t)t * n_q + h) * HEAD_DIM + sub * 8;
         } else {
-            const size_t at = ((size_t)page * n_kv * page_size + (pos - slot * page_size)) * HEAD_DIM + sub * 8;
-            k_dst = k_pages + at;
-            v_dst = v_pages + at;
+            const int pos = positions[t];
+            const int slot = pos / page_size;
+            const int page = slot < table_width ? block_table[(size_t)entry_of_token[t] * table_width + slot] : -1;
+            if (page < 0) {                       // unmapped page: refuse, never write
+                if (sub == 0) atomicExch(status, 2);
+            } else {
+                const int g = is_k ? h - n_q : h - n_q - n_kv;
+                dst = (is_k ? k_pages : v_pages) +
+                      (((size_t)page * n_kv + g) * page_size + (pos - slot * page_size)) * HEAD_DIM + sub * 8;
+            }
         }
     }
-    // the thread's 8 (cos, sin) pairs and norm weights, the same for every head
-    const bool low = sub < LPH / 2;
-    float4 cs[4];
-    if (cos_sin != nullptr) {
-        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)t * HALF + (sub % (LPH / 2)) * 8);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) cs[i] = cs4[i];
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (active) raw = *reinterpret_cast<const uint4*>(qkv + (size_t)t * ld_qkv + (size_t)h * HEAD_DIM + sub * 8);
+    if (valid && !is_q && !is_k) {                // values: copy
+        if (dst) *reinterpret_cast<uint4*>(dst) = cache_values_bf16x8(raw);
+        dst = nullptr;
     }
-    float wq[8], wk[8];
+    // queries and keys.  No lane leaves early: a warp holds several heads, and
+    // the lanes of value heads or beyond the last head take part in the shuffles.
+    float x[8];
+    {
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { x[2 * i] = __low2float(h2[i]); x[2 * i + 1] = __high2float(h2[i]); }
+    }
+    const void* nw = is_q ? q_norm_w : k_norm_w;
     if (q_norm_w != nullptr) {                    // both weights or neither (checked by the host)
-        if (norm_dtype == KIPP_DT_F32) {
+        float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                wq[i] = reinterpret_cast<const float*>(q_norm_w)[sub * 8 + i];
-                wk[i] = reinterpret_cast<const float*>(k_norm_w)[sub * 8 + i];
-            }
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float scale = 1.0f / sqrtf(ss / (float)HEAD_DIM + eps);
+        float w[8];
+        if (!active) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = 0.f;
+        } else if (norm_dtype == KIPP_DT_F32) {
+            const float4 a = reinterpret_cast<const float4*>(nw)[sub * 2], b = reinterpret_cast<const float4*>(nw)[sub * 2 + 1];
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
         } else {
+            const uint4 a = reinterpret_cast<const uint4*>(nw)[sub];
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&a);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                wq[i] = __bfloat162float(reinterpret_cast<const bf16*>(q_norm_w)[sub * 8 + i]);
-                wk[i] = __bfloat162float(reinterpret_cast<const bf16*>(k_norm_w)[sub * 8 + i]);
-            }
+            for (int i = 0; i < 4; ++i) { w[2 * i] = __low2float(h2[i]); w[2 * i + 1] = __high2float(h2[i]); }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] * scale * w[i];
+    }
+    if (cos_sin != nullptr) {
+        const bool low = sub < LPH / 2;
+        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)t * HALF + (sub % (LPH / 2)) * 8);
+        float4 cs[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cs[i] = active ? cs4[i] : make_float4(1.f, 0.f, 1.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[i], LPH / 2);
+            const float c = (i & 1) ? cs[i >> 1].z : cs[i >> 1].x;
+            const float sn = (i & 1) ? cs[i >> 1].w : cs[i >> 1].y;
+            // low half: a c - b s with b = partner; high half: b c + a s with a = partner
+            x[i] = low ? x[i] * c - other * sn : x[i] * c + other * sn;
         }
     }
-    const bf16* src = qkv + (size_t)t * ld_qkv + sub * 8;
-    // No lane leaves early: a warp holds several heads, and the lanes of value heads or
-    // beyond the last head take part in the shuffles (every thread makes every pass).
-#pragma unroll 2
-    for (int h0 = 0; h0 < heads; h0 += HEADS_PER_PASS) {
-        const int h = h0 + threadIdx.x / LPH;
-        const bool valid = h < heads;
-        const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
-        bf16* dst = nullptr;
-        if (valid) {
-            if (is_q) dst = q_out + ((size_t)t * n_q + h) * HEAD_DIM + sub * 8;
-            else if (k_dst != nullptr)
-                dst = is_k ? k_dst + (size_t)(h - n_q) * page_size * HEAD_DIM
-                           : v_dst + (size_t)(h - n_q - n_kv) * page_size * HEAD_DIM;
-        }
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (dst) raw = *reinterpret_cast<const uint4*>(src + (size_t)h * HEAD_DIM);
-        if (valid && !is_q && !is_k) {            // values: copy
-            if (dst) *reinterpret_cast<uint4*>(dst) = cache_values_bf16x8(raw);
-            dst = nullptr;
-        }
-        float x[8];
-        {
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    if (dst) {
+        uint4 out;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) { x[2 * i] = __low2float(h2[i]); x[2 * i + 1] = __high2float(h2[i]); }
-        }
-        if (q_norm_w != nullptr) {
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
-#pragma unroll
-            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const float scale = 1.0f / sqrtf(ss / (float)HEAD_DIM + eps);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = x[i] * scale * (is_q ? wq[i] : wk[i]);
-        }
-        if (cos_sin != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float other = __shfl_xor_sync(0xffffffffu, x[i], LPH / 2);
-                const float c = (i & 1) ? cs[i >> 1].z : cs[i >> 1].x;
-                const float sn = (i & 1) ? cs[i >> 1].w : cs[i >> 1].y;
-                // low half: a c - b s with b = partner; high half: b c + a s with a = partner
-                x[i] = low ? x[i] * c - other * sn : x[i] * c + other * sn;
-            }
-        }
-        if (dst) {
-            uint4 out;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-            *reinterpret_cast<uint4*>(dst) = is_q ? out : cache_values_bf16x8(out);
-        }
+        for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+        *reinterpret_cast<uint4*>(dst) = is_q ? out : cache_values_bf16x8(out);
     }
 }
 
@@ -348,7 +331,9 @@ int launch_rope_bf16(const void* qkv, int ld_qkv, void* q_out, void* k_pages, vo
                      const void* k_norm_w, int norm_dtype, float eps, const float2* cos_sin, const int* positions,
                      const int* entry_of_token, const int* block_table, int table_width, int page_size, int tokens,
                      int n_q, int n_kv, int write_cache, int* status, cudaStream_t s) {
-    return kipp_launch(qk_norm_rope_write_bf16_kernel<HEAD_DIM>, dim3((unsigned)tokens), dim3(256), 0, s, 1,
+    constexpr int HEADS_PER_BLOCK = 256 / (HEAD_DIM / 8);
+    const unsigned bx = (unsigned)((n_q + 2 * n_kv + HEADS_PER_BLOCK - 1) / HEADS_PER_BLOCK);
+    return kipp_launch(qk_norm_rope_write_bf16_kernel<HEAD_DIM>, dim3(bx, (unsigned)tokens), dim3(256), 0, s, 1,
                        (const bf16*)qkv, ld_qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, q_norm_w, k_norm_w,
                        norm_dtype, eps, cos_sin, positions, entry_of_token, block_table, table_width, page_size,
                        n_q, n_kv, write_cache, status);
@@ -398,7 +383,7 @@ extern "C" int kipp_qk_norm_rope_write(
     if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages |
                            (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0;
-    if (dtype == KIPP_DT_BF16 && aligned && ld_qkv % 8 == 0 &&
+    if (dtype == KIPP_DT_BF16 && aligned && ld_qkv % 8 == 0 && tokens <= 65535 &&
         (cos_sin == nullptr || rotary_dim == head_dim) && (q_norm_w == nullptr) == (k_norm_w == nullptr) &&
         (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
         const float2* cs = rotary_dim == 0 ? nullptr : (const float2*)cos_sin;
