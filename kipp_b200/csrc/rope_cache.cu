@@ -221,14 +221,39 @@ int launch_rope(const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v
                        write_cache, status);
 }
 // Fast path for bfloat16 with head_dim 64, 128 or 256 and a rotation over the
-// whole head (or none): HEAD_DIM / 8 neighbouring lanes share a (token, head),
-// each holds 8 consecutive elements (one 16-byte load and store), the partner of
-// a rotated pair sits HEAD_DIM / 16 lanes away and is fetched with one shuffle
-// per element.  Grid (blocks of heads, tokens): no division per thread but the
-// page lookup.  About a seventh of the instructions of the kernel above, which
-// for a 2,048-token portion was bound by instruction issue, not by memory.
+// whole head (or none): HEAD_DIM / 16 neighbouring lanes share a (token, head); a
+// lane holds 8 consecutive elements of the head's first half and the 8 elements
+// half a head further, which are the partners of its rotated pairs (two 16-byte
+// loads and stores, no exchange between lanes but the norm's sum).  Grid (blocks of
+// heads, tokens): no division per thread but the page lookup.  (The kernel is bound
+// by the instructions it issues, not by memory: the version with 8 elements per
+// lane and one shuffle per rotated element took 276 instructions per warp and
+// 23 us for a 2,048-token portion of 48 heads.)
+__device__ __forceinline__ void unpack8(float (&x)[8], const uint4& raw) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { x[2 * i] = __low2float(h2[i]); x[2 * i + 1] = __high2float(h2[i]); }
+}
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+    uint4 out;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    return out;
+}
+// elements first .. first + 7 of a norm weight (16-byte aligned)
+__device__ __forceinline__ void load_w8(float (&w)[8], const void* nw, int norm_dtype, int first) {
+    if (norm_dtype == KIPP_DT_F32) {
+        const float4 a = reinterpret_cast<const float4*>(nw)[first / 4], b = reinterpret_cast<const float4*>(nw)[first / 4 + 1];
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    } else {
+        unpack8(w, reinterpret_cast<const uint4*>(nw)[first / 8]);
+    }
+}
+
+constexpr int ROPE_THREADS = 128;    // a block per 128 / (HEAD_DIM / 16) heads of a token: few idle lanes in the last block
 template <int HEAD_DIM>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(ROPE_THREADS)
 qk_norm_rope_write_bf16_kernel(
     const bf16* __restrict__ qkv, int ld_qkv, bf16* __restrict__ q_out,
     bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
@@ -236,18 +261,18 @@ qk_norm_rope_write_bf16_kernel(
     const float2* __restrict__ cos_sin, const int* __restrict__ positions,
     const int* __restrict__ entry_of_token, const int* __restrict__ block_table, int table_width,
     int page_size, int n_q, int n_kv, int write_cache, int* __restrict__ status) {
-    constexpr int LPH = HEAD_DIM / 8;            // lanes per head
+    constexpr int LPH = HEAD_DIM / 16;           // lanes per head
     constexpr int HALF = HEAD_DIM / 2;
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y;
-    const int h = blockIdx.x * (256 / LPH) + (threadIdx.x / LPH);
+    const int h = blockIdx.x * (ROPE_THREADS / LPH) + (threadIdx.x / LPH);
     const int sub = threadIdx.x % LPH;
     const bool valid = h < n_q + 2 * n_kv;
     const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
-    const bool active = valid && (is_q || write_cache);
+    const bool active = valid && (is_q || (write_cache & 1));
 
-    bf16* dst = nullptr;
+    bf16* dst = nullptr;                         // of the lane's first 8 elements; the others HALF further
     if (active) {
         if (is_q) {
             dst = q_out + ((size_t)t * n_q + h) * HEAD_DIM + sub * 8;
@@ -264,65 +289,56 @@ qk_norm_rope_write_bf16_kernel(
             }
         }
     }
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (active) raw = *reinterpret_cast<const uint4*>(qkv + (size_t)t * ld_qkv + (size_t)h * HEAD_DIM + sub * 8);
+    uint4 raw_lo = make_uint4(0u, 0u, 0u, 0u), raw_hi = raw_lo;
+    if (dst) {
+        const bf16* src = qkv + (size_t)t * ld_qkv + (size_t)h * HEAD_DIM + sub * 8;
+        raw_lo = *reinterpret_cast<const uint4*>(src);
+        raw_hi = *reinterpret_cast<const uint4*>(src + HALF);
+    }
     if (valid && !is_q && !is_k) {                // values: copy
-        if (dst) *reinterpret_cast<uint4*>(dst) = cache_values_bf16x8(raw);
+        if (dst) {
+            *reinterpret_cast<uint4*>(dst) = cache_values_bf16x8(raw_lo);
+            *reinterpret_cast<uint4*>(dst + HALF) = cache_values_bf16x8(raw_hi);
+        }
         dst = nullptr;
     }
     // queries and keys.  No lane leaves early: a warp holds several heads, and
     // the lanes of value heads or beyond the last head take part in the shuffles.
-    float x[8];
-    {
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { x[2 * i] = __low2float(h2[i]); x[2 * i + 1] = __high2float(h2[i]); }
-    }
-    const void* nw = is_q ? q_norm_w : k_norm_w;
+    float a[8], b[8];
+    unpack8(a, raw_lo);
+    unpack8(b, raw_hi);
     if (q_norm_w != nullptr) {                    // both weights or neither (checked by the host)
         float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+        for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
 #pragma unroll
         for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         const float scale = 1.0f / sqrtf(ss / (float)HEAD_DIM + eps);
-        float w[8];
-        if (!active) {
+        if (dst) {
+            const void* nw = is_q ? q_norm_w : k_norm_w;
+            float wa[8], wb[8];
+            load_w8(wa, nw, norm_dtype, sub * 8);
+            load_w8(wb, nw, norm_dtype, HALF + sub * 8);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) w[i] = 0.f;
-        } else if (norm_dtype == KIPP_DT_F32) {
-            const float4 a = reinterpret_cast<const float4*>(nw)[sub * 2], b = reinterpret_cast<const float4*>(nw)[sub * 2 + 1];
-            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-        } else {
-            const uint4 a = reinterpret_cast<const uint4*>(nw)[sub];
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { w[2 * i] = __low2float(h2[i]); w[2 * i + 1] = __high2float(h2[i]); }
+            for (int i = 0; i < 8; ++i) { a[i] = a[i] * scale * wa[i]; b[i] = b[i] * scale * wb[i]; }
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = x[i] * scale * w[i];
     }
-    if (cos_sin != nullptr) {
-        const bool low = sub < LPH / 2;
-        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)t * HALF + (sub % (LPH / 2)) * 8);
-        float4 cs[4];
+    if (cos_sin != nullptr && dst) {
+        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)t * HALF + sub * 8);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) cs[i] = active ? cs4[i] : make_float4(1.f, 0.f, 1.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, x[i], LPH / 2);
-            const float c = (i & 1) ? cs[i >> 1].z : cs[i >> 1].x;
-            const float sn = (i & 1) ? cs[i >> 1].w : cs[i >> 1].y;
-            // low half: a c - b s with b = partner; high half: b c + a s with a = partner
-            x[i] = low ? x[i] * c - other * sn : x[i] * c + other * sn;
+        for (int i = 0; i < 4; ++i) {
+            const float4 cs = cs4[i];             // (cos, sin) of pairs 2 i and 2 i + 1
+            const float a0 = a[2 * i], b0 = b[2 * i], a1 = a[2 * i + 1], b1 = b[2 * i + 1];
+            a[2 * i] = a0 * cs.x - b0 * cs.y;
+            b[2 * i] = b0 * cs.x + a0 * cs.y;
+            a[2 * i + 1] = a1 * cs.z - b1 * cs.w;
+            b[2 * i + 1] = b1 * cs.z + a1 * cs.w;
         }
     }
     if (dst) {
-        uint4 out;
-        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-        *reinterpret_cast<uint4*>(dst) = is_q ? out : cache_values_bf16x8(out);
+        const uint4 lo = pack8(a), hi = pack8(b);
+        *reinterpret_cast<uint4*>(dst) = is_q ? lo : cache_values_bf16x8(lo);
+        *reinterpret_cast<uint4*>(dst + HALF) = is_q ? hi : cache_values_bf16x8(hi);
     }
 }
 
@@ -331,9 +347,9 @@ int launch_rope_bf16(const void* qkv, int ld_qkv, void* q_out, void* k_pages, vo
                      const void* k_norm_w, int norm_dtype, float eps, const float2* cos_sin, const int* positions,
                      const int* entry_of_token, const int* block_table, int table_width, int page_size, int tokens,
                      int n_q, int n_kv, int write_cache, int* status, cudaStream_t s) {
-    constexpr int HEADS_PER_BLOCK = 256 / (HEAD_DIM / 8);
+    constexpr int HEADS_PER_BLOCK = ROPE_THREADS / (HEAD_DIM / 16);
     const unsigned bx = (unsigned)((n_q + 2 * n_kv + HEADS_PER_BLOCK - 1) / HEADS_PER_BLOCK);
-    return kipp_launch(qk_norm_rope_write_bf16_kernel<HEAD_DIM>, dim3(bx, (unsigned)tokens), dim3(256), 0, s, 1,
+    return kipp_launch(qk_norm_rope_write_bf16_kernel<HEAD_DIM>, dim3(bx, (unsigned)tokens), dim3(ROPE_THREADS), 0, s, 1,
                        (const bf16*)qkv, ld_qkv, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, q_norm_w, k_norm_w,
                        norm_dtype, eps, cos_sin, positions, entry_of_token, block_table, table_width, page_size,
                        n_q, n_kv, write_cache, status);
