@@ -12,21 +12,28 @@
 //              and half of the output columns;
 //   warp 8     gathers the key and value tiles page by page with TMA (one box
 //              per lane, 128-byte swizzle) into a two-stage ring;
-//   warp 9     one thread issues the products.
-// Per tile of 64 keys: S = Q K^T (128 x 64 x D) into the score buffer in tensor
-// memory; the softmax threads take their scores into registers and release the
-// buffer at once, so S of the next tile runs while they scale, mask, take the
-// running maximum (exchanged between the two threads of a row through shared
-// memory) and form p = 2^(s - m), which goes as bfloat16 into one of two weight
-// buffers in tensor memory.  The running maximum moves only when a tile exceeds
+//   warp 9     one thread issues the score products S = Q K^T;
+//   warp 10    one thread issues the output products O += P V.
+// (Two issuing threads: one thread that waited for four barriers and issued twelve
+// products and five commits per tile took 1,700 cycles for that, sharing its scheduler
+// with busy softmax warps, while the tensor pipe needs 512 per tile and the softmax
+// warps 900: the issuing thread was the kernel's bottleneck.  The two chains, scores
+// and outputs, meet only through the softmax warps.)
+// Per tile of 64 keys: S = Q K^T (128 x 64 x D) into one of two score buffers in
+// tensor memory, up to two tiles ahead of the softmax threads; these take their scores
+// into registers, scale, mask, take the running maximum (exchanged between the two
+// threads of a row through shared memory) and form p = 2^(s - m), which goes as
+// bfloat16 over the first half of the tile's own score buffer (the buffer is free for
+// the scores of tile i + 2 when O += P V of tile i has read it).  The running maximum
+// moves only when a tile exceeds
 // it by more than 2^8 (numerator and denominator carry the same reference), so the
 // output accumulator in tensor memory is rescaled rarely.  O += P V (128 x D x 64)
 // takes P from tensor memory and V as an MN-major shared-memory operand; it runs
 // while the next tile is in the softmax.  Everything is handed over through
 // mbarriers; every wait is bounded in time, and on a time-out status[1] is set
 // and the CTA drains and frees its tensor memory.  Two CTAs fit an SM (98 KB
-// shared memory, 256 tensor-memory columns each: 64 scores, 2 x 32 weights, 128
-// output).  All arithmetic outside the MMAs is float32.
+// shared memory, 256 tensor-memory columns each: 2 x 64 scores with the weights
+// inside, 128 output).  All arithmetic outside the MMAs is float32.
 //
 // The gather costs one TMA box per page and 64-column half (with 16-slot pages 16
 // boxes of 2 KB a tile; the kernel is then 3 % slower than with pages of 64 slots,
@@ -54,7 +61,7 @@ constexpr int BM = 128;            // query rows per CTA = MMA M
 constexpr int BN = 64;             // keys per tile
 constexpr float RESCALE_SLACK = 8.f;   // log2 of the largest weight a stale running maximum may give
 constexpr int SOFTMAX_THREADS = 256;  // two threads per query row: each half of a tile's keys
-constexpr int THREADS = 320;          // + the TMA warp and the MMA warp
+constexpr int THREADS = 352;          // + the TMA warp and the two MMA warps
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -173,7 +180,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// true in one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+    return chosen != 0;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Two float32 operations in one instruction, a maximum of three (sm_100): the softmax warps
+// stand in the chain from a tile's scores to the next but one's, instruction by instruction.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<unsigned long long*>(&b)), "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)),
+        "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 // Shared-memory operand descriptor (sm_100), 128-byte swizzle.  K-major tiles:
 // rows of 128 bytes, 8-row groups `sbo` bytes apart.  MN-major tiles (values):
@@ -239,8 +271,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* k_empty = bars + 3;       // [2] its S product has read it                 (1, by commit)
     uint64_t* v_full = bars + 5;        // [2]
     uint64_t* v_empty = bars + 7;       // [2] its O product has read it
-    uint64_t* s_full = bars + 9;        // the score buffer holds S of a tile             (1, by commit)
-    uint64_t* s_free = bars + 10;       // every softmax warp has its scores in registers (8 = softmax warps)
+    uint64_t* s_full = bars + 9;        // [2] a score buffer holds S of a tile           (1, by commit)
     uint64_t* p_full = bars + 11;       // [2] a weight buffer holds a tile's weights, O is rescaled (8)
     uint64_t* p_empty = bars + 13;      // [2] O += P V has read it (and is complete)     (1, by commit)
     uint64_t* o_final = bars + 15;      // the last O += P V is complete                  (1, by commit)
@@ -248,29 +279,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     pdl_launch_dependents();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        mbar_init(q_full, SOFTMAX_THREADS);
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
-            mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
-            mbar_init(&p_full[b], SOFTMAX_THREADS / 32); mbar_init(&p_empty[b], 1);
-        }
-        mbar_init(s_full, 1); mbar_init(s_free, SOFTMAX_THREADS / 32);
-        mbar_init(o_final, 1);
-        *abort_flag = (q_tile & 1023u) ? 1 : 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    // columns: scores [0, 64); two weight buffers [64, 96) and [96, 128) (pairs of
-    // bfloat16); output [128, 128 + D)
-    const uint32_t tmem_s = tmem_base, tmem_p = tmem_base + BN, tmem_o = tmem_base + 2 * BN;
-    pdl_wait();
-
+    // (What is read before the dependency wait below comes with the step's lists, which a
+    // copy brought before any kernel of the step started: the loads, three in a row, run
+    // while the barriers and the tensor memory are set up.)
     // Grid (heads, tiles), the last tile of the list first: within an entry the later
     // tiles see more keys, and the long ones should not be the last to start; the
     // heads of a tile, which share its keys and values, start together.
@@ -284,6 +295,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int lo = p.window > 0 ? max(0, tile_first - p.window + 1) : 0, hi = tile_last;
     const int first_tile = lo / BN, last_tile = hi / BN;
     const int n_tiles = last_tile - first_tile + 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, SOFTMAX_THREADS);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
+            mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
+            mbar_init(&p_full[b], SOFTMAX_THREADS / 32); mbar_init(&p_empty[b], 1);
+        }
+        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
+        mbar_init(o_final, 1);
+        *abort_flag = (q_tile & 1023u) ? 1 : 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // columns: two score buffers [0, 64) and [64, 128); the weights of a tile (pairs of
+    // bfloat16, 32 columns) overwrite the first half of the tile's own score buffer once
+    // its scores are in registers; output [128, 128 + D)
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * BN;
+    pdl_wait();
+
 
     if (warp == 8) {
         // ------------------------------------------------------------ TMA producer
@@ -352,52 +387,63 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
     } else if (warp == 9) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t IDESC_S = idesc(BM, BN, 0);
-            constexpr uint32_t IDESC_O = idesc(BM, D, 1);
-            bool ok = true;
-            // S(tile i) = Q K^T into the score buffer from key stage i & 1
-            auto issue_scores = [&](int i) {
-                const int b = i & 1;
-                if (ok && !mbar_wait(&k_full[b], (i >> 1) & 1, abort_flag)) ok = false;
-                tc_fence_after();
+        // ------------------------------------------------------------ MMA issuer: scores
+        // The whole warp walks the loop and waits; one elected lane issues.  (With one lane
+        // alone in a branch of its own the operands of every product came out of that
+        // lane's registers, and a product took 60 to 80 cycles to issue.)
+        constexpr uint32_t IDESC_S = idesc(BM, BN, 0);
+        bool ok = mbar_wait(q_full, 0, abort_flag);
+        // S(tile i) = Q K^T into score buffer i & 1 from key stage i & 1, as soon as the
+        // output product of tile i - 2 has read the weights that lie in that buffer:
+        // up to two tiles ahead of the softmax warps, never waiting for them
+        for (int i = 0; i < n_tiles; ++i) {
+            const int b = i & 1, use = i >> 1;
+            // (the keys land long before the buffer is free: that wait first, so that nothing
+            // stands between the buffer's release and the products)
+            if (ok && !mbar_wait(&k_full[b], use & 1, abort_flag)) ok = false;
+            if (i >= 2 && ok && !mbar_wait(&p_empty[b], (use - 1) & 1, abort_flag)) ok = false;
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            const uint32_t acc = tmem_s + b * BN;
+            const uint32_t k_stage = k_tiles + b * C::KV_BYTES;
+            if (elect_one()) {
 #pragma unroll
                 for (int hh = 0; hh < C::HALVES; ++hh) {
                     const uint64_t qd = smem_desc(q_tile + hh * (BM * 128), 0, 1024);
-                    const uint64_t kd = smem_desc(k_tiles + b * C::KV_BYTES + hh * (BN * 128), 0, 1024);
+                    const uint64_t kd = smem_desc(k_stage + hh * (BN * 128), 0, 1024);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_s, qd + 2 * k, kd + 2 * k, IDESC_S, (hh | k) ? 1u : 0u);
+                        umma_bf16(acc, qd + 2 * k, kd + 2 * k, IDESC_S, (hh | k) ? 1u : 0u);
                 }
-                umma_commit(s_full);
+                umma_commit(&s_full[b]);
                 umma_commit(&k_empty[b]);
-            };
-            if (!mbar_wait(q_full, 0, abort_flag)) ok = false;
-            issue_scores(0);
-            for (int i = 0; i < n_tiles; ++i) {
-                const int b = i & 1, use = i >> 1;
-                // S of the next tile as soon as the softmax warps hold this tile's scores
-                // in registers: it runs while they work on them
-                if (i + 1 < n_tiles) {
-                    if (ok && !mbar_wait(s_free, i & 1, abort_flag)) ok = false;
-                    issue_scores(i + 1);
-                }
-                // the tile's weights are in weight buffer b, O is rescaled, its values have landed
-                if (ok && !mbar_wait(&p_full[b], use & 1, abort_flag)) ok = false;
-                if (ok && !mbar_wait(&v_full[b], use & 1, abort_flag)) ok = false;
-                tc_fence_after();
-                const uint64_t vd = smem_desc(v_tiles + b * C::KV_BYTES, p.v_lbo, p.v_sbo);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------ MMA issuer: outputs
+        constexpr uint32_t IDESC_O = idesc(BM, D, 1);
+        bool ok = true;
+        for (int i = 0; i < n_tiles; ++i) {
+            const int b = i & 1, use = i >> 1;
+            // the tile's weights are in its score buffer, O is rescaled, its values have landed
+            if (ok && !mbar_wait(&v_full[b], use & 1, abort_flag)) ok = false;
+            if (ok && !mbar_wait(&p_full[b], use & 1, abort_flag)) ok = false;
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            const uint64_t vd = smem_desc(v_tiles + b * C::KV_BYTES, p.v_lbo, p.v_sbo);
+            const uint32_t weights = tmem_s + b * BN;
+            if (elect_one()) {
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k)
                     // 16 keys further: 8 columns of P; 16 rows = 2048 bytes in the value tile
-                    umma_bf16_a_tmem(tmem_o, tmem_p + b * (BN / 2) + 8 * k, vd + 128 * k, IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16_a_tmem(tmem_o, weights + 8 * k, vd + 128 * k, IDESC_O, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&v_empty[b]);
                 umma_commit(&p_empty[b]);
                 if (i == n_tiles - 1) umma_commit(o_final);
             }
+            __syncwarp();
         }
-        __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax warps 0-7
         // the query tile: rows beyond the entry are zero
@@ -429,15 +475,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         // once the abort flag is up the remaining waits return at once.)
         for (int i = 0; i < n_tiles; ++i) {
             const int kt = first_tile + i, b = i & 1, use = i >> 1;
-            if (!mbar_wait(s_full, i & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 1); ok = false; }
+            if (!mbar_wait(&s_full[b], use & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 1); ok = false; }
             tc_fence_after();
             constexpr int HB = BN / 2;                     // keys per thread
             float s[HB];
-            tmem_ld32(tmem_s + t_lane + ch * HB, s);
-            // the scores are in registers: the buffer may take the next tile's
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free);
+            tmem_ld32(tmem_s + b * BN + t_lane + ch * HB, s);
             const int j0 = kt * BN + ch * HB;
             // Masking only where the tile crosses a row's limits (the diagonal, a
             // window's edge, rows beyond the entry): decided per warp.
@@ -450,7 +492,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             float raw = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < HB; ++j) raw = fmaxf(raw, s[j]);
+            for (int j = 0; j < HB; j += 2) raw = max3(raw, s[j], s[j + 1]);
             // the row's maximum over both halves: through shared memory, between the two warps of the row
             {
                 float* xb = xchg + b * (2 * BM);
@@ -466,29 +508,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const float mx = (cand > m_run + RESCALE_SLACK || m_run == -INFINITY) ? fmaxf(m_run, cand) : m_run;
             const float corr = (m_run == -INFINITY) ? 0.f : (mx == m_run ? 1.f : fast_exp2(m_run - mx));
             const float neg_base = (mx == -INFINITY) ? 0.f : -mx;
-            float sum = 0.f;
+            float2 sum2 = make_float2(0.f, 0.f);
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), base2 = make_float2(neg_base, neg_base);
             uint32_t packed[HB / 2];
 #pragma unroll
             for (int j = 0; j < HB; j += 2) {
-                const float p0 = fast_exp2(fmaf(s[j], p.scale_log2, neg_base));
-                const float p1 = fast_exp2(fmaf(s[j + 1], p.scale_log2, neg_base));
-                sum += p0 + p1;
-                __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                const float2 x = fma2(make_float2(s[j], s[j + 1]), scale2, base2);
+                const float2 pw = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                sum2 = add2(sum2, pw);
+                __nv_bfloat162 pk = __floats2bfloat162_rn(pw.x, pw.y);
                 packed[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
             }
-            l_run = l_run * corr + sum;                    // this thread's half of the row's sum
+            l_run = l_run * corr + (sum2.x + sum2.y);      // this thread's half of the row's sum
             m_run = mx;
-            // The weights of this thread's keys go to weight buffer b, once the product
-            // that read its earlier weights (tile i - 2) is complete.
-            if (i >= 2) {
-                if (!mbar_wait(&p_empty[b], (use - 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
-                tc_fence_after();
-            }
-            tmem_st16_words(tmem_p + b * (BN / 2) + t_lane + ch * (HB / 2), packed);
+            // The weights of this thread's keys go over the first half of the tile's own
+            // score buffer: both threads of the row hold their scores in registers since
+            // they met at the exchange of the maxima above.
+            tmem_st16_words(tmem_s + b * BN + t_lane + ch * (HB / 2), packed);
             // rescale the output accumulator when some row of the warp moved its maximum
             // (this thread: its half of the columns), once O += P V of the tile before
-            // is complete: that is the latest product on the other weight buffer (the one
-            // before it there was waited for in the iteration before this one).
+            // is complete: that is the latest product (the one before it was complete before
+            // this tile's scores could be made).
             if (i > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
                 if (!mbar_wait(&p_empty[b ^ 1], ((i - 1) >> 1) & 1, abort_flag)) { if (ok) atomicMax(&p.status[2], 2); ok = false; }
                 tc_fence_after();

@@ -20,6 +20,7 @@ __device__ __forceinline__ bool kipp_mbar_try_wait(uint64_t* bar, uint32_t parit
 
 __device__ __forceinline__ bool kipp_mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                        long long limit_cycles) {
+    if (kipp_mbar_try_wait(bar, parity)) return true;      // mostly the phase is complete already: no clock read
     const long long t0 = clock64();
     for (unsigned i = 0;; ++i) {
         if (kipp_mbar_try_wait(bar, parity)) return true;
