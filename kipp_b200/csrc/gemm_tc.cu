@@ -181,6 +181,15 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
         ::"r"(smem_u32(bar)), "h"((uint16_t)3)
         : "memory");
 }
+// true in one lane of the (converged) warp.  The warps that issue copies and products walk
+// their loops and wait as whole warps and let one elected lane issue: with a single lane in a
+// branch of its own the operands of every product come out of that lane's registers, and a
+// product was measured to take 60 to 80 cycles to issue instead of about 40.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+    return chosen != 0;
+}
 __device__ __forceinline__ void tcgen05_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -395,58 +404,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
-        if (lane == 0) {
+        {
             // Weights do not depend on the kernels before this one: the first
             // ring of weight tiles is on its way before the dependency wait; the
             // activation tiles follow after it.
             const int ahead = min(n_kb, C::STAGES);
-            for (int i = 0; i < ahead; ++i) {
-                uint8_t* wt = tiles + (size_t)i * C::STAGE_BYTES;
-                mbar_expect_tx(&full[i], C::STAGE_BYTES);
-                tma_load_2d(wt, &map_w, &full[i], (kb_begin + i) * TILE_K, f0);
+            if (elect_one()) {
+                for (int i = 0; i < ahead; ++i) {
+                    uint8_t* wt = tiles + (size_t)i * C::STAGE_BYTES;
+                    mbar_expect_tx(&full[i], C::STAGE_BYTES);
+                    tma_load_2d(wt, &map_w, &full[i], (kb_begin + i) * TILE_K, f0);
+                }
             }
+            __syncwarp();
             pdl_wait();
-            for (int i = 0; i < ahead; ++i) {
-                uint8_t* xt = tiles + (size_t)i * C::STAGE_BYTES + C::W_BYTES;
-                tma_load_2d(xt, &map_x, &full[i], (kb_begin + i) * TILE_K, t0);
+            if (elect_one()) {
+                for (int i = 0; i < ahead; ++i) {
+                    uint8_t* xt = tiles + (size_t)i * C::STAGE_BYTES + C::W_BYTES;
+                    tma_load_2d(xt, &map_x, &full[i], (kb_begin + i) * TILE_K, t0);
+                }
             }
+            __syncwarp();
             for (int i = ahead; i < n_kb; ++i) {
                 const int s = i % C::STAGES;
                 const uint32_t ph = (i / C::STAGES) & 1;
-                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1, abort_flag))) break;
                 uint8_t* wt = tiles + (size_t)s * C::STAGE_BYTES;
                 uint8_t* xt = wt + C::W_BYTES;
-                mbar_expect_tx(&full[s], C::STAGE_BYTES);
                 const int k = (kb_begin + i) * TILE_K;
-                tma_load_2d(wt, &map_w, &full[s], k, f0);
-                tma_load_2d(xt, &map_x, &full[s], k, t0);
+                if (elect_one()) {
+                    mbar_expect_tx(&full[s], C::STAGE_BYTES);
+                    tma_load_2d(wt, &map_w, &full[s], k, f0);
+                    tma_load_2d(xt, &map_x, &full[s], k, t0);
+                }
+                __syncwarp();
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        {
             constexpr uint32_t idesc = umma_idesc(UMMA_M, TILE_T);
             bool ok = true;
             for (int i = 0; i < n_kb && ok; ++i) {
                 const int s = i % C::STAGES;
                 const uint32_t ph = (i / C::STAGES) & 1;
-                if (!mbar_wait(&full[s], ph, abort_flag)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph, abort_flag))) { ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t wa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
                 const uint64_t wd = umma_smem_desc(wa), xd = umma_smem_desc(wa + C::W_BYTES);
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+                    for (int k = 0; k < TILE_K / UMMA_K; ++k) {
 #pragma unroll
-                    for (int h = 0; h < C::HALVES; ++h) {
-                        // advance 16 elements = 32 bytes inside the swizzled row: +2 in the address
-                        // field; the second 128 features start 128 rows = 16 KB further: +1024
-                        umma_bf16(tmem_base + h * TILE_T, wd + 2 * k + h * 1024, xd + 2 * k, idesc,
-                                  (i | k) ? 1u : 0u);
+                        for (int h = 0; h < C::HALVES; ++h) {
+                            // advance 16 elements = 32 bytes inside the swizzled row: +2 in the address
+                            // field; the second 128 features start 128 rows = 16 KB further: +1024
+                            umma_bf16(tmem_base + h * TILE_T, wd + 2 * k + h * 1024, xd + 2 * k, idesc,
+                                      (i | k) ? 1u : 0u);
+                        }
                     }
+                    umma_commit(&empty[s]);            // stage reusable when these MMAs are done
                 }
-                umma_commit(&empty[s]);            // stage reusable when these MMAs are done
+                __syncwarp();
             }
-            if (ok) umma_commit(acc_ready);
+            if (ok && elect_one()) umma_commit(acc_ready);
+            __syncwarp();
         }
     } else {
         // ---------------------------------------------------------------- epilogue warps 2..9
