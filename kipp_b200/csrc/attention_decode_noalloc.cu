@@ -36,8 +36,10 @@ int scratch_for_current_device(float** out) {
 }
 }  // namespace
 
+// partial outputs and (max, sum) pairs of every split (this entry point cuts every token into
+// splits of the given length, which needs nothing more)
 extern "C" long long kipp_attn_decode_noalloc_scratch_bytes(int n, int n_q, int head_dim, int max_splits) {
-    return kipp_attn_decode_scratch_bytes(n, n_q, head_dim, max_splits);
+    return (long long)n * n_q * max_splits * (head_dim + 2) * 4;
 }
 
 extern "C" int kipp_attn_decode_mma_noalloc(void* out, const void* q, const void* k_pages, const void* v_pages,
@@ -49,12 +51,12 @@ extern "C" int kipp_attn_decode_mma_noalloc(void* out, const void* q, const void
     if (n <= 0) return 0;
     if (n_q <= 0 || head_dim <= 0 || max_splits <= 0) return KIPP_ERR_ARG;
     // refuse before anything is launched: the built-in scratch has one size
-    if (kipp_attn_decode_scratch_bytes(n, n_q, head_dim, max_splits) > KIPP_NOALLOC_SCRATCH_BYTES)
+    if (kipp_attn_decode_noalloc_scratch_bytes(n, n_q, head_dim, max_splits) > KIPP_NOALLOC_SCRATCH_BYTES)
         return KIPP_ERR_SCRATCH;
     float* scratch = nullptr;
     const int rc = scratch_for_current_device(&scratch);
     if (rc) return rc;
     return kipp_attn_decode_mma(out, q, k_pages, v_pages, q_start, context_len, block_table, table_width,
                                 page_size, rows, n, n_q, n_kv, head_dim, scale, window, max_splits, split_keys, 0,
-                                scratch, stream);
+                                0, scratch, stream);
 }

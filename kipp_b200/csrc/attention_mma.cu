@@ -316,6 +316,8 @@ struct DecodeParams {
     const float2* cos_sin;      // [token][D / 2] (cos, sin), or nullptr: no rotation
     bf16* k_write; bf16* v_write;   // the pools, writable; nullptr: this run does not write its cache
     int* status;
+    int* n_splits_out;          // stream cut: [n][n_kv] splits of each pair, written for the merge; else nullptr
+    int stream_ctas;            // stream cut: the grid
 };
 
 // The per-head norm and the rotation of one head vector, one warp: lane l holds
@@ -412,34 +414,20 @@ __host__ __device__ __forceinline__ int decode_split_keys(int kv_len, int max_sp
     return keys;
 }
 
+// One split of one (token, kv head) pair: keys lo .. hi of entry `entry` (decoded token n of the
+// step), split `split` of `n_splits`.  `first`: the CTA's first piece of work (it may fetch tiles
+// before the dependency wait and makes that wait); all threads of the CTA call this together.
 template <int D>
-__global__ void __launch_bounds__(THREADS)
-attn_decode_kernel(const DecodeParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+__device__ __forceinline__ void decode_split(const DecodeParams& p, uint8_t* smem, int n, int entry, int g, int lo,
+                                             int hi, int split, int n_splits, bool first) {
     constexpr int TILE_BYTES = TILE_KEYS * D * 2;
     constexpr int STAGES = DECODE_STAGES;
     const uint32_t k_base = smem_u32(smem), v_base = k_base + STAGES * TILE_BYTES;
-    pdl_launch_dependents();
-    // (What is read before the dependency wait below comes with the step's lists, which a
-    // copy brought before any kernel of the step started, or lies in the cache since
-    // earlier steps.)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 2, t4 = lane & 3;
-    // Grid (kv heads, tokens, splits): the splits are the slowest dimension, so the CTAs
-    // that have work come first in launch order and all start at once; those of
-    // splits a step does not use come after and leave at once.  (With the splits as
-    // x, 1,664 of 2,048 CTAs of a batch-8 step were empty ones interleaved with the
-    // working ones, and the last working CTA started microseconds late.)
-    const int n = blockIdx.y, entry = p.rows[n], g = blockIdx.x, split = blockIdx.z;
     const int group = p.n_q / p.n_kv;
     const int tok = p.q_start[entry];
     const int pos = p.context_len[entry];                  // position of the decoded token
-    const int kv_len = pos + 1;
-    const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const int split_keys = decode_split_keys(kv_len, p.max_splits, __ldg(p.split_keys + n * p.split_stride));
-    const int n_splits = (kv_len + split_keys - 1) / split_keys;
-    if (split >= n_splits) return;
-    const int lo = max(first_key, split * split_keys), hi = min(pos, (split + 1) * split_keys - 1);
     const int* table = p.block_table + (size_t)entry * p.table_width;
     float* my_ml = p.part_ml + (((size_t)n * p.n_q + g * group) * p.max_splits + split) * 2;
     float* my_o = p.part_o + (((size_t)n * p.n_q + g * group) * p.max_splits + split) * D;
@@ -449,7 +437,7 @@ attn_decode_kernel(const DecodeParams p) {
     // this one ends, unless one of them holds the token's own position: its key and
     // value are this step's (made below, or by the kernel before this one).
     const int first_tile = lo / TILE_KEYS, last_tile = hi / TILE_KEYS, n_tiles = last_tile - first_tile + 1;
-    const bool early = lo <= hi && (first_tile + min(STAGES - 1, n_tiles)) * TILE_KEYS <= pos;
+    const bool early = first && lo <= hi && (first_tile + min(STAGES - 1, n_tiles)) * TILE_KEYS <= pos;
     if (early) {
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
@@ -459,7 +447,7 @@ attn_decode_kernel(const DecodeParams p) {
             cp_async_commit();
         }
     }
-    pdl_wait();
+    if (first) pdl_wait();
     if (lo > hi) {                                         // split wholly behind the window
         for (int i = threadIdx.x; i < group; i += THREADS) {
             my_ml[i * head_stride_ml] = -INFINITY;
@@ -642,6 +630,102 @@ attn_decode_kernel(const DecodeParams p) {
     }
 }
 
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();
+    // (What is read before the dependency wait comes with the step's lists, which a
+    // copy brought before any kernel of the step started, or lies in the cache since
+    // earlier steps.)
+    // Grid (kv heads, tokens, splits): the splits are the slowest dimension, so the CTAs
+    // that have work come first in launch order and all start at once; those of
+    // splits a step does not use come after and leave at once.  (With the splits as
+    // x, 1,664 of 2,048 CTAs of a batch-8 step were empty ones interleaved with the
+    // working ones, and the last working CTA started microseconds late.)
+    const int n = blockIdx.y, entry = p.rows[n], g = blockIdx.x, split = blockIdx.z;
+    const int pos = p.context_len[entry];
+    const int kv_len = pos + 1;
+    const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int split_keys = decode_split_keys(kv_len, p.max_splits, __ldg(p.split_keys + n * p.split_stride));
+    const int n_splits = (kv_len + split_keys - 1) / split_keys;
+    if (split >= n_splits) return;
+    decode_split<D>(p, smem, n, entry, g, max(first_key, split * split_keys), min(pos, (split + 1) * split_keys - 1),
+                    split, n_splits, true);
+}
+
+// The same work cut differently (DecodeParams::stream): the 64-key tiles of all (token, kv head)
+// pairs of the step, pair after pair, are dealt out in equal runs to the CTAs of ONE wave, so a
+// CTA's set-up and the merge of its four warps are paid once per run instead of once per short
+// split, and all CTAs end together however the pairs and lengths fall (a step of 64 tokens with
+// 2,048 keys each: 434 CTAs of 39 tiles instead of 1,536 of 11, four waves).  A run may end one
+// pair and begin the next; each piece is a split of its pair, numbered in key order, and the
+// pair's first piece notes the number of splits for the merge.  Tiles per run: the total over
+// the grid, rounded up, but at least what keeps a pair within max_splits pieces.
+constexpr int STREAM_MAX_TOKENS = 1024;
+struct StreamCut { int per, total; };
+// cum[i] = key tiles of the decoded tokens before i (of one kv head); returns the tiles per run
+__device__ __forceinline__ StreamCut stream_cut(const DecodeParams& p, int n_tokens, int runs, int* cum, int* scratch) {
+    int most = 0;
+    for (int i = threadIdx.x; i < n_tokens; i += blockDim.x) {
+        const int pos = p.context_len[p.rows[i]];
+        const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int tiles = pos / TILE_KEYS - first_key / TILE_KEYS + 1;
+        cum[i + 1] = tiles;
+        most = max(most, tiles);
+    }
+    if (threadIdx.x == 0) { cum[0] = 0; *scratch = 0; }
+    __syncthreads();
+    atomicMax(scratch, most);
+    if (threadIdx.x == 0)
+        for (int i = 0; i < n_tokens; ++i) cum[i + 1] += cum[i];           // few hundred entries at most
+    __syncthreads();
+    StreamCut c;
+    c.total = cum[n_tokens] * p.n_kv;
+    const int longest = *scratch;
+    c.per = max(max((c.total + runs - 1) / runs, (longest + p.max_splits - 2) / max(p.max_splits - 1, 1)), 1);
+    return c;
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_stream_kernel(const DecodeParams p, int n_tokens) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int cum[STREAM_MAX_TOKENS + 1];
+    __shared__ int longest_s;
+    pdl_launch_dependents();
+    const StreamCut cut = stream_cut(p, n_tokens, (int)gridDim.x, cum, &longest_s);
+    int idx = (int)blockIdx.x * cut.per;
+    const int end = min(cut.total, idx + cut.per);
+    bool first = true;
+    while (idx < end) {
+        // the pair the run's next tile belongs to: tokens in order, their kv heads in order
+        int lo_n = 0, hi_n = n_tokens - 1;
+        while (lo_n < hi_n) {
+            const int mid = (lo_n + hi_n + 1) >> 1;
+            if (cum[mid] * p.n_kv <= idx) lo_n = mid; else hi_n = mid - 1;
+        }
+        const int n = lo_n, tiles = cum[n + 1] - cum[n];
+        const int within = idx - cum[n] * p.n_kv, g = within / tiles, t_in = within - g * tiles;
+        const int take = min(tiles - t_in, end - idx);
+        const int pair_first = cum[n] * p.n_kv + g * tiles;
+        const int run_first = pair_first / cut.per, run_last = (pair_first + tiles - 1) / cut.per;
+        const int n_splits = run_last - run_first + 1, split = (int)blockIdx.x - run_first;
+        const int entry = p.rows[n];
+        const int pos = p.context_len[entry];
+        const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const int tile0 = first_key / TILE_KEYS + t_in;
+        if (t_in == 0 && threadIdx.x == 0) p.n_splits_out[n * p.n_kv + g] = n_splits;
+        decode_split<D>(p, smem, n, entry, g, max(first_key, tile0 * TILE_KEYS),
+                        min(pos, (tile0 + take) * TILE_KEYS - 1), split, n_splits, first);
+        first = false;
+        idx += take;
+        __syncthreads();                                   // the merge's shared memory before the next piece's tiles
+    }
+    // (a CTA without a run leaves without the dependency wait: it touched nothing but the lists)
+}
+
 // The merge of a token's splits: a warp per head, WARPS heads per block.  (Merging inside the
 // split kernel, by the CTA that finishes a token's last split, was measured and is no faster:
 // one CTA then does behind a fence what this launch spreads over many while the next kernel
@@ -651,7 +735,8 @@ attn_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_
                          const float* __restrict__ part_ml, const int* __restrict__ rows,
                          const int* __restrict__ q_start, const int* __restrict__ context_len,
                          int n_q, int head_dim, int max_splits,
-                         const int* __restrict__ split_keys_ptr, int split_stride) {
+                         const int* __restrict__ split_keys_ptr, int split_stride,
+                         const int* __restrict__ n_splits_info, int n_kv) {
     __shared__ float weight[WARPS * 64];           // max_splits <= 64 checked by the launcher
     pdl_launch_dependents();
     pdl_wait();
@@ -659,9 +744,14 @@ attn_decode_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_
     const int n = blockIdx.y, h = blockIdx.x * WARPS + warp;
     if (h >= n_q) return;
     const int entry = rows[n];
-    const int kv_len = context_len[entry] + 1;
-    const int split_keys = decode_split_keys(kv_len, max_splits, __ldg(split_keys_ptr + n * split_stride));
-    const int n_splits = (kv_len + split_keys - 1) / split_keys;
+    int n_splits;
+    if (n_splits_info != nullptr) {                // the stream cut noted the pair's splits
+        n_splits = n_splits_info[n * n_kv + h / (n_q / n_kv)];
+    } else {
+        const int kv_len = context_len[entry] + 1;
+        const int split_keys = decode_split_keys(kv_len, max_splits, __ldg(split_keys_ptr + n * split_stride));
+        n_splits = (kv_len + split_keys - 1) / split_keys;
+    }
     if (n_splits == 1) return;                     // the split kernel wrote the result itself
     const size_t head = (size_t)n * n_q + h;
     warp_merge_head(out + ((size_t)q_start[entry] * n_q + h) * head_dim, part_ml + head * max_splits * 2,
@@ -682,7 +772,7 @@ template <int D> int launch_prefill(const PrefillParams& p, int items, cudaStrea
 inline int launch_merge(const DecodeParams& p, void* out, int n, int head_dim, cudaStream_t s) {
     return kipp_launch(attn_decode_merge_kernel, dim3((p.n_q + WARPS - 1) / WARPS, n), dim3(THREADS), 0, s, 1,
                        (bf16*)out, (const float*)p.part_o, (const float*)p.part_ml, p.rows, p.q_start, p.context_len,
-                       p.n_q, head_dim, p.max_splits, p.split_keys, p.split_stride);
+                       p.n_q, head_dim, p.max_splits, p.split_keys, p.split_stride, (const int*)p.n_splits_out, p.n_kv);
 }
 
 template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s) {
@@ -694,6 +784,15 @@ template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s)
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
+    }
+    if (p.n_splits_out != nullptr) {
+        static bool configured_stream = false;
+        if (!configured_stream) {
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_stream_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            if (e != cudaSuccess) return (int)e;
+            configured_stream = true;
+        }
+        return kipp_launch(attn_decode_stream_kernel<D>, dim3(p.stream_ctas), dim3(THREADS), SMEM, s, 1, p, n);
     }
     if (n > 65535) return KIPP_ERR_ARG;
     return kipp_launch(attn_decode_kernel<D>, dim3(p.n_kv, n, p.max_splits), dim3(THREADS), SMEM, s, 1, p);
@@ -728,20 +827,26 @@ extern "C" int kipp_attn_prefill_mma(void* out, const void* q, const void* k_pag
 
 // Bytes of scratch for n decode entries: partial outputs and (max, sum) pairs.
 extern "C" long long kipp_attn_decode_scratch_bytes(int n, int n_q, int head_dim, int max_splits) {
-    return (long long)n * n_q * max_splits * (head_dim + 2) * 4;
+    return (long long)n * n_q * max_splits * (head_dim + 2) * 4 + (long long)n * n_q * 4;   // and the pairs' split counts
 }
 
+// Whether a step of n decoded tokens can be cut as a stream (kipp_attn_decode_mma, stream_ctas > 0).
+extern "C" int kipp_attn_decode_stream_ok(int n, int max_splits) { return n > 0 && n <= STREAM_MAX_TOKENS && max_splits >= 2; }
+
 // Single decoded tokens: `rows` lists the n entries; scratch as sized above
-// (part_o first, then part_ml), 16-byte aligned.
+// (part_o first, then part_ml, then the split counts), 16-byte aligned.  stream_ctas > 0: the
+// step's key tiles are dealt out in equal runs to that many CTAs (attn_decode_stream_kernel;
+// split_keys is not read); 0: every token is cut into splits of split_keys keys.
 extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
                                     const int* q_start, const int* context_len, const int* block_table,
                                     int table_width, int page_size, const int* rows, int n, int n_q, int n_kv,
                                     int head_dim, float scale, int window, int max_splits,
-                                    const int* split_keys, int split_stride, float* scratch, void* stream) {
+                                    const int* split_keys, int split_stride, int stream_ctas, float* scratch,
+                                    void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
-        max_splits > 64 || split_keys == nullptr || scratch == nullptr || ((uintptr_t)scratch & 15) ||
-        ((uintptr_t)out & 7))
+        max_splits > 64 || scratch == nullptr || ((uintptr_t)scratch & 15) || ((uintptr_t)out & 7) || stream_ctas < 0 ||
+        (stream_ctas > 0 ? !kipp_attn_decode_stream_ok(n, max_splits) : split_keys == nullptr))
         return KIPP_ERR_ARG;
     DecodeParams p;
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages;
@@ -754,6 +859,8 @@ extern "C" int kipp_attn_decode_mma(void* out, const void* q, const void* k_page
     p.scale_log2 = scale * 1.4426950408889634f;
     p.qkv = nullptr; p.ld_qkv = 0; p.q_norm_w = p.k_norm_w = nullptr; p.norm_dtype = 0; p.eps = 0.f;
     p.cos_sin = nullptr; p.k_write = p.v_write = nullptr; p.status = nullptr;
+    p.stream_ctas = stream_ctas;
+    p.n_splits_out = stream_ctas > 0 ? reinterpret_cast<int*>(p.part_ml + (size_t)n * n_q * max_splits * 2) : nullptr;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
     if (rc) return rc;
@@ -828,11 +935,12 @@ extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long 
                                           const int* q_start, const int* context_len, const int* block_table,
                                           int table_width, int page_size, const int* rows, int n, int n_q,
                                           int n_kv, int head_dim, float scale, int window, int max_splits,
-                                          const int* split_keys, int split_stride, float* scratch, int* status,
-                                          void* stream) {
+                                          const int* split_keys, int split_stride, int stream_ctas, float* scratch,
+                                          int* status, void* stream) {
     if (n <= 0) return 0;
     if (!kipp_attn_decode_supported(head_dim, n_q, n_kv) || page_size <= 0 || window < 0 || max_splits <= 0 ||
-        max_splits > 64 || split_keys == nullptr || scratch == nullptr || ((uintptr_t)scratch & 15) ||
+        max_splits > 64 || scratch == nullptr || ((uintptr_t)scratch & 15) || stream_ctas < 0 ||
+        (stream_ctas > 0 ? !kipp_attn_decode_stream_ok(n, max_splits) : split_keys == nullptr) ||
         ((uintptr_t)out & 7) || status == nullptr || qkv == nullptr ||
         ld_qkv < (long long)(n_q + 2 * n_kv) * head_dim || ld_qkv > 0x7fffffffLL ||
         (q_norm_w == nullptr) != (k_norm_w == nullptr))
@@ -853,6 +961,8 @@ extern "C" int kipp_attn_decode_mma_fused(void* out, const void* qkv, long long 
     p.k_write = write_cache ? (bf16*)k_pages : nullptr;
     p.v_write = write_cache ? (bf16*)v_pages : nullptr;
     p.status = status;
+    p.stream_ctas = stream_ctas;
+    p.n_splits_out = stream_ctas > 0 ? reinterpret_cast<int*>(p.part_ml + (size_t)n * n_q * max_splits * 2) : nullptr;
     cudaStream_t s = (cudaStream_t)stream;
     int rc = head_dim == 64 ? launch_decode<64>(p, n, s) : launch_decode<128>(p, n, s);
     if (rc) return rc;

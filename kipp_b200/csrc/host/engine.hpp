@@ -324,7 +324,7 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
         cos_sin = static_cast<const float*>(it->second);
     }
     void* attn = ctx.workspace->buffer("attn_out", (size_t)T * q_dim_ * es);
-    const AttentionWork work = AttentionPlanner::work_of(m, planner_key_);
+    const AttentionWork work = planner_->work_of(m);
     const void* qn = qk_norm_ ? q_norm_ : nullptr;
     const void* kn = qk_norm_ ? k_norm_ : nullptr;
     if (Ops::attention_decode_fused_ok(work, ctx.dtype, heads_, kv_heads_, head_dim_, rot)) {
@@ -873,7 +873,7 @@ inline void Engine::feedback_tail(StepGraph& g) {
     ops_.burst_advance(const_cast<int*>(g.meta.token_ids), const_cast<int*>(g.meta.positions),
                        const_cast<int*>(g.meta.context_len), g.next_tokens.as<int>(), g.ring.as<int>(),
                        g.counter.as<int>(), n, burst_ring_rows);
-    for (auto& p : planners_) p->advance_on_device(ops_, g.meta.work.at(p->key()).data(), g.meta.context_len, n);
+    for (auto& p : planners_) p->advance_on_device(ops_, g.meta.shape, g.meta.work.at(p->key()).data(), g.meta.context_len, n);
 }
 
 // Runs a step through its captured graph.  The first step of a key runs the kernels directly and

@@ -21,6 +21,8 @@ struct AttentionWork {
     const int* decode_rows = nullptr;      // [n_decode] entries that bring one token
     int n_decode = 0;
     const int* split_keys = nullptr;       // [n_decode] keys per split of each decoded token
+    int stream_ctas = 0;                   // > 0: the decoded tokens' key tiles are dealt out in equal runs to
+                                           // that many CTAs instead (split_keys is not read)
     const int* prefill_work = nullptr;     // [(entry, first token)] per 64-token tile, entries of > 1 token
     int n_prefill_items = 0;
     const int* all_work = nullptr;         // the same over every entry
@@ -173,8 +175,18 @@ public:
         return f(head_dim, n_q, n_kv) != 0 && g(page_size) != 0;
     }
 
+    // The stream cut of a step's decoded tokens, where the planner asks for it and the kernel takes the step.
+    static bool decode_stream_ok(int n_decode) {
+        using Fn = int (*)(int, int);
+        static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_decode_stream_ok");
+        return f(n_decode, DECODE_MAX_SPLITS) != 0;
+    }
+    static int decode_stream_ctas(const AttentionWork& work) {
+        return work.stream_ctas > 0 && decode_stream_ok(work.n_decode) ? work.stream_ctas : 0;
+    }
+
     float* decode_scratch(int n, int n_q, int head_dim) {
-        size_t floats = (size_t)n * n_q * DECODE_MAX_SPLITS * (head_dim + 2);
+        size_t floats = (size_t)n * n_q * DECODE_MAX_SPLITS * (head_dim + 2) + (size_t)n * n_q;
         if (floats < (1u << 20)) floats = 1u << 20;
         return workspace->get<float>("attention_decode_scratch", floats);
     }
@@ -212,13 +224,13 @@ public:
                                 const int* context_len, int n_q, int n_kv, int head_dim, float scale, int window) {
         using Fn = int (*)(void*, const void*, long long, void*, void*, const void*, const void*, int, float, const void*,
                            int, const int*, const int*, const int*, int, int, const int*, int, int, int, int, float, int,
-                           int, const int*, int, float*, int*, void*);
+                           int, const int*, int, int, float*, int*, void*);
         static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_decode_mma_fused");
         float* scratch = decode_scratch(work.n_decode, n_q, head_dim);
         run(f(out, qkv, ld_qkv, cache.k_pages, cache.v_pages, q_norm_w, k_norm_w, norm_dtype, eps, cos_sin,
               write_cache ? 1 : 0, q_start, context_len, cache.block_table, cache.table_width, cache.page_size,
               work.decode_rows, work.n_decode, n_q, n_kv, head_dim, scale, window, DECODE_MAX_SPLITS, work.split_keys, 1,
-              scratch, status, stream),
+              decode_stream_ctas(work), scratch, status, stream),
             "attn_decode_mma_fused", 2);
         ++fused_decode_launches;
     }
@@ -311,12 +323,12 @@ private:
         }
         if (use_decode) {
             using Fn = int (*)(void*, const void*, const void*, const void*, const int*, const int*, const int*, int, int,
-                               const int*, int, int, int, int, float, int, int, const int*, int, float*, void*);
+                               const int*, int, int, int, int, float, int, int, const int*, int, int, float*, void*);
             static Fn f = kernel_symbol<Fn>("attention_mma", "kipp_attn_decode_mma");
             float* scratch = decode_scratch(work.n_decode, n_q, head_dim);
             run(f(out, q, cache.k_pages, cache.v_pages, q_start, context_len, cache.block_table, cache.table_width,
                   cache.page_size, work.decode_rows, work.n_decode, n_q, n_kv, head_dim, scale, window,
-                  DECODE_MAX_SPLITS, work.split_keys, 1, scratch, stream),
+                  DECODE_MAX_SPLITS, work.split_keys, 1, decode_stream_ctas(work), scratch, stream),
                 "attn_decode_mma", 2);
         }
     }

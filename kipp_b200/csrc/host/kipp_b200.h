@@ -100,6 +100,7 @@ int kipp_part_tensor_specs(const char* part_json, const char* prefix, const char
 /* Keys per split that the paged attention's planner chooses for `decoded` tokens whose longest
    context is `longest` keys (own_length: for one token of that context alone). */
 int kipp_attention_split_length(int decoded, int longest, int kv_heads, int sm_count, int own_length);
+int kipp_attention_stream_pays(int decoded, const int* keys, int kv_heads, int sm_count);
 /* Names of the registered architectures and part kinds, as a JSON object of two lists. */
 const char* kipp_registered(void);
 

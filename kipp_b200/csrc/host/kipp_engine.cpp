@@ -160,6 +160,19 @@ int kipp_attention_split_length(int decoded, int longest, int kv_heads, int sm_c
     return AttentionPlanner(kv_heads, sm_count, false).step_split_length(decoded, longest);
 }
 
+// Whether the planner deals a step of `decoded` single tokens with these numbers of keys out as a
+// stream over one wave of CTAs (1) or cuts each into splits of the step's length (0).
+int kipp_attention_stream_pays(int decoded, const int* keys, int kv_heads, int sm_count) {
+    StepShape s;
+    s.entries = decoded;
+    for (int i = 0; i < decoded; ++i) {
+        s.q_lens.push_back(1);
+        s.starts.push_back(keys[i] - 1);
+    }
+    s.tokens = decoded;
+    return AttentionPlanner(kv_heads, sm_count, false).stream_pays(s) ? 1 : 0;
+}
+
 const char* kipp_registered(void) {
     ensure_registered();
     Json j = Json::object();

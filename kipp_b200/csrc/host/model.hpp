@@ -81,8 +81,10 @@ public:
     virtual int sections() const = 0;
     virtual void sizes(const StepShape& shape, int* ints_per_section) const = 0;
     virtual void fill(const StepShape& shape, int* const* host_sections) const = 0;
-    // after every entry moved on by one token on the device (a burst of decode steps)
-    virtual void advance_on_device(Ops& ops, int* const* device_sections, const int* context_len, int entries) const {}
+    // after every entry moved on by one token on the device (a burst of decode steps); `shape`
+    // is the step's as the host packed it
+    virtual void advance_on_device(Ops& ops, const StepShape& shape, int* const* device_sections,
+                                   const int* context_len, int entries) const {}
 };
 
 struct StepMeta {

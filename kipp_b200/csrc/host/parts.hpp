@@ -146,6 +146,7 @@ public:
     static constexpr int TILE = 64;
     static constexpr int CTA_FIXED_TILES = 5;   // what a decode CTA costs beside its key tiles, in 64-key tiles
     static constexpr int CTAS_PER_SM = 3;
+    static constexpr double STREAM_MARGIN = 1.15;   // the stream cut must look this much better to be taken
 
     AttentionPlanner(int kv_heads, int sm_count, bool own_length)
         : kv_heads_(kv_heads), resident_(CTAS_PER_SM * std::max(sm_count, 1)), own_length_(own_length) {}
@@ -220,12 +221,47 @@ public:
         }
     }
 
-    void advance_on_device(Ops& ops, int* const* sec, const int* context_len, int entries) const override {
+    void advance_on_device(Ops& ops, const StepShape& s, int* const* sec, const int* context_len,
+                           int entries) const override {
+        // (the stream cut reads the lengths itself: no keys per split to bring up to date)
+        if (stream_pays(s)) return;
         ops.decode_replan(sec[1], context_len, sec[0], entries, kv_heads_, resident_, CTA_FIXED_TILES,
                           Ops::DECODE_MAX_SPLITS, own_length_ ? 1 : 0);
     }
 
-    static AttentionWork work_of(const StepMeta& meta, const std::string& key) {
+    // Whether the decoded tokens of a step are better cut as a stream over one wave of CTAs (see
+    // attn_decode_stream_kernel) than into splits of the step's length: where the splits need
+    // more than one wave or leave much of one empty (64 tokens of 2,048 keys: 5.93 against 6.26
+    // ms a step; 8 tokens: 2.67 against 2.49, a run then spans two pairs and pays their set-up
+    // twice, hence the margin).  Never where every token's splits are to come from its own length.
+    bool stream_pays(const StepShape& s) const {
+        if (own_length_) return false;
+        long long tiles = 0;
+        int longest = 0, decoded = 0;
+        for (int i = 0; i < s.entries; ++i) {
+            if (s.q_lens[(size_t)i] != 1) continue;
+            const int keys = s.starts[(size_t)i] + 1;
+            tiles += (keys + TILE - 1) / TILE;
+            longest = std::max(longest, keys);
+            ++decoded;
+        }
+        if (decoded == 0 || !Ops::decode_stream_ok(decoded)) return false;
+        const long long pairs = (long long)decoded * kv_heads_;
+        const int most = (longest + TILE - 1) / TILE;
+        const int k = step_split_length(decoded, longest) / TILE;
+        const long long splits = (most + k - 1) / k;
+        const double split_cost = (double)((pairs * splits + resident_ - 1) / resident_) * (k + CTA_FIXED_TILES);
+        const long long total = tiles * kv_heads_;
+        const long long per = std::max<long long>({(total + resident_ - 1) / resident_,
+                                                   (most + Ops::DECODE_MAX_SPLITS - 2) / (Ops::DECODE_MAX_SPLITS - 1), 1});
+        const double pieces = 1.0 + (double)per * (double)pairs / (double)total;      // pairs a run touches
+        const double stream_cost = (double)per + CTA_FIXED_TILES * pieces;
+        return stream_cost * STREAM_MARGIN < split_cost;
+    }
+
+    AttentionWork work_of(const StepMeta& meta) const {
+        const std::string key = this->key();
+        const int stream_ctas = stream_pays(meta.shape) ? resident_ : 0;
         AttentionWork w;
         auto it = meta.work.find(key);
         if (it == meta.work.end()) fail(KIPP_E_STATE, "the step carries no work lists for " + key);
@@ -233,6 +269,7 @@ public:
         const std::vector<int>& n = meta.work_sizes.at(key);
         w.decode_rows = sec[0]; w.n_decode = n[0];
         w.split_keys = sec[1];
+        w.stream_ctas = stream_ctas;
         w.prefill_work = sec[2]; w.n_prefill_items = n[2] / 2;
         w.all_work = sec[3]; w.n_all_items = n[3] / 2;
         w.prefill_work128 = sec[4]; w.n_prefill_items128 = n[4] / 2;
@@ -328,7 +365,7 @@ public:
     std::optional<PagedKVSpec> cache_spec() const override { return PagedKVSpec{kv_heads_, head_dim_, window_}; }
     std::shared_ptr<WorkPlanner> planner(const DeviceInfo& dev, bool own_length) override {
         auto p = std::make_shared<AttentionPlanner>(kv_heads_, dev.sm_count, own_length);
-        planner_key_ = p->key();
+        planner_ = p;
         return p;
     }
     void bind(Binder& b, const std::string& p) override {
@@ -372,7 +409,7 @@ private:
     float scale_ = 1.f;
     int q_dim_ = 0, kv_dim_ = 0, dtype_ = BF16, norm_dtype_ = F32;
     void *w_qkv_ = nullptr, *w_o_ = nullptr, *q_norm_ = nullptr, *k_norm_ = nullptr;
-    std::string planner_key_;
+    std::shared_ptr<AttentionPlanner> planner_;
 };
 
 // Dense SwiGLU feed-forward: x += W_down (silu(W_gate n) * (W_up n)) (src/kipp.c:2994-3010,

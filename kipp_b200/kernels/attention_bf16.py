@@ -66,7 +66,7 @@ def choose(meta, n_q, n_kv, head_dim, page_size) -> str:
 def decode_scratch(device: torch.device, n: int, n_q: int, head_dim: int) -> torch.Tensor:
     """float32 scratch of the split-K decode kernel: partial outputs and
     (max, sum) pairs of every split, kept per device and grown on demand."""
-    floats = n * n_q * MAX_SPLITS * (head_dim + 2)
+    floats = n * n_q * MAX_SPLITS * (head_dim + 2) + n * n_q
     key = (device.type, device.index)
     cur = _scratch.get(key)
     if cur is None or cur.numel() < floats:
@@ -79,8 +79,20 @@ def decode_scratch(device: torch.device, n: int, n_q: int, head_dim: int) -> tor
     return cur
 
 
+def stream_ctas(device: torch.device) -> int:
+    """The grid of the stream cut of the decode attention: one wave, three CTAs per SM."""
+    return 3 * torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def stream_ok(n_decode: int) -> bool:
+    f = _fn("attention_mma", "kipp_attn_decode_stream_ok", [c_int, c_int])
+    return bool(f(n_decode, MAX_SPLITS))
+
+
 def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv, head_dim, scale,
-        window, status) -> None:
+        window, status, stream: bool = True) -> None:
+    """``stream``: the decoded tokens' key tiles are dealt out in equal runs to one wave of
+    CTAs; False: every token is cut into splits of ``meta.decode_split_keys`` keys."""
     if impl != "mma":
         raise KernelError(f"unknown attention implementation {impl!r}")
     if q.dtype != torch.bfloat16:
@@ -105,11 +117,13 @@ def run(impl, out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv,
         scratch = decode_scratch(q.device, meta.n_decode, n_q, head_dim)
         f = _fn("attention_mma", "kipp_attn_decode_mma",
                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p])
+                 c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                 c_void_p])
+        ctas = stream_ctas(q.device) if stream and stream_ok(meta.n_decode) else 0
         _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(meta.q_start),
                  _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
                  _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale),
-                 int(window or 0), MAX_SPLITS, _ptr(meta.decode_split_keys), _split_stride(meta),
+                 int(window or 0), MAX_SPLITS, _ptr(meta.decode_split_keys), _split_stride(meta), ctas,
                  _ptr(scratch), _stream()),
                "attn_decode_mma")
 
@@ -144,7 +158,7 @@ def decode_fused_ok(meta, q_dtype, n_q: int, n_kv: int, head_dim: int, rotary_di
 
 
 def decode_fused(out, qkv, k_pages, v_pages, q_norm_w, k_norm_w, eps, cos_sin, write_cache: bool, meta,
-                 block_table, page_size, n_q, n_kv, head_dim, scale, window, status) -> None:
+                 block_table, page_size, n_q, n_kv, head_dim, scale, window, status, stream: bool = True) -> None:
     """Attention of a step of decoded tokens straight from the raw q/k/v projection:
     the per-head norm, the rotation and the write of the new key and value happen in
     the attention kernel (no launch of their own)."""
@@ -160,10 +174,12 @@ def decode_fused(out, qkv, k_pages, v_pages, q_norm_w, k_norm_w, eps, cos_sin, w
     f = _fn("attention_mma", "kipp_attn_decode_mma_fused",
             [c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
-             c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+             c_float, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    ctas = stream_ctas(qkv.device) if stream and stream_ok(meta.n_decode) else 0
     _check(f(_ptr(out), _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(q_norm_w), _ptr(k_norm_w),
              norm_dtype, float(eps), _ptr(cos_sin), 1 if write_cache else 0, _ptr(meta.q_start),
              _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
              _ptr(meta.decode_rows), meta.n_decode, n_q, n_kv, head_dim, float(scale), int(window or 0),
-             MAX_SPLITS, _ptr(meta.decode_split_keys), _split_stride(meta), _ptr(scratch), _ptr(status), _stream()),
+             MAX_SPLITS, _ptr(meta.decode_split_keys), _split_stride(meta), ctas, _ptr(scratch), _ptr(status),
+             _stream()),
            "attn_decode_mma_fused")

@@ -99,6 +99,7 @@ _SIGNATURES = {
     "kipp_plan_tensor_specs": (_i, [c_char_p, _cpp]),
     "kipp_part_tensor_specs": (_i, [c_char_p, c_char_p, _cpp]),
     "kipp_attention_split_length": (_i, [_i, _i, _i, _i, _i]),
+    "kipp_attention_stream_pays": (_i, [_i, ctypes.POINTER(ctypes.c_int), _i, _i]),
     "kipp_registered": (c_char_p, []),
     "kipp_weights_open": (_i, [c_char_p, POINTER(_vp)]),
     "kipp_weights_close": (None, [_vp]),

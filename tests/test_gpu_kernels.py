@@ -1,6 +1,7 @@
 """Each kernel alone against a plain float64 PyTorch reference of the same
 operation, at sizes other than the engine's, in float32 and bfloat16."""
 import math
+import random
 
 import numpy as np
 import pytest
@@ -445,6 +446,11 @@ def test_attention_tensor_core(shape, window):
         ref = attention_ref(meta, table, q, kp, vp, layout, page, window, 1 / math.sqrt(D))
         assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2), (shape, li, window)
         assert st.tolist() == [0, 0, 0, 0]
+        # the decoded tokens cut into splits of a given length instead of dealt out as a stream
+        out1 = torch.full_like(q, 9.0)
+        attention_bf16.run("mma", out1, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D),
+                           window, st, stream=False)
+        assert torch.allclose(out1.double().cpu(), ref, rtol=2e-2, atol=2e-2), (shape, li, window)
         attention_bf16.PREFILL_TC = False
         try:
             out2 = torch.full_like(q, 9.0)
@@ -701,6 +707,12 @@ def test_decode_attention_fused_with_norm_rotation_and_cache_write(case):
     assert torch.allclose(k1.float(), k2.float(), rtol=1e-2, atol=1e-2)
     assert float((k1.float() - kp.float()).abs().sum()) > 0          # keys were written
     assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    k4, v4 = kp.clone(), vp.clone()
+    got4 = torch.full_like(q, 7.0)
+    attention_bf16.decode_fused(got4, qkv, k4, v4, qw, kw, 1e-6, cos_sin, True, meta, meta.block_tables[0], page,
+                                nq, nkv, D, 1 / math.sqrt(D), window, st, stream=False)
+    assert torch.equal(k4, k2) and torch.equal(v4, v2)            # splits of a given length: the same cache
+    assert torch.allclose(got4.float(), want.float(), rtol=2e-2, atol=2e-2)
     # reading another run's cache: nothing is written
     k3, v3 = k1.clone(), v1.clone()
     got3 = torch.zeros_like(q)
@@ -708,6 +720,44 @@ def test_decode_attention_fused_with_norm_rotation_and_cache_write(case):
                                  page, nq, nkv, D, 1 / math.sqrt(D), window, st)
     assert torch.equal(k3, k1) and torch.equal(v3, v1)
     assert torch.allclose(got3.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("window", [None, 500])
+@pytest.mark.parametrize("shape", [dict(D=128, nq=8, nkv=2, page=16), dict(D=64, nq=6, nkv=3, page=32),
+                                   dict(D=128, nq=16, nkv=1, page=16)])
+def test_decode_attention_dealt_out_as_a_stream(shape, window):
+    """Many decoded tokens of very different lengths: the key tiles of all (token, kv head)
+    pairs are dealt out in equal runs to one wave of CTAs, so runs end inside pairs and span
+    several short ones; every token against the plain reference, and against the kernel
+    that cuts each token into splits of its own.  A far key that stands out must be found
+    wherever the cuts fall."""
+    from kipp_b200.kernels import attention_bf16
+    D, nq, nkv, page = shape["D"], shape["nq"], shape["nkv"], shape["page"]
+    rng = random.Random(D + nq)
+    layout = [(rng.choice([0, 1, 63, 64, 65, 200, 1000, 2500, 4000]) + rng.randrange(3), 1) for _ in range(70)]
+    layout[5] = (6000, 1)
+    meta, table, q, kp, vp = attention_case(31, D, nq, nkv, page, layout, torch.bfloat16)
+    # one key far back in the longest request that the query of that token points at
+    e, far = 5, 777
+    pg, slot = int(table[e, far // page]), far % page
+    kp[pg, :, slot, :] = 0
+    kp[pg, :, slot, 0] = 30.0
+    q[e, :, :] = 0
+    q[e, :, 0] = 30.0
+    st = status()
+    attention_bf16.decode_scratch(torch.device(DEV), meta.tokens, nq, D).fill_(float("nan"))
+    out = torch.full_like(q, 9.0)
+    attention_bf16.run("mma", out, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D), window, st)
+    ref = attention_ref(meta, table, q, kp, vp, layout, page, window, 1 / math.sqrt(D))
+    assert torch.allclose(out.double().cpu(), ref, rtol=2e-2, atol=2e-2)
+    if window is None:                           # the far key takes all the weight
+        assert torch.allclose(out[e].float().cpu(), vp[pg, :, slot, :].float().cpu().repeat_interleave(nq // nkv, 0),
+                              rtol=2e-2, atol=2e-2)
+    out1 = torch.full_like(q, 9.0)
+    attention_bf16.run("mma", out1, q, kp, vp, meta, meta.block_tables[0], page, nq, nkv, D, 1 / math.sqrt(D), window,
+                       st, stream=False)
+    assert torch.allclose(out1.float(), out.float(), rtol=2e-2, atol=2e-2)
+    assert st.tolist() == [0, 0, 0, 0]
 
 
 def test_a_bounded_wait_runs_out_and_reports():

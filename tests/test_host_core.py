@@ -55,3 +55,9 @@ def test_split_rule_of_the_decode_attention():
     assert lib.kipp_attention_split_length(1, 700, 8, 148, 1) == 128
     assert lib.kipp_attention_split_length(1, 300, 8, 148, 1) == 64
     assert lib.kipp_attention_split_length(1, 2049, 8, 148, 1) == 320
+    # dealt out as a stream where splits of one length would need several waves or leave one half empty
+    def stream(n, keys):
+        arr = (ctypes.c_int * n)(*([keys] * n))
+        return lib.kipp_attention_stream_pays(n, arr, 8, 148)
+    assert [stream(n, 2049) for n in (1, 8, 16, 64)] == [0, 0, 0, 1]      # 512 pairs on 444 places: four waves of splits
+    assert stream(8, 8031) == 0 and stream(64, 4097) == 1

@@ -52,11 +52,12 @@ def plain_attention_of(meta, table, q, kp, vp, contexts, page, window, D):
 
 
 def reference_entry(meta, q, kp, vp, n_q, n_kv, D, page, window):
-    """The existing entry point: scratch comes from the caller (torch)."""
-    from kipp_b200 import kernels
+    """The existing entry point: scratch comes from the caller (torch); every token cut into
+    splits of the given length, as the entry point without allocation cuts them."""
+    from kipp_b200.kernels import attention_bf16
     out = torch.zeros_like(q)
-    kernels.attention(out, q, kp, vp, meta, meta.block_tables[0], page, n_q, n_kv, D, 1 / math.sqrt(D),
-                      window, torch.zeros(4, dtype=torch.int32, device=DEV), impl="mma")
+    attention_bf16.run("mma", out, q, kp, vp, meta, meta.block_tables[0], page, n_q, n_kv, D, 1 / math.sqrt(D),
+                       window, torch.zeros(4, dtype=torch.int32, device=DEV), stream=False)
     return out
 
 
