@@ -327,6 +327,17 @@ template <int D>
 __device__ __forceinline__ void warp_norm_rope(float (&x)[D / 32], const void* norm_w, int norm_dtype, float eps,
                                                const float2* cs_row, int lane) {
     constexpr int NE = D / 32;
+    // the weights and the (cos, sin) pairs first: their loads travel while the sum is formed
+    float w[NE];
+    float2 cs[NE / 2];
+    if (norm_w != nullptr) {
+#pragma unroll
+        for (int j = 0; j < NE; ++j) w[j] = load_w(norm_w, norm_dtype, lane + 32 * j);
+    }
+    if (cs_row != nullptr) {
+#pragma unroll
+        for (int j = 0; j < NE / 2; ++j) cs[j] = cs_row[lane + 32 * j];
+    }
     if (norm_w != nullptr) {
         float ss = 0.f;
 #pragma unroll
@@ -334,15 +345,14 @@ __device__ __forceinline__ void warp_norm_rope(float (&x)[D / 32], const void* n
         ss = warp_sum(ss);
         const float scale = 1.0f / sqrtf(ss / (float)D + eps);
 #pragma unroll
-        for (int j = 0; j < NE; ++j) x[j] = x[j] * scale * load_w(norm_w, norm_dtype, lane + 32 * j);
+        for (int j = 0; j < NE; ++j) x[j] = x[j] * scale * w[j];
     }
     if (cs_row != nullptr) {
 #pragma unroll
         for (int j = 0; j < NE / 2; ++j) {
-            const float2 cs = cs_row[lane + 32 * j];
             const float a = x[j], b = x[j + NE / 2];
-            x[j] = a * cs.x - b * cs.y;
-            x[j + NE / 2] = b * cs.x + a * cs.y;
+            x[j] = a * cs[j].x - b * cs[j].y;
+            x[j + NE / 2] = b * cs[j].x + a * cs[j].y;
         }
     }
 }
@@ -591,15 +601,18 @@ __device__ __forceinline__ void decode_split(const DecodeParams& p, uint8_t* sme
     __syncthreads();
     float* w_m = reinterpret_cast<float*>(smem);                  // [WARPS][16]
     float* w_l = w_m + WARPS * 16;                                // [WARPS][16]
-    float* w_o = w_l + WARPS * 16;                                // [WARPS][16][D]
+    float* w_o = w_l + WARPS * 16;                                // [WARPS][16][D + 8]
+    // (rows 8 floats longer than a head: the eight rows a warp's lanes write at once then fall on
+    // four groups of banks instead of one)
+    constexpr int WO = D + 8;
     if (t4 == 0) {
         w_m[warp * 16 + g4] = m0; w_m[warp * 16 + g4 + 8] = m1;
         w_l[warp * 16 + g4] = l0; w_l[warp * 16 + g4 + 8] = l1;
     }
 #pragma unroll
     for (int d = 0; d < D / 8; ++d) {
-        float* r0 = w_o + ((size_t)warp * 16 + g4) * D + d * 8 + 2 * t4;
-        float* r1 = w_o + ((size_t)warp * 16 + g4 + 8) * D + d * 8 + 2 * t4;
+        float* r0 = w_o + ((size_t)warp * 16 + g4) * WO + d * 8 + 2 * t4;
+        float* r1 = w_o + ((size_t)warp * 16 + g4 + 8) * WO + d * 8 + 2 * t4;
         r0[0] = o[d][0]; r0[1] = o[d][1];
         r1[0] = o[d][2]; r1[1] = o[d][3];
     }
@@ -615,7 +628,7 @@ __device__ __forceinline__ void decode_split(const DecodeParams& p, uint8_t* sme
             const float wm = w_m[w * 16 + row];
             const float c = (wm == -INFINITY) ? 0.f : exp2f(wm - m);
             l += w_l[w * 16 + row] * c;
-            acc += w_o[((size_t)w * 16 + row) * D + d] * c;
+            acc += w_o[((size_t)w * 16 + row) * WO + d] * c;
         }
         if (n_splits == 1) {
             // nothing to merge: this is the token's result
@@ -777,7 +790,7 @@ inline int launch_merge(const DecodeParams& p, void* out, int n, int head_dim, c
 
 template <int D> int launch_decode(const DecodeParams& p, int n, cudaStream_t s) {
     constexpr int PIPE = 2 * DECODE_STAGES * TILE_KEYS * D * 2 + 16 * D * 2;   // tiles, and the group's queries
-    constexpr int MERGE = (2 * WARPS * 16 + WARPS * 16 * D) * 4;
+    constexpr int MERGE = (2 * WARPS * 16 + WARPS * 16 * (D + 8)) * 4;
     constexpr int SMEM = PIPE > MERGE ? PIPE : MERGE;
     static bool configured = false;
     if (!configured) {
