@@ -1,5 +1,9 @@
-// Greedy and temperature sampling on the device, one thread block per row of
-// logits.
+// Greedy and temperature sampling on the device.  A row of logits is worked on by a team:
+// one thread block, or for long rows a thread-block cluster of eight whose blocks take an
+// eighth of the row each and put their counts and sums together through distributed shared
+// memory (every block reads all eight and decides alike, so nothing is broadcast; the
+// cluster's hardware barrier stands between writing and reading).  One block alone scanned a
+// 151,936-entry row some fifteen times at 40 to 70 us a scan.
 //
 // The token drawn is the one the reference's host sampler draws from the same
 // logits and the same uniform number (kipp_sample_ex, src/kipp.c:3433-3559):
@@ -33,9 +37,32 @@ __device__ __forceinline__ unsigned desc_key(float x) {
     return ~k;
 }
 
+// ---- the team of blocks that shares a row (a cluster along x; one block when launched without)
+__device__ __forceinline__ int team_size() { unsigned n; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n)); return (int)n; }
+__device__ __forceinline__ int team_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return (int)r; }
+// all threads of all blocks of the team: what was written to shared memory before is visible after
+__device__ __forceinline__ void team_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t team_addr(const void* p, int rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ unsigned team_ld_u32(const void* p, int rank) {
+    unsigned v; asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(team_addr(p, rank)) : "memory"); return v;
+}
+__device__ __forceinline__ float team_ld_f32(const void* p, int rank) {
+    float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(team_addr(p, rank)) : "memory"); return v;
+}
+__device__ __forceinline__ double team_ld_f64(const void* p, int rank) {
+    double v; asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(team_addr(p, rank)) : "memory"); return v;
+}
+
 struct RowCtx {
     const float* v;
     int n;
+    int lo, hi;                 // this block's part of the row
     float inv_t, smax, cutoff;
     // filters
     bool has_topk;   unsigned topk_key, topk_tok;
@@ -60,8 +87,10 @@ __device__ __forceinline__ bool member(const RowCtx& c, int i, unsigned& key, fl
 }
 
 struct Shared {
-    unsigned cnt[256];
+    unsigned cnt[256];          // this block's part of the row
     double wsum[256];
+    unsigned cnt_all[256];      // the team's: the blocks' parts added in block order
+    double wsum_all[256];
     float red_val[32];
     int red_idx[32];
     double red_d[32];
@@ -81,7 +110,7 @@ __device__ void histogram_pass(const RowCtx& c, Shared& sh, int level, unsigned 
     for (int b = threadIdx.x; b < 256; b += blockDim.x) { sh.cnt[b] = 0; sh.wsum[b] = 0.0; }
     __syncthreads();
     int cur = -1; unsigned ccnt = 0; double cw = 0.0;
-    for (int i = threadIdx.x; i < c.n; i += blockDim.x) {
+    for (int i = c.lo + threadIdx.x; i < c.hi; i += blockDim.x) {
         unsigned key; float w;
         if (!member(c, i, key, w)) continue;
         unsigned digit;
@@ -104,6 +133,22 @@ __device__ void histogram_pass(const RowCtx& c, Shared& sh, int level, unsigned 
     }
     if (cur >= 0) { atomicAdd(&sh.cnt[cur], ccnt); atomicAdd(&sh.wsum[cur], cw); }
     __syncthreads();
+    // the team's histogram: every block adds the blocks' parts in block order
+    team_sync();
+    const int blocks = team_size();
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) {
+        unsigned n8[8]; double w8[8];                // all loads first: they travel together
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            n8[r] = r < blocks ? team_ld_u32(&sh.cnt[b], r) : 0u;
+            w8[r] = r < blocks ? team_ld_f64(&sh.wsum[b], r) : 0.0;
+        }
+        unsigned n = 0; double w = 0.0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) { n += n8[r]; w += w8[r]; }
+        sh.cnt_all[b] = n; sh.wsum_all[b] = w;
+    }
+    team_sync();                                   // nobody clears its part while another still reads it
 }
 
 // Position selection in the (value desc, token asc) order of the current set.
@@ -119,26 +164,59 @@ __device__ void select(const RowCtx& c, Shared& sh, int mode, unsigned long long
     double w_before = 0.0;
     for (int level = 0; level < 8; ++level) {
         histogram_pass(c, sh, level, prefix_key, prefix_tok);
-        if (threadIdx.x == 0) {
-            unsigned long long cb = cnt_before; double wb = w_before;
-            int chosen = -1, last_nonempty = -1;
-            unsigned long long cb_last = 0; double wb_last = 0.0;
-            for (int b = 0; b < 256; ++b) {
-                const unsigned n = sh.cnt[b];
-                if (n == 0) continue;
-                last_nonempty = b; cb_last = cb; wb_last = wb;
-                bool hit;
-                if (mode == MODE_COUNT) hit = cb + n >= target_count;
-                else if (mode == MODE_W_GE) hit = wb + sh.wsum[b] >= target_w;
-                else hit = wb + sh.wsum[b] > target_w;
-                if (hit) { chosen = b; break; }
-                cb += n; wb += sh.wsum[b];
+        if (threadIdx.x < 32) {
+            // The first bucket (in order) at which the running count or weight reaches the target,
+            // else the last bucket that is not empty.  One warp: a lane walks over its eight
+            // buckets from the sums of the lanes before it (one thread alone took 256 dependent
+            // steps, some 5 us a level).
+            const int lane = threadIdx.x;
+            unsigned n8[8]; double w8[8];
+            unsigned long long ln = 0; double lw = 0.0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                n8[j] = sh.cnt_all[8 * lane + j]; w8[j] = sh.wsum_all[8 * lane + j];
+                ln += n8[j]; lw += w8[j];
             }
-            if (chosen < 0) { chosen = last_nonempty; cb = cb_last; wb = wb_last; }
-            sh.found = chosen;
-            sh.sel_cnt_before = cb; sh.sel_w_before = wb;
-            sh.sel_bucket_cnt = chosen >= 0 ? sh.cnt[chosen] : 0;
-            sh.d_val = chosen >= 0 ? wb + sh.wsum[chosen] : wb;
+            unsigned long long pn = ln; double pw = lw;             // inclusive over the lanes
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long tn = __shfl_up_sync(0xffffffffu, pn, o);
+                const double tw = __shfl_up_sync(0xffffffffu, pw, o);
+                if (lane >= o) { pn += tn; pw += tw; }
+            }
+            unsigned long long cb = __shfl_up_sync(0xffffffffu, pn, 1);
+            double wb = __shfl_up_sync(0xffffffffu, pw, 1);
+            if (lane == 0) { cb = 0; wb = 0.0; }
+            cb += cnt_before; wb += w_before;
+            int chosen = -1, last_nonempty = -1;
+            unsigned long long cb_hit = 0, cb_last = 0; double wb_hit = 0.0, wb_last = 0.0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (n8[j] == 0 || chosen >= 0) continue;
+                last_nonempty = 8 * lane + j; cb_last = cb; wb_last = wb;
+                bool hit;
+                if (mode == MODE_COUNT) hit = cb + n8[j] >= target_count;
+                else if (mode == MODE_W_GE) hit = wb + w8[j] >= target_w;
+                else hit = wb + w8[j] > target_w;
+                if (hit) { chosen = 8 * lane + j; cb_hit = cb; wb_hit = wb; }
+                else { cb += n8[j]; wb += w8[j]; }
+            }
+            const unsigned hits = __ballot_sync(0xffffffffu, chosen >= 0);
+            const unsigned some = __ballot_sync(0xffffffffu, last_nonempty >= 0);
+            int src = -1;                                            // the lane whose answer counts
+            if (hits) src = __ffs(hits) - 1;
+            else if (some) { src = 31 - __clz(some); chosen = last_nonempty; cb_hit = cb_last; wb_hit = wb_last; }
+            if (lane == src) {
+                sh.found = chosen;
+                sh.sel_cnt_before = cb_hit; sh.sel_w_before = wb_hit;
+                sh.sel_bucket_cnt = sh.cnt_all[chosen];
+                sh.d_val = wb_hit + sh.wsum_all[chosen];
+            } else if (src < 0 && lane == 0) {
+                sh.found = -1;
+                sh.sel_cnt_before = cnt_before; sh.sel_w_before = w_before;
+                sh.sel_bucket_cnt = 0;
+                sh.d_val = w_before;
+            }
         }
         __syncthreads();
         const int chosen = sh.found;
@@ -155,13 +233,16 @@ __device__ void select(const RowCtx& c, Shared& sh, int mode, unsigned long long
             // One element has this value: find its token in one pass.
             if (threadIdx.x == 0) sh.i_val = 0x7fffffff;
             __syncthreads();
-            for (int i = threadIdx.x; i < c.n; i += blockDim.x) {
+            for (int i = c.lo + threadIdx.x; i < c.hi; i += blockDim.x) {
                 unsigned key; float w;
                 if (member(c, i, key, w) && key == prefix_key) atomicMin(&sh.i_val, i);
             }
             __syncthreads();
-            out_key = prefix_key; out_tok = (unsigned)sh.i_val; out_cum = cum_incl;
-            __syncthreads();
+            team_sync();
+            int first = 0x7fffffff;
+            for (int r = 0; r < team_size(); ++r) first = min(first, (int)team_ld_u32(&sh.i_val, r));
+            team_sync();
+            out_key = prefix_key; out_tok = (unsigned)first; out_cum = cum_incl;
             return;
         }
     }
@@ -256,6 +337,30 @@ __global__ void argmax_merge_kernel(const ArgmaxPart* __restrict__ parts, int n_
     if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
 }
 
+// The sum of the weights of the current set: the blocks' sums added in block order.
+__device__ double team_weight_sum(const RowCtx& c, Shared& sh) {
+    double local = 0.0;
+    for (int i = c.lo + threadIdx.x; i < c.hi; i += blockDim.x) {
+        unsigned kk; float w;
+        if (member(c, i, kk, w)) local += (double)w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if ((threadIdx.x & 31) == 0) sh.red_d[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh.red_d[w];
+        sh.d_val = t;
+    }
+    __syncthreads();
+    team_sync();
+    double total = 0.0;
+    for (int b = 0; b < team_size(); ++b) total += team_ld_f64(&sh.d_val, b);
+    team_sync();
+    return total;
+}
+
 __global__ void __launch_bounds__(THREADS)
 sample_rows_kernel(const float* __restrict__ logits, long long ld, int n,
                    const float* __restrict__ temperature, const int* __restrict__ top_k,
@@ -264,17 +369,32 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int n,
     __shared__ Shared sh;
     pdl_launch_dependents();
     pdl_wait();
-    const int r = blockIdx.x;
+    const int blocks = team_size(), rank = team_rank();
+    const int r = blockIdx.x / blocks;
     const float* v = logits + (size_t)r * ld;
+    const int part = ((n + blocks - 1) / blocks + 3) & ~3;
+    const int lo = min(n, rank * part), hi = min(n, lo + part);
+    // the row's first maximum: each block's over its part, then the first of those
     float best_v; int best_i;
-    block_argmax(v, n, sh, best_v, best_i);
+    block_argmax_raw(v + lo, hi - lo, sh, best_v, best_i);
+    if (threadIdx.x == 0) { sh.f_val = best_v; sh.i_val = best_i == 0x7fffffff ? best_i : lo + best_i; }
+    __syncthreads();
+    team_sync();
+    best_v = -INFINITY; best_i = 0x7fffffff;
+    for (int b = 0; b < blocks; ++b) {
+        const float ov = team_ld_f32(&sh.f_val, b);
+        const int oi = (int)team_ld_u32(&sh.i_val, b);
+        if (ov > best_v || (ov == best_v && oi < best_i)) { best_v = ov; best_i = oi; }
+    }
+    if (best_i == 0x7fffffff) best_i = 0;
+    team_sync();
     const float T = temperature[r];
     if (!(T > 0.0f)) {
-        if (threadIdx.x == 0) out[r] = best_i;
+        if (threadIdx.x == 0 && rank == 0) out[r] = best_i;
         return;
     }
     RowCtx c;
-    c.v = v; c.n = n;
+    c.v = v; c.n = n; c.lo = lo; c.hi = hi;
     c.inv_t = 1.0f / T;
     c.smax = v[best_i] * c.inv_t;
     c.cutoff = c.smax - 20.0f;
@@ -299,52 +419,16 @@ sample_rows_kernel(const float* __restrict__ logits, long long ld, int n,
     const float tp = top_p[r];
     double kept;
     if (tp < 1.0f) {
-        // total = sum of all weights: select with an unreachable target returns
-        // the last element and the sum before it; simpler: one pass for the sum.
-        double local = 0.0;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            unsigned kk; float w;
-            if (member(c, i, kk, w)) local += (double)w;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-        if ((threadIdx.x & 31) == 0) sh.red_d[threadIdx.x >> 5] = local;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            double t = 0.0;
-            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh.red_d[w];
-            sh.d_val = t;
-        }
-        __syncthreads();
-        const double total = sh.d_val;
-        __syncthreads();
+        const double total = team_weight_sum(c, sh);
         select(c, sh, MODE_W_GE, 0, (double)tp * total, key, tok, cum);
         c.has_nucleus = true; c.nuc_key = key; c.nuc_tok = tok;
         kept = cum;
     } else {
-        // kept = total: the draw's own selection needs only u * total; get total
-        // from a selection that never hits (returns the sum up to the last).
-        double local = 0.0;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            unsigned kk; float w;
-            if (member(c, i, kk, w)) local += (double)w;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-        if ((threadIdx.x & 31) == 0) sh.red_d[threadIdx.x >> 5] = local;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            double t = 0.0;
-            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh.red_d[w];
-            sh.d_val = t;
-        }
-        __syncthreads();
-        kept = sh.d_val;
-        __syncthreads();
+        kept = team_weight_sum(c, sh);
     }
     const double draw = uniform[r] * kept;
     select(c, sh, MODE_W_GT, 0, draw, key, tok, cum);
-    if (threadIdx.x == 0) out[r] = (key == 0xffffffffu && tok == 0 && kept == 0.0) ? best_i : (int)tok;
+    if (threadIdx.x == 0 && rank == 0) out[r] = (key == 0xffffffffu && tok == 0 && kept == 0.0) ? best_i : (int)tok;
 }
 
 // Logit bias, then repetition / presence / frequency penalties over each row's
@@ -461,8 +545,19 @@ extern "C" int kipp_sample_rows(const float* logits, long long ld, int rows, int
                                 const float* min_p, const double* uniform, int* out, void* stream) {
     if (rows <= 0) return 0;
     if (n <= 0) return KIPP_ERR_ARG;
-    return kipp_launch(sample_rows_kernel, dim3(rows), dim3(THREADS), 0, (cudaStream_t)stream, 1, logits, ld, n,
-                       temperature, top_k, top_p, min_p, uniform, out);
+    // long rows: a cluster of up to eight blocks a row (at most eight: the kernel's loops over the
+    // team are unrolled to that), as many as keep all rows' blocks within one wave of the GPU
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    int blocks = 1;
+    while (blocks < 8 && n >= 16384 * blocks && (long long)rows * blocks * 2 <= sms) blocks *= 2;
+    if ((long long)rows * blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return kipp_launch_cluster(sample_rows_kernel, dim3((unsigned)(rows * blocks)), dim3(THREADS), 0, (cudaStream_t)stream,
+                               dim3(blocks, 1, 1), logits, ld, n, temperature, top_k, top_p, min_p, uniform, out);
 }
 
 extern "C" int kipp_apply_penalties(float* logits, long long ld, int rows, int n, const int* recent,
