@@ -18,9 +18,9 @@
 // that order is found by radix selection over the (value, token) keys, with
 // per-bucket counts and weight sums, four 8-bit passes over the value and,
 // only among equal values, four over the token id.  Bucket sums add the same
-// float32 weights in another order than the reference's running double sum, so
-// a draw that lies within double rounding of a boundary may pick the
-// neighbour.
+// float32 weights as integers in units of 2^-40 (see weight_units) where the
+// reference keeps a running double sum, so a draw that lies within 2^-23 of a
+// boundary may pick the neighbour.
 //
 // Also here: the penalties and logit bias the reference applies before
 // sampling (apply_bias_and_penalties, src/kipp.c:3386-3431).
@@ -55,6 +55,9 @@ __device__ __forceinline__ unsigned team_ld_u32(const void* p, int rank) {
 __device__ __forceinline__ float team_ld_f32(const void* p, int rank) {
     float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(team_addr(p, rank)) : "memory"); return v;
 }
+__device__ __forceinline__ unsigned long long team_ld_u64(const void* p, int rank) {
+    unsigned long long v; asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(team_addr(p, rank)) : "memory"); return v;
+}
 __device__ __forceinline__ double team_ld_f64(const void* p, int rank) {
     double v; asm volatile("ld.shared::cluster.f64 %0, [%1];" : "=d"(v) : "r"(team_addr(p, rank)) : "memory"); return v;
 }
@@ -88,7 +91,7 @@ __device__ __forceinline__ bool member(const RowCtx& c, int i, unsigned& key, fl
 
 struct Shared {
     unsigned cnt[256];          // this block's part of the row
-    double wsum[256];
+    unsigned long long wfix[256];   // weight sums in units of 2^-40 (see weight_units)
     unsigned cnt_all[256];      // the team's: the blocks' parts added in block order
     double wsum_all[256];
     float red_val[32];
@@ -103,50 +106,69 @@ struct Shared {
 
 enum { MODE_COUNT = 0, MODE_W_GE = 1, MODE_W_GT = 2 };
 
+// Weights are summed as integers, in units of 2^-40 of the top weight (1): integer sums do not
+// depend on their order, so a row's draw is the same whichever block or lane adds first, and
+// the lanes of a warp that hit the same bucket add their weights with the warp's integer
+// reduction and ONE atomic instead of 32 that the hardware runs one after the other (with
+// float64 atomics the passes were bound by exactly that).  A weight is at least e^-20 = 2^-29,
+// so it keeps eleven bits and more; a row's sums stay below 2^58.  Against the reference's
+// running float64 sum a draw within 2^-23 of a boundary may pick the neighbour.
+constexpr double WEIGHT_UNIT = 1.0 / 1099511627776.0;      // 2^-40
+__device__ __forceinline__ unsigned long long weight_units(float w) {
+    return (unsigned long long)((double)w * 1099511627776.0);
+}
+// Sum of `v` over the lanes of `peers` (all of them call this with the same mask; v < 2^41).
+__device__ __forceinline__ unsigned long long peers_sum(unsigned peers, unsigned long long v) {
+    const unsigned lo = __reduce_add_sync(peers, (unsigned)(v & 0xfffffu));          // 32 x 2^20 < 2^32
+    const unsigned hi = __reduce_add_sync(peers, (unsigned)(v >> 20));               // 32 x 2^21 < 2^32
+    return ((unsigned long long)hi << 20) + lo;
+}
+
 // One histogram pass.  level 0..3: value key digits (high to low); level 4..7:
 // token digits among elements whose key == prefix_key.
 __device__ void histogram_pass(const RowCtx& c, Shared& sh, int level, unsigned prefix_key,
                                unsigned prefix_tok) {
-    for (int b = threadIdx.x; b < 256; b += blockDim.x) { sh.cnt[b] = 0; sh.wsum[b] = 0.0; }
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) { sh.cnt[b] = 0; sh.wfix[b] = 0ull; }
     __syncthreads();
-    int cur = -1; unsigned ccnt = 0; double cw = 0.0;
-    for (int i = c.lo + threadIdx.x; i < c.hi; i += blockDim.x) {
-        unsigned key; float w;
-        if (!member(c, i, key, w)) continue;
-        unsigned digit;
-        if (level < 4) {
-            const int shift = 24 - 8 * level;
-            if (level > 0 && (key >> (shift + 8)) != (prefix_key >> (shift + 8))) continue;
-            digit = (key >> shift) & 0xffu;
-        } else {
-            if (key != prefix_key) continue;
-            const int shift = 24 - 8 * (level - 4);
-            const unsigned tok = (unsigned)i;
-            if (level > 4 && (tok >> (shift + 8)) != (prefix_tok >> (shift + 8))) continue;
-            digit = (tok >> shift) & 0xffu;
+    // whole warps walk the part (every lane makes every round): the lanes of a round that fall
+    // into one bucket are found with match.any and add as one
+    const int lane = threadIdx.x & 31;
+    for (int base = c.lo + (int)(threadIdx.x - lane); base < c.hi; base += blockDim.x) {
+        const int i = base + lane;
+        unsigned key = 0; float w = 0.f;
+        unsigned digit = 256u;                                  // no bucket: not in the set at this level
+        if (i < c.hi && member(c, i, key, w)) {
+            if (level < 4) {
+                const int shift = 24 - 8 * level;
+                if (level == 0 || (key >> (shift + 8)) == (prefix_key >> (shift + 8))) digit = (key >> shift) & 0xffu;
+            } else if (key == prefix_key) {
+                const int shift = 24 - 8 * (level - 4);
+                const unsigned tok = (unsigned)i;
+                if (level == 4 || (tok >> (shift + 8)) == (prefix_tok >> (shift + 8))) digit = (tok >> shift) & 0xffu;
+            }
         }
-        if ((int)digit != cur) {
-            if (cur >= 0) { atomicAdd(&sh.cnt[cur], ccnt); atomicAdd(&sh.wsum[cur], cw); }
-            cur = (int)digit; ccnt = 0; cw = 0.0;
+        const unsigned peers = __match_any_sync(0xffffffffu, digit);
+        const unsigned long long units = peers_sum(peers, digit < 256u ? weight_units(w) : 0ull);
+        if (digit < 256u && lane == __ffs(peers) - 1) {
+            atomicAdd(&sh.cnt[digit], (unsigned)__popc(peers));
+            atomicAdd(&sh.wfix[digit], units);
         }
-        ccnt += 1; cw += (double)w;
     }
-    if (cur >= 0) { atomicAdd(&sh.cnt[cur], ccnt); atomicAdd(&sh.wsum[cur], cw); }
     __syncthreads();
     // the team's histogram: every block adds the blocks' parts in block order
     team_sync();
     const int blocks = team_size();
     for (int b = threadIdx.x; b < 256; b += blockDim.x) {
-        unsigned n8[8]; double w8[8];                // all loads first: they travel together
+        unsigned n8[8]; unsigned long long w8[8];    // all loads first: they travel together
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             n8[r] = r < blocks ? team_ld_u32(&sh.cnt[b], r) : 0u;
-            w8[r] = r < blocks ? team_ld_f64(&sh.wsum[b], r) : 0.0;
+            w8[r] = r < blocks ? team_ld_u64(&sh.wfix[b], r) : 0ull;
         }
-        unsigned n = 0; double w = 0.0;
+        unsigned n = 0; unsigned long long w = 0ull;
 #pragma unroll
         for (int r = 0; r < 8; ++r) { n += n8[r]; w += w8[r]; }
-        sh.cnt_all[b] = n; sh.wsum_all[b] = w;
+        sh.cnt_all[b] = n; sh.wsum_all[b] = (double)w * WEIGHT_UNIT;
     }
     team_sync();                                   // nobody clears its part while another still reads it
 }
@@ -339,26 +361,26 @@ __global__ void argmax_merge_kernel(const ArgmaxPart* __restrict__ parts, int n_
 
 // The sum of the weights of the current set: the blocks' sums added in block order.
 __device__ double team_weight_sum(const RowCtx& c, Shared& sh) {
-    double local = 0.0;
+    unsigned long long local = 0ull;
     for (int i = c.lo + threadIdx.x; i < c.hi; i += blockDim.x) {
         unsigned kk; float w;
-        if (member(c, i, kk, w)) local += (double)w;
+        if (member(c, i, kk, w)) local += weight_units(w);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-    if ((threadIdx.x & 31) == 0) sh.red_d[threadIdx.x >> 5] = local;
+    if ((threadIdx.x & 31) == 0) sh.red_u[threadIdx.x >> 5] = local;
     __syncthreads();
     if (threadIdx.x == 0) {
-        double t = 0.0;
-        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh.red_d[w];
-        sh.d_val = t;
+        unsigned long long t = 0ull;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sh.red_u[w];
+        sh.u_val = t;
     }
     __syncthreads();
     team_sync();
-    double total = 0.0;
-    for (int b = 0; b < team_size(); ++b) total += team_ld_f64(&sh.d_val, b);
+    unsigned long long total = 0ull;
+    for (int b = 0; b < team_size(); ++b) total += team_ld_u64(&sh.u_val, b);
     team_sync();
-    return total;
+    return (double)total * WEIGHT_UNIT;
 }
 
 __global__ void __launch_bounds__(THREADS)
