@@ -170,7 +170,7 @@ def main() -> int:
         cfg["num_hidden_layers"] = args.layers
     config = config_from_dict(cfg)
     K, W, B, R = args.steps, args.warmup, args.batch, max(args.repeats, 1)
-    span = R * K + W + 2
+    span = R * K + W + 2 + 4                 # the timed steps and four more for the kernel shares
     batches = [B] if args.skip_points else sorted({1, 8, B, 64})
     cache_tokens = max([B * (args.context + PAGE)] +
                        [b * (POINT_PROMPT + span + PAGE) for b in batches if b != B])
@@ -277,6 +277,13 @@ def main() -> int:
     ctx_mid = headline_ctx + W + R * K / 2.0
     step_bytes = weight_bytes + B * ctx_mid * kv_bytes_token
     achieved = step_bytes / (ms_step / 1e3) / 1e9
+    # Where the step's time goes: four steps without graphs, an event after every launch
+    # (Engine.profile_start/stop); shares of the time between the events, by kernel.
+    eng.profile_start()
+    ring = eng.decode_burst(rids, prompt(len(rids)), 4)
+    spent = eng.profile_stop()
+    total_spent = sum(spent.values()) or 1.0
+    shares = {k: round(v / total_spent, 3) for k, v in sorted(spent.items(), key=lambda kv: -kv[1])[:8]}
     for r in rids:
         eng.finish(r)
     eng.runtime.check_status()
@@ -339,7 +346,9 @@ def main() -> int:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
-                     "bytes_per_step": int(step_bytes), "peak_source": pk_src},
+                     "bytes_per_step": int(step_bytes), "peak_source": pk_src,
+                     "kernel_shares": shares,
+                     "kernel_shares_note": "four steps without graphs, CUDA events between the launches"},
         "points": points,
     }
     print(json.dumps(record))

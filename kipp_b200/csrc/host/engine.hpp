@@ -164,6 +164,14 @@ public:
     void read_logits(float* out, size_t capacity);
     void synchronize();
     void decode_burst(const int64_t* requests, const int32_t* tokens, int n, int steps, int32_t* out_host);
+    // kernel name -> milliseconds between profile(true) and profile(false), as JSON
+    void profile(bool on) {
+        if (on) { ops_.profile_start(); return; }
+        Json j = Json::object();
+        for (auto& kv : ops_.profile_stop()) j.set(kv.first, kv.second);
+        profile_json_ = j.dump();
+    }
+    const std::string& profile_json() const { return profile_json_; }
     void sample(const kipp_sample_params* params, uint64_t* rng_states, int n_rows, int32_t* out_host);
 
     // one part of one layer alone, for tests of the parts (see api.cpp)
@@ -253,8 +261,9 @@ private:
     StepGraph& graph_for(const std::string& key, bool feedback, int batch);
     void feedback_tail(StepGraph& g);
     bool shape_repeats(const StepShape& shape, const std::vector<int>& rows_per_entry);
-    bool graphable() const { return opt_.cuda_graphs && graph_safe_; }
+    bool graphable() const { return opt_.cuda_graphs && graph_safe_ && !ops_.profiling; }
 
+    std::string profile_json_ = "{}";
     kipp_engine_options opt_;
     int dtype_;
     DeviceInfo device_;

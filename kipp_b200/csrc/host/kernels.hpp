@@ -125,7 +125,8 @@ public:
             using Fn = int (*)(void*, int, const void*, const void*, int, int, int, long long, long long, long long, int,
                                int, int, int, const NormFold*, int*, void*);
             static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_fold");
-            run(f(out, out_dtype, a, w, M, N, K, lda, ldw, ldc, (int)epilogue, 0, 0, 0, fold, status, stream), "gemm_tc");
+            run(f(out, out_dtype, a, w, M, N, K, lda, ldw, ldc, (int)epilogue, 0, 0, 0, fold, status, stream), "gemm_tc", 1,
+                profiling ? format("gemm_tc %d x %d", N, K).c_str() : nullptr);
             if (fold != nullptr && fold->ssq_in != nullptr) ++folded_norms;
         } else {
             using Fn = int (*)(void*, int, const void*, const void*, int, int, int, int, int, int, int, int, void*);
@@ -289,9 +290,10 @@ public:
     }
 
 private:
-    void run(int code, const char* what, int kernels = 1) {
+    void run(int code, const char* what, int kernels = 1, const char* label = nullptr) {
         kernel_check(code, what);
         launches += kernels;
+        if (profiling) mark(label ? label : what);
     }
 
     void attention_tensor_core(void* out, const void* q, const PagedCacheView& cache, const AttentionWork& work,
@@ -331,6 +333,47 @@ private:
                   DECODE_MAX_SPLITS, work.split_keys, 1, decode_stream_ctas(work), scratch, stream),
                 "attn_decode_mma", 2);
         }
+    }
+
+public:
+    // Where a step's time goes: while `profiling` is set every launch is followed by an event on
+    // the stream; profile_stop() waits for them and gives the time between consecutive events
+    // per kernel name in milliseconds (steps run without graphs meanwhile, so gaps between
+    // launches are part of the figures: read them as shares).
+    bool profiling = false;
+    void profile_start() {
+        profile_clear();
+        profiling = true;
+        mark("(start)");
+    }
+    std::vector<std::pair<std::string, double>> profile_stop() {
+        profiling = false;
+        std::vector<std::pair<std::string, double>> out;
+        if (!marks_.empty()) cuda_check(cudaEventSynchronize(marks_.back().second), "profile events");
+        for (size_t i = 1; i < marks_.size(); ++i) {
+            float ms = 0.f;
+            cuda_check(cudaEventElapsedTime(&ms, marks_[i - 1].second, marks_[i].second), "profile events");
+            bool found = false;
+            for (auto& kv : out)
+                if (kv.first == marks_[i].first) { kv.second += ms; found = true; break; }
+            if (!found) out.emplace_back(marks_[i].first, (double)ms);
+        }
+        profile_clear();
+        return out;
+    }
+    ~Ops() { profile_clear(); }
+
+private:
+    std::vector<std::pair<std::string, cudaEvent_t>> marks_;
+    void mark(const std::string& what) {
+        cudaEvent_t ev = nullptr;
+        cuda_check(cudaEventCreate(&ev), "profile event");
+        cuda_check(cudaEventRecord(ev, (cudaStream_t)stream), "profile event");
+        marks_.emplace_back(what, ev);
+    }
+    void profile_clear() {
+        for (auto& m : marks_) cudaEventDestroy(m.second);
+        marks_.clear();
     }
 
 public:

@@ -233,6 +233,12 @@ int kipp_engine_debug_set_status(kipp_engine* engine, int word, int value);
 int kipp_engine_last_rows(kipp_engine* engine);
 /* Waits for the engine's stream and checks the kernels' status words. */
 int kipp_engine_synchronize(kipp_engine* engine);
+/* Where a step's time goes.  Between kipp_engine_profile(e, 1) and kipp_engine_profile(e, 0) steps
+ * run without CUDA graphs and every kernel launch is followed by an event; afterwards
+ * kipp_engine_profile_json gives {"kernel name": milliseconds, ...} (time between consecutive
+ * events, so the gaps between launches are inside: read the figures as shares). */
+int kipp_engine_profile(kipp_engine* engine, int on);
+const char* kipp_engine_profile_json(kipp_engine* engine);
 
 /*
  * Greedy decoding of `steps` tokens for every listed live request without the host in the

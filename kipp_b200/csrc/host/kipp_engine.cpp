@@ -297,6 +297,10 @@ int kipp_engine_debug_set_status(kipp_engine* e, int word, int value) {
     return guarded(e->error, [&] { e->engine->debug_set_status(word, value); });
 }
 int kipp_engine_last_rows(kipp_engine* e) { return e->engine->last_rows(); }
+int kipp_engine_profile(kipp_engine* e, int on) {
+    return guarded(e->error, [&] { e->engine->profile(on != 0); });
+}
+const char* kipp_engine_profile_json(kipp_engine* e) { return e->engine->profile_json().c_str(); }
 int kipp_engine_synchronize(kipp_engine* e) {
     return guarded(e->error, [&] { e->engine->synchronize(); });
 }

@@ -451,6 +451,17 @@ class Engine:
         gave up a wait."""
         self._check(self._lib.kipp_engine_synchronize(self._h))
 
+    def profile_start(self) -> None:
+        """From here on steps run without CUDA graphs and every kernel launch is followed
+        by an event on the engine's stream (see :meth:`profile_stop`)."""
+        self._check(self._lib.kipp_engine_profile(self._h, 1))
+
+    def profile_stop(self) -> dict:
+        """{kernel name: milliseconds} since :meth:`profile_start`: the time between
+        consecutive events, so the gaps between launches are inside; read as shares."""
+        self._check(self._lib.kipp_engine_profile(self._h, 0))
+        return json.loads(self._lib.kipp_engine_profile_json(self._h).decode())
+
     def decode_burst(self, requests: list, tokens: list[int], steps: int) -> torch.Tensor:
         """Greedy decoding of ``steps`` tokens for every request without the host in
         the loop.  ``tokens[i]`` is the next token of ``requests[i]`` (its logits

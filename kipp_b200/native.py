@@ -124,6 +124,8 @@ _SIGNATURES = {
     "kipp_engine_step": (_i, [_vp, POINTER(StepEntryC), _i, POINTER(_vp), _ip]),
     "kipp_engine_read_logits": (_i, [_vp, _vp, c_size_t]),
     "kipp_engine_synchronize": (_i, [_vp]),
+    "kipp_engine_profile": (_i, [_vp, _i]),
+    "kipp_engine_profile_json": (c_char_p, [_vp]),
     "kipp_engine_last_rows": (_i, [_vp]),
     "kipp_engine_debug_set_status": (_i, [_vp, _i, _i]),
     "kipp_engine_decode_burst": (_i, [_vp, POINTER(c_int64), POINTER(c_int32), _i, _i, _vp]),

@@ -489,3 +489,23 @@ def test_engine_in_32_bit_against_the_reference_oracle_with_rounded_keys_and_val
                    max_requests=1, max_batch_tokens=64)
     other = plain.step([StepEntry("g", toks, [len(toks) - 1])], check=True).cpu().double()
     assert 0 < nmse(other[0], logits[-1]) < 1e-3
+
+
+def test_profile_gives_the_kernels_of_a_step():
+    """Between profile_start and profile_stop steps run without graphs and an event follows
+    every launch: the kernels of a decode step with the time between the events."""
+    from kipp_b200.engine import Engine, StepEntry
+    eng = Engine.from_folder(model_folder("E"), dtype="bfloat16", page_size=16, cache_tokens=512, max_requests=2,
+                             max_batch_tokens=128)
+    toks = random_tokens("E", 40, seed=3)
+    eng.step([StepEntry("a", toks[:30], [])], check=True)
+    replays = eng.graph_replays
+    eng.profile_start()
+    for t in toks[30:34]:
+        eng.step([StepEntry("a", [t], [0])])
+    spent = eng.profile_stop()
+    assert eng.graph_replays == replays
+    assert {"attn_decode_mma_fused", "embed_gather"} <= set(spent) and all(v >= 0 for v in spent.values())
+    assert sum(k.startswith("gemm_tc ") for k in spent) >= 4                 # the products by shape
+    assert 0 < sum(spent.values()) < 1000
+    eng.step([StepEntry("a", [toks[34]], [0])], check=True)          # and on with graphs
