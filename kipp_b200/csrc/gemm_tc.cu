@@ -527,6 +527,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     // ------------------------------------------------------------------- split-K fix-up
     if (p.splits > 1) {
+        // The residual values (and the norm weight) this thread adds to below are asked for before
+        // the barrier and arrive under it: behind it they cost a trip to the L2 and back on a
+        // path that is all latency (measured: 1,500 cycles from the barrier to the last store).
+        constexpr int PRE = 4;
+        float old_c[PRE] = {0.f, 0.f, 0.f, 0.f};
+        float next_norm_w = 0.f;
+        if (warp >= 2 && p.epilogue == EPI_ADD) {
+            const int f = f0 + (warp & 3) * 32 + lane;
+            const int per = (TILE_T + p.splits - 1) / p.splits;
+            const int j0 = split * per, j1 = min(TILE_T, j0 + per);
+            if (f < p.features) {
+#pragma unroll
+                for (int k = 0; k < PRE; ++k) {
+                    const int j = j0 + ((warp - 2) >> 2) + 2 * k;
+                    if (j < j1 && t0 + j < p.tokens) old_c[k] = reinterpret_cast<const float*>(p.C)[(size_t)(t0 + j) * p.ldc + f];
+                }
+                if (p.xn != nullptr) next_norm_w = load_w(p.norm_w, p.norm_w_dtype, f);
+            }
+        }
         // all threads of all CTAs of the cluster: partial sums are visible afterwards
         asm volatile("barrier.cluster.arrive.release.aligned;\n"
                      "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
@@ -543,7 +562,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int s = 0; s < 8; ++s)
                 asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[s]) : "r"(local),
                              "r"(s < p.splits ? s : 0));
+            int k = -1;
             for (int j = j0 + cg; j < j1; j += 2) {
+                ++k;
+                const float old_pre = k == 0 ? old_c[0] : (k == 1 ? old_c[1] : (k == 2 ? old_c[2] : old_c[3]));
                 // all loads of a token first (they overlap), then the sum in split order
                 float part[8];
 #pragma unroll
@@ -571,14 +593,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     float r = 0.f;
                     if (valid) {
                         float* c = reinterpret_cast<float*>(p.C) + (size_t)t * p.ldc + f;
-                        r = *c + v;
+                        r = (k < PRE ? old_pre : *c) + v;
                         *c = r;
                     }
-                    emit_for_next_norm(p, r, valid, t, f, lane, valid ? load_w(p.norm_w, p.norm_w_dtype, f) : 0.f);
+                    emit_for_next_norm(p, r, valid, t, f, lane, next_norm_w);
                 } else if (t < p.tokens && f < p.features) {
                     if (p.out_dtype == KIPP_DT_F32) {
                         float* c = reinterpret_cast<float*>(p.C) + (size_t)t * p.ldc + f;
-                        *c = p.epilogue == EPI_ADD ? *c + v : v;
+                        *c = p.epilogue == EPI_ADD ? (k < PRE ? old_pre : *c) + v : v;
                     } else {
                         reinterpret_cast<bf16*>(p.C)[(size_t)t * p.ldc + f] = __float2bfloat16_rn(v);
                     }
