@@ -1379,6 +1379,7 @@ inline std::string Engine::info_json() {
     counters.set("tc_prefill_launches", ops_.tc_prefill_launches);
     counters.set("fused_decode_launches", ops_.fused_decode_launches);
     counters.set("folded_norms", ops_.folded_norms);
+    counters.set("stream_decode_launches", ops_.stream_decode_launches);
     j.set("counters", std::move(counters));
     info_ = j.dump();
     return info_;

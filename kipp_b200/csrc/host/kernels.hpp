@@ -234,6 +234,7 @@ public:
               decode_stream_ctas(work), scratch, status, stream),
             "attn_decode_mma_fused", 2);
         ++fused_decode_launches;
+        if (decode_stream_ctas(work) > 0) ++stream_decode_launches;
     }
 
     // The first maximum of each row; long rows are shared among blocks (two launches then).
@@ -380,6 +381,7 @@ public:
     long long tc_prefill_launches = 0;      // launches of the tcgen05 prompt attention (tests look at it)
     long long fused_decode_launches = 0;
     long long folded_norms = 0;          // norms that ran inside the products around them
+    long long stream_decode_launches = 0;   // decode attention dealt out as a stream
 };
 
 }  // namespace kipp

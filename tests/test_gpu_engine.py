@@ -509,3 +509,27 @@ def test_profile_gives_the_kernels_of_a_step():
     assert sum(k.startswith("gemm_tc ") for k in spent) >= 4                 # the products by shape
     assert 0 < sum(spent.values()) < 1000
     eng.step([StepEntry("a", [toks[34]], [0])], check=True)          # and on with graphs
+
+
+def test_many_decoded_tokens_are_dealt_out_as_a_stream():
+    """230 requests with 1,000 cached tokens each decode together: 460 (token, kv head) pairs
+    on 444 places would need several waves of splits, so the planner deals the key tiles out
+    as a stream.  Every request holds the same tokens: each row of logits against the plain
+    model."""
+    from kipp_b200.engine import Engine, StepEntry
+    n, length = 230, 1000
+    eng = Engine.from_folder(model_folder("E"), dtype="bfloat16", page_size=16, cache_tokens=n * (length + 32),
+                             max_requests=n, max_batch_tokens=2048)
+    toks = random_tokens("E", length + 2, seed=21)
+    rids = [("s", i) for i in range(n)]
+    for i in range(0, n, 2):
+        eng.step([StepEntry(r, toks[:length], []) for r in rids[i:i + 2]])
+    before = eng.info()["counters"]["stream_decode_launches"]
+    for k in range(2):
+        out = eng.step([StepEntry(r, [toks[length + k]], [0]) for r in rids], check=True).double().cpu()
+        want = plain_logits("E", "bfloat16", toks[:length + k + 1])[-1]
+        for row in (0, 1, n // 2, n - 1):
+            assert_close(out[row], want, "bfloat16", f"row {row} of step {k}")
+        assert float((out - out[0]).abs().max()) <= 2e-2 * float(out[0].abs().max())
+    assert eng.info()["counters"]["stream_decode_launches"] > before
+    eng.cache.check()
