@@ -42,6 +42,7 @@
 //
 // No multicast: every CTA fetches its own tiles.
 #include "common.cuh"
+#include "head_math.cuh"
 #include "mbarrier.cuh"
 #include <cuda.h>
 #include <mutex>
@@ -50,6 +51,21 @@
 #define EPI_STORE 0
 #define EPI_ADD 1
 #define EPI_SWIGLU 2
+
+// Where the rows of a fused q/k/v projection go when they skip the stored product: the rows are
+// [n_q query heads | n_kv key heads | n_kv value heads] of 128 features; queries and keys get their
+// per-head RMSNorm (both weights or neither) and the half-split rotation, queries land in q_out,
+// keys and values in the pages of the token's request.  The arithmetic is that of
+// kipp_qk_norm_rope_write on the product rounded to bfloat16, bit for bit.
+struct kipp_gemm_head_sink {
+    void* q_out;                       // bf16 [tokens, n_q, 128]
+    void* k_pages; void* v_pages;      // bf16 [page][kv head][slot][128]
+    const void* q_norm_w; const void* k_norm_w; int norm_dtype; float eps;
+    const void* cos_sin;               // float2 [64, tokens] (kipp_rope_table_by_pair), or NULL: no rotation
+    const int* positions; const int* entry_of_token; const int* block_table;
+    int table_width, page_size, n_q, n_kv;
+    int write_cache;                   // bit 0: write keys and values
+};
 
 namespace {
 
@@ -254,6 +270,8 @@ template <int TILE_T, int TILE_F> struct Cfg {
                                    TILE_T * 4 /*per-token factors*/;
 };
 
+constexpr int SINK_HEAD = 128;
+
 struct Params {
     void* C;
     int out_dtype;          // KIPP_DT_*
@@ -273,6 +291,7 @@ struct Params {
     float* ssq_out; int ssq_slots;
     const float* ssq_in; int ssq_in_slots;
     float inv_n, eps;
+    kipp_gemm_head_sink heads;   // the HEADS form of the pair kernel only
 };
 
 // What the next norm needs of a new residual value r of token t, feature f (see Params): called
@@ -714,11 +733,152 @@ __device__ __forceinline__ void epilogue_row16(const Params& p, const float* v, 
     }
 }
 
+// 16 columns of a head's first half (from column 16 j) and their partners half a head further, as
+// the stored product would hold them: times the row's factor (if the product's input lacks one),
+// rounded to bfloat16, in pairs (words 0-7 the first half's values, 8-15 their partners).
+__device__ __forceinline__ void sink_load(uint32_t taddr_head, int j, bool scaled, float rstd, uint32_t* words) {
+    uint32_t r0[16], r1[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r0[0]), "=r"(r0[1]), "=r"(r0[2]), "=r"(r0[3]), "=r"(r0[4]), "=r"(r0[5]), "=r"(r0[6]), "=r"(r0[7]),
+          "=r"(r0[8]), "=r"(r0[9]), "=r"(r0[10]), "=r"(r0[11]), "=r"(r0[12]), "=r"(r0[13]), "=r"(r0[14]), "=r"(r0[15])
+        : "r"(taddr_head + 16 * j));
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r1[0]), "=r"(r1[1]), "=r"(r1[2]), "=r"(r1[3]), "=r"(r1[4]), "=r"(r1[5]), "=r"(r1[6]), "=r"(r1[7]),
+          "=r"(r1[8]), "=r"(r1[9]), "=r"(r1[10]), "=r"(r1[11]), "=r"(r1[12]), "=r"(r1[13]), "=r"(r1[14]), "=r"(r1[15])
+        : "r"(taddr_head + SINK_HEAD / 2 + 16 * j));
+    // the registers of both loads are inputs of the wait, so nothing reads them before it
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r0[0]), "+r"(r0[1]), "+r"(r0[2]), "+r"(r0[3]), "+r"(r0[4]), "+r"(r0[5]), "+r"(r0[6]), "+r"(r0[7]),
+                   "+r"(r0[8]), "+r"(r0[9]), "+r"(r0[10]), "+r"(r0[11]), "+r"(r0[12]), "+r"(r0[13]), "+r"(r0[14]),
+                   "+r"(r0[15]), "+r"(r1[0]), "+r"(r1[1]), "+r"(r1[2]), "+r"(r1[3]), "+r"(r1[4]), "+r"(r1[5]),
+                   "+r"(r1[6]), "+r"(r1[7]), "+r"(r1[8]), "+r"(r1[9]), "+r"(r1[10]), "+r"(r1[11]), "+r"(r1[12]),
+                   "+r"(r1[13]), "+r"(r1[14]), "+r"(r1[15]));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+        float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+        if (scaled) {
+            a0 = __fmul_rn(a0, rstd); a1 = __fmul_rn(a1, rstd);
+            b0 = __fmul_rn(b0, rstd); b1 = __fmul_rn(b1, rstd);
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a0, a1), hi = __floats2bfloat162_rn(b0, b1);
+        words[i] = *reinterpret_cast<const uint32_t*>(&lo);
+        words[8 + i] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+}
+// Values 8 u .. 8 u + 7 of a block of sink_load's words (u = 0, 1) and their partners.
+__device__ __forceinline__ void sink_unpack(const uint32_t* words, int u, float (&a)[8], float (&b)[8]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = words[4 * u + i], hi = words[8 + 4 * u + i];
+        a[2 * i] = __uint_as_float(lo << 16); a[2 * i + 1] = __uint_as_float(lo & 0xffff0000u);
+        b[2 * i] = __uint_as_float(hi << 16); b[2 * i + 1] = __uint_as_float(hi & 0xffff0000u);
+    }
+}
+
+// Where head h of token t goes (see kipp_gemm_head_sink), or nullptr: nothing to write.  Needs
+// nothing of the product, so it is looked up while the tile's MMAs still run.
+__device__ __forceinline__ bf16* sink_dst(const Params& p, int t, int h) {
+    const kipp_gemm_head_sink& s = p.heads;
+    if (t >= p.tokens || h >= s.n_q + 2 * s.n_kv) return nullptr;
+    if (h < s.n_q) return reinterpret_cast<bf16*>(s.q_out) + ((size_t)t * s.n_q + h) * SINK_HEAD;
+    if (!(s.write_cache & 1)) return nullptr;
+    const int pos = s.positions[t];
+    const int slot = pos / s.page_size;
+    const int page = slot < s.table_width ? s.block_table[(size_t)s.entry_of_token[t] * s.table_width + slot] : -1;
+    if (page < 0) {                               // unmapped page: refuse, never write
+        atomicExch(p.status, 2);
+        return nullptr;
+    }
+    const bool is_k = h < s.n_q + s.n_kv;
+    const int g = is_k ? h - s.n_q : h - s.n_q - s.n_kv;
+    return reinterpret_cast<bf16*>(is_k ? s.k_pages : s.v_pages) +
+           (((size_t)page * s.n_kv + g) * s.page_size + (pos - slot * s.page_size)) * SINK_HEAD;
+}
+
+// The (cos, sin) of token t's pairs first .. first + 7 from the table laid out by pair.
+__device__ __forceinline__ void sink_angles(const Params& p, int t, int first, bool wanted, float2 (&cs)[8]) {
+    const float2* at = reinterpret_cast<const float2*>(p.heads.cos_sin) + (size_t)first * p.tokens + t;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cs[i] = wanted ? at[(size_t)i * p.tokens] : make_float2(1.f, 0.f);
+}
+
+// One head (SINK_HEAD accumulator columns from `taddr_head`) of token t, held by one thread, on its
+// way to `dst` (sink_dst).  Called by whole warps: the head h is the same for all lanes, the
+// tokens differ.  The head is read once and kept as bfloat16 pairs (the rounding of the stored
+// product) while its sum of squares forms; the angles of 8 pairs are fetched 8 pairs ahead.
+__device__ __forceinline__ void sink_head(const Params& p, uint32_t taddr_head, int t, int h, float rstd, bf16* dst) {
+    const kipp_gemm_head_sink& s = p.heads;
+    constexpr int BLOCKS = SINK_HEAD / 32;        // of 16 values and their 16 partners
+    const bool is_q = h < s.n_q;
+    const bool turns = h < s.n_q + s.n_kv;        // values are copied
+    const bool normed = turns && s.q_norm_w != nullptr;
+    const bool rotates = turns && s.cos_sin != nullptr;
+    const bool scaled = p.ssq_in != nullptr;
+    float2 cs[8];
+    if (rotates) sink_angles(p, t, 0, dst != nullptr, cs);
+    uint32_t words[BLOCKS * 16];
+    float part[2 * BLOCKS];
+#pragma unroll
+    for (int j = 0; j < BLOCKS; ++j) {
+        sink_load(taddr_head, j, scaled, rstd, words + 16 * j);
+        if (normed) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                float a[8], b[8];
+                sink_unpack(words + 16 * j, u, a, b);
+                part[2 * j + u] = head_ssq8(a, b);
+            }
+        }
+    }
+    const float scale = normed ? head_rstd(head_ssq_tree(part), SINK_HEAD, s.eps) : 1.0f;
+    const void* nw = is_q ? s.q_norm_w : s.k_norm_w;
+#pragma unroll
+    for (int j = 0; j < BLOCKS; ++j) {
+        uint4 out_lo[2], out_hi[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int first = 16 * j + 8 * u;      // of the 8 values in the head's first half
+            float2 cs_next[8];
+            if (rotates && first + 8 < SINK_HEAD / 2) sink_angles(p, t, first + 8, dst != nullptr, cs_next);
+            float a[8], b[8];
+            sink_unpack(words + 16 * j, u, a, b);
+            if (normed) {
+                float wa[8], wb[8];
+                load_w8(wa, nw, s.norm_dtype, first);
+                load_w8(wb, nw, s.norm_dtype, SINK_HEAD / 2 + first);
+                head_scale8(a, scale, wa);
+                head_scale8(b, scale, wb);
+            }
+            if (rotates) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) head_rotate(a[i], b[i], cs[i]);
+                if (first + 8 < SINK_HEAD / 2) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) cs[i] = cs_next[i];
+                }
+            }
+            out_lo[u] = pack8(a);
+            out_hi[u] = pack8(b);
+            if (!is_q) { out_lo[u] = cache_values_bf16x8(out_lo[u]); out_hi[u] = cache_values_bf16x8(out_hi[u]); }
+        }
+        if (dst != nullptr) {                      // 32 bytes of each half of the head side by side
+            uint4* lo = reinterpret_cast<uint4*>(dst + 16 * j);
+            uint4* hi = reinterpret_cast<uint4*>(dst + SINK_HEAD / 2 + 16 * j);
+            lo[0] = out_lo[0]; lo[1] = out_lo[1];
+            hi[0] = out_hi[0]; hi[1] = out_hi[1];
+        }
+    }
+}
+
 // Epilogue of one 128-token x TILE_N tile by one warp: its 32 tokens (tensor-memory
 // lanes of `taddr`), its share `cg` (0 or 1) of the feature columns.
-template <int TILE_N, bool REDUCE>
+template <int TILE_N, bool REDUCE, bool HEADS = false>
 __device__ __forceinline__ void tokm_epilogue_tile(const Params& p, const CUtensorMap* map_c, uint32_t taddr,
-                                                   uint8_t* box, int t_warp, int f0, int cg, int lane, bool ok) {
+                                                   uint8_t* box, int t_warp, int f0, int cg, int lane, bool ok,
+                                                   bf16* head_dst = nullptr) {
     constexpr int HALF = (TILE_N / 2 + 15) / 16 * 16;
     const int t = t_warp + lane;
     if constexpr (REDUCE) {
@@ -748,6 +908,11 @@ __device__ __forceinline__ void tokm_epilogue_tile(const Params& p, const CUtens
             float sum = 0.f;
             for (int i = 0; i < p.ssq_in_slots; ++i) sum += row[i];
             rstd = 1.0f / sqrtf(sum * p.inv_n + p.eps);
+        }
+        if constexpr (HEADS) {
+            static_assert(TILE_N == 2 * SINK_HEAD, "a head per half of the tile's columns");
+            sink_head(p, taddr + cg * SINK_HEAD, t, f0 / SINK_HEAD + cg, rstd, ok ? head_dst : nullptr);
+            return;
         }
 #pragma unroll 1
         for (int c = cg * HALF; c < min(TILE_N, (cg + 1) * HALF); c += 16) {
@@ -942,7 +1107,7 @@ template <int TILE_N, bool REDUCE> struct CfgPair {
     static_assert(STAGE_BYTES % 1024 == 0 && SUB_BYTES % 1024 == 0, "swizzled tiles start on 1,024 bytes");
 };
 
-template <int TILE_N, bool REDUCE>
+template <int TILE_N, bool REDUCE, bool HEADS = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_c, const Params p) {
@@ -1065,10 +1230,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int b = tile_iter % C::ACCS, use = tile_iter / C::ACCS;
             const int t_warp = (tile % m_tiles) * (2 * UMMA_M) + (int)rank * UMMA_M + q * 32;
             const int f0 = (tile / m_tiles) * TILE_N;
+            bf16* head_dst = nullptr;
+            if constexpr (HEADS) head_dst = sink_dst(p, t_warp + lane, f0 / SINK_HEAD + cg);
             if (ok && !mbar_wait(&acc_full[b], use & 1, abort_flag)) ok = false;
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + b * C::TMEM_COLS + ((uint32_t)(q * 32) << 16);
-            tokm_epilogue_tile<TILE_N, REDUCE>(p, &map_c, taddr, box, t_warp, f0, cg, lane, ok);
+            tokm_epilogue_tile<TILE_N, REDUCE, HEADS>(p, &map_c, taddr, box, t_warp, f0, cg, lane, ok, head_dst);
             // this warp has read its part of the accumulator: hand it back to the first CTA
             tcgen05_fence_before();
             __syncwarp();
@@ -1198,13 +1365,13 @@ int launch_tokm_n(int tile_n, const CUtensorMap& mw, const CUtensorMap& mx, cons
     return KIPP_ERR_ARG;
 }
 
-template <int TILE_N, bool REDUCE>
+template <int TILE_N, bool REDUCE, bool HEADS = false>
 int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mc, const Params& p, int total,
                 cudaStream_t s) {
     using C = CfgPair<TILE_N, REDUCE>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TILE_N, REDUCE>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TILE_N, REDUCE, HEADS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -1212,7 +1379,7 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap&
     // persistent: at most one pair of CTAs per pair of SMs
     const int pairs = sm_count() / 2;
     // the two CTAs of an MMA pair are neighbours along x
-    return kipp_launch_cluster(gemm_tc_pair_kernel<TILE_N, REDUCE>, dim3(2 * (total < pairs ? total : pairs)),
+    return kipp_launch_cluster(gemm_tc_pair_kernel<TILE_N, REDUCE, HEADS>, dim3(2 * (total < pairs ? total : pairs)),
                                dim3(THREADS), C::SMEM, s, dim3(2, 1, 1), mw, mx, mc, p);
 }
 template <bool REDUCE>
@@ -1334,6 +1501,38 @@ extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const vo
                                  int want_tile, int want_tile_f, const kipp_gemm_norm_fold* fold, int* status,
                                  void* stream);
 
+// Whether a fused q/k/v projection of this many tokens can hand its heads straight to attention
+// (kipp_gemm_tc_heads): the kernel that does it is the one for prompt-sized batches, its tile holds
+// two heads of 128, and the rotation covers the whole head or nothing.
+extern "C" int kipp_gemm_tc_heads_ok(int tokens, int head_dim, int rotary_dim) {
+    return tokens >= 1024 && head_dim == SINK_HEAD && (rotary_dim == 0 || rotary_dim == head_dim);
+}
+
+namespace {
+int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens, int features, int K, long long ldx,
+                long long ldw, long long ldc, int epilogue, int splits, int want_tile, int want_tile_f,
+                const kipp_gemm_norm_fold* fold, const kipp_gemm_head_sink* sink, int* status, void* stream);
+}
+
+// X W^T of a fused q/k/v projection whose rows go on as `sink` says; nothing is stored as a
+// product.  `fold` may carry the row factors of a deferred norm (ssq_in), as in kipp_gemm_tc_fold.
+extern "C" int kipp_gemm_tc_heads(const void* X, const void* W, int tokens, int features, int K, long long ldx,
+                                  long long ldw, const kipp_gemm_norm_fold* fold, const kipp_gemm_head_sink* sink,
+                                  int* status, void* stream) {
+    if (tokens <= 0 || features <= 0) return 0;
+    if (sink == nullptr || !kipp_gemm_tc_heads_ok(tokens, SINK_HEAD, 0)) return KIPP_ERR_ARG;
+    if (sink->n_q <= 0 || sink->n_kv <= 0 || features != (sink->n_q + 2 * sink->n_kv) * SINK_HEAD) return KIPP_ERR_ARG;
+    if (sink->page_size <= 0 || sink->table_width < 0) return KIPP_ERR_ARG;
+    if ((sink->q_norm_w == nullptr) != (sink->k_norm_w == nullptr)) return KIPP_ERR_ARG;
+    if (sink->norm_dtype != KIPP_DT_F32 && sink->norm_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
+    if (((uintptr_t)sink->q_out | (uintptr_t)sink->k_pages | (uintptr_t)sink->v_pages | (uintptr_t)sink->q_norm_w |
+         (uintptr_t)sink->k_norm_w | (uintptr_t)sink->cos_sin) & 15)
+        return -3;
+    if (fold != nullptr && fold->norm_w != nullptr) return KIPP_ERR_ARG;
+    return gemm_tc_run(nullptr, KIPP_DT_BF16, X, W, tokens, features, K, ldx, ldw, features, EPI_STORE, 0, 0, 0, fold,
+                       sink, status, stream);
+}
+
 extern "C" int kipp_gemm_tc(void* C, int out_dtype, const void* X, const void* W, int tokens, int features,
                             int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
                             int want_tile, int want_tile_f, int* status, void* stream) {
@@ -1345,6 +1544,14 @@ extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const vo
                                  int K, long long ldx, long long ldw, long long ldc, int epilogue, int splits,
                                  int want_tile, int want_tile_f, const kipp_gemm_norm_fold* fold, int* status,
                                  void* stream) {
+    return gemm_tc_run(C, out_dtype, X, W, tokens, features, K, ldx, ldw, ldc, epilogue, splits, want_tile,
+                       want_tile_f, fold, nullptr, status, stream);
+}
+
+namespace {
+int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens, int features, int K, long long ldx,
+                long long ldw, long long ldc, int epilogue, int splits, int want_tile, int want_tile_f,
+                const kipp_gemm_norm_fold* fold, const kipp_gemm_head_sink* sink, int* status, void* stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (fold != nullptr) {
         if (fold->norm_w != nullptr &&
@@ -1374,11 +1581,12 @@ extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const vo
         long long cost_pair = 0, cost_one = 0;
         const int n_pair = pick_tile_n(tokens, features, true, &cost_pair);
         const int n_one = pick_tile_n(tokens, features, false, &cost_one);
-        const bool pair = want_tile_f < 0 ? want_tile_f <= -1000
-                                          : (tokens >= 1024 && (epilogue != EPI_ADD || cost_pair < cost_one));
-        const int tile_n = want_tile_f <= -1000 ? -want_tile_f - 1000
-                           : want_tile_f < 0    ? -want_tile_f
-                                                : (pair ? n_pair : n_one);
+        const bool pair = sink != nullptr || (want_tile_f < 0 ? want_tile_f <= -1000
+                                                              : (tokens >= 1024 && (epilogue != EPI_ADD || cost_pair < cost_one)));
+        const int tile_n = sink != nullptr        ? 2 * SINK_HEAD
+                           : want_tile_f <= -1000 ? -want_tile_f - 1000
+                           : want_tile_f < 0      ? -want_tile_f
+                                                  : (pair ? n_pair : n_one);
         if (tile_n < 128 || tile_n > (pair ? 320 : 256) || tile_n % 32) return KIPP_ERR_ARG;
         CUtensorMap mw, mx, mc;
         // a CTA of a pair loads its half of the weight rows of each MMA (two MMAs above 256 features)
@@ -1404,6 +1612,10 @@ extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const vo
         const long long total = (long long)((tokens + rows - 1) / rows) * ((features + tile_n - 1) / tile_n);
         if (total > 0x7fffffffLL) return KIPP_ERR_ARG;
         cudaStream_t s = (cudaStream_t)stream;
+        if (sink != nullptr) {
+            p.heads = *sink;
+            return launch_pair<2 * SINK_HEAD, false, true>(mw, mx, mc, p, (int)total, s);
+        }
         if (pair)
             return reduce ? launch_pair_n<true>(tile_n, mw, mx, mc, p, (int)total, s)
                           : launch_pair_n<false>(tile_n, mw, mx, mc, p, (int)total, s);
@@ -1447,3 +1659,4 @@ extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const vo
     default: return launch<256, 128>(mw, mx, p, grid, s);
     }
 }
+}  // namespace

@@ -312,22 +312,23 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
     Ops& ops = *ctx.ops;
     const StepMeta& m = *ctx.meta;
     const int qkv_cols = q_dim_ + 2 * kv_dim_;
-    void* qkv = ctx.workspace->buffer("qkv", (size_t)T * qkv_cols * es);
     NormFold fold_in, fold_out;
-    ops.gemm(qkv, ctx.dtype, qkv_cols, h, hidden_, w_qkv_, hidden_, dtype_, T, qkv_cols, hidden_, EPI_STORE,
-             fold_input(ctx, fold_in));
     const PagedCacheView cache = ctx.cache_view(run, mixer_slot);       // pages of this run's cache id
-    const float* cos_sin = nullptr;
     const int rot = position_->rotary_dim();
+    const bool to_heads = ctx.dtype == dtype_ && !ctx.kv_round_bf16 &&
+                          Ops::projection_to_heads_ok(dtype_, h, hidden_, w_qkv_, hidden_, T, head_dim_, rot);
+    const float* cos_sin = nullptr;
     if (rot > 0) {
-        // the step's (cos, sin) table: the same for every layer that rotates alike
-        const std::string key = "rope/" + position_->table_key();
+        // the step's (cos, sin) table: the same for every layer that rotates alike; laid out by
+        // pair for the projection that rotates its own heads
+        const std::string key = (to_heads ? "rope by pair/" : "rope/") + position_->table_key();
         auto it = ctx.step_cache.find(key);
         if (it == ctx.step_cache.end()) {
             int made = 0;
-            for (auto& kv : ctx.step_cache) made += kv.first.rfind("rope/", 0) == 0;
+            for (auto& kv : ctx.step_cache) made += kv.first.rfind("rope", 0) == 0;
             float* table = ctx.workspace->get<float>("rope_table_" + std::to_string(made), (size_t)T * rot);
-            ops.rope_table(table, m.positions, position_->inv_freq_device(), T, rot / 2);
+            if (to_heads) ops.rope_table_by_pair(table, m.positions, position_->inv_freq_device(), T, rot / 2);
+            else ops.rope_table(table, m.positions, position_->inv_freq_device(), T, rot / 2);
             it = ctx.step_cache.emplace(key, table).first;
         }
         cos_sin = static_cast<const float*>(it->second);
@@ -336,18 +337,32 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
     const AttentionWork work = planner_->work_of(m);
     const void* qn = qk_norm_ ? q_norm_ : nullptr;
     const void* kn = qk_norm_ ? k_norm_ : nullptr;
-    if (Ops::attention_decode_fused_ok(work, ctx.dtype, heads_, kv_heads_, head_dim_, rot)) {
-        // decoded tokens only: norm, rotation and the cache write happen inside the attention
-        // kernel, straight from the projection's output
-        ops.attention_decode_fused(attn, qkv, qkv_cols, cache, qn, kn, norm_dtype_, eps_, cos_sin, run.writes_cache,
-                                   work, m.q_start, m.context_len, heads_, kv_heads_, head_dim_, scale_, window_);
-    } else {
+    if (to_heads) {
+        // a prompt-sized step: the projection's epilogue norms, rotates and writes the cache
         void* q = ctx.workspace->buffer("q", (size_t)T * q_dim_ * es);
-        const int write = (run.writes_cache ? 1 : 0) | (ctx.kv_round_bf16 && ctx.dtype == F32 ? 2 : 0);
-        ops.qk_norm_rope_write(qkv, qkv_cols, q, cache, ctx.dtype, qn, kn, norm_dtype_, eps_, cos_sin, rot,
-                               m.positions, m.entry_of_token, T, heads_, kv_heads_, head_dim_, write);
+        ops.projection_to_heads(h, hidden_, w_qkv_, hidden_, T, qkv_cols, hidden_, fold_input(ctx, fold_in), cache, q,
+                                qn, kn, norm_dtype_, eps_, cos_sin, m.positions, m.entry_of_token, heads_, kv_heads_,
+                                run.writes_cache);
         ops.attention(attn, q, cache, ctx.dtype, work, m.positions, m.entry_of_token, m.q_start, m.context_len,
                       heads_, kv_heads_, head_dim_, scale_, window_);
+    } else {
+        void* qkv = ctx.workspace->buffer("qkv", (size_t)T * qkv_cols * es);
+        ops.gemm(qkv, ctx.dtype, qkv_cols, h, hidden_, w_qkv_, hidden_, dtype_, T, qkv_cols, hidden_, EPI_STORE,
+                 fold_input(ctx, fold_in));
+        if (Ops::attention_decode_fused_ok(work, ctx.dtype, heads_, kv_heads_, head_dim_, rot)) {
+            // decoded tokens only: norm, rotation and the cache write happen inside the attention
+            // kernel, straight from the projection's output
+            ops.attention_decode_fused(attn, qkv, qkv_cols, cache, qn, kn, norm_dtype_, eps_, cos_sin,
+                                       run.writes_cache, work, m.q_start, m.context_len, heads_, kv_heads_, head_dim_,
+                                       scale_, window_);
+        } else {
+            void* q = ctx.workspace->buffer("q", (size_t)T * q_dim_ * es);
+            const int write = (run.writes_cache ? 1 : 0) | (ctx.kv_round_bf16 && ctx.dtype == F32 ? 2 : 0);
+            ops.qk_norm_rope_write(qkv, qkv_cols, q, cache, ctx.dtype, qn, kn, norm_dtype_, eps_, cos_sin, rot,
+                                   m.positions, m.entry_of_token, T, heads_, kv_heads_, head_dim_, write);
+            ops.attention(attn, q, cache, ctx.dtype, work, m.positions, m.entry_of_token, m.q_start, m.context_len,
+                          heads_, kv_heads_, head_dim_, scale_, window_);
+        }
     }
     const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
     ops.gemm(residual, F32, hidden_, attn, q_dim_, w_o_, q_dim_, dtype_, T, hidden_, q_dim_, EPI_ADD, emit);
@@ -1380,6 +1395,7 @@ inline std::string Engine::info_json() {
     counters.set("fused_decode_launches", ops_.fused_decode_launches);
     counters.set("folded_norms", ops_.folded_norms);
     counters.set("stream_decode_launches", ops_.stream_decode_launches);
+    counters.set("projections_to_heads", ops_.projections_to_heads);
     j.set("counters", std::move(counters));
     info_ = j.dump();
     return info_;

@@ -48,6 +48,24 @@ struct NormFold {
     float inv_n = 0.f, eps = 0.f;
 };
 
+// Where the rows of a fused q/k/v projection go when they skip the stored product
+// (kipp_gemm_tc_heads): per-head norm, rotation, queries to q_out, keys and values into the pages.
+// The layout is the kernel library's kipp_gemm_head_sink.
+struct HeadSink {
+    void* q_out = nullptr;
+    void* k_pages = nullptr;
+    void* v_pages = nullptr;
+    const void* q_norm_w = nullptr;
+    const void* k_norm_w = nullptr;
+    int norm_dtype = 0;
+    float eps = 0.f;
+    const void* cos_sin = nullptr;
+    const int* positions = nullptr;
+    const int* entry_of_token = nullptr;
+    const int* block_table = nullptr;
+    int table_width = 0, page_size = 0, n_q = 0, n_kv = 0, write_cache = 0;
+};
+
 struct PagedCacheView {
     void* k_pages = nullptr;               // [pages, kv_heads, page_size, head_dim] of one run's cache
     void* v_pages = nullptr;
@@ -136,10 +154,46 @@ public:
         }
     }
 
+    // Whether the fused q/k/v projection of a step can do per-head norm, rotation and the cache
+    // write in its own epilogue (projection_to_heads) instead of storing the product.
+    static bool projection_to_heads_ok(int dtype, const void* a, long long lda, const void* w, long long ldw, int M,
+                                       int head_dim, int rotary_dim) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_heads_ok");
+        return gemm_tc_ok(dtype, a, lda, w, ldw) && f(M, head_dim, rotary_dim) != 0;
+    }
+    // a [M, K] x w [(n_q + 2 n_kv) head_dim, K]^T with what qk_norm_rope_write does to the product
+    // in the epilogue (the same bits); `fold` may carry the row factors of a deferred norm, and
+    // `cos_sin` is the step's rope_table_by_pair.
+    void projection_to_heads(const void* a, long long lda, const void* w, long long ldw, int M, int N, int K,
+                             const NormFold* fold, const PagedCacheView& cache, void* q_out, const void* q_norm_w,
+                             const void* k_norm_w, int norm_dtype, float eps, const float* cos_sin,
+                             const int* positions, const int* entry_of_token, int n_q, int n_kv, bool write_cache) {
+        HeadSink sink;
+        sink.q_out = q_out; sink.k_pages = cache.k_pages; sink.v_pages = cache.v_pages;
+        sink.q_norm_w = q_norm_w; sink.k_norm_w = k_norm_w; sink.norm_dtype = norm_dtype; sink.eps = eps;
+        sink.cos_sin = cos_sin; sink.positions = positions; sink.entry_of_token = entry_of_token;
+        sink.block_table = cache.block_table; sink.table_width = cache.table_width; sink.page_size = cache.page_size;
+        sink.n_q = n_q; sink.n_kv = n_kv; sink.write_cache = write_cache ? 1 : 0;
+        using Fn = int (*)(const void*, const void*, int, int, int, long long, long long, const NormFold*,
+                           const HeadSink*, int*, void*);
+        static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_heads");
+        run(f(a, w, M, N, K, lda, ldw, fold, &sink, status, stream), "gemm_tc_heads", 1,
+            profiling ? format("gemm_tc %d x %d to heads", N, K).c_str() : nullptr);
+        if (fold != nullptr && fold->ssq_in != nullptr) ++folded_norms;
+        ++projections_to_heads;
+    }
+
     // float32 [tokens, half, 2]: (cos, sin) of position * inv_freq, made once per step.
     void rope_table(float* out, const int* positions, const float* inv_freq, int tokens, int half) {
         using Fn = int (*)(void*, const int*, const float*, int, int, void*);
         static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_rope_table");
+        run(f(out, positions, inv_freq, tokens, half, stream), "rope_table");
+    }
+    // The same values as float32 [half, tokens, 2], as projection_to_heads reads them.
+    void rope_table_by_pair(float* out, const int* positions, const float* inv_freq, int tokens, int half) {
+        using Fn = int (*)(void*, const int*, const float*, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_rope_table_by_pair");
         run(f(out, positions, inv_freq, tokens, half, stream), "rope_table");
     }
 
@@ -382,6 +436,7 @@ public:
     long long fused_decode_launches = 0;
     long long folded_norms = 0;          // norms that ran inside the products around them
     long long stream_decode_launches = 0;   // decode attention dealt out as a stream
+    long long projections_to_heads = 0;     // q/k/v projections with norm, rotation and cache write inside
 };
 
 }  // namespace kipp

@@ -22,6 +22,7 @@
 // position p of entry e lives in page table[e][p / page_size], slot
 // p % page_size.
 #include "common.cuh"
+#include "head_math.cuh"
 
 namespace {
 constexpr int MAX_PER_LANE = 8;   // head_dim <= 512 (pairs: 256 per half / 32 lanes)
@@ -229,28 +230,6 @@ int launch_rope(const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v
 // by the instructions it issues, not by memory: the version with 8 elements per
 // lane and one shuffle per rotated element took 276 instructions per warp and
 // 23 us for a 2,048-token portion of 48 heads.)
-__device__ __forceinline__ void unpack8(float (&x)[8], const uint4& raw) {
-    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { x[2 * i] = __low2float(h2[i]); x[2 * i + 1] = __high2float(h2[i]); }
-}
-__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
-    uint4 out;
-    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
-    return out;
-}
-// elements first .. first + 7 of a norm weight (16-byte aligned)
-__device__ __forceinline__ void load_w8(float (&w)[8], const void* nw, int norm_dtype, int first) {
-    if (norm_dtype == KIPP_DT_F32) {
-        const float4 a = reinterpret_cast<const float4*>(nw)[first / 4], b = reinterpret_cast<const float4*>(nw)[first / 4 + 1];
-        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-    } else {
-        unpack8(w, reinterpret_cast<const uint4*>(nw)[first / 8]);
-    }
-}
-
 constexpr int ROPE_THREADS = 128;    // a block per 128 / (HEAD_DIM / 16) heads of a token: few idle lanes in the last block
 template <int HEAD_DIM>
 __global__ void __launch_bounds__(ROPE_THREADS)
@@ -308,33 +287,20 @@ qk_norm_rope_write_bf16_kernel(
     unpack8(a, raw_lo);
     unpack8(b, raw_hi);
     if (q_norm_w != nullptr) {                    // both weights or neither (checked by the host)
-        float ss = 0.f;
+        float ss = head_ssq8(a, b);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
-#pragma unroll
-        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        const float scale = 1.0f / sqrtf(ss / (float)HEAD_DIM + eps);
+        for (int o = LPH / 2; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+        const float scale = head_rstd(ss, HEAD_DIM, eps);
         if (dst) {
             const void* nw = is_q ? q_norm_w : k_norm_w;
             float wa[8], wb[8];
             load_w8(wa, nw, norm_dtype, sub * 8);
             load_w8(wb, nw, norm_dtype, HALF + sub * 8);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { a[i] = a[i] * scale * wa[i]; b[i] = b[i] * scale * wb[i]; }
+            head_scale8(a, scale, wa);
+            head_scale8(b, scale, wb);
         }
     }
-    if (cos_sin != nullptr && dst) {
-        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)t * HALF + sub * 8);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float4 cs = cs4[i];             // (cos, sin) of pairs 2 i and 2 i + 1
-            const float a0 = a[2 * i], b0 = b[2 * i], a1 = a[2 * i + 1], b1 = b[2 * i + 1];
-            a[2 * i] = a0 * cs.x - b0 * cs.y;
-            b[2 * i] = b0 * cs.x + a0 * cs.y;
-            a[2 * i + 1] = a1 * cs.z - b1 * cs.w;
-            b[2 * i + 1] = b1 * cs.z + a1 * cs.w;
-        }
-    }
+    if (cos_sin != nullptr && dst) head_rotate8(a, b, cos_sin + (size_t)t * HALF + sub * 8);
     if (dst) {
         const uint4 lo = pack8(a), hi = pack8(b);
         *reinterpret_cast<uint4*>(dst) = is_q ? lo : cache_values_bf16x8(lo);
@@ -359,12 +325,13 @@ int launch_rope_bf16(const void* qkv, int ld_qkv, void* q_out, void* k_pages, vo
 // rotated pair: float32 angle as the reference forms it ((float)position *
 // frequency, src/kipp.c:2374), full-range cosf/sinf.
 __global__ void rope_table_kernel(float2* __restrict__ out, const int* __restrict__ positions,
-                                  const float* __restrict__ inv_freq, int tokens, int half) {
+                                  const float* __restrict__ inv_freq, int tokens, int half, int by_pair) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= tokens * half) return;
-    const int t = i / half, k = i - t * half;
+    // by_pair: out[pair][token], and a warp's threads are neighbouring tokens of one pair
+    const int t = by_pair ? i % tokens : i / half, k = by_pair ? i / tokens : i - t * half;
     const float angle = (float)positions[t] * inv_freq[k];
     float s, c;
     sincosf(angle, &s, &c);
@@ -378,7 +345,18 @@ extern "C" int kipp_rope_table(void* out, const int* positions, const float* inv
     const long long n = (long long)tokens * half;
     if (n > 0x7fffffffLL) return KIPP_ERR_ARG;
     return kipp_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 1,
-                       (float2*)out, positions, inv_freq, tokens, half);
+                       (float2*)out, positions, inv_freq, tokens, half, 0);
+}
+
+// The same values laid out [half, tokens]: for readers whose neighbouring threads hold
+// neighbouring tokens (the projection epilogue that rotates its own heads).
+extern "C" int kipp_rope_table_by_pair(void* out, const int* positions, const float* inv_freq, int tokens, int half,
+                                       void* stream) {
+    if (tokens <= 0 || half <= 0) return 0;
+    const long long n = (long long)tokens * half;
+    if (n > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return kipp_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       (float2*)out, positions, inv_freq, tokens, half, 1);
 }
 
 extern "C" int kipp_qk_norm_rope_write(

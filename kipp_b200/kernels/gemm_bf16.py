@@ -50,6 +50,48 @@ def fold_scale(ssq: torch.Tensor, n: int, eps: float) -> NormFold:
     return NormFold(None, 0, None, 0, None, _ptr(ssq), ssq.shape[1], 1.0 / n, eps)
 
 
+class HeadSink(ctypes.Structure):
+    """kipp_gemm_head_sink of the kernel library: where the rows of a fused q/k/v
+    projection go when they skip the stored product."""
+    _fields_ = [("q_out", c_void_p), ("k_pages", c_void_p), ("v_pages", c_void_p),
+                ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("norm_dtype", c_int), ("eps", ctypes.c_float),
+                ("cos_sin", c_void_p), ("positions", c_void_p), ("entry_of_token", c_void_p),
+                ("block_table", c_void_p), ("table_width", c_int), ("page_size", c_int),
+                ("n_q", c_int), ("n_kv", c_int), ("write_cache", c_int)]
+
+
+def heads_ok(tokens: int, head_dim: int, rotary_dim: int) -> bool:
+    """Whether `run_heads` takes a step of this many tokens."""
+    return bool(_fn("gemm_tc", "kipp_gemm_tc_heads_ok", [c_int, c_int, c_int])(tokens, head_dim, rotary_dim))
+
+
+def run_heads(a, w, q_out, k_pages, v_pages, q_norm_w, k_norm_w, eps, cos_sin, positions, entry_of_token,
+              block_table, n_q, n_kv, write_cache=True, status=None, fold: NormFold | None = None) -> None:
+    """The fused q/k/v projection a @ w.T of a prompt-sized step with per-head norm,
+    rotation and the cache write in its epilogue (head_dim 128): what
+    `run` followed by `ops.qk_norm_rope_write` gives, bit for bit.  ``cos_sin`` is
+    ``ops.rope_table(..., by_pair=True)`` or None."""
+    if cos_sin is not None and tuple(cos_sin.shape) != (64, a.shape[0], 2):
+        raise KernelError("gemm_tc_heads: cos_sin must be the step's table laid out by pair, [64, tokens, 2]")
+    if not tc_ok(a, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned bases and row pitches")
+    N, K = w.shape
+    if status is None:
+        status = _status(a.device)
+    sink = HeadSink(_ptr(q_out), _ptr(k_pages), _ptr(v_pages),
+                    _ptr(q_norm_w) if q_norm_w is not None else None,
+                    _ptr(k_norm_w) if k_norm_w is not None else None,
+                    dtype_code(q_norm_w.dtype) if q_norm_w is not None else 0, eps,
+                    _ptr(cos_sin) if cos_sin is not None else None, _ptr(positions), _ptr(entry_of_token),
+                    _ptr(block_table), block_table.shape[1], k_pages.shape[2], n_q, n_kv, int(write_cache))
+    f = _fn("gemm_tc", "kipp_gemm_tc_heads",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, ctypes.POINTER(NormFold),
+             ctypes.POINTER(HeadSink), c_void_p, c_void_p])
+    _check(f(_ptr(a), _ptr(w), a.shape[0], N, K, a.stride(0), w.stride(0),
+             ctypes.byref(fold) if fold is not None else None, ctypes.byref(sink), _ptr(status), _stream()),
+           "gemm_tc_heads")
+
+
 def run(impl, out, a, w, epilogue, M, splits: int = 0, status=None, tile: int = 0, tile_f: int = 0,
         fold: NormFold | None = None) -> None:
     if impl != "tc":

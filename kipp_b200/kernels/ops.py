@@ -176,16 +176,19 @@ def gemm(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: str = "s
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, tokens: int,
-               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, by_pair: bool = False) -> torch.Tensor:
     """float32 [tokens, len(inv_freq), 2]: (cos, sin) of position * inv_freq, made
-    once per step and read by every layer's rotation."""
+    once per step and read by every layer's rotation.  ``by_pair``: the same values
+    as [len(inv_freq), tokens, 2], for the projection that rotates its own heads."""
     _int32(positions, "positions")
     if inv_freq.dtype != torch.float32 or not inv_freq.is_contiguous():
         raise KernelError("rope_table: inv_freq must be contiguous float32")
     half = inv_freq.numel()
     if out is None:
-        out = torch.empty((tokens, half, 2), dtype=torch.float32, device=positions.device)
-    f = _fn("rope_cache", "kipp_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+        shape = (half, tokens, 2) if by_pair else (tokens, half, 2)
+        out = torch.empty(shape, dtype=torch.float32, device=positions.device)
+    f = _fn("rope_cache", "kipp_rope_table_by_pair" if by_pair else "kipp_rope_table",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
     _check(f(_ptr(out), _ptr(positions), _ptr(inv_freq), tokens, half, _stream()), "rope_table")
     return out
 

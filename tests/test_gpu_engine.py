@@ -390,6 +390,36 @@ def test_the_serving_kernels_ran_at_the_benchmark_head_size():
     assert c["folded_norms"] >= 4 and c["folded_norms"] % 4 == 0       # 2 layers: 4 of a step's 5 norms
 
 
+def test_a_long_portion_norms_rotates_and_writes_the_cache_in_its_projection():
+    """Configuration E (128-wide heads): a portion of 1,024 tokens and more, beside a second
+    request in the same step, leaves q, k and v through the projection's own epilogue; fed
+    in shorter portions the same tokens take the separate kernel.  Either way the end of the
+    prompt, the tokens decoded after it and the request beside it match the plain model."""
+    from kipp_b200.engine import Engine, StepEntry
+    folder = model_folder("E")
+    opts = dict(dtype="bfloat16", page_size=16, cache_tokens=4096, max_requests=2, max_batch_tokens=1280)
+    toks = random_tokens("E", 1150, seed=12)
+    other = random_tokens("E", 40, seed=13)
+    ref = plain_logits("E", "bfloat16", toks[:1104])
+    ref_other = plain_logits("E", "bfloat16", other)
+    for cut in (1100, 400):
+        eng = Engine.from_folder(folder, **opts)
+        for lo in range(0, 1100, cut):
+            hi = min(1100, lo + cut)
+            batch = [StepEntry("a", toks[lo:hi], [hi - lo - 1] if hi == 1100 else [])]
+            if lo == 0:
+                batch.append(StepEntry("b", other, [39]))
+            out = eng.step(batch, check=True)
+            out = out.cpu() if out is not None else out
+            if hi == 1100:
+                assert_close(out[:1], ref[[1099]], "bfloat16", f"end of the prompt, portions of {cut}")
+            if lo == 0:
+                assert_close(out[-1:], ref_other[[39]], "bfloat16", f"the request beside it, portions of {cut}")
+        rows = [eng.step([StepEntry("a", [t], [0])], check=True).cpu().clone() for t in toks[1100:1104]]
+        assert_close(torch.cat(rows), ref[[1100, 1101, 1102, 1103]], "bfloat16", f"decoded after portions of {cut}")
+        assert (eng.info()["counters"]["projections_to_heads"] > 0) == (cut == 1100)
+
+
 def test_logit_rows_are_limited():
     from kipp_b200.engine import Engine, StepEntry
     eng = Engine.from_folder(model_folder("A"), dtype="float32", page_size=16, cache_tokens=256, max_requests=2,

@@ -309,6 +309,84 @@ def test_qk_norm_rope_write(case, dtype):
     assert float(kp2.float().abs().sum()) == 0.0
 
 
+@pytest.mark.parametrize("case", [
+    dict(T=1024, nq=4, nkv=2, K=192, norm=True, rot=True, page=16, scaled=False),
+    dict(T=1300, nq=5, nkv=1, K=320, norm=True, rot=True, page=8, scaled=True, w16=True),   # 7 heads: half a tile empty
+    dict(T=1100, nq=2, nkv=2, K=128, norm=False, rot=True, page=64, scaled=False),
+    dict(T=1030, nq=3, nkv=3, K=256, norm=True, rot=False, page=32, scaled=True),
+])
+def test_projection_hands_its_heads_to_attention(case):
+    """The q/k/v projection of a prompt-sized step with per-head norm, rotation and
+    the cache write in its epilogue: the same bits as the stored product followed
+    by `qk_norm_rope_write`, with and without the row factors of a deferred norm;
+    two requests in the step, permuted pages, a token count that fills no tile."""
+    from kipp_b200.kernels import gemm_bf16
+    D = 128
+    T, nq, nkv, K, page = case["T"], case["nq"], case["nkv"], case["K"], case["page"]
+    assert gemm_bf16.heads_ok(T, D, D if case["rot"] else 0) and not gemm_bf16.heads_ok(1023, D, D)
+    assert not gemm_bf16.heads_ok(T, 64, 64) and not gemm_bf16.heads_ok(T, D, 64)
+    g = torch.Generator().manual_seed(T + nq)
+    n_a = 37
+    entries = [StepEntry("a", [0] * n_a, []), StepEntry("b", [0] * (T - n_a), [])]
+    starts = [29, 3]
+    width = -(-(T + 40) // page)
+    perm = torch.randperm(2 * width, generator=g).int().numpy().reshape(2, width)
+    meta = pack_step(entries, starts, [0, 1], [perm.astype(np.int32)], torch.device(DEV))
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn((nq + 2 * nkv) * D, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).to(DEV)
+    wdt = torch.bfloat16 if case.get("w16") else torch.float32
+    qw = (1 + 0.2 * torch.randn(D, generator=g)).to(wdt).to(DEV) if case["norm"] else None
+    kw = (1 + 0.2 * torch.randn(D, generator=g)).to(wdt).to(DEV) if case["norm"] else None
+    inv = None
+    cos_sin = by_pair = None
+    if case["rot"]:
+        i = torch.arange(D // 2, dtype=torch.float32)
+        inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), (-(2.0 * i) / D).double()).float().to(DEV)
+        cos_sin = ops().rope_table(meta.positions, inv, T)
+        by_pair = ops().rope_table(meta.positions, inv, T, by_pair=True)
+        assert torch.equal(by_pair.transpose(0, 1), cos_sin)
+    fold = None
+    if case["scaled"]:
+        ssq = (torch.rand(T, 3, generator=g) * 40 + 1).to(DEV)
+        fold = gemm_bf16.fold_scale(ssq, 96, 1e-5)
+    st = status()
+
+    def pools():
+        return (torch.zeros(T, nq, D, dtype=torch.bfloat16, device=DEV),
+                torch.zeros(2 * width, nkv, page, D, dtype=torch.bfloat16, device=DEV),
+                torch.zeros(2 * width, nkv, page, D, dtype=torch.bfloat16, device=DEV))
+    q1, k1, v1 = pools()
+    qkv = torch.empty(T, (nq + 2 * nkv) * D, dtype=torch.bfloat16, device=DEV)
+    gemm_bf16.run("tc", qkv, a, w, "store", T, fold=fold, status=st)
+    ops().qk_norm_rope_write(qkv, q1, k1, v1, qw, kw, 1e-6, inv, D if case["rot"] else 0, meta.positions,
+                             meta.entry_of_token, meta.block_tables[0], page, T, nq, nkv, D, True, st,
+                             cos_sin=cos_sin)
+    q2, k2, v2 = pools()
+    gemm_bf16.run_heads(a, w, q2, k2, v2, qw, kw, 1e-6, by_pair, meta.positions, meta.entry_of_token,
+                        meta.block_tables[0], nq, nkv, status=st, fold=fold)
+    torch.cuda.synchronize()
+    assert st.tolist() == [0, 0, 0, 0]
+    assert float(q1.float().abs().sum()) > 0 and float(k1.float().abs().sum()) > 0
+    assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(v1, v2)
+    # a run that reads another run's cache writes nothing
+    q3, k3, v3 = pools()
+    gemm_bf16.run_heads(a, w, q3, k3, v3, qw, kw, 1e-6, by_pair, meta.positions, meta.entry_of_token,
+                        meta.block_tables[0], nq, nkv, write_cache=False, status=st, fold=fold)
+    assert torch.equal(q1, q3) and float(k3.float().abs().sum()) == 0.0 and float(v3.float().abs().sum()) == 0.0
+    # an unmapped page is refused through the status word and nothing is written there
+    table = meta.block_tables[0].clone()
+    table[1, 5] = -1
+    q4, k4, v4 = pools()
+    gemm_bf16.run_heads(a, w, q4, k4, v4, qw, kw, 1e-6, by_pair, meta.positions, meta.entry_of_token, table,
+                        nq, nkv, status=st, fold=fold)
+    assert st.tolist() == [2, 0, 0, 0]
+    st.zero_()
+    untouched = int(perm[1, 5])
+    assert float(k4[untouched].float().abs().sum()) == 0.0
+    others = [i for i in range(2 * width) if i != untouched]
+    assert torch.equal(k4[others], k1[others]) and torch.equal(q4, q1)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D", [48, 128])
 def test_no_infinity_or_nan_reaches_the_cache(D, dtype):
