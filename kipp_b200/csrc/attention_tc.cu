@@ -258,7 +258,7 @@ template <int D>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __grid_constant__ CUtensorMap map_k4, const __grid_constant__ CUtensorMap map_v4,
-                       const Params p) {
+                       const __grid_constant__ CUtensorMap map_q, const Params p) {
     using C = Cfg<D>;
     extern __shared__ __align__(1024) uint8_t smem[];     // swizzled tiles need 1024-byte alignment
     const uint32_t q_tile = smem_u32(smem);
@@ -266,7 +266,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t v_tiles = k_tiles + 2 * C::KV_BYTES;            // [2 stages]
     float* xchg = reinterpret_cast<float*>(smem + C::Q_BYTES + 4 * C::KV_BYTES);      // [parity][half][row]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::Q_BYTES + 4 * C::KV_BYTES + C::XCHG_BYTES);
-    uint64_t* q_full = bars;            // the query tile is in shared memory            (256 arrivals)
+    uint64_t* q_full = bars;            // the query tile is in shared memory            (1 + bytes)
     uint64_t* k_full = bars + 1;        // [2] a key stage has landed                    (1 + bytes)
     uint64_t* k_empty = bars + 3;       // [2] its S product has read it                 (1, by commit)
     uint64_t* v_full = bars + 5;        // [2]
@@ -297,7 +297,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int n_tiles = last_tile - first_tile + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(q_full, SOFTMAX_THREADS);
+        mbar_init(q_full, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&k_full[b], 1); mbar_init(&k_empty[b], 1);
             mbar_init(&v_full[b], 1); mbar_init(&v_empty[b], 1);
@@ -329,6 +329,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const bool has_box = rb * p.box_rows < BN;
         const uint32_t dst_off = (uint32_t)(half * (BN * 128) + rb * p.box_rows * 128);
         bool ok = true;
+        // The query tile first: rows [qs + tile_tok, + 128) of head h, a box per 64-column half.
+        // Rows past the entry's end are another entry's queries (or zeros past the step's last
+        // token): their scores are masked and their output rows are never stored.
+        if (lane == 0) mbar_expect_tx(q_full, C::Q_BYTES);
+        __syncwarp();
+        if (lane < C::HALVES) tma_load_2d(q_tile + lane * (BM * 128), &map_q, q_full, h * D + lane * 64, qs + tile_tok);
         // (This warp shares its scheduler with busy softmax warps and the stages come
         // back to it just in time: every instruction between a stage's release and
         // the issue of its load counts, so what can be is computed before the loop.)
@@ -446,21 +452,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
     } else {
         // ------------------------------------------------------------ softmax warps 0-7
-        // the query tile: rows beyond the entry are zero
-        {
-            constexpr int CHUNKS = D / 8;
-            for (int i = threadIdx.x; i < BM * CHUNKS; i += SOFTMAX_THREADS) {
-                const int r = i / CHUNKS, chunk = i % CHUNKS;
-                const int tk = tile_tok + r;
-                const bool there = tk < q_len;
-                const bf16* src = p.q + ((size_t)(qs + (there ? tk : 0)) * p.n_q + h) * D + chunk * 8;
-                cp_async16(q_tile + tile_off<BM>(chunk >> 3, r, chunk & 7), src, there ? 16 : 0);
-            }
-            cp_async_commit();
-            cp_async_wait<0>();
-            fence_async_proxy();                           // cp.async wrote; the tensor core reads
-            mbar_arrive(q_full);
-        }
         // Threads r and r + 128 share query row r.  Warps w and w + 4 hold the same 32
         // rows (a warp reaches the tensor-memory lanes 32 (w % 4) .. + 31).
         const int row = threadIdx.x & (BM - 1), ch = threadIdx.x >> 7;
@@ -665,7 +656,7 @@ int pool_map4(CUtensorMap* out, const void* ptr, int n_pages, int n_kv, int page
 }
 
 template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mk4, const CUtensorMap& mv4,
-                            const Params& p, int items, cudaStream_t s) {
+                            const CUtensorMap& mq, const Params& p, int items, cudaStream_t s) {
     using C = Cfg<D>;
     static bool configured = false;
     if (!configured) {
@@ -674,7 +665,7 @@ template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, mk4, mv4, p);
+    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, mk4, mv4, mq, p);
 }
 }  // namespace
 
@@ -689,8 +680,10 @@ extern "C" int kipp_attn_prefill_tc_page_ok(int page_size) {
 }
 
 // Prompt portions: `work` lists (entry, first token) of every 128-token tile.
+// q: bf16 [tokens][n_q][head_dim], all of the step's tokens (the query tiles come by TMA, which
+// fills what lies past the last token with zeros).
 // k_pages and v_pages: one layer's pool, bf16 [n_pages][n_kv][page_size][head_dim].
-extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_pages, const void* v_pages,
+extern "C" int kipp_attn_prefill_tc(void* out, const void* q, int tokens, const void* k_pages, const void* v_pages,
                                     int n_pages, const int* q_start, const int* context_len,
                                     const int* block_table, int table_width, int page_size, const int* work,
                                     int items, int n_q, int n_kv, int head_dim, float scale, int window,
@@ -698,7 +691,7 @@ extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_page
     if (items <= 0) return 0;
     if (items > 65535) return KIPP_ERR_ARG;
     if (!kipp_attn_prefill_tc_supported(head_dim, n_q, n_kv) || !kipp_attn_prefill_tc_page_ok(page_size) ||
-        n_pages <= 0 || window < 0 || status == nullptr)
+        n_pages <= 0 || window < 0 || status == nullptr || tokens <= 0)
         return KIPP_ERR_ARG;
     if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || ((uintptr_t)out & 15))
         return -3;
@@ -731,6 +724,9 @@ extern "C" int kipp_attn_prefill_tc(void* out, const void* q, const void* k_page
         rc = pool_map4(&mv4, v_pages, n_pages, n_kv, page_size, head_dim, p.pages_per_box);
         if (rc) return rc;
     }
+    CUtensorMap mq;
+    rc = pool_map(&mq, q, tokens, n_q * head_dim, BM);
+    if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 64 ? launch<64>(mk, mv, mk4, mv4, p, items, s) : launch<128>(mk, mv, mk4, mv4, p, items, s);
+    return head_dim == 64 ? launch<64>(mk, mv, mk4, mv4, mq, p, items, s) : launch<128>(mk, mv, mk4, mv4, mq, p, items, s);
 }

@@ -362,10 +362,10 @@ private:
         if (prefill_tensor_core && work.n_prefill_items128 > 0 && work.longest_portion >= PREFILL_TC_MIN_TOKENS &&
             (use_decode || work.n_decode == 0) && aligned &&
             attention_tc_supported(head_dim, n_q, n_kv, cache.page_size)) {
-            using Fn = int (*)(void*, const void*, const void*, const void*, int, const int*, const int*, const int*, int,
-                               int, const int*, int, int, int, int, float, int, int*, void*);
+            using Fn = int (*)(void*, const void*, int, const void*, const void*, int, const int*, const int*, const int*,
+                               int, int, const int*, int, int, int, int, float, int, int*, void*);
             static Fn f = kernel_symbol<Fn>("attention_tc", "kipp_attn_prefill_tc");
-            run(f(out, q, cache.k_pages, cache.v_pages, cache.n_pages, q_start, context_len, cache.block_table,
+            run(f(out, q, work.tokens, cache.k_pages, cache.v_pages, cache.n_pages, q_start, context_len, cache.block_table,
                   cache.table_width, cache.page_size, work.prefill_work128, work.n_prefill_items128, n_q, n_kv,
                   head_dim, scale, window, status, stream),
                 "attn_prefill_tc");

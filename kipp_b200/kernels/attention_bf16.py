@@ -50,10 +50,12 @@ def prefill_tc(out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv
     if not (k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.shape == v_pages.shape
             and tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)):
         raise KernelError("attn_prefill_tc: pages must be contiguous [pages, n_kv, page_size, head_dim]")
+    if not q.is_contiguous() or tuple(q.shape[1:]) != (n_q, head_dim):
+        raise KernelError("attn_prefill_tc: q must be contiguous [tokens, n_q, head_dim]")
     f = _fn("attention_tc", "kipp_attn_prefill_tc",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
-             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
-    _check(f(_ptr(out), _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(meta.q_start),
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(out), _ptr(q), q.shape[0], _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(meta.q_start),
              _ptr(meta.context_len), _ptr(block_table), block_table.shape[1], page_size,
              _ptr(meta.prefill_work128), meta.n_prefill_items128, n_q, n_kv, head_dim, float(scale),
              int(window or 0), _ptr(status), _stream()), "attn_prefill_tc")
