@@ -418,6 +418,18 @@ def test_a_long_portion_norms_rotates_and_writes_the_cache_in_its_projection():
         rows = [eng.step([StepEntry("a", [t], [0])], check=True).cpu().clone() for t in toks[1100:1104]]
         assert_close(torch.cat(rows), ref[[1100, 1101, 1102, 1103]], "bfloat16", f"decoded after portions of {cut}")
         assert (eng.info()["counters"]["projections_to_heads"] > 0) == (cut == 1100)
+    # the same shape again and again is captured in a graph: four prompts of 1,024 tokens, no sync
+    # in between, each against the plain model
+    eng = Engine.from_folder(folder, **opts)
+    prompts = [random_tokens("E", 1024, seed=20 + i) for i in range(4)]
+    outs = []
+    for i, pr in enumerate(prompts):
+        outs.append(eng.step([StepEntry(("g", i), pr, [1023])]).clone())
+        eng.finish(("g", i))
+    eng.synchronize()
+    assert eng.graph_replays >= 1 and eng.info()["counters"]["projections_to_heads"] > 0
+    for i, pr in enumerate(prompts):
+        assert_close(outs[i].cpu(), plain_logits("E", "bfloat16", pr)[[1023]], "bfloat16", f"prompt {i} of a repeated shape")
 
 
 def test_logit_rows_are_limited():
