@@ -653,7 +653,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // so it writes 16-byte vectors and SwiGLU pairs sit in one thread: an eighth of
 // the instructions of the feature-per-thread epilogue above, which matters
 // because the epilogue is not hidden behind the next tile's MMAs.
-constexpr int TOKM_TILE_FIXED = 64;              // fixed part of a tile's time, in feature columns
+constexpr int TOKM_TILE_FIXED = 96;              // fixed part of a tile's time, in feature columns
 constexpr int RED_BOX = 32;                     // the residual add goes out in boxes of 32 tokens x 32 features
 constexpr int RED_BYTES = RED_BOX * RED_BOX * 4;
 template <int TILE_N, bool REDUCE> struct CfgTok {
@@ -1581,8 +1581,13 @@ int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens
         long long cost_pair = 0, cost_one = 0;
         const int n_pair = pick_tile_n(tokens, features, true, &cost_pair);
         const int n_one = pick_tile_n(tokens, features, false, &cost_one);
+        // (From 1,536 tokens on the pair also takes the add where the rounds tie: sweeps over 768 to
+        // 4,096 tokens at 2,560, 6,144 and 19,456 features, K 2,560 to 9,728: the pair's tiles of 224
+        // or 256 features 6 to 13 % ahead at 1,536, 3,072 and 4,096 tokens, one CTA per tile 4 to 7 %
+        // ahead at 1,024.)
+        const bool add_pair = tokens >= 1536 ? cost_pair <= cost_one : cost_pair < cost_one;
         const bool pair = sink != nullptr || (want_tile_f < 0 ? want_tile_f <= -1000
-                                                              : (tokens >= 1024 && (epilogue != EPI_ADD || cost_pair < cost_one)));
+                                                              : (tokens >= 1024 && (epilogue != EPI_ADD || add_pair)));
         const int tile_n = sink != nullptr        ? 2 * SINK_HEAD
                            : want_tile_f <= -1000 ? -want_tile_f - 1000
                            : want_tile_f < 0      ? -want_tile_f
