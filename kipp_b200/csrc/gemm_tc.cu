@@ -1568,7 +1568,20 @@ int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens
     // Prompt-sized batches: tokens as the M operand (want_tile_f < 0 forces it with
     // the feature tile -want_tile_f).  The residual add needs a tensor map over C.
     const bool c_map_ok = epilogue != EPI_ADD || (ldc % 4 == 0 && ((uintptr_t)C & 15) == 0);
-    if ((want_tile == 0 && want_tile_f == 0 && tokens >= 512 && c_map_ok) || want_tile_f < 0) {
+    // Between 33 and 511 tokens a store or SwiGLU product also goes this way where its tiles of 128
+    // tokens fill most of the SMs: the few-token kernel streams the weights once per 64 tokens, and
+    // even at one pass its 128-feature tiles lose against one round of wider tiles here (gate/up
+    // 19,456 x 2,560: 19.3 against 22.6 us at 64 tokens, 19.7 against 36.4 at 128, 45.7 against 85.2
+    // at 511; the head 151,936 x 2,560: 120 against 129 us at 64 tokens, 200 against 292 at 256;
+    // q/k/v 6,144 x 2,560, 39 to 48 tiles: 14.3 against 10.9 us, so it stays).  The residual add stays
+    // with the few-token kernel up to 511 tokens (9.8 against 21 us at 64 tokens, even at 511).
+    bool mid_fills = false;
+    if (splits == 0 && want_tile == 0 && want_tile_f == 0 && tokens > 32 && tokens < 512 && epilogue != EPI_ADD) {
+        const int n = pick_tile_n(tokens, features, false);
+        const long long tiles = (long long)((tokens + UMMA_M - 1) / UMMA_M) * ((features + n - 1) / n);
+        mid_fills = 4 * tiles >= 3LL * sm_count();
+    }
+    if ((want_tile == 0 && want_tile_f == 0 && tokens >= 512 && c_map_ok) || want_tile_f < 0 || mid_fills) {
         const bool reduce = epilogue == EPI_ADD && c_map_ok;     // else a thread per token adds in place
         // want_tile_f: -N = one CTA per tile, -(1000 + N) = a pair of CTAs per 256-token tile
         // By default: the pair kernel from 1,024 tokens on, except for the residual

@@ -106,11 +106,14 @@ def test_gemm_simt(dtype, shape, epilogue):
 
 @pytest.mark.parametrize("epilogue", ["store", "add", "swiglu"])
 @pytest.mark.parametrize("shape", [(1, 128, 64), (8, 256, 128), (17, 250, 192), (64, 1000, 136),
-                                   (100, 384, 2568), (300, 640, 520), (5, 2560, 1216)])
+                                   (100, 384, 2568), (300, 640, 520), (5, 2560, 1216), (40, 14400, 136),
+                                   (100, 14400, 72)])
 def test_gemm_tensor_core(shape, epilogue):
     """tcgen05 kernel: integer data must come out exactly (any wrong tile,
     swizzle or split shows), random data within bfloat16 rounding; K splits of
-    1, a forced 3 and the cluster maximum 8."""
+    1, a forced 3 and the cluster maximum 8.  The last two shapes have so many
+    features that, left to itself (splits 0), a store or SwiGLU product of 33 to
+    511 tokens takes the kernel with the tokens as rows."""
     from kipp_b200.kernels import gemm_bf16
     M, N, K = shape
     g = torch.Generator().manual_seed(M * 7 + N)
