@@ -72,6 +72,9 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
@@ -93,6 +96,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// A box from shared memory to a 2-dimensional map (what lies outside the tensor is dropped).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the sources of all earlier bulk-groups of this thread have been read
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // Box of a 4-dimensional map: columns x, slot y, kv head z, page w.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z,
                                             int w) {
@@ -258,7 +270,8 @@ template <int D>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __grid_constant__ CUtensorMap map_k4, const __grid_constant__ CUtensorMap map_v4,
-                       const __grid_constant__ CUtensorMap map_q, const Params p) {
+                       const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_out,
+                       const Params p) {
     using C = Cfg<D>;
     extern __shared__ __align__(1024) uint8_t smem[];     // swizzled tiles need 1024-byte alignment
     const uint32_t q_tile = smem_u32(smem);
@@ -549,11 +562,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const float l_row = l_run + xl[(ch ^ 1) * BM + row];
         const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
         bf16* dst = p.out + ((size_t)(qs + (live ? tok : 0)) * p.n_q + h) * D;
+        // Where all 32 rows of the warp belong to the entry, its 32 x 64 block of the output goes
+        // through shared memory (the query tile's, no product reads it any more; 128-byte rows,
+        // swizzled as the unit expects) and leaves as ONE box: a thread's own stores would touch 16
+        // bytes of 32 different lines each.  A warp at the entry's ragged end writes its rows itself.
+        const int w4 = warp & 3;
+        const bool as_box = (D == 128) && tile_tok + w4 * 32 + 31 < q_len;
+        const uint32_t box = q_tile + ch * (BM * 128) + w4 * (32 * 128);     // 4 KB, 1,024-byte aligned
 #pragma unroll 1
         for (int c = ch * (D / 2); c < (ch + 1) * (D / 2); c += 32) {
             float o[32];
             tmem_ld32(tmem_o + t_lane + c, o);
-            if (ok && live) {
+            if (ok && (live || as_box)) {
                 uint4 pk[4];
                 uint32_t* w = reinterpret_cast<uint32_t*>(pk);
 #pragma unroll
@@ -561,8 +581,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(o[2 * k] * inv, o[2 * k + 1] * inv);
                     w[k] = *reinterpret_cast<uint32_t*>(&h2);
                 }
+                if (as_box) {
+                    const int chunk0 = (c - ch * (D / 2)) >> 3;               // 16-byte chunk of the 128-byte row
 #pragma unroll
-                for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(dst + c)[k] = pk[k];
+                    for (int k = 0; k < 4; ++k)
+                        st_shared_v4(box + lane * 128 + (((chunk0 + k) ^ (lane & 7)) << 4), pk[k]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(dst + c)[k] = pk[k];
+                }
+            }
+        }
+        if (as_box) {
+            fence_async_proxy();                           // these stores before the unit's read
+            __syncwarp();
+            if (lane == 0 && ok) {
+                tma_store_2d(&map_out, box, h * D + ch * 64, qs + tile_tok + w4 * 32);
+                bulk_commit();
+                bulk_wait_read();                          // the shared memory outlives the read
             }
         }
     }
@@ -656,7 +692,7 @@ int pool_map4(CUtensorMap* out, const void* ptr, int n_pages, int n_kv, int page
 }
 
 template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mk4, const CUtensorMap& mv4,
-                            const CUtensorMap& mq, const Params& p, int items, cudaStream_t s) {
+                            const CUtensorMap& mq, const CUtensorMap& mo, const Params& p, int items, cudaStream_t s) {
     using C = Cfg<D>;
     static bool configured = false;
     if (!configured) {
@@ -665,7 +701,7 @@ template <int D> int launch(const CUtensorMap& mk, const CUtensorMap& mv, const 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, mk4, mv4, mq, p);
+    return kipp_launch(attn_prefill_tc_kernel<D>, dim3(p.n_q, items), dim3(THREADS), C::SMEM, s, 1, mk, mv, mk4, mv4, mq, mo, p);
 }
 }  // namespace
 
@@ -727,6 +763,10 @@ extern "C" int kipp_attn_prefill_tc(void* out, const void* q, int tokens, const 
     CUtensorMap mq;
     rc = pool_map(&mq, q, tokens, n_q * head_dim, BM);
     if (rc) return rc;
+    CUtensorMap mo;                                  // the output as [tokens, n_q x head_dim]: boxes of 32 rows
+    rc = pool_map(&mo, out, tokens, n_q * head_dim, 32);
+    if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    return head_dim == 64 ? launch<64>(mk, mv, mk4, mv4, mq, p, items, s) : launch<128>(mk, mv, mk4, mv4, mq, p, items, s);
+    return head_dim == 64 ? launch<64>(mk, mv, mk4, mv4, mq, mo, p, items, s)
+                          : launch<128>(mk, mv, mk4, mv4, mq, mo, p, items, s);
 }

@@ -52,6 +52,8 @@ def prefill_tc(out, q, k_pages, v_pages, meta, block_table, page_size, n_q, n_kv
         raise KernelError("attn_prefill_tc: pages must be contiguous [pages, n_kv, page_size, head_dim]")
     if not q.is_contiguous() or tuple(q.shape[1:]) != (n_q, head_dim):
         raise KernelError("attn_prefill_tc: q must be contiguous [tokens, n_q, head_dim]")
+    if not out.is_contiguous() or out.shape != q.shape:
+        raise KernelError("attn_prefill_tc: out must be contiguous and of q's shape")
     f = _fn("attention_tc", "kipp_attn_prefill_tc",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
              c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
