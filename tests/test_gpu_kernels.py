@@ -181,6 +181,44 @@ def test_gemm_tensor_core_tokens_as_rows(shape, epilogue):
     assert gemm_bf16.status_word(torch.device(DEV)).tolist() == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_gemm_tensor_core_left_to_choose_its_kernel(seed):
+    """Shapes drawn around every boundary of the choice of kernel and tile (tokens 1 to
+    2,100, features 8 to 20,000, K 8 to 4,104, ragged in every direction), the three
+    epilogues, both output types, with and without the row factors of a deferred norm:
+    whatever kernel the launcher takes, the product matches the plain one."""
+    from kipp_b200.kernels import gemm_bf16
+    rng = random.Random(seed)
+    for trial in range(40):
+        M = rng.choice([1, 3, 8, 16, 17, 31, 32, 33, 40, 64, 65, 100, 128, 200, 256, 300, 400, 511, 512, 513, 700,
+                        1000, 1023, 1024, 1025, 1300, 1536, 2048, 2100])
+        N = rng.choice([8, 24, 128, 136, 256, 1000, 2560, 2568, 4096, 6144, 9000, 14400, 19456, 20000])
+        K = rng.choice([8, 64, 72, 128, 520, 1024, 2560, 4104])
+        epilogue = rng.choice(["store", "add", "swiglu"])
+        g = torch.Generator(device=DEV).manual_seed(1000 * seed + trial)
+        a = torch.randn(M, K, generator=g, device=DEV).to(torch.bfloat16)
+        w = (torch.randn(N, K, generator=g, device=DEV) * 0.1).to(torch.bfloat16)
+        odt = torch.float32 if epilogue == "add" else rng.choice([torch.float32, torch.bfloat16])
+        out = torch.randn(M, N // 2 if epilogue == "swiglu" else N, generator=g, device=DEV).to(odt)
+        prod = a.double() @ w.double().t()
+        fold = None
+        if epilogue != "add" and rng.random() < 0.4:
+            ssq = torch.rand(M, 5, generator=g, device=DEV) * 30 + 1
+            fold = gemm_bf16.fold_scale(ssq, 77, 1e-5)
+            prod = prod * torch.rsqrt(ssq.double().sum(1) / 77 + 1e-5)[:, None]
+        if epilogue == "add":
+            ref = out.double() + prod
+        elif epilogue == "swiglu":
+            ref = prod[:, 0::2] / (1 + torch.exp(-prod[:, 0::2])) * prod[:, 1::2]
+        else:
+            ref = prod
+        gemm_bf16.run("tc", out, a, w, epilogue, M, fold=fold)
+        scale = float(ref.abs().max()) + 1e-9
+        err = float((out.double() - ref).abs().max()) / scale
+        assert err <= (2e-5 if odt == torch.float32 else 1e-2), (M, N, K, epilogue, odt, fold is not None, err)
+    assert gemm_bf16.status_word(torch.device(DEV)).tolist() == [0, 0, 0, 0]
+
+
 @pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", [(1, 128, 64), (8, 256, 128), (17, 224, 192), (64, 992, 136), (100, 384, 2568),
                                    (300, 640, 520), (5, 2560, 1216)])
