@@ -4,7 +4,7 @@ under baseline/_ref, with the compiler flags of its own Makefile (CFLAGS, NVCCFL
 cuda-generic target's -gencode list, to which the B200's own architecture is added through
 the Makefile's CUDA_GENERIC_ARCH_FLAGS variable so that nothing is compiled at load time).
 
-    python baseline/build_reference.py [/path/to/Kipp]
+    python baseline/build_reference.py /path/to/Kipp
 
 The sources are copied, not changed.  bench.py --impl reference loads the library with
 ctypes and drives it through its public API (src/kipp.h).
@@ -26,7 +26,10 @@ def run(cmd, cwd):
 
 
 def main() -> int:
-    source = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    source = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KIPP_REFERENCE_SOURCE", "")
+    if not os.path.isdir(source):
+        print("usage: build_reference.py /path/to/Kipp (or KIPP_REFERENCE_SOURCE)", file=sys.stderr)
+        return 2
     src = os.path.join(REF, "src_tree")
     if os.path.isdir(src):
         shutil.rmtree(src)

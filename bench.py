@@ -5,7 +5,7 @@ fraction of the measured roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
 
-The model has the layer sizes of the Qwen3-4B row of BASELINE.json with random
+The model has the layer sizes of the 4B benchmark configuration (the qwen3-4b preset) with random
 bfloat16 weights made on the device; prompts are seeded random token ids.  A
 "step" is one decode step of the whole batch.  Prints ONE JSON line.
 """
@@ -25,10 +25,10 @@ sys.path.insert(0, ROOT)
 
 from kipp_b200.config.presets import load_preset  # noqa: E402
 
-# BASELINE.json configs[2] (Qwen3-4B-shaped): the sizes and the weight seed are the preset's
+# the 4B benchmark configuration (Qwen3-4B-shaped): the sizes and the weight seed are the preset's
 QWEN3_4B, _INIT_4B = load_preset("qwen3-4b")
 WEIGHT_SEED = int(_INIT_4B["seed"])
-CONTEXT = 8192            # BASELINE.json configs[2]: context length 8192
+CONTEXT = 8192            # the 4B benchmark configuration's context length
 POINT_PROMPT = 2048       # ... decode at batch 1/8/64 with 2,048-token prompts
 PREFILL_TOKENS = 2048
 PAGE = 16

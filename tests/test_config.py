@@ -100,7 +100,7 @@ def test_registry_takes_another_architecture():
 
 def test_presets_are_data_and_valid():
     """Every preset file parses into a valid typed configuration; the benchmark
-    preset has the sizes BASELINE.json configs[2] names."""
+    preset has the sizes of the 4B benchmark configuration."""
     from kipp_b200.config import config_from_dict, load_preset, preset_names
     names = preset_names()
     assert {"tiny-a", "tiny-b", "qwen3-4b", "qwen3-8b", "qwen3-32b"} <= set(names)

@@ -114,7 +114,7 @@ def greedy_plain(name, dtype, prompt, steps):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_through_the_entry_point(name, dtype):
-    """BASELINE's tiny workloads: A = prompts of 5/17/33 tokens, 8 greedy steps,
+    """The tiny benchmark workloads: A = prompts of 5/17/33 tokens, 8 greedy steps,
     page 16; B = prompts of 1/64/100/200, portions of 48 mixed with decoding,
     page 8."""
     from kipp_b200.engine.llm import LLM
