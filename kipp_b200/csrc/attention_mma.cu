@@ -446,8 +446,15 @@ __device__ __forceinline__ void decode_split(const DecodeParams& p, uint8_t* sme
     // The first tiles of the split are fetched before the wait, while the kernel before
     // this one ends, unless one of them holds the token's own position: its key and
     // value are this step's (made below, or by the kernel before this one).
+    // (The CTA that makes the token's key and value itself, the fused form's last split, may
+    // fetch that tile early all the same: it puts the new key and value into the tile in shared
+    // memory as well as into the cache, over whatever the cache held at that slot.)
     const int first_tile = lo / TILE_KEYS, last_tile = hi / TILE_KEYS, n_tiles = last_tile - first_tile + 1;
-    const bool early = first && lo <= hi && (first_tile + min(STAGES - 1, n_tiles)) * TILE_KEYS <= pos;
+    const int ahead_tiles = min(STAGES - 1, n_tiles);
+    const bool own_in_ahead = lo <= hi && pos / TILE_KEYS - first_tile < ahead_tiles && pos <= hi;
+    const bool makes_own = p.qkv != nullptr && split == n_splits - 1 && p.k_write != nullptr;
+    const bool early = first && lo <= hi && (!own_in_ahead || makes_own);
+    const bool patch = early && own_in_ahead;
     if (early) {
 #pragma unroll
         for (int s = 0; s < STAGES - 1; ++s) {
@@ -472,6 +479,10 @@ __device__ __forceinline__ void decode_split(const DecodeParams& p, uint8_t* sme
         // shared memory (behind the tiles); the split that holds the token's own position
         // also makes the new key and value and puts them into the cache.
         constexpr int NE = D / 32;
+        if (patch) {                                     // the tiles fetched early have landed, for every thread
+            cp_async_wait<0>();
+            __syncthreads();
+        }
         bf16* q_s = reinterpret_cast<bf16*>(smem + 2 * STAGES * TILE_BYTES);   // [16][D]
         const bf16* raw = p.qkv + (size_t)tok * p.ld_qkv;
         const float2* cs_row = p.cos_sin != nullptr ? p.cos_sin + (size_t)tok * (D / 2) : nullptr;
@@ -498,6 +509,16 @@ __device__ __forceinline__ void decode_split(const DecodeParams& p, uint8_t* sme
                 bf16* dst = (warp == 0 ? p.k_write : p.v_write) + at;
 #pragma unroll
                 for (int j = 0; j < NE; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(cache_value(x[j]));
+                if (patch) {
+                    const int ti = pos / TILE_KEYS - first_tile, row = pos - (first_tile + ti) * TILE_KEYS;
+                    uint8_t* tile = smem + (warp == 0 ? 0 : STAGES * TILE_BYTES) + ti * TILE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < NE; ++j) {
+                        const int e = lane + 32 * j;
+                        *reinterpret_cast<bf16*>(tile + tile_offset<D>(row, e >> 3) + (e & 7) * 2) =
+                            __float2bfloat16_rn(cache_value(x[j]));
+                    }
+                }
             }
             __threadfence();                                       // before this CTA gathers that page
         }
